@@ -1,0 +1,107 @@
+/*
+ * ixb200 -- C ABI of the B200 (sm_100a) INT8-X weight path.
+ *
+ * One shared library, plain pointers and sizes, no framework types.  Every
+ * pointer named "device" is a CUDA device pointer on the current device; every
+ * call launches on the given stream and returns without synchronising.  All
+ * functions return 0 on success and a non-zero IXB_E_* code otherwise;
+ * ixb_last_error() then gives a message for the calling thread.
+ *
+ * The packed tensor layout is exactly the dict produced by the reference's
+ * quantiser (ixrun/quantize.py:110-122): two nested bitmaps and three value
+ * streams for a row-major [out_f, in_f] int8 code matrix, plus one bf16 scale.
+ *
+ * Each entry point names the reference interface it stands in for.
+ */
+#ifndef IXB200_H
+#define IXB200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define IXB_OK 0
+#define IXB_E_ARG 1        /* bad argument (null pointer, shape, alignment) */
+#define IXB_E_UNSUPPORTED 2 /* shape outside what the kernels handle */
+#define IXB_E_CUDA 3       /* a CUDA runtime call failed */
+#define IXB_E_SCRATCH 4    /* scratch/workspace too small */
+
+typedef void *ixb_stream_t; /* cudaStream_t */
+
+/* Device-resident packed tensor (reference: the GPU buffers StreamingLinear
+ * registers, ixrun/engine.py:58-66).  Stream base pointers must be 16-byte
+ * aligned; lengths are exact (no padding is assumed or read). */
+typedef struct ixb_packed {
+    const void *b1;       /* int32 words, bit e      = element e is level 1 */
+    int64_t b1_words;
+    const void *b2;       /* int32 words, bit r      = r-th non-L1 element is level 2 */
+    int64_t b2_words;
+    const void *l1;       /* int32 words, 3-bit fields, code+3   */
+    int64_t l1_words;
+    const void *l2;       /* int32 words, 5-bit fields, code+15  */
+    int64_t l2_words;
+    const void *l3;       /* bytes, code+127 */
+    int64_t l3_bytes;
+    const void *scale;    /* one bf16 */
+    int64_t out_f;
+    int64_t in_f;
+} ixb_packed;
+
+/* library / device facts */
+int ixb_version(void);
+const char *ixb_last_error(void);
+/* number of kernels this library has launched in this process (all threads) */
+int64_t ixb_launch_count(void);
+
+/*
+ * Rank prefix tables.  q1[u], q2[u] = number of level-1 / level-2 elements
+ * strictly before flat position u*gran, u in [0, n_units).
+ *   gran = 1024  replaces precompute_block_offsets (ixrun/triton_kernels.py:180-220)
+ *   gran = in_f  replaces compute_row_prefixes(packed)        (ixrun/fused.py:60-65)
+ *   gran = chunk replaces compute_row_prefixes(packed, chunk) (ixrun/fused.py:67-78)
+ * `ws` is device workspace of at least ixb_prefix_workspace_bytes(N) bytes.
+ */
+size_t ixb_prefix_workspace_bytes(int64_t n_elements);
+int ixb_prefix_tables(const ixb_packed *w, int64_t gran, int64_t n_units,
+                      int32_t *q1_device, int32_t *q2_device,
+                      void *ws_device, size_t ws_bytes, ixb_stream_t stream);
+
+/*
+ * Packed streams -> dense matrix.  blk_q1/blk_q2 are the gran=1024 tables.
+ *   out_kind 0: int8 codes      (the integers ixrun/quantize.py:65-72 produced)
+ *   out_kind 1: bf16 weights    (replaces _ix_decode_kernel + launcher,
+ *                                ixrun/triton_kernels.py:68-177, :224-259, and
+ *                                StreamingLinear._decode, ixrun/engine.py:109-133)
+ */
+int ixb_decode(const ixb_packed *w, const int32_t *blk_q1, const int32_t *blk_q2,
+               void *out_device, int out_kind, ixb_stream_t stream);
+
+/*
+ * Fused decode + matrix product for m_rows activations (1 <= m_rows <= 8):
+ *   y[m][n] = sum_k float(x[m][k]) * float(bf16(code[n][k] * scale))  (+ bias[n])
+ * accumulated in fp32; decoded weights never reach device memory.
+ * Replaces fused_gemv / _ix_gemv_kernel / _ix_gemv_split_kernel
+ * (ixrun/fused.py:84-179, :209-294, :297-347) including the caller-side
+ * zeroing and bf16 cast of the split-K path (ixrun/engine.py:145-159).
+ *   x       bf16 [m_rows][in_f], row stride in_f
+ *   bias    bf16 [out_f] or NULL; added after the sum is rounded to the
+ *           output type when y is bf16 (ixrun/engine.py:166-168)
+ *   y       bf16 or fp32 [m_rows][out_f]
+ *   scratch device memory of ixb_gemv_scratch_bytes() bytes whose first 256
+ *           bytes were zero before the first call; the library leaves them
+ *           zero again.  One call at a time per scratch buffer.
+ * Requires in_f % 32 == 0.
+ */
+size_t ixb_gemv_scratch_bytes(int64_t out_f, int64_t in_f, int64_t m_rows);
+int ixb_gemv(const ixb_packed *w, const int32_t *blk_q1, const int32_t *blk_q2,
+             const void *x_device, int64_t m_rows, const void *bias_device,
+             void *y_device, int y_is_f32,
+             void *scratch_device, size_t scratch_bytes, ixb_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* IXB200_H */

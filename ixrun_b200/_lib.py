@@ -1,0 +1,98 @@
+"""ctypes binding of ``libixb200.so`` (the C ABI declared in ``include/ixb200.h``).
+
+There is no fallback: if the library is missing and cannot be built, or a call
+fails, an exception is raised.  torch is used only to own device memory and to
+name the current stream; the library itself sees raw pointers.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+import torch
+
+from . import build as _build
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_lib = None
+
+SYMBOLS = (
+    "ixb_version", "ixb_last_error", "ixb_launch_count",
+    "ixb_prefix_workspace_bytes", "ixb_prefix_tables",
+    "ixb_decode", "ixb_gemv_scratch_bytes", "ixb_gemv",
+)
+
+
+class IxbError(RuntimeError):
+    """A call into libixb200 returned a non-zero status."""
+
+
+class Packed(C.Structure):
+    """Mirror of ``struct ixb_packed``."""
+
+    _fields_ = [
+        ("b1", C.c_void_p), ("b1_words", C.c_int64),
+        ("b2", C.c_void_p), ("b2_words", C.c_int64),
+        ("l1", C.c_void_p), ("l1_words", C.c_int64),
+        ("l2", C.c_void_p), ("l2_words", C.c_int64),
+        ("l3", C.c_void_p), ("l3_bytes", C.c_int64),
+        ("scale", C.c_void_p),
+        ("out_f", C.c_int64), ("in_f", C.c_int64),
+    ]
+
+
+def lib():
+    """Load (building first if the in-tree .so is missing or stale)."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    so = _build.SO
+    if _build.is_stale():
+        try:
+            so = _build.build()
+        except Exception as e:  # no silent fallback
+            if not os.path.exists(so):
+                raise IxbError(f"libixb200.so is not built and cannot be built here: {e}") from e
+    L = C.CDLL(so)
+    vp, i64, sz = C.c_void_p, C.c_int64, C.c_size_t
+    L.ixb_version.restype = C.c_int
+    L.ixb_last_error.restype = C.c_char_p
+    L.ixb_launch_count.restype = i64
+    L.ixb_prefix_workspace_bytes.restype = sz
+    L.ixb_prefix_workspace_bytes.argtypes = [i64]
+    L.ixb_prefix_tables.restype = C.c_int
+    L.ixb_prefix_tables.argtypes = [C.POINTER(Packed), i64, i64, vp, vp, vp, sz, vp]
+    L.ixb_decode.restype = C.c_int
+    L.ixb_decode.argtypes = [C.POINTER(Packed), vp, vp, vp, C.c_int, vp]
+    L.ixb_gemv_scratch_bytes.restype = sz
+    L.ixb_gemv_scratch_bytes.argtypes = [i64, i64, i64]
+    L.ixb_gemv.restype = C.c_int
+    L.ixb_gemv.argtypes = [C.POINTER(Packed), vp, vp, vp, i64, vp, vp, C.c_int, vp, sz, vp]
+    _lib = L
+    return L
+
+
+def check(rc: int):
+    if rc != 0:
+        raise IxbError(f"ixb200 error {rc}: {lib().ixb_last_error().decode()}")
+
+
+def stream_ptr(device=None) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def _p(t: torch.Tensor | None) -> int | None:
+    return None if t is None or t.numel() == 0 else t.data_ptr()
+
+
+def packed_struct(b1, b2, l1, l2, l3, scale, out_f: int, in_f: int) -> Packed:
+    """Build the C struct from device tensors (kept alive by the caller)."""
+    for t in (b1, b2, l1, l2, l3, scale):
+        if not t.is_cuda:
+            raise IxbError("packed streams must live on a CUDA device")
+        if not t.is_contiguous():
+            raise IxbError("packed streams must be contiguous")
+    return Packed(
+        _p(b1), b1.numel(), _p(b2), b2.numel(), _p(l1), l1.numel(), _p(l2), l2.numel(),
+        _p(l3), l3.numel(), scale.data_ptr(), out_f, in_f,
+    )

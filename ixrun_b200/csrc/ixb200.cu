@@ -1,0 +1,529 @@
+// ixb200: C-ABI entry points and kernels of the B200 INT8-X weight path.
+// Built for sm_100a only.  See include/ixb200.h for the contract of each call.
+#include "../../include/ixb200.h"
+#include "ixb_common.cuh"
+
+#include <atomic>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+
+namespace ixb {
+
+// ----------------------------------------------------------------- errors ---
+static thread_local char g_err[512] = "";
+static std::atomic<long long> g_launches{0};
+
+static int fail(int code, const char *fmt, ...)
+{
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+    return code;
+}
+
+#define IXB_CUDA(call)                                                                        \
+    do {                                                                                      \
+        cudaError_t e_ = (call);                                                              \
+        if (e_ != cudaSuccess)                                                                \
+            return fail(IXB_E_CUDA, "%s failed: %s", #call, cudaGetErrorString(e_));          \
+    } while (0)
+
+static int launch_check(const char *what)
+{
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return fail(IXB_E_CUDA, "launch of %s failed: %s", what, cudaGetErrorString(e));
+    return IXB_OK;
+}
+
+static int num_sms()
+{
+    static int cached[64] = {0};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    if (!cached[dev]) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+        cached[dev] = n;
+    }
+    return cached[dev];
+}
+
+static int to_streams(const ixb_packed *w, Streams *s)
+{
+    if (!w) return fail(IXB_E_ARG, "packed tensor is NULL");
+    if (w->out_f <= 0 || w->in_f <= 0) return fail(IXB_E_ARG, "bad shape %lld x %lld", (long long)w->out_f, (long long)w->in_f);
+    long long n = (long long)w->out_f * w->in_f;
+    // bit positions (5 bits per element at most) are carried in 32 bits
+    if (n > 800000000LL) return fail(IXB_E_UNSUPPORTED, "tensor of %lld elements is too large (max 8e8)", n);
+    if (!w->b1 || !w->scale) return fail(IXB_E_ARG, "b1/scale pointer is NULL");
+    if (w->b1_words != (n + 31) / 32) return fail(IXB_E_ARG, "b1_words %lld != ceil(N/32)", (long long)w->b1_words);
+    if ((w->b2_words && !w->b2) || (w->l1_words && !w->l1) || (w->l2_words && !w->l2) || (w->l3_bytes && !w->l3))
+        return fail(IXB_E_ARG, "non-empty stream with NULL pointer");
+    const void *ptrs[5] = {w->b1, w->b2, w->l1, w->l2, w->l3};
+    for (int i = 0; i < 5; ++i)
+        if (ptrs[i] && ((uintptr_t)ptrs[i] & 15u)) return fail(IXB_E_ARG, "stream %d is not 16-byte aligned", i);
+    s->b1 = (const uint32_t *)w->b1;
+    s->b2 = (const uint32_t *)w->b2;
+    s->l1 = (const uint32_t *)w->l1;
+    s->l2 = (const uint32_t *)w->l2;
+    s->l3 = (const uint8_t *)w->l3;
+    s->b1_words = (uint32_t)w->b1_words;
+    s->b2_words = (uint32_t)w->b2_words;
+    s->l1_words = (uint32_t)w->l1_words;
+    s->l2_words = (uint32_t)w->l2_words;
+    s->l3_bytes = (uint32_t)w->l3_bytes;
+    s->scale = (const __nv_bfloat16 *)w->scale;
+    s->n = (uint32_t)n;
+    s->out_f = (uint32_t)w->out_f;
+    s->in_f = (uint32_t)w->in_f;
+    return IXB_OK;
+}
+
+// ------------------------------------------------------- prefix tables ------
+// cnt1[b] = number of level-1 elements in rank block b (one warp per block)
+__global__ void k_count_l1(Streams s, uint32_t nb, int32_t *cnt1)
+{
+    uint32_t b = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    int lane = threadIdx.x & 31;
+    if (b >= nb) return;
+    uint32_t c = __popc(ldw(s.b1, b * 32u + lane, s.b1_words));
+    c = __reduce_add_sync(0xffffffffu, c);
+    if (lane == 0) cnt1[b] = (int32_t)c;
+}
+
+// in-place exclusive scan of n int32 values by one CTA of 1024 threads
+__global__ void __launch_bounds__(1024) k_excl_scan(const int32_t *in, int32_t *out, uint32_t n)
+{
+    __shared__ uint32_t warp_tot[32];
+    __shared__ uint32_t carry_s;
+    int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    if (threadIdx.x == 0) carry_s = 0;
+    __syncthreads();
+    for (uint32_t base = 0; base < n; base += 1024) {
+        uint32_t i = base + threadIdx.x;
+        uint32_t v = i < n ? (uint32_t)in[i] : 0u;
+        uint32_t inc = warp_incl_scan(v, lane);
+        if (lane == 31) warp_tot[wid] = inc;
+        __syncthreads();
+        if (wid == 0) {
+            uint32_t t = warp_tot[lane];
+            uint32_t ti = warp_incl_scan(t, lane);
+            warp_tot[lane] = ti - t;
+        }
+        __syncthreads();
+        uint32_t carry = carry_s;
+        uint32_t excl = carry + warp_tot[wid] + inc - v;
+        if (i < n) out[i] = (int32_t)excl;
+        __syncthreads();
+        if (threadIdx.x == 1023) carry_s = excl + v;
+        __syncthreads();
+    }
+}
+
+// number of set B2 bits in bit range [r0, r1), computed by one warp
+__device__ __forceinline__ uint32_t b2_range_count(const Streams &s, uint32_t r0, uint32_t r1, int lane)
+{
+    uint32_t c = 0;
+    if (r1 > r0) {
+        uint32_t w0 = r0 >> 5, w1 = (r1 - 1) >> 5;
+        for (uint32_t w = w0 + lane; w <= w1; w += 32) {
+            uint32_t v = ldw(s.b2, w, s.b2_words);
+            if (w == w0) v &= ~lowmask(r0 & 31u);
+            if (w == w1) v &= lowmask(((r1 - 1) & 31u) + 1u);
+            c += __popc(v);
+        }
+    }
+    return __reduce_add_sync(0xffffffffu, c);
+}
+
+// cnt2[b] = number of level-2 elements in rank block b, from the B2 bits of
+// the block's non-L1 rank range
+__global__ void k_count_l2(Streams s, uint32_t nb, const int32_t *a_blk, const int32_t *cnt1, int32_t *cnt2)
+{
+    uint32_t b = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    int lane = threadIdx.x & 31;
+    if (b >= nb) return;
+    uint32_t e0 = b * (uint32_t)kBlk;
+    uint32_t e1 = min(e0 + (uint32_t)kBlk, s.n);
+    uint32_t r0 = e0 - (uint32_t)a_blk[b];
+    uint32_t r1 = r0 + (e1 - e0) - (uint32_t)cnt1[b];
+    uint32_t c = b2_range_count(s, r0, r1, lane);
+    if (lane == 0) cnt2[b] = (int32_t)c;
+}
+
+// q1[u], q2[u] at flat position u*gran from the block tables (one warp per unit)
+__global__ void k_unit_prefix(Streams s, uint32_t gran, uint32_t n_units, const int32_t *a_blk,
+                              const int32_t *c_blk, int32_t *q1, int32_t *q2)
+{
+    uint32_t u = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    int lane = threadIdx.x & 31;
+    if (u >= n_units) return;
+    unsigned long long p64 = (unsigned long long)u * gran;
+    uint32_t p = p64 > s.n ? s.n : (uint32_t)p64;
+    uint32_t nb = (s.n + kBlk - 1) / kBlk;
+    uint32_t b = p >> 10;
+    uint32_t a, c;
+    if (b >= nb) {   // p == n on a block boundary: totals = last block's prefix + its counts
+        b = nb - 1;
+    }
+    uint32_t e0 = b * (uint32_t)kBlk;
+    // level-1 elements in [e0, p): whole words plus a masked partial word
+    uint32_t wi = (e0 >> 5) + lane;
+    uint32_t v = ldw(s.b1, wi, s.b1_words);
+    uint32_t nfull = (p - e0) >> 5, rem = (p - e0) & 31u;
+    if ((uint32_t)lane > nfull) v = 0;
+    else if ((uint32_t)lane == nfull) v &= lowmask(rem);
+    uint32_t k1 = __reduce_add_sync(0xffffffffu, __popc(v));
+    a = (uint32_t)a_blk[b] + k1;
+    uint32_t r0 = e0 - (uint32_t)a_blk[b];
+    uint32_t r1 = p - a;
+    c = (uint32_t)c_blk[b] + b2_range_count(s, r0, r1, lane);
+    if (lane == 0) { q1[u] = (int32_t)a; q2[u] = (int32_t)c; }
+}
+
+// ------------------------------------------------------------- decode -------
+// One warp per rank block, lane = bitmap word.  OUT = 0: int8 codes, 1: bf16.
+template <int OUT>
+__global__ void __launch_bounds__(256) k_decode(Streams s, const int32_t *q1, const int32_t *q2, void *out)
+{
+    __shared__ uint32_t tab[kLutSize];
+    float sc = __bfloat162float(*s.scale);
+    for (int e = threadIdx.x; e < kLutSize; e += blockDim.x) {
+        int code = lut_code(e);
+        if (OUT == 0) tab[e] = (uint32_t)(code & 0xff);
+        else tab[e] = (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn((float)code * sc));
+    }
+    __syncthreads();
+    uint32_t nb = (s.n + kBlk - 1) / kBlk;
+    uint32_t b = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    int lane = threadIdx.x & 31;
+    if (b >= nb) return;
+    uint32_t e0 = (b * 32u + lane) * 32u;
+    uint32_t valid = e0 >= s.n ? 0u : min(32u, s.n - e0);
+    WordRanks w = block_ranks(s, b, (uint32_t)q1[b], (uint32_t)q2[b], lane, valid);
+    if (OUT == 0) {
+        uint32_t r[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) r[i] = 0;
+        decode_word(s, w, [](int) {}, [&](int i, uint32_t off) {
+            uint32_t v = *(const uint32_t *)((const char *)tab + off);
+            r[i >> 2] |= v << (8 * (i & 3));
+        });
+        int8_t *o = (int8_t *)out + e0;
+        if (valid == 32) {
+            ((uint4 *)o)[0] = make_uint4(r[0], r[1], r[2], r[3]);
+            ((uint4 *)o)[1] = make_uint4(r[4], r[5], r[6], r[7]);
+        } else {
+            for (uint32_t i = 0; i < valid; ++i) o[i] = (int8_t)((r[i >> 2] >> (8 * (i & 3))) & 0xff);
+        }
+    } else {
+        uint32_t r[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) r[i] = 0;
+        decode_word(s, w, [](int) {}, [&](int i, uint32_t off) {
+            uint32_t v = *(const uint32_t *)((const char *)tab + off);
+            r[i >> 1] |= v << (16 * (i & 1));
+        });
+        uint16_t *o = (uint16_t *)out + e0;
+        if (valid == 32) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) ((uint4 *)o)[j] = make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
+        } else {
+            for (uint32_t i = 0; i < valid; ++i) o[i] = (uint16_t)((r[i >> 1] >> (16 * (i & 1))) & 0xffff);
+        }
+    }
+}
+
+// --------------------------------------------------------------- gemv -------
+// Work split: the tensor's rank blocks are dealt to warps in contiguous runs of
+// `bpw` blocks.  A warp sums, per output row it touches, the products of its
+// run; a row that lies entirely inside one run is written straight to y, a row
+// shared between runs goes to one fp32 slot per (row, run) and is summed in run
+// order by the last CTA to finish (no atomics on data, same bits every run).
+constexpr int kGemvThreads = 256;
+constexpr int kGemvCtasPerSm = 2;
+
+struct GemvPlan {
+    uint32_t nb;        // rank blocks
+    uint32_t grid;      // CTAs
+    uint32_t warps;     // total warps
+    uint32_t bpw;       // blocks per warp
+    uint32_t pmax;      // slots per row
+};
+
+static GemvPlan make_plan(uint32_t out_f, uint32_t in_f)
+{
+    GemvPlan p;
+    unsigned long long n = (unsigned long long)out_f * in_f;
+    p.nb = (uint32_t)((n + kBlk - 1) / kBlk);
+    uint32_t wpc = kGemvThreads / 32;
+    uint32_t max_grid = (uint32_t)num_sms() * kGemvCtasPerSm;
+    uint32_t want = (p.nb + wpc - 1) / wpc;
+    p.grid = want < max_grid ? want : max_grid;
+    if (p.grid == 0) p.grid = 1;
+    p.warps = p.grid * wpc;
+    p.bpw = (p.nb + p.warps - 1) / p.warps;
+    uint32_t row_blocks = (in_f + kBlk - 1) / kBlk + 1;   // blocks one row can touch
+    p.pmax = (row_blocks + p.bpw - 1) / p.bpw + 1;
+    return p;
+}
+
+__device__ __forceinline__ float bf16lo(uint32_t v) { return __uint_as_float(v << 16); }
+__device__ __forceinline__ float bf16hi(uint32_t v) { return __uint_as_float(v & 0xffff0000u); }
+
+template <int M>
+__global__ void __launch_bounds__(kGemvThreads, kGemvCtasPerSm)
+k_gemv(Streams s, const int32_t *__restrict__ q1, const int32_t *__restrict__ q2,
+       const __nv_bfloat16 *__restrict__ x, const __nv_bfloat16 *__restrict__ bias, void *y, int y_f32,
+       float *slots, uint32_t *ticket, GemvPlan plan)
+{
+    __shared__ float lut[kLutSize];
+    __shared__ uint32_t is_last;
+    {
+        float sc = __bfloat162float(*s.scale);
+        for (int e = threadIdx.x; e < kLutSize; e += blockDim.x)
+            lut[e] = __bfloat162float(__float2bfloat16_rn((float)lut_code(e) * sc));
+    }
+    __syncthreads();
+
+    const int lane = threadIdx.x & 31;
+    const uint32_t gw = blockIdx.x * (kGemvThreads / 32) + (threadIdx.x >> 5);
+    const uint32_t b_begin = gw * plan.bpw;
+    const uint32_t b_end = min(b_begin + plan.bpw, plan.nb);
+
+    auto emit = [&](uint32_t row, const float (&acc)[M]) {
+        // all words of `row` inside this warp's run?
+        uint32_t fb = (uint32_t)(((unsigned long long)row * s.in_f) >> 10);
+        uint32_t lb = (uint32_t)((((unsigned long long)(row + 1) * s.in_f) - 1) >> 10);
+        bool whole = fb >= b_begin && lb < b_end;
+#pragma unroll
+        for (int m = 0; m < M; ++m) {
+            float v = warp_sum(acc[m]);
+            if (lane == 0) {
+                if (whole) {
+                    size_t o = (size_t)m * s.out_f + row;
+                    if (y_f32) {
+                        ((float *)y)[o] = bias ? v + __bfloat162float(bias[row]) : v;
+                    } else {
+                        __nv_bfloat16 h = __float2bfloat16_rn(v);
+                        if (bias) h = __hadd(h, bias[row]);
+                        ((__nv_bfloat16 *)y)[o] = h;
+                    }
+                } else {
+                    uint32_t piece = gw - fb / plan.bpw;
+                    slots[((size_t)m * s.out_f + row) * plan.pmax + piece] = v;
+                }
+            }
+        }
+    };
+
+    if (b_begin < b_end) {
+        float acc[M];
+#pragma unroll
+        for (int m = 0; m < M; ++m) acc[m] = 0.f;
+        uint32_t cur_row = (uint32_t)(((unsigned long long)b_begin * kBlk) / s.in_f);
+
+        for (uint32_t b = b_begin; b < b_end; ++b) {
+            uint32_t e0 = (b * 32u + lane) * 32u;
+            uint32_t valid = e0 < s.n ? 32u : 0u;
+            WordRanks w = block_ranks(s, b, (uint32_t)__ldg(q1 + b), (uint32_t)__ldg(q2 + b), lane, valid);
+            uint32_t lrow = valid ? e0 / s.in_f : 0xffffffffu;
+            uint32_t k0 = valid ? e0 - lrow * s.in_f : 0u;
+            float part[M];
+#pragma unroll
+            for (int m = 0; m < M; ++m) part[m] = 0.f;
+            uint4 xv[M];
+            decode_word(
+                s, w,
+                [&](int q) {
+#pragma unroll
+                    for (int m = 0; m < M; ++m)
+                        xv[m] = valid ? __ldg((const uint4 *)(x + (size_t)m * s.in_f + k0) + q) : make_uint4(0, 0, 0, 0);
+                },
+                [&](int i, uint32_t off) {
+                    float wt = *(const float *)((const char *)lut + off);
+#pragma unroll
+                    for (int m = 0; m < M; ++m) {
+                        const int j = i & 7;
+                        uint32_t pr = j < 2 ? xv[m].x : (j < 4 ? xv[m].y : (j < 6 ? xv[m].z : xv[m].w));
+                        float xf = (j & 1) ? bf16hi(pr) : bf16lo(pr);
+                        part[m] = fmaf(xf, wt, part[m]);
+                    }
+                });
+            // fold this word's sums into the per-row accumulators
+            if (__all_sync(0xffffffffu, !valid || lrow == cur_row)) {
+#pragma unroll
+                for (int m = 0; m < M; ++m) acc[m] += part[m];
+            } else {
+                bool used = !valid;
+                while (true) {
+                    if (!used && lrow == cur_row) {
+#pragma unroll
+                        for (int m = 0; m < M; ++m) acc[m] += part[m];
+                        used = true;
+                    }
+                    uint32_t pending = __ballot_sync(0xffffffffu, !used);
+                    if (!pending) break;
+                    emit(cur_row, acc);
+#pragma unroll
+                    for (int m = 0; m < M; ++m) acc[m] = 0.f;
+                    cur_row = __shfl_sync(0xffffffffu, lrow, __ffs(pending) - 1);
+                }
+            }
+            // a row that ends exactly at this block's end is complete
+            uint32_t next_e = (b + 1) * (uint32_t)kBlk;
+            if (next_e >= s.n || next_e == (cur_row + 1) * s.in_f) {
+                emit(cur_row, acc);
+#pragma unroll
+                for (int m = 0; m < M; ++m) acc[m] = 0.f;
+                cur_row += 1;
+            }
+        }
+        // run ended inside a row
+        uint32_t end_e = min(b_end * (uint32_t)kBlk, s.n);
+        if (end_e < s.n && end_e != cur_row * s.in_f) emit(cur_row, acc);
+    }
+
+    // ---- last CTA sums the rows that were shared between runs
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        uint32_t t = atomicAdd(ticket, 1u);
+        is_last = (t == gridDim.x - 1);
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    uint32_t n_runs = (plan.nb + plan.bpw - 1) / plan.bpw;
+    for (uint32_t g = 1 + threadIdx.x; g < n_runs; g += blockDim.x) {
+        unsigned long long e = (unsigned long long)g * plan.bpw * kBlk;   // first element of run g
+        uint32_t row = (uint32_t)(e / s.in_f);
+        unsigned long long row_e0 = (unsigned long long)row * s.in_f;
+        if (e == row_e0) continue;                                   // run starts on a row boundary
+        unsigned long long prev = (unsigned long long)(g - 1) * plan.bpw * kBlk;
+        if (prev > row_e0) continue;                                 // an earlier run boundary owns this row
+        uint32_t fb = (uint32_t)(row_e0 >> 10);
+        uint32_t lb = (uint32_t)((row_e0 + s.in_f - 1) >> 10);
+        uint32_t np = lb / plan.bpw - fb / plan.bpw + 1;
+        for (int m = 0; m < M; ++m) {
+            const float *sl = slots + ((size_t)m * s.out_f + row) * plan.pmax;
+            float v = 0.f;
+            for (uint32_t p = 0; p < np; ++p) v += __ldcg(sl + p);
+            size_t o = (size_t)m * s.out_f + row;
+            if (y_f32) {
+                ((float *)y)[o] = bias ? v + __bfloat162float(bias[row]) : v;
+            } else {
+                __nv_bfloat16 h = __float2bfloat16_rn(v);
+                if (bias) h = __hadd(h, bias[row]);
+                ((__nv_bfloat16 *)y)[o] = h;
+            }
+        }
+    }
+    if (threadIdx.x == 0) *ticket = 0;
+}
+
+template <int M>
+static void launch_gemv(const Streams &s, const int32_t *q1, const int32_t *q2, const void *x, const void *bias,
+                        void *y, int y_f32, float *slots, uint32_t *ticket, const GemvPlan &p, cudaStream_t st)
+{
+    k_gemv<M><<<p.grid, kGemvThreads, 0, st>>>(s, q1, q2, (const __nv_bfloat16 *)x, (const __nv_bfloat16 *)bias, y,
+                                               y_f32, slots, ticket, p);
+}
+
+}  // namespace ixb
+
+// =============================================================== C ABI =======
+using namespace ixb;
+
+extern "C" int ixb_version(void) { return 100; }
+extern "C" const char *ixb_last_error(void) { return g_err; }
+extern "C" int64_t ixb_launch_count(void) { return (int64_t)g_launches.load(); }
+
+extern "C" size_t ixb_prefix_workspace_bytes(int64_t n_elements)
+{
+    size_t nb = (size_t)((n_elements + kBlk - 1) / kBlk);
+    return 4 * nb * sizeof(int32_t) + 256;
+}
+
+extern "C" int ixb_prefix_tables(const ixb_packed *w, int64_t gran, int64_t n_units, int32_t *q1, int32_t *q2,
+                                 void *ws, size_t ws_bytes, ixb_stream_t stream)
+{
+    Streams s;
+    int rc = to_streams(w, &s);
+    if (rc) return rc;
+    if (!q1 || !q2 || !ws) return fail(IXB_E_ARG, "q1/q2/workspace is NULL");
+    if (gran <= 0 || n_units <= 0) return fail(IXB_E_ARG, "gran and n_units must be positive");
+    if ((unsigned long long)(n_units - 1) * (unsigned long long)gran > s.n)
+        return fail(IXB_E_ARG, "unit %lld starts beyond the tensor", (long long)(n_units - 1));
+    if (gran > 0x7fffffffLL) return fail(IXB_E_ARG, "gran too large");
+    if (ws_bytes < ixb_prefix_workspace_bytes(s.n)) return fail(IXB_E_SCRATCH, "prefix workspace too small");
+    cudaStream_t st = (cudaStream_t)stream;
+    uint32_t nb = (s.n + kBlk - 1) / kBlk;
+    int32_t *cnt1 = (int32_t *)ws, *a_blk = cnt1 + nb, *cnt2 = a_blk + nb, *c_blk = cnt2 + nb;
+    uint32_t grid = (nb + 7) / 8;
+    k_count_l1<<<grid, 256, 0, st>>>(s, nb, cnt1);
+    if ((rc = launch_check("k_count_l1"))) return rc;
+    k_excl_scan<<<1, 1024, 0, st>>>(cnt1, a_blk, nb);
+    if ((rc = launch_check("k_excl_scan"))) return rc;
+    k_count_l2<<<grid, 256, 0, st>>>(s, nb, a_blk, cnt1, cnt2);
+    if ((rc = launch_check("k_count_l2"))) return rc;
+    k_excl_scan<<<1, 1024, 0, st>>>(cnt2, c_blk, nb);
+    if ((rc = launch_check("k_excl_scan"))) return rc;
+    k_unit_prefix<<<(unsigned)((n_units + 7) / 8), 256, 0, st>>>(s, (uint32_t)gran, (uint32_t)n_units, a_blk, c_blk, q1, q2);
+    return launch_check("k_unit_prefix");
+}
+
+extern "C" int ixb_decode(const ixb_packed *w, const int32_t *blk_q1, const int32_t *blk_q2, void *out, int out_kind,
+                          ixb_stream_t stream)
+{
+    Streams s;
+    int rc = to_streams(w, &s);
+    if (rc) return rc;
+    if (!blk_q1 || !blk_q2 || !out) return fail(IXB_E_ARG, "table/output pointer is NULL");
+    if ((uintptr_t)out & 15u) return fail(IXB_E_ARG, "output is not 16-byte aligned");
+    uint32_t nb = (s.n + kBlk - 1) / kBlk;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (out_kind == 0) k_decode<0><<<(nb + 7) / 8, 256, 0, st>>>(s, blk_q1, blk_q2, out);
+    else if (out_kind == 1) k_decode<1><<<(nb + 7) / 8, 256, 0, st>>>(s, blk_q1, blk_q2, out);
+    else return fail(IXB_E_ARG, "out_kind must be 0 (int8 codes) or 1 (bf16)");
+    return launch_check("k_decode");
+}
+
+extern "C" size_t ixb_gemv_scratch_bytes(int64_t out_f, int64_t in_f, int64_t m_rows)
+{
+    if (out_f <= 0 || in_f <= 0 || m_rows <= 0) return 0;
+    GemvPlan p = make_plan((uint32_t)out_f, (uint32_t)in_f);
+    return 256 + (size_t)m_rows * (size_t)out_f * p.pmax * sizeof(float);
+}
+
+extern "C" int ixb_gemv(const ixb_packed *w, const int32_t *blk_q1, const int32_t *blk_q2, const void *x,
+                        int64_t m_rows, const void *bias, void *y, int y_is_f32, void *scratch, size_t scratch_bytes,
+                        ixb_stream_t stream)
+{
+    Streams s;
+    int rc = to_streams(w, &s);
+    if (rc) return rc;
+    if (!blk_q1 || !blk_q2 || !x || !y || !scratch) return fail(IXB_E_ARG, "NULL pointer argument");
+    if (m_rows < 1 || m_rows > 8) return fail(IXB_E_UNSUPPORTED, "m_rows=%lld outside 1..8", (long long)m_rows);
+    if (s.in_f % 32u) return fail(IXB_E_UNSUPPORTED, "in_f=%u is not a multiple of 32", s.in_f);
+    if ((uintptr_t)x & 15u) return fail(IXB_E_ARG, "x is not 16-byte aligned");
+    if (scratch_bytes < ixb_gemv_scratch_bytes(s.out_f, s.in_f, m_rows)) return fail(IXB_E_SCRATCH, "gemv scratch too small");
+    GemvPlan p = make_plan(s.out_f, s.in_f);
+    uint32_t *ticket = (uint32_t *)scratch;
+    float *slots = (float *)((char *)scratch + 256);
+    cudaStream_t st = (cudaStream_t)stream;
+    switch (m_rows) {
+    case 1: launch_gemv<1>(s, blk_q1, blk_q2, x, bias, y, y_is_f32, slots, ticket, p, st); break;
+    case 2: launch_gemv<2>(s, blk_q1, blk_q2, x, bias, y, y_is_f32, slots, ticket, p, st); break;
+    case 3: launch_gemv<3>(s, blk_q1, blk_q2, x, bias, y, y_is_f32, slots, ticket, p, st); break;
+    case 4: launch_gemv<4>(s, blk_q1, blk_q2, x, bias, y, y_is_f32, slots, ticket, p, st); break;
+    case 5: launch_gemv<5>(s, blk_q1, blk_q2, x, bias, y, y_is_f32, slots, ticket, p, st); break;
+    case 6: launch_gemv<6>(s, blk_q1, blk_q2, x, bias, y, y_is_f32, slots, ticket, p, st); break;
+    case 7: launch_gemv<7>(s, blk_q1, blk_q2, x, bias, y, y_is_f32, slots, ticket, p, st); break;
+    default: launch_gemv<8>(s, blk_q1, blk_q2, x, bias, y, y_is_f32, slots, ticket, p, st); break;
+    }
+    return launch_check("k_gemv");
+}
