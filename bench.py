@@ -1,0 +1,330 @@
+"""Benchmark of the INT8-X hot path: batch-1 fused decode+GEMV over the packed
+down_proj tensor (5120 x 17408), reported as packed-weight GB/s.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+One step = one pass of y = W x over the whole packed tensor.  Algorithmic bytes
+per step = the reference's `total_bytes` of the packed tensor + 2*in_f (x) +
+2*out_f (y); rank tables and padding are not counted.  Timed steps rotate over
+four device copies of the packed streams (242 MB > L2), so every step reads
+its weights from HBM.  At N > 1 the tensor is split by columns (row-parallel
+linear: each rank owns in_f/N columns of every row) and the partial outputs are
+summed with one NCCL all-reduce per step.
+
+`--impl reference` times the CPU port of the reference's own layer path (decode
+to bf16, then matmul) on the host cores instead.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+import numpy as np
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+OUT_F, IN_F = 5120, 17408
+COPIES = 4
+METRIC = "fused decode+GEMV packed-weight bandwidth (batch 1)"
+UNIT = "GB/s"
+
+
+def measured_peak():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
+    return 6650.0, "fallback (6.65 TB/s, earlier measurement on this pool)"
+
+
+class ClockSampler(threading.Thread):
+    """Polls SM clock and throttle reasons through NVML while a region runs."""
+
+    def __init__(self, index: int, period_s: float = 0.01):
+        super().__init__(daemon=True)
+        self.index, self.period, self.samples, self.reasons = index, period_s, [], set()
+        self.max_mhz = None
+        self._stop_evt = threading.Event()
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def _once(self):
+        nv = self.nv
+        self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+        try:
+            r = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+        except Exception:
+            r = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+        names = {
+            "hw_slowdown": 0x8, "sw_power_cap": 0x4, "sw_thermal_slowdown": 0x20,
+            "hw_thermal_slowdown": 0x40, "hw_power_brake_slowdown": 0x80,
+        }
+        for k, bit in names.items():
+            if r & bit:
+                self.reasons.add(k)
+
+    def run(self):
+        if self.nv is None:
+            return
+        while not self._stop_evt.is_set():
+            try:
+                self._once()
+            except Exception:
+                break
+            time.sleep(self.period)
+
+    def stop(self) -> dict:
+        self._stop_evt.set()
+        self.join(timeout=2)
+        if self.nv is not None and not self.samples:
+            try:
+                self._once()
+            except Exception:
+                pass
+        med = float(np.median(self.samples)) if self.samples else None
+        return {"sm_mhz": med, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
+                "samples": len(self.samples)}
+
+
+def algorithmic_bytes(total_bytes: int) -> int:
+    return total_bytes + 2 * IN_F + 2 * OUT_F
+
+
+# ----------------------------------------------------------------- CPU arm ---
+def cpu_layer_gbs(steps: int, warmup: int, seed: int = 0):
+    """Oracle port of the reference's CPU layer path on the host cores."""
+    from ixrun_b200.synth import laplace_codes
+    from oracle import ixb_oracle as O
+
+    codes = laplace_codes(OUT_F, IN_F, seed)
+    sc = int(O.f32_to_bf16_bits(np.array([2.0 ** -9], dtype=np.float32))[0])
+    p = O.pack_codes(codes, OUT_F, IN_F, sc)
+    layer = O.LayerCPU(p)
+    x = O.f32_to_bf16_bits(np.random.default_rng(1).standard_normal((1, IN_F)).astype(np.float32))
+    for _ in range(warmup):
+        layer(x)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        layer(x)
+    dt = (time.perf_counter() - t0) / steps
+    return algorithmic_bytes(p["total_bytes"]) / dt / 1e9, dt, O.num_threads()
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    steps = max(1, min(args.steps, 8))       # a step is a full 89 M-weight layer on the CPU (~1 s)
+    warm = max(1, min(args.warmup, 2))
+    gbs, dt, cores = cpu_layer_gbs(steps, warm)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": gbs, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": steps, "warmup": warm, "ms_per_step": dt * 1e3, "higher_is_better": True,
+        "scaling": "strong" if args.gpus > 1 else "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"down_proj {OUT_F}x{IN_F} batch 1, decode to bf16 then matmul, host cores"},
+        "cpu_baseline": {"value": gbs, "unit": UNIT, "cores": cores, "kind": "port",
+                         "sample": f"{steps} full {OUT_F}x{IN_F} layers"},
+        "e2e": {"value": gbs, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ----------------------------------------------------------------- GPU arm ---
+def run_gpu(args):
+    import torch.distributed as dist
+
+    from ixrun_b200 import _lib
+    from ixrun_b200.engine import StreamingLinear
+    from ixrun_b200.quantize import pack_codes
+    from ixrun_b200.synth import laplace_codes
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU path); use --impl reference for the CPU arm")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
+
+    # ---- synthetic layer, column shard of this rank
+    codes = laplace_codes(OUT_F, IN_F, seed=0).reshape(OUT_F, IN_F)
+    scale = torch.tensor(2.0 ** -9, dtype=torch.bfloat16)
+    full_bytes = pack_codes(codes.reshape(-1), scale, OUT_F, IN_F)["total_bytes"] if world > 1 else None
+    in_loc = IN_F // world
+    shard = np.ascontiguousarray(codes[:, rank * in_loc:(rank + 1) * in_loc])
+    packed = pack_codes(shard.reshape(-1), scale, OUT_F, in_loc)
+    if full_bytes is None:
+        full_bytes = packed["total_bytes"]
+    alg_bytes = algorithmic_bytes(full_bytes)
+    alg_bytes_rank = packed["total_bytes"] + 2 * in_loc + 2 * OUT_F
+    layers = [StreamingLinear(packed) for _ in range(COPIES)]
+    g = torch.Generator().manual_seed(1)
+    x_host = torch.randn(1, IN_F, generator=g).bfloat16()[:, rank * in_loc:(rank + 1) * in_loc].contiguous().pin_memory()
+    x = x_host.to(dev)
+    y32 = torch.empty(1, OUT_F, dtype=torch.float32, device=dev)
+    y16 = torch.empty(1, OUT_F, dtype=torch.bfloat16, device=dev)
+
+    def step(i):
+        lay = layers[i % COPIES]
+        if world > 1:
+            lay._dp.gemv(x, out=y32)
+            dist.all_reduce(y32)
+            y16.copy_(y32)
+        else:
+            lay._dp.gemv(x, out=y16)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for i in range(max(args.warmup, 3)):
+        step(i)
+    barrier()
+
+    # ---- timed region: K steps, device timed, max over ranks
+    graph = None
+    if world == 1:
+        # one CUDA graph holding the K launches keeps host launch gaps out of the device time
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            step(0)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for i in range(args.steps):
+                step(i)
+        graph.replay()      # untimed: first replay uploads the graph
+        torch.cuda.synchronize()
+    launches0 = _lib.lib().ixb_launch_count()
+    sampler = ClockSampler(local)
+    sampler.start()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    if graph is not None:
+        graph.replay()
+    else:
+        for i in range(args.steps):
+            step(i)
+    e1.record()
+    barrier()
+    clocks = sampler.stop()
+    ms = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    launches = args.steps if graph is not None else _lib.lib().ixb_launch_count() - launches0
+    ms_per_step = ms / args.steps
+    value = alg_bytes / (ms_per_step * 1e-3) / 1e9
+
+    # ---- dominant kernel alone (rank-local shard), CUDA events on the launching stream
+    reps = max(20, min(args.steps, 200))
+    kt = []
+    for i in range(reps):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        layers[i % COPIES]._dp.gemv(x, out=y16)
+        b.record()
+        b.synchronize()
+        kt.append(a.elapsed_time(b))
+    k_ms = float(np.mean(kt)) if graph is None else ms_per_step
+    peak, peak_src = measured_peak()
+    achieved = alg_bytes_rank / (k_ms * 1e-3) / 1e9
+
+    # ---- end to end through the module API with host buffers
+    y_host = torch.empty(1, OUT_F, dtype=torch.bfloat16).pin_memory()
+    e2e_steps = max(10, min(args.steps, 200))
+
+    def e2e_step(i):
+        xd = x_host.to(dev, non_blocking=True)
+        if world > 1:
+            layers[i % COPIES]._dp.gemv(xd, out=y32)
+            dist.all_reduce(y32)
+            y_host.copy_(y32.to(torch.bfloat16), non_blocking=True)
+        else:
+            y_host.copy_(layers[i % COPIES](xd), non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    for i in range(3):
+        e2e_step(i)
+    barrier()
+    t0 = time.perf_counter()
+    for i in range(e2e_steps):
+        e2e_step(i)
+    barrier()
+    e2e_s = (time.perf_counter() - t0) / e2e_steps
+    if world > 1:
+        t = torch.tensor([e2e_s], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_s = float(t.item())
+
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
+        "scaling": "strong" if world > 1 else "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {
+            "workload": f"down_proj {OUT_F}x{IN_F} batch 1 fused decode+GEMV, (3,5,8) codes ~ round(Laplace(0,4.4))",
+            "algorithmic_bytes_per_step": alg_bytes,
+            "l2": f"timed steps rotate over {COPIES} device copies of the packed streams ({COPIES * full_bytes // world / 1e6:.0f} MB per GPU)",
+            "parallelism": "single GPU" if world == 1 else f"tp{world}: column shards of in_f, one NCCL all-reduce of y per step",
+            "timed_with": "CUDA events around one graph replay of K launches" if graph is not None else "CUDA events around K eager steps",
+        },
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                     "traffic": None, "peak_source": peak_src, "kernel": "k_gemv<1>",
+                     "algorithmic_bytes_per_launch": alg_bytes_rank, "launch_ms": k_ms},
+        "e2e": {"value": alg_bytes / e2e_s / 1e9, "unit": UNIT, "h2d_bytes_per_step": 2 * in_loc,
+                "d2h_bytes_per_step": 2 * OUT_F, "ms_per_step": e2e_s * 1e3, "steps": e2e_steps},
+        "gpu_launches": int(launches),
+        "clocks": clocks,
+    }
+    if rank == 0:
+        if world == 1:
+            cpu_steps = 3
+            gbs, dt, cores = cpu_layer_gbs(cpu_steps, 1)
+            line["cpu_baseline"] = {"value": gbs, "unit": UNIT, "cores": cores, "kind": "port",
+                                    "sample": f"{cpu_steps} full {OUT_F}x{IN_F} layers, {dt * 1e3:.0f} ms each"}
+        traffic = os.path.join(ROOT, "profiles", "gemv_traffic.json")
+        if os.path.exists(traffic):
+            with open(traffic) as f:
+                line["roofline"]["traffic"] = json.load(f).get("dram_bytes_per_launch")
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=400)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_gpu(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -189,10 +189,10 @@ __global__ void k_unit_prefix(Streams s, uint32_t gran, uint32_t n_units, const 
 template <int OUT>
 __global__ void __launch_bounds__(256) k_decode(Streams s, const int32_t *q1, const int32_t *q2, void *out)
 {
-    __shared__ uint32_t tab[kLutSize];
+    __shared__ __align__(2048) uint32_t tab[kTabEntries];
     float sc = __bfloat162float(*s.scale);
-    for (int e = threadIdx.x; e < kLutSize; e += blockDim.x) {
-        int code = lut_code(e);
+    for (int e = threadIdx.x; e < kTabEntries; e += blockDim.x) {
+        int code = tab_code(e);
         if (OUT == 0) tab[e] = (uint32_t)(code & 0xff);
         else tab[e] = (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn((float)code * sc));
     }
@@ -203,48 +203,44 @@ __global__ void __launch_bounds__(256) k_decode(Streams s, const int32_t *q1, co
     if (b >= nb) return;
     uint32_t e0 = (b * 32u + lane) * 32u;
     uint32_t valid = e0 >= s.n ? 0u : min(32u, s.n - e0);
-    WordRanks w = block_ranks(s, b, (uint32_t)q1[b], (uint32_t)q2[b], lane, valid);
-    if (OUT == 0) {
-        uint32_t r[8];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) r[i] = 0;
-        decode_word(s, w, [](int) {}, [&](int i, uint32_t off) {
-            uint32_t v = *(const uint32_t *)((const char *)tab + off);
-            r[i >> 2] |= v << (8 * (i & 3));
-        });
-        int8_t *o = (int8_t *)out + e0;
-        if (valid == 32) {
-            ((uint4 *)o)[0] = make_uint4(r[0], r[1], r[2], r[3]);
-            ((uint4 *)o)[1] = make_uint4(r[4], r[5], r[6], r[7]);
+    GlobalSrc src{s};
+    WordRanks w = block_ranks(src, ldw(s.b1, b * 32u + lane, s.b1_words), b, (uint32_t)q1[b], (uint32_t)q2[b], lane, valid);
+    WordCursors c = word_cursors(w);
+    const uint32_t tab_addr = (uint32_t)__cvta_generic_to_shared(tab);
+    constexpr int kPer = OUT == 0 ? 4 : 2;          // elements per 32-bit output register
+    constexpr int kBits = OUT == 0 ? 8 : 16;
+    if (__any_sync(0xffffffffu, c.max_l3 > 3u || valid != 32u)) {
+        // rare: a group with more than 3 level-3 elements, or the tensor's ragged end
+        if (OUT == 0) {
+            int8_t *o = (int8_t *)out + e0;
+            decode_word_any(src, w, c, tab, [](int) {}, [&](int i, uint32_t v) { if ((uint32_t)i < valid) o[i] = (int8_t)v; });
         } else {
-            for (uint32_t i = 0; i < valid; ++i) o[i] = (int8_t)((r[i >> 2] >> (8 * (i & 3))) & 0xff);
+            uint16_t *o = (uint16_t *)out + e0;
+            decode_word_any(src, w, c, tab, [](int) {}, [&](int i, uint32_t v) { if ((uint32_t)i < valid) o[i] = (uint16_t)v; });
         }
-    } else {
-        uint32_t r[16];
-#pragma unroll
-        for (int i = 0; i < 16; ++i) r[i] = 0;
-        decode_word(s, w, [](int) {}, [&](int i, uint32_t off) {
-            uint32_t v = *(const uint32_t *)((const char *)tab + off);
-            r[i >> 1] |= v << (16 * (i & 1));
-        });
-        uint16_t *o = (uint16_t *)out + e0;
-        if (valid == 32) {
-#pragma unroll
-            for (int j = 0; j < 4; ++j) ((uint4 *)o)[j] = make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
-        } else {
-            for (uint32_t i = 0; i < valid; ++i) o[i] = (uint16_t)((r[i >> 1] >> (16 * (i & 1))) & 0xffff);
-        }
+        return;
     }
+    uint32_t r[32 / kPer];
+#pragma unroll
+    for (int i = 0; i < 32 / kPer; ++i) r[i] = 0;
+    decode_word_fast(src, w, c, tab_addr, [](int) {}, [&](int i, uint32_t v) { r[i / kPer] |= v << (kBits * (i % kPer)); });
+    uint4 *o = (uint4 *)((char *)out + (size_t)e0 * (OUT == 0 ? 1 : 2));
+#pragma unroll
+    for (int j = 0; j < 8 / kPer; ++j) o[j] = make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
 }
 
 // --------------------------------------------------------------- gemv -------
 // Work split: the tensor's rank blocks are dealt to warps in contiguous runs of
-// `bpw` blocks.  A warp sums, per output row it touches, the products of its
-// run; a row that lies entirely inside one run is written straight to y, a row
-// shared between runs goes to one fp32 slot per (row, run) and is summed in run
-// order by the last CTA to finish (no atomics on data, same bits every run).
+// `bpw` blocks.  Each warp streams its run through a private ring of
+// shared-memory slots filled with cp.async one block ahead of the decoder.  A
+// warp sums, per output row it touches, the products of its run; a row that
+// lies entirely inside one run is written straight to y, a row shared between
+// runs goes to one fp32 slot per (row, run) and is summed in run order by the
+// last CTA to finish (no atomics on data, same bits every run).
 constexpr int kGemvThreads = 256;
+constexpr int kGemvWarps = kGemvThreads / 32;
 constexpr int kGemvCtasPerSm = 2;
+constexpr int kStages = 2;
 
 struct GemvPlan {
     uint32_t nb;        // rank blocks
@@ -252,22 +248,26 @@ struct GemvPlan {
     uint32_t warps;     // total warps
     uint32_t bpw;       // blocks per warp
     uint32_t pmax;      // slots per row
+    uint32_t x_smem;    // 1: activations are staged in shared memory
+    uint32_t smem;      // dynamic shared memory bytes
 };
 
-static GemvPlan make_plan(uint32_t out_f, uint32_t in_f)
+static GemvPlan make_plan(uint32_t out_f, uint32_t in_f, uint32_t m_rows)
 {
     GemvPlan p;
     unsigned long long n = (unsigned long long)out_f * in_f;
     p.nb = (uint32_t)((n + kBlk - 1) / kBlk);
-    uint32_t wpc = kGemvThreads / 32;
     uint32_t max_grid = (uint32_t)num_sms() * kGemvCtasPerSm;
-    uint32_t want = (p.nb + wpc - 1) / wpc;
+    uint32_t want = (p.nb + kGemvWarps - 1) / kGemvWarps;
     p.grid = want < max_grid ? want : max_grid;
     if (p.grid == 0) p.grid = 1;
-    p.warps = p.grid * wpc;
+    p.warps = p.grid * kGemvWarps;
     p.bpw = (p.nb + p.warps - 1) / p.warps;
     uint32_t row_blocks = (in_f + kBlk - 1) / kBlk + 1;   // blocks one row can touch
     p.pmax = (row_blocks + p.bpw - 1) / p.bpw + 1;
+    uint32_t xbytes = m_rows * in_f * 2u;
+    p.x_smem = xbytes <= 36u * 1024u;
+    p.smem = 2u * kTabBytes + kGemvWarps * kStages * Slot::kWords * 4u + (p.x_smem ? xbytes : 0u);
     return p;
 }
 
@@ -280,17 +280,31 @@ k_gemv(Streams s, const int32_t *__restrict__ q1, const int32_t *__restrict__ q2
        const __nv_bfloat16 *__restrict__ x, const __nv_bfloat16 *__restrict__ bias, void *y, int y_f32,
        float *slots, uint32_t *ticket, GemvPlan plan)
 {
-    __shared__ float lut[kLutSize];
+    extern __shared__ __align__(16) uint32_t smem_raw[];
     __shared__ uint32_t is_last;
+    // the table must sit on a 2 KB boundary of the shared window
+    const uint32_t pad = (2048u - ((uint32_t)__cvta_generic_to_shared(smem_raw) & 2047u)) & 2047u;
+    uint32_t *smem = smem_raw + pad / 4u;
+    float *lut = (float *)smem;
+    const uint32_t tab_addr = (uint32_t)__cvta_generic_to_shared(lut);
+    uint32_t *ring = smem + kTabEntries + (threadIdx.x >> 5) * (kStages * Slot::kWords);
+    const __nv_bfloat16 *xs = (const __nv_bfloat16 *)(smem + kTabEntries + kGemvWarps * kStages * Slot::kWords);
     {
         float sc = __bfloat162float(*s.scale);
-        for (int e = threadIdx.x; e < kLutSize; e += blockDim.x)
-            lut[e] = __bfloat162float(__float2bfloat16_rn((float)lut_code(e) * sc));
+        for (int e = threadIdx.x; e < kTabEntries; e += blockDim.x)
+            lut[e] = __bfloat162float(__float2bfloat16_rn((float)tab_code(e) * sc));
+        if (plan.x_smem) {
+            uint32_t nchunk = (uint32_t)M * s.in_f / 8u;   // in_f % 32 == 0
+            for (uint32_t c = threadIdx.x; c < nchunk; c += blockDim.x)
+                ((uint4 *)xs)[c] = __ldg((const uint4 *)x + c);
+        } else {
+            xs = x;
+        }
     }
     __syncthreads();
 
     const int lane = threadIdx.x & 31;
-    const uint32_t gw = blockIdx.x * (kGemvThreads / 32) + (threadIdx.x >> 5);
+    const uint32_t gw = blockIdx.x * kGemvWarps + (threadIdx.x >> 5);
     const uint32_t b_begin = gw * plan.bpw;
     const uint32_t b_end = min(b_begin + plan.bpw, plan.nb);
 
@@ -326,33 +340,67 @@ k_gemv(Streams s, const int32_t *__restrict__ q1, const int32_t *__restrict__ q2
         for (int m = 0; m < M; ++m) acc[m] = 0.f;
         uint32_t cur_row = (uint32_t)(((unsigned long long)b_begin * kBlk) / s.in_f);
 
+        // rank-table entries of the current block and the two after it
+        uint32_t a0 = (uint32_t)__ldg(q1 + b_begin), c0 = (uint32_t)__ldg(q2 + b_begin);
+        uint32_t a1 = 0, c1 = 0;
+        if (b_begin + 1 < plan.nb) { a1 = (uint32_t)__ldg(q1 + b_begin + 1); c1 = (uint32_t)__ldg(q2 + b_begin + 1); }
+        SlotSrc cur = stage_block(s, b_begin, b_begin + 1 == plan.nb, a0, c0, a1, c1, ring, lane);
+        cp_async_commit();
+
         for (uint32_t b = b_begin; b < b_end; ++b) {
+            const uint32_t st = (b - b_begin) % kStages;
+            uint32_t *slot = ring + st * Slot::kWords;
+            // start fetching the next block of the run while this one is decoded
+            SlotSrc nxt = cur;
+            uint32_t a2 = 0, c2 = 0;
+            if (b + 1 < b_end) {
+                if (b + 2 < plan.nb) { a2 = (uint32_t)__ldg(q1 + b + 2); c2 = (uint32_t)__ldg(q2 + b + 2); }
+                nxt = stage_block(s, b + 1, b + 2 == plan.nb, a1, c1, a2, c2,
+                                  ring + ((st + 1) % kStages) * Slot::kWords, lane);
+            }
+            cp_async_commit();
+            cp_async_wait<1>();
+            __syncwarp();
+
             uint32_t e0 = (b * 32u + lane) * 32u;
             uint32_t valid = e0 < s.n ? 32u : 0u;
-            WordRanks w = block_ranks(s, b, (uint32_t)__ldg(q1 + b), (uint32_t)__ldg(q2 + b), lane, valid);
+            WordRanks w = block_ranks(cur, slot[Slot::kB1 + lane], b, a0, c0, lane, valid);
             uint32_t lrow = valid ? e0 / s.in_f : 0xffffffffu;
             uint32_t k0 = valid ? e0 - lrow * s.in_f : 0u;
+            WordCursors c = word_cursors(w);
             float part[M];
 #pragma unroll
             for (int m = 0; m < M; ++m) part[m] = 0.f;
-            uint4 xv[M];
-            decode_word(
-                s, w,
-                [&](int q) {
+            if (__any_sync(0xffffffffu, c.max_l3 > 3u)) {
+                // rare: a group of 8 elements holds more than 3 level-3 values
+                decode_word_any(cur, w, c, (const uint32_t *)lut, [](int) {}, [&](int i, uint32_t v) {
 #pragma unroll
                     for (int m = 0; m < M; ++m)
-                        xv[m] = valid ? __ldg((const uint4 *)(x + (size_t)m * s.in_f + k0) + q) : make_uint4(0, 0, 0, 0);
-                },
-                [&](int i, uint32_t off) {
-                    float wt = *(const float *)((const char *)lut + off);
-#pragma unroll
-                    for (int m = 0; m < M; ++m) {
-                        const int j = i & 7;
-                        uint32_t pr = j < 2 ? xv[m].x : (j < 4 ? xv[m].y : (j < 6 ? xv[m].z : xv[m].w));
-                        float xf = (j & 1) ? bf16hi(pr) : bf16lo(pr);
-                        part[m] = fmaf(xf, wt, part[m]);
-                    }
+                        part[m] = fmaf(__bfloat162float(xs[(size_t)m * s.in_f + k0 + i]), __uint_as_float(v), part[m]);
                 });
+            } else {
+                uint4 xv[M];
+                decode_word_fast(
+                    cur, w, c, tab_addr,
+                    [&](int q) {
+#pragma unroll
+                        for (int m = 0; m < M; ++m) xv[m] = *((const uint4 *)(xs + (size_t)m * s.in_f + k0) + q);
+                    },
+                    [&](int i, uint32_t v) {
+                        float wt = __uint_as_float(v);
+#pragma unroll
+                        for (int m = 0; m < M; ++m) {
+                            const int j = i & 7;
+                            uint32_t pr = j < 2 ? xv[m].x : (j < 4 ? xv[m].y : (j < 6 ? xv[m].z : xv[m].w));
+                            float xf = (j & 1) ? bf16hi(pr) : bf16lo(pr);
+                            part[m] = fmaf(xf, wt, part[m]);
+                        }
+                    });
+            }
+            if (!valid) {
+#pragma unroll
+                for (int m = 0; m < M; ++m) part[m] = 0.f;
+            }
             // fold this word's sums into the per-row accumulators
             if (__all_sync(0xffffffffu, !valid || lrow == cur_row)) {
 #pragma unroll
@@ -381,7 +429,11 @@ k_gemv(Streams s, const int32_t *__restrict__ q1, const int32_t *__restrict__ q2
                 for (int m = 0; m < M; ++m) acc[m] = 0.f;
                 cur_row += 1;
             }
+            __syncwarp();
+            cur = nxt;
+            a0 = a1; c0 = c1; a1 = a2; c1 = c2;
         }
+        cp_async_wait<0>();
         // run ended inside a row
         uint32_t end_e = min(b_end * (uint32_t)kBlk, s.n);
         if (end_e < s.n && end_e != cur_row * s.in_f) emit(cur_row, acc);
@@ -429,7 +481,12 @@ template <int M>
 static void launch_gemv(const Streams &s, const int32_t *q1, const int32_t *q2, const void *x, const void *bias,
                         void *y, int y_f32, float *slots, uint32_t *ticket, const GemvPlan &p, cudaStream_t st)
 {
-    k_gemv<M><<<p.grid, kGemvThreads, 0, st>>>(s, q1, q2, (const __nv_bfloat16 *)x, (const __nv_bfloat16 *)bias, y,
+    static bool attr_set = false;   // opt in to more than 48 KB of dynamic shared memory, once per instantiation
+    if (!attr_set) {
+        cudaFuncSetAttribute(k_gemv<M>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        attr_set = true;
+    }
+    k_gemv<M><<<p.grid, kGemvThreads, p.smem, st>>>(s, q1, q2, (const __nv_bfloat16 *)x, (const __nv_bfloat16 *)bias, y,
                                                y_f32, slots, ticket, p);
 }
 
@@ -495,7 +552,7 @@ extern "C" int ixb_decode(const ixb_packed *w, const int32_t *blk_q1, const int3
 extern "C" size_t ixb_gemv_scratch_bytes(int64_t out_f, int64_t in_f, int64_t m_rows)
 {
     if (out_f <= 0 || in_f <= 0 || m_rows <= 0) return 0;
-    GemvPlan p = make_plan((uint32_t)out_f, (uint32_t)in_f);
+    GemvPlan p = make_plan((uint32_t)out_f, (uint32_t)in_f, (uint32_t)m_rows);
     return 256 + (size_t)m_rows * (size_t)out_f * p.pmax * sizeof(float);
 }
 
@@ -511,7 +568,7 @@ extern "C" int ixb_gemv(const ixb_packed *w, const int32_t *blk_q1, const int32_
     if (s.in_f % 32u) return fail(IXB_E_UNSUPPORTED, "in_f=%u is not a multiple of 32", s.in_f);
     if ((uintptr_t)x & 15u) return fail(IXB_E_ARG, "x is not 16-byte aligned");
     if (scratch_bytes < ixb_gemv_scratch_bytes(s.out_f, s.in_f, m_rows)) return fail(IXB_E_SCRATCH, "gemv scratch too small");
-    GemvPlan p = make_plan(s.out_f, s.in_f);
+    GemvPlan p = make_plan(s.out_f, s.in_f, (uint32_t)m_rows);
     uint32_t *ticket = (uint32_t *)scratch;
     float *slots = (float *)((char *)scratch + 256);
     cudaStream_t st = (cudaStream_t)stream;

@@ -17,24 +17,6 @@ namespace ixb {
 constexpr int kBlk = 1024;        // elements per rank block (one warp iteration)
 constexpr int kWarp = 32;
 
-// Dequantisation table, indexed by "level slot":
-//   level 1 symbol s (0..6)   -> entry 12 + s
-//   level 2 symbol s (0..31)  -> entry s        (valid symbols 0..11, 19..30)
-//   level 3 byte   b (0..255) -> entry 32 + b
-// Every symbol a valid stream can hold for levels 1 and 2 sits in its own
-// shared-memory bank (12..18 are never level-2 symbols), so the per-element
-// lookup of the two common levels is conflict-free.
-constexpr int kLutL1 = 12;
-constexpr int kLutL3 = 32;
-constexpr int kLutSize = 288;
-
-__host__ __device__ inline int lut_code(int entry)
-{
-    if (entry >= kLutL3) return entry - kLutL3 - 127;
-    if (entry >= kLutL1 && entry < kLutL1 + 7) return entry - kLutL1 - 3;
-    return entry - 15;
-}
-
 struct Streams {
     const uint32_t *b1, *b2, *l1, *l2;
     const uint8_t *l3;
@@ -73,90 +55,295 @@ __device__ __forceinline__ uint32_t ldw(const uint32_t *p, uint32_t i, uint32_t 
     return i < n ? __ldg(p + i) : 0u;
 }
 
-// 32 bits of a word stream starting at bit position `bit` (zero beyond the end)
-__device__ __forceinline__ uint32_t fetch32(const uint32_t *p, uint32_t words, uint32_t bit)
-{
-    uint32_t wi = bit >> 5;
-    return __funnelshift_r(ldw(p, wi, words), ldw(p, wi + 1, words), bit & 31u);
-}
+// ---------------------------------------------------------------- sources ---
+// A "source" hands out 32-bit words of the four rank-addressed streams.  Stream
+// positions given to it are relative to its own origin (org_*), which is 0 for
+// global memory and the staged slice's first word for shared memory.
 
-__device__ __forceinline__ uint64_t fetch64(const uint32_t *p, uint32_t words, uint32_t bit)
-{
-    uint32_t wi = bit >> 5, sh = bit & 31u;
-    uint32_t w0 = ldw(p, wi, words), w1 = ldw(p, wi + 1, words), w2 = ldw(p, wi + 2, words);
-    return (uint64_t)__funnelshift_r(w0, w1, sh) | ((uint64_t)__funnelshift_r(w1, w2, sh) << 32);
-}
+// Streams read straight from global memory, zero beyond each stream's end.
+struct GlobalSrc {
+    const Streams &s;
+    static constexpr uint32_t org_b2 = 0, org_l1 = 0, org_l2 = 0, org_l3 = 0;   // bits, bits, bits, bytes
+    __device__ __forceinline__ uint32_t b2w(uint32_t i) const { return ldw(s.b2, i, s.b2_words); }
+    __device__ __forceinline__ uint32_t l1w(uint32_t i) const { return ldw(s.l1, i, s.l1_words); }
+    __device__ __forceinline__ uint32_t l2w(uint32_t i) const { return ldw(s.l2, i, s.l2_words); }
+    __device__ __forceinline__ uint32_t l3w(uint32_t i) const
+    {
+        uint32_t byte0 = 4u * i;
+        if (byte0 + 4u <= s.l3_bytes) return __ldg((const uint32_t *)s.l3 + i);
+        uint32_t v = 0;
+        for (uint32_t k = 0; k < 4u; ++k)
+            if (byte0 + k < s.l3_bytes) v |= (uint32_t)__ldg(s.l3 + byte0 + k) << (8u * k);
+        return v;
+    }
+};
+
+// Slices of one rank block staged in shared memory (zero-filled past the end
+// of a stream, two spare words after every slice).
+struct SlotSrc {
+    const uint32_t *b2, *l1, *l2, *l3;
+    uint32_t org_b2, org_l1, org_l2, org_l3;
+    __device__ __forceinline__ uint32_t b2w(uint32_t i) const { return b2[i]; }
+    __device__ __forceinline__ uint32_t l1w(uint32_t i) const { return l1[i]; }
+    __device__ __forceinline__ uint32_t l2w(uint32_t i) const { return l2[i]; }
+    __device__ __forceinline__ uint32_t l3w(uint32_t i) const { return l3[i]; }
+};
 
 // Per-lane rank state of one 32-element bitmap word.
 struct WordRanks {
-    uint32_t m1;   // B1 word: bit i = element i is level 1
-    uint32_t m2;   // B2 bits of this word's non-L1 elements, in order, LSB first
-    uint32_t a;    // global L1 rank of the word's first L1 element
-    uint32_t c;    // global L2 rank of the word's first L2 element
-    uint32_t t;    // global L3 index of the word's first L3 element
+    uint32_t m1;     // B1 word: bit i = element i is level 1
+    uint32_t m2;     // B2 bits of this word's non-L1 elements, in order, LSB first
+    uint32_t bit1;   // source-relative bit position of the word's first L1 field
+    uint32_t bit2;   // source-relative bit position of the word's first L2 field
+    uint32_t byte3;  // source-relative byte position of the word's first L3 byte
 };
 
-// Ranks for the 32 words of rank block `blk` (lane = word).  `valid` is the
-// number of real elements in this lane's word (32 except at the tensor's end).
-__device__ __forceinline__ WordRanks block_ranks(const Streams &s, uint32_t blk, uint32_t a_blk,
+// Ranks for the 32 words of rank block `blk` (lane = word) from the block's B1
+// word of this lane.  `valid` is the number of real elements in this lane's
+// word (32 except at the tensor's end); a_blk / c_blk are the block's entries
+// of the rank tables.
+template <class Src>
+__device__ __forceinline__ WordRanks block_ranks(const Src &src, uint32_t m1, uint32_t blk, uint32_t a_blk,
                                                  uint32_t c_blk, int lane, uint32_t valid)
 {
     WordRanks w;
-    uint32_t wi = blk * 32u + lane;
-    w.m1 = ldw(s.b1, wi, s.b1_words);
-    uint32_t n1 = __popc(w.m1);
+    w.m1 = m1;
+    uint32_t n1 = __popc(m1);
     uint32_t ex1 = warp_incl_scan(n1, lane) - n1;
-    uint32_t nn = valid - n1;                              // non-L1 elements in this word
-    uint32_t nn_before = 32u * lane - ex1;                 // ... in earlier words of the block
-    uint32_t r = blk * (uint32_t)kBlk - a_blk + nn_before; // global non-L1 rank
-    w.m2 = fetch32(s.b2, s.b2_words, r) & lowmask(nn);
+    uint32_t nn = valid - n1;                               // non-L1 elements in this word
+    uint32_t r = blk * (uint32_t)kBlk - a_blk + 32u * lane - ex1;   // global non-L1 rank
+    uint32_t rb = valid ? r - src.org_b2 : 0u;              // words past the tensor's end read slot word 0
+    w.m2 = __funnelshift_r(src.b2w(rb >> 5), src.b2w((rb >> 5) + 1), rb & 31u) & lowmask(nn);
     uint32_t n2 = __popc(w.m2);
     uint32_t ex2 = warp_incl_scan(n2, lane) - n2;
-    w.a = a_blk + ex1;
-    w.c = c_blk + ex2;
-    w.t = r - w.c;
+    uint32_t a = a_blk + ex1, c = c_blk + ex2;
+    w.bit1 = valid ? a * 3u - src.org_l1 : 0u;
+    w.bit2 = valid ? c * 5u - src.org_l2 : 0u;
+    w.byte3 = valid ? (r - c) - src.org_l3 : 0u;
     return w;
 }
 
-// Decode the 32 elements of one word in order.  pre(q) runs before each group
-// of 8 elements (q = 0..3); sink(i, off) receives the
-// element index i (compile-time after unrolling) and the byte offset of the
-// element's entry in a 4-byte-per-entry table laid out as described above.
-template <class Pre, class Sink>
-__device__ __forceinline__ void decode_word(const Streams &s, const WordRanks &w, Pre &&pre, Sink &&sink)
+// Dequantisation table used by decode_word: 512 four-byte entries, 2 KB
+// aligned in shared memory.
+//   level 2 symbol s -> byte offset 4 s          (entries 0..31)
+//   level 1 symbol s -> byte offset 128 + 4 s    (entries 32..38)
+//   level 3 byte b   -> byte offset 1024 + 4 b   (entries 256..511)
+// The three levels are looked up by separate predicated loads, so only symbols
+// of one level meet in a load: 7 resp. 24 distinct valid symbols, each in its
+// own bank.
+constexpr uint32_t kOffL1 = 128;
+constexpr uint32_t kOffL3 = 1024;
+constexpr int kTabEntries = 512;
+constexpr int kTabBytes = kTabEntries * 4;
+
+__host__ __device__ inline int tab_code(int entry)
 {
+    if (entry >= 256) return entry - 256 - 127;
+    if (entry >= 32 && entry < 40) return entry - 32 - 3;
+    return entry - 15;   // entries 40..255 are never read
+}
+
+// Stream cursors of a word at the four 8-element group boundaries.
+struct WordCursors {
+    uint32_t b1p[4], b2p[4], b3p[4];   // bit positions (source relative) of L1 / L2 / L3 data
+    uint32_t nn[4];                    // non-L1 elements before the group
+    uint32_t max_l3;                   // largest number of level-3 elements in one group
+};
+
+__device__ __forceinline__ WordCursors word_cursors(const WordRanks &w)
+{
+    WordCursors c;
+    uint32_t k1[5], k2[5];
+    k1[0] = 0; k2[0] = 0;
+#pragma unroll
+    for (int q = 1; q < 4; ++q) k1[q] = __popc(w.m1 & ((1u << (8 * q)) - 1u));
+    k1[4] = __popc(w.m1);
+#pragma unroll
+    for (int q = 1; q <= 4; ++q) k2[q] = __popc(w.m2 & lowmask(8u * q - k1[q]));
+    c.max_l3 = 0;
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+        c.nn[q] = 8u * q - k1[q];
+        c.b1p[q] = w.bit1 + 3u * k1[q];
+        c.b2p[q] = w.bit2 + 5u * k2[q];
+        c.b3p[q] = (w.byte3 + c.nn[q] - k2[q]) * 8u;
+        uint32_t l3 = (8u - (k1[q + 1] - k1[q])) - (k2[q + 1] - k2[q]);
+        c.max_l3 = max(c.max_l3, l3);
+    }
+    return c;
+}
+
+// One element of the branch-free decoder.  Exactly one of the three predicated
+// table loads executes; queues hold their fields pre-multiplied by 4.
+#define IXB_ELEM(BITMASK)                                                                         \
+    asm("{\n\t"                                                                                   \
+        ".reg .pred p1, p2, p3;\n\t"                                                              \
+        ".reg .b32 t, a1, a2, a3;\n\t"                                                            \
+        "and.b32 t, %6, " #BITMASK ";\n\t"                                                        \
+        "setp.ne.u32 p1, t, 0;\n\t"                                                               \
+        "and.b32 t, %5, 1;\n\t"                                                                   \
+        "setp.ne.and.u32 p2, t, 0, !p1;\n\t"                                                      \
+        "setp.eq.and.u32 p3, t, 0, !p1;\n\t"                                                      \
+        "lop3.b32 a1, %1, 28, %7, 0xEA;\n\t"                                                      \
+        "lop3.b32 a2, %2, 124, %8, 0xEA;\n\t"                                                     \
+        "lop3.b32 a3, %4, 1020, %9, 0xEA;\n\t"                                                    \
+        "@p1 ld.shared.b32 %0, [a1];\n\t"                                                         \
+        "@p2 ld.shared.b32 %0, [a2];\n\t"                                                         \
+        "@p3 ld.shared.b32 %0, [a3];\n\t"                                                         \
+        "@p1 shr.u32 %1, %1, 3;\n\t"                                                              \
+        "@p2 shf.r.wrap.b32 %2, %2, %3, 5;\n\t"                                                   \
+        "@p2 shr.u32 %3, %3, 5;\n\t"                                                              \
+        "@p3 shr.u32 %4, %4, 8;\n\t"                                                              \
+        "@!p1 shr.u32 %5, %5, 1;\n\t"                                                             \
+        "}"                                                                                       \
+        : "=r"(wv), "+r"(q1), "+r"(q2lo), "+r"(q2hi), "+r"(q3), "+r"(mq)                          \
+        : "r"(m1), "r"(tL1), "r"(tL2), "r"(tL3))
+
+// Decode the 32 elements of one word in order, without data-dependent
+// branches.  `tab` is the shared-window address of the 2 KB-aligned table
+// above.  pre(q) runs before each group of 8 elements (q = 0..3); sink(i, v)
+// receives the element index i (a compile-time constant after unrolling) and
+// the element's 32-bit table entry.  Requires c.max_l3 <= 3 (a group's level-3
+// bytes are carried in one register); decode_word_any has no such limit.
+template <class Src, class Pre, class Sink>
+__device__ __forceinline__ void decode_word_fast(const Src &src, const WordRanks &w, const WordCursors &c,
+                                                 uint32_t tab, Pre &&pre, Sink &&sink)
+{
+    const uint32_t m1 = w.m1;
+    const uint32_t tL2 = tab, tL1 = tab + kOffL1, tL3 = tab + kOffL3;
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
         pre(q);
-        // stream cursors at the start of this group of 8 elements
-        uint32_t k1 = q ? __popc(w.m1 & ((1u << (8 * q)) - 1u)) : 0u;
-        uint32_t nnq = 8u * q - k1;
-        uint32_t k2 = q ? __popc(w.m2 & lowmask(nnq)) : 0u;
-        uint32_t q1 = fetch32(s.l1, s.l1_words, (w.a + k1) * 3u) << 2;   // <= 24 bits used
-        uint64_t q2 = fetch64(s.l2, s.l2_words, (w.c + k2) * 5u) << 2;   // <= 40 bits used
-        uint32_t mq = w.m2 >> nnq;
-        uint32_t t = w.t + nnq - k2;
-#pragma unroll
+        uint32_t i1 = c.b1p[q] >> 5, i2 = c.b2p[q] >> 5, i3 = c.b3p[q] >> 5;
+        uint32_t q1 = __funnelshift_r(src.l1w(i1), src.l1w(i1 + 1), c.b1p[q] & 31u) << 2;   // 8 x 3 bits
+        uint32_t x0 = src.l2w(i2), x1 = src.l2w(i2 + 1), x2 = src.l2w(i2 + 2);
+        uint32_t f0 = __funnelshift_r(x0, x1, c.b2p[q] & 31u), f1 = __funnelshift_r(x1, x2, c.b2p[q] & 31u);
+        uint32_t q2lo = f0 << 2, q2hi = __funnelshift_l(f0, f1, 2);                          // 8 x 5 bits
+        uint32_t q3 = __funnelshift_r(src.l3w(i3), src.l3w(i3 + 1), c.b3p[q] & 31u) << 2;   // 3 bytes
+        uint32_t mq = w.m2 >> c.nn[q];
+        uint32_t wv;
+#define IXB_E(j, mask)                      \
+    IXB_ELEM(mask);                         \
+    sink(8 * q + j, wv);
+        if (q == 0) { IXB_E(0, 0x1) IXB_E(1, 0x2) IXB_E(2, 0x4) IXB_E(3, 0x8) IXB_E(4, 0x10) IXB_E(5, 0x20) IXB_E(6, 0x40) IXB_E(7, 0x80) }
+        if (q == 1) { IXB_E(0, 0x100) IXB_E(1, 0x200) IXB_E(2, 0x400) IXB_E(3, 0x800) IXB_E(4, 0x1000) IXB_E(5, 0x2000) IXB_E(6, 0x4000) IXB_E(7, 0x8000) }
+        if (q == 2) { IXB_E(0, 0x10000) IXB_E(1, 0x20000) IXB_E(2, 0x40000) IXB_E(3, 0x80000) IXB_E(4, 0x100000) IXB_E(5, 0x200000) IXB_E(6, 0x400000) IXB_E(7, 0x800000) }
+        if (q == 3) { IXB_E(0, 0x1000000) IXB_E(1, 0x2000000) IXB_E(2, 0x4000000) IXB_E(3, 0x8000000) IXB_E(4, 0x10000000) IXB_E(5, 0x20000000) IXB_E(6, 0x40000000) IXB_E(7, 0x80000000) }
+#undef IXB_E
+    }
+}
+
+// Same contract without the limit on level-3 elements per group (plain C++,
+// 64-bit level-3 queue); used for the rare words that exceed it.
+template <class Src, class Pre, class Sink>
+__device__ __noinline__ void decode_word_any(const Src &src, const WordRanks &w, const WordCursors &c,
+                                             const uint32_t *tab_ptr, Pre &&pre, Sink &&sink)
+{
+#pragma unroll 1
+    for (int q = 0; q < 4; ++q) {
+        pre(q);
+        uint32_t i1 = c.b1p[q] >> 5, i2 = c.b2p[q] >> 5, i3 = c.b3p[q] >> 5;
+        uint32_t q1 = __funnelshift_r(src.l1w(i1), src.l1w(i1 + 1), c.b1p[q] & 31u);
+        uint32_t x0 = src.l2w(i2), x1 = src.l2w(i2 + 1), x2 = src.l2w(i2 + 2);
+        uint64_t q2 = (uint64_t)__funnelshift_r(x0, x1, c.b2p[q] & 31u) |
+                      ((uint64_t)__funnelshift_r(x1, x2, c.b2p[q] & 31u) << 32);
+        uint32_t y0 = src.l3w(i3), y1 = src.l3w(i3 + 1), y2 = src.l3w(i3 + 2);
+        uint64_t q3 = (uint64_t)__funnelshift_r(y0, y1, c.b3p[q] & 31u) |
+                      ((uint64_t)__funnelshift_r(y1, y2, c.b3p[q] & 31u) << 32);
+        uint32_t mq = w.m2 >> c.nn[q];
+#pragma unroll 1
         for (int j = 0; j < 8; ++j) {
             const int i = 8 * q + j;
-            uint32_t off;
+            uint32_t entry;
             if ((w.m1 >> i) & 1u) {
-                off = (q1 & 28u) + kLutL1 * 4u;
+                entry = 32u + (q1 & 7u);
                 q1 >>= 3;
             } else {
                 if (mq & 1u) {
-                    off = (uint32_t)q2 & 124u;
+                    entry = (uint32_t)q2 & 31u;
                     q2 >>= 5;
                 } else {
-                    uint32_t b = t < s.l3_bytes ? (uint32_t)__ldg(s.l3 + t) : 0u;
-                    off = kLutL3 * 4u + 4u * b;
-                    ++t;
+                    entry = 256u + ((uint32_t)q3 & 255u);
+                    q3 >>= 8;
                 }
                 mq >>= 1;
             }
-            sink(i, off);
+            sink(i, tab_ptr[entry]);
         }
     }
+}
+
+// ---------------------------------------------------------------- staging ---
+// Shared-memory slot of one rank block (32-bit words).  Each slice starts on a
+// 16-byte boundary of its stream and is followed by two spare words, so the
+// decoder's look-ahead reads never leave the slot.
+struct Slot {
+    static constexpr int kB1 = 0, kB1Chunks = 8;      //  32 words
+    static constexpr int kB2 = 32, kB2Chunks = 10;    //  40 words: 1024 bits + misalignment + spare
+    static constexpr int kL1 = 72, kL1Chunks = 26;    // 104 words: 3072 bits ...
+    static constexpr int kL2 = 176, kL2Chunks = 42;   // 168 words: 5120 bits ...
+    static constexpr int kL3 = 344, kL3Chunks = 66;   // 264 words: 1024 bytes ...
+    static constexpr int kWords = 608;
+};
+
+__device__ __forceinline__ void cp_async_16(uint32_t *dst_smem, const void *src, uint32_t valid_bytes)
+{
+    uint32_t d = (uint32_t)__cvta_generic_to_shared(dst_smem);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(valid_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// Copy 16-byte chunks [c_lo, c_hi) of a stream of `bytes` bytes into dst
+// (zero beyond the stream's end); the whole warp takes part.
+__device__ __forceinline__ void stage_chunks(uint32_t *dst, const void *base, uint32_t bytes, uint32_t c_lo,
+                                             uint32_t c_hi, int lane)
+{
+    for (uint32_t c = c_lo + lane; c < c_hi; c += 32) {
+        uint32_t off = c * 16u;
+        uint32_t valid = bytes > off ? min(16u, bytes - off) : 0u;
+        uint32_t *d = dst + (c - c_lo) * 4u;
+        if (valid) cp_async_16(d, (const char *)base + off, valid);
+        else *(uint4 *)d = make_uint4(0, 0, 0, 0);
+    }
+}
+
+// Issue the asynchronous copies of rank block `b` into `slot` and describe the
+// result.  (a0, c0) are the block's rank-table entries, (a1, c1) those of the
+// next block (ignored for the last block, whose slices run to the stream end).
+__device__ __forceinline__ SlotSrc stage_block(const Streams &s, uint32_t b, bool last, uint32_t a0, uint32_t c0,
+                                               uint32_t a1, uint32_t c1, uint32_t *slot, int lane)
+{
+    SlotSrc src;
+    uint32_t e1 = min((b + 1u) * (uint32_t)kBlk, s.n);
+    uint32_t r0 = b * (uint32_t)kBlk - a0, r1 = e1 - a1;
+    // bit ranges of the four rank-addressed slices
+    uint32_t lo[4] = {r0, a0 * 3u, c0 * 5u, (r0 - c0) * 8u};
+    uint32_t hi[4] = {r1, a1 * 3u, c1 * 5u, (r1 - c1) * 8u};
+    const uint32_t bytes[4] = {s.b2_words * 4u, s.l1_words * 4u, s.l2_words * 4u, s.l3_bytes};
+    const void *base[4] = {s.b2, s.l1, s.l2, s.l3};
+    const int at[4] = {Slot::kB2, Slot::kL1, Slot::kL2, Slot::kL3};
+    const uint32_t cap[4] = {Slot::kB2Chunks, Slot::kL1Chunks, Slot::kL2Chunks, Slot::kL3Chunks};
+    uint32_t org[4];
+    stage_chunks(slot + Slot::kB1, s.b1, s.b1_words * 4u, b * 8u, b * 8u + 8u, lane);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        uint32_t c_lo = lo[k] >> 7;                                   // 128 bits per chunk
+        uint32_t w_hi = last ? ((bytes[k] + 3u) >> 2) : ((hi[k] + 31u) >> 5);
+        uint32_t c_hi = min((w_hi + 2u + 3u) >> 2, c_lo + cap[k]);
+        stage_chunks(slot + at[k], base[k], bytes[k], c_lo, c_hi, lane);
+        org[k] = c_lo * 128u;
+    }
+    src.b2 = slot + Slot::kB2;
+    src.l1 = slot + Slot::kL1;
+    src.l2 = slot + Slot::kL2;
+    src.l3 = slot + Slot::kL3;
+    src.org_b2 = org[0];
+    src.org_l1 = org[1];
+    src.org_l2 = org[2];
+    src.org_l3 = org[3] >> 3;
+    return src;
 }
 
 }  // namespace ixb
