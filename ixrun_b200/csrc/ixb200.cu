@@ -237,10 +237,14 @@ __global__ void __launch_bounds__(256) k_decode(Streams s, const int32_t *q1, co
 // lies entirely inside one run is written straight to y, a row shared between
 // runs goes to one fp32 slot per (row, run) and is summed in run order by the
 // last CTA to finish (no atomics on data, same bits every run).
-constexpr int kGemvThreads = 256;
+constexpr int kGemvThreads = 512;
 constexpr int kGemvWarps = kGemvThreads / 32;
-constexpr int kGemvCtasPerSm = 2;
+constexpr int kGemvCtasPerSm = 1;
 constexpr int kStages = 2;
+constexpr uint32_t kGemvSmemBudget = 200u * 1024u;
+
+// where the kernel reads activations from
+enum XMode { kXF32Smem = 0, kXBf16Smem = 1, kXBf16Global = 2 };
 
 struct GemvPlan {
     uint32_t nb;        // rank blocks
@@ -248,7 +252,7 @@ struct GemvPlan {
     uint32_t warps;     // total warps
     uint32_t bpw;       // blocks per warp
     uint32_t pmax;      // slots per row
-    uint32_t x_smem;    // 1: activations are staged in shared memory
+    uint32_t xmode;     // XMode
     uint32_t smem;      // dynamic shared memory bytes
 };
 
@@ -265,42 +269,49 @@ static GemvPlan make_plan(uint32_t out_f, uint32_t in_f, uint32_t m_rows)
     p.bpw = (p.nb + p.warps - 1) / p.warps;
     uint32_t row_blocks = (in_f + kBlk - 1) / kBlk + 1;   // blocks one row can touch
     p.pmax = (row_blocks + p.bpw - 1) / p.bpw + 1;
-    uint32_t xbytes = m_rows * in_f * 2u;
-    p.x_smem = xbytes <= 36u * 1024u;
-    p.smem = 2u * kTabBytes + kGemvWarps * kStages * Slot::kWords * 4u + (p.x_smem ? xbytes : 0u);
+    uint32_t fixed = 2048u + kGemvWarps * kStages * Slot::kWords * 4u;   // alignment slack + rings
+    uint32_t x32 = m_rows * ((in_f + 1023u) / 1024u) * 4096u, x16 = m_rows * in_f * 2u;
+    if (fixed + x32 <= kGemvSmemBudget) { p.xmode = kXF32Smem; p.smem = fixed + x32; }
+    else if (fixed + x16 <= kGemvSmemBudget) { p.xmode = kXBf16Smem; p.smem = fixed + x16; }
+    else { p.xmode = kXBf16Global; p.smem = fixed; }
     return p;
 }
 
 __device__ __forceinline__ float bf16lo(uint32_t v) { return __uint_as_float(v << 16); }
 __device__ __forceinline__ float bf16hi(uint32_t v) { return __uint_as_float(v & 0xffff0000u); }
 
-template <int M>
+template <int M, int XM>
 __global__ void __launch_bounds__(kGemvThreads, kGemvCtasPerSm)
 k_gemv(Streams s, const int32_t *__restrict__ q1, const int32_t *__restrict__ q2,
        const __nv_bfloat16 *__restrict__ x, const __nv_bfloat16 *__restrict__ bias, void *y, int y_f32,
        float *slots, uint32_t *ticket, GemvPlan plan)
 {
-    extern __shared__ __align__(16) uint32_t smem_raw[];
+    extern __shared__ __align__(16) uint32_t smem[];
     __shared__ uint32_t is_last;
-    // the table must sit on a 2 KB boundary of the shared window
-    const uint32_t pad = (2048u - ((uint32_t)__cvta_generic_to_shared(smem_raw) & 2047u)) & 2047u;
-    uint32_t *smem = smem_raw + pad / 4u;
-    float *lut = (float *)smem;
-    const uint32_t tab_addr = (uint32_t)__cvta_generic_to_shared(lut);
-    uint32_t *ring = smem + kTabEntries + (threadIdx.x >> 5) * (kStages * Slot::kWords);
-    const __nv_bfloat16 *xs = (const __nv_bfloat16 *)(smem + kTabEntries + kGemvWarps * kStages * Slot::kWords);
+    uint32_t *ring = smem + (threadIdx.x >> 5) * (kStages * Slot::kWords);
+    uint32_t *xs_raw = smem + kGemvWarps * kStages * Slot::kWords;
+    uint32_t s2;
     {
-        float sc = __bfloat162float(*s.scale);
-        for (int e = threadIdx.x; e < kTabEntries; e += blockDim.x)
-            lut[e] = __bfloat162float(__float2bfloat16_rn((float)tab_code(e) * sc));
-        if (plan.x_smem) {
+        uint32_t sb = (uint32_t)__bfloat16_as_ushort(*s.scale);
+        s2 = sb | (sb << 16);
+        if (XM == kXF32Smem) {
+            // fp32 copy of x, laid out so that the 32 lanes of a warp (consecutive 32-element
+            // words) read consecutive 16-byte chunks: element k of a row sits at
+            //   ((k / 1024) * 8 + (k % 32) / 4) * 128 + ((k / 32) % 32) * 4 + k % 4
+            const uint32_t xstride = ((s.in_f + 1023u) / 1024u) * 1024u;
+            for (uint32_t i = threadIdx.x; i < (uint32_t)M * s.in_f; i += blockDim.x) {
+                uint32_t m = i / s.in_f, k = i - m * s.in_f;
+                uint32_t pos = ((k >> 10) * 8u + ((k & 31u) >> 2)) * 128u + ((k >> 5) & 31u) * 4u + (k & 3u);
+                ((float *)xs_raw)[m * xstride + pos] = __bfloat162float(x[i]);
+            }
+        } else if (XM == kXBf16Smem) {
             uint32_t nchunk = (uint32_t)M * s.in_f / 8u;   // in_f % 32 == 0
             for (uint32_t c = threadIdx.x; c < nchunk; c += blockDim.x)
-                ((uint4 *)xs)[c] = __ldg((const uint4 *)x + c);
-        } else {
-            xs = x;
+                ((uint4 *)xs_raw)[c] = __ldg((const uint4 *)x + c);
         }
     }
+    const float *xs32 = (const float *)xs_raw;
+    const __nv_bfloat16 *xs16 = XM == kXBf16Global ? x : (const __nv_bfloat16 *)xs_raw;
     __syncthreads();
 
     const int lane = threadIdx.x & 31;
@@ -344,7 +355,8 @@ k_gemv(Streams s, const int32_t *__restrict__ q1, const int32_t *__restrict__ q2
         uint32_t a0 = (uint32_t)__ldg(q1 + b_begin), c0 = (uint32_t)__ldg(q2 + b_begin);
         uint32_t a1 = 0, c1 = 0;
         if (b_begin + 1 < plan.nb) { a1 = (uint32_t)__ldg(q1 + b_begin + 1); c1 = (uint32_t)__ldg(q2 + b_begin + 1); }
-        SlotSrc cur = stage_block(s, b_begin, b_begin + 1 == plan.nb, a0, c0, a1, c1, ring, lane);
+        const StageRole ra = role_a(s, lane), rb = role_b(s, lane);
+        SlotSrc cur = stage_block(s, ra, rb, b_begin, b_begin + 1 == plan.nb, a0, c0, a1, c1, ring, lane);
         cp_async_commit();
 
         for (uint32_t b = b_begin; b < b_end; ++b) {
@@ -355,7 +367,7 @@ k_gemv(Streams s, const int32_t *__restrict__ q1, const int32_t *__restrict__ q2
             uint32_t a2 = 0, c2 = 0;
             if (b + 1 < b_end) {
                 if (b + 2 < plan.nb) { a2 = (uint32_t)__ldg(q1 + b + 2); c2 = (uint32_t)__ldg(q2 + b + 2); }
-                nxt = stage_block(s, b + 1, b + 2 == plan.nb, a1, c1, a2, c2,
+                nxt = stage_block(s, ra, rb, b + 1, b + 2 == plan.nb, a1, c1, a2, c2,
                                   ring + ((st + 1) % kStages) * Slot::kWords, lane);
             }
             cp_async_commit();
@@ -364,27 +376,63 @@ k_gemv(Streams s, const int32_t *__restrict__ q1, const int32_t *__restrict__ q2
 
             uint32_t e0 = (b * 32u + lane) * 32u;
             uint32_t valid = e0 < s.n ? 32u : 0u;
-            WordRanks w = block_ranks(cur, slot[Slot::kB1 + lane], b, a0, c0, lane, valid);
+            WordRanks w;
+            if (cur.too_big) w = block_ranks(GlobalSrc{s}, ldw(s.b1, b * 32u + lane, s.b1_words), b, a0, c0, lane, valid);
+            else w = block_ranks(cur, valid ? slot[Slot::kB1 + lane] : 0u, b, a0, c0, lane, valid);
             uint32_t lrow = valid ? e0 / s.in_f : 0xffffffffu;
             uint32_t k0 = valid ? e0 - lrow * s.in_f : 0u;
+            // float4 index of this word's first chunk in the swizzled fp32 copy of x
+            const uint32_t xstride = ((s.in_f + 1023u) / 1024u) * 1024u;
+            const uint32_t xword = (k0 >> 10) * 256u + ((k0 >> 5) & 31u);
             WordCursors c = word_cursors(w);
             float part[M];
 #pragma unroll
             for (int m = 0; m < M; ++m) part[m] = 0.f;
-            if (__any_sync(0xffffffffu, c.max_l3 > 3u)) {
-                // rare: a group of 8 elements holds more than 3 level-3 values
-                decode_word_any(cur, w, c, (const uint32_t *)lut, [](int) {}, [&](int i, uint32_t v) {
+            if (cur.too_big || __any_sync(0xffffffffu, c.max_l3 > 4u)) {
+                // rare: a group of 8 elements holds more than 4 level-3 values, or the block's
+                // slices did not fit the slot (then everything is read from global memory)
+                float sc = __uint_as_float(s2 << 16);
+                auto slow_sink = [&](int i, int code) {
+                    float wt = __bfloat162float(__float2bfloat16_rn((float)code * sc));
 #pragma unroll
-                    for (int m = 0; m < M; ++m)
-                        part[m] = fmaf(__bfloat162float(xs[(size_t)m * s.in_f + k0 + i]), __uint_as_float(v), part[m]);
-                });
-            } else {
-                uint4 xv[M];
-                decode_word_fast(
-                    cur, w, c, tab_addr,
+                    for (int m = 0; m < M; ++m) {
+                        float xf = XM == kXF32Smem
+                                       ? xs32[(size_t)m * xstride + xword * 4u + ((uint32_t)i >> 2) * 128u + ((uint32_t)i & 3u)]
+                                       : __bfloat162float(xs16[(size_t)m * s.in_f + k0 + i]);
+                        part[m] = fmaf(xf, wt, part[m]);
+                    }
+                };
+                if (cur.too_big) decode_word_slow(GlobalSrc{s}, w, c, slow_sink);
+                else decode_word_slow(cur, w, c, slow_sink);
+            } else if (XM == kXF32Smem) {
+                float4 xa[M], xb[M];
+                decode_word_arith(
+                    cur, w, c, s2,
                     [&](int q) {
 #pragma unroll
-                        for (int m = 0; m < M; ++m) xv[m] = *((const uint4 *)(xs + (size_t)m * s.in_f + k0) + q);
+                        for (int m = 0; m < M; ++m) {
+                            const float4 *px = (const float4 *)(xs32 + (size_t)m * xstride) + xword + 64 * q;
+                            xa[m] = px[0];
+                            xb[m] = px[32];
+                        }
+                    },
+                    [&](int i, uint32_t v) {
+                        float wt = __uint_as_float(v);
+#pragma unroll
+                        for (int m = 0; m < M; ++m) {
+                            const int j = i & 7;
+                            float xf = j == 0 ? xa[m].x : j == 1 ? xa[m].y : j == 2 ? xa[m].z : j == 3 ? xa[m].w
+                                     : j == 4 ? xb[m].x : j == 5 ? xb[m].y : j == 6 ? xb[m].z : xb[m].w;
+                            part[m] = fmaf(xf, wt, part[m]);
+                        }
+                    });
+            } else {
+                uint4 xv[M];
+                decode_word_arith(
+                    cur, w, c, s2,
+                    [&](int q) {
+#pragma unroll
+                        for (int m = 0; m < M; ++m) xv[m] = *((const uint4 *)(xs16 + (size_t)m * s.in_f + k0) + q);
                     },
                     [&](int i, uint32_t v) {
                         float wt = __uint_as_float(v);
@@ -477,17 +525,26 @@ k_gemv(Streams s, const int32_t *__restrict__ q1, const int32_t *__restrict__ q2
     if (threadIdx.x == 0) *ticket = 0;
 }
 
+template <int M, int XM>
+static void launch_gemv_x(const Streams &s, const int32_t *q1, const int32_t *q2, const void *x, const void *bias,
+                          void *y, int y_f32, float *slots, uint32_t *ticket, const GemvPlan &p, cudaStream_t st)
+{
+    static bool attr_set = false;   // opt in to more than 48 KB of dynamic shared memory, once per instantiation
+    if (!attr_set) {
+        cudaFuncSetAttribute(k_gemv<M, XM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kGemvSmemBudget);
+        attr_set = true;
+    }
+    k_gemv<M, XM><<<p.grid, kGemvThreads, p.smem, st>>>(s, q1, q2, (const __nv_bfloat16 *)x,
+                                                        (const __nv_bfloat16 *)bias, y, y_f32, slots, ticket, p);
+}
+
 template <int M>
 static void launch_gemv(const Streams &s, const int32_t *q1, const int32_t *q2, const void *x, const void *bias,
                         void *y, int y_f32, float *slots, uint32_t *ticket, const GemvPlan &p, cudaStream_t st)
 {
-    static bool attr_set = false;   // opt in to more than 48 KB of dynamic shared memory, once per instantiation
-    if (!attr_set) {
-        cudaFuncSetAttribute(k_gemv<M>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-        attr_set = true;
-    }
-    k_gemv<M><<<p.grid, kGemvThreads, p.smem, st>>>(s, q1, q2, (const __nv_bfloat16 *)x, (const __nv_bfloat16 *)bias, y,
-                                               y_f32, slots, ticket, p);
+    if (p.xmode == kXF32Smem) launch_gemv_x<M, kXF32Smem>(s, q1, q2, x, bias, y, y_f32, slots, ticket, p, st);
+    else if (p.xmode == kXBf16Smem) launch_gemv_x<M, kXBf16Smem>(s, q1, q2, x, bias, y, y_f32, slots, ticket, p, st);
+    else launch_gemv_x<M, kXBf16Global>(s, q1, q2, x, bias, y, y_f32, slots, ticket, p, st);
 }
 
 }  // namespace ixb

@@ -83,6 +83,7 @@ struct GlobalSrc {
 struct SlotSrc {
     const uint32_t *b2, *l1, *l2, *l3;
     uint32_t org_b2, org_l1, org_l2, org_l3;
+    bool too_big;   // a slice did not fit its slot region: the slot is not usable for this block
     __device__ __forceinline__ uint32_t b2w(uint32_t i) const { return b2[i]; }
     __device__ __forceinline__ uint32_t l1w(uint32_t i) const { return l1[i]; }
     __device__ __forceinline__ uint32_t l2w(uint32_t i) const { return l2[i]; }
@@ -233,6 +234,70 @@ __device__ __forceinline__ void decode_word_fast(const Src &src, const WordRanks
     }
 }
 
+// One element of the table-free decoder used by the fused GEMV: the element's
+// code is rebuilt as a float with the 2^23 mantissa trick, and the weight
+// bf16(code * scale) comes from one packed bf16 multiply whose upper half is
+// the (exactly rounded) product and whose lower half is 0 * scale = 0 -- read
+// as fp32 that register is the weight itself.  On sm_100 logic/shift/compare
+// instructions issue at half the rate of add/FMA and on their own pipe, so the
+// step splits its work: two of the queue shifts are written as high-half
+// multiplies and the B2 queue (kept left-aligned, next bit in the sign) is
+// advanced with an add, which balances the two pipes.
+#define IXB_ELEM_ARITH(BITMASK)                                                                   \
+    asm("{\n\t"                                                                                   \
+        ".reg .pred p1, p2, p3;\n\t"                                                              \
+        ".reg .b32 t, f, c;\n\t"                                                                  \
+        "and.b32 t, %6, " #BITMASK ";\n\t"                                                        \
+        "setp.ne.u32 p1, t, 0;\n\t"                                                               \
+        "setp.lt.and.s32 p2, %5, 0, !p1;\n\t"                                                     \
+        "setp.ge.and.s32 p3, %5, 0, !p1;\n\t"                                                     \
+        "lop3.b32 f, %1, 7, 0x4B000000, 0xEA;\n\t"                                                \
+        "sub.f32 c, f, 0f4B000003;\n\t"                                                           \
+        "@p2 lop3.b32 f, %2, 31, 0x4B000000, 0xEA;\n\t"                                           \
+        "@p2 sub.f32 c, f, 0f4B00000F;\n\t"                                                       \
+        "@p3 lop3.b32 f, %4, 255, 0x4B000000, 0xEA;\n\t"                                          \
+        "@p3 sub.f32 c, f, 0f4B00007F;\n\t"                                                       \
+        "mul.rn.bf16x2 %0, c, %7;\n\t"                                                            \
+        "@p1 mul.hi.u32 %1, %1, 0x20000000;\n\t"                                                  \
+        "@p2 shf.r.wrap.b32 %2, %2, %3, 5;\n\t"                                                   \
+        "@p2 shr.u32 %3, %3, 5;\n\t"                                                              \
+        "@p3 mul.hi.u32 %4, %4, 0x01000000;\n\t"                                                  \
+        "@!p1 add.u32 %5, %5, %5;\n\t"                                                            \
+        "}"                                                                                       \
+        : "=r"(wv), "+r"(q1), "+r"(q2lo), "+r"(q2hi), "+r"(q3), "+r"(mq)                          \
+        : "r"(m1), "r"(s2))
+
+// Table-free variant of decode_word_fast: sink(i, v) receives the fp32 bit
+// pattern of the element's weight bf16(code * scale).  `s2` holds the bf16
+// scale in both halves.  Requires c.max_l3 <= 4.
+template <class Src, class Pre, class Sink>
+__device__ __forceinline__ void decode_word_arith(const Src &src, const WordRanks &w, const WordCursors &c,
+                                                  uint32_t s2, Pre &&pre, Sink &&sink)
+{
+    const uint32_t m1 = w.m1;
+    const uint32_t brev_m2 = __brev(w.m2);
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+        pre(q);
+        uint32_t i1 = c.b1p[q] >> 5, i2 = c.b2p[q] >> 5, i3 = c.b3p[q] >> 5;
+        uint32_t q1 = __funnelshift_r(src.l1w(i1), src.l1w(i1 + 1), c.b1p[q] & 31u);        // 8 x 3 bits
+        uint32_t x0 = src.l2w(i2), x1 = src.l2w(i2 + 1), x2 = src.l2w(i2 + 2);
+        uint32_t q2lo = __funnelshift_r(x0, x1, c.b2p[q] & 31u);                            // 8 x 5 bits
+        uint32_t q2hi = __funnelshift_r(x1, x2, c.b2p[q] & 31u);
+        uint32_t q3 = __funnelshift_r(src.l3w(i3), src.l3w(i3 + 1), c.b3p[q] & 31u);        // 4 bytes
+        uint32_t mq = brev_m2 << c.nn[q];                                                   // next B2 bit in the sign
+        uint32_t wv;
+#define IXB_E(j, mask)                      \
+    IXB_ELEM_ARITH(mask);                   \
+    sink(8 * q + j, wv);
+        if (q == 0) { IXB_E(0, 0x1) IXB_E(1, 0x2) IXB_E(2, 0x4) IXB_E(3, 0x8) IXB_E(4, 0x10) IXB_E(5, 0x20) IXB_E(6, 0x40) IXB_E(7, 0x80) }
+        if (q == 1) { IXB_E(0, 0x100) IXB_E(1, 0x200) IXB_E(2, 0x400) IXB_E(3, 0x800) IXB_E(4, 0x1000) IXB_E(5, 0x2000) IXB_E(6, 0x4000) IXB_E(7, 0x8000) }
+        if (q == 2) { IXB_E(0, 0x10000) IXB_E(1, 0x20000) IXB_E(2, 0x40000) IXB_E(3, 0x80000) IXB_E(4, 0x100000) IXB_E(5, 0x200000) IXB_E(6, 0x400000) IXB_E(7, 0x800000) }
+        if (q == 3) { IXB_E(0, 0x1000000) IXB_E(1, 0x2000000) IXB_E(2, 0x4000000) IXB_E(3, 0x8000000) IXB_E(4, 0x10000000) IXB_E(5, 0x20000000) IXB_E(6, 0x40000000) IXB_E(7, 0x80000000) }
+#undef IXB_E
+    }
+}
+
 // Same contract without the limit on level-3 elements per group (plain C++,
 // 64-bit level-3 queue); used for the rare words that exceed it.
 template <class Src, class Pre, class Sink>
@@ -273,6 +338,36 @@ __device__ __noinline__ void decode_word_any(const Src &src, const WordRanks &w,
     }
 }
 
+// Plain sequential decode of one word: sink(i, code) with the int8 code value.
+// No limit on level-3 elements; used by the fused GEMV for the rare words the
+// fast decoders cannot take.
+template <class Src, class Sink>
+__device__ __noinline__ void decode_word_slow(const Src &src, const WordRanks &w, const WordCursors &c, Sink &&sink)
+{
+    uint32_t b1p = c.b1p[0], b2p = c.b2p[0], b3p = c.b3p[0] >> 3;
+    uint32_t mq = w.m2;
+#pragma unroll 1
+    for (int i = 0; i < 32; ++i) {
+        int code;
+        if ((w.m1 >> i) & 1u) {
+            uint32_t v = __funnelshift_r(src.l1w(b1p >> 5), src.l1w((b1p >> 5) + 1), b1p & 31u);
+            code = (int)(v & 7u) - 3;
+            b1p += 3;
+        } else {
+            if (mq & 1u) {
+                uint32_t v = __funnelshift_r(src.l2w(b2p >> 5), src.l2w((b2p >> 5) + 1), b2p & 31u);
+                code = (int)(v & 31u) - 15;
+                b2p += 5;
+            } else {
+                code = (int)((src.l3w(b3p >> 2) >> (8u * (b3p & 3u))) & 255u) - 127;
+                b3p += 1;
+            }
+            mq >>= 1;
+        }
+        sink(i, code);
+    }
+}
+
 // ---------------------------------------------------------------- staging ---
 // Shared-memory slot of one rank block (32-bit words).  Each slice starts on a
 // 16-byte boundary of its stream and is followed by two spare words, so the
@@ -282,8 +377,9 @@ struct Slot {
     static constexpr int kB2 = 32, kB2Chunks = 10;    //  40 words: 1024 bits + misalignment + spare
     static constexpr int kL1 = 72, kL1Chunks = 26;    // 104 words: 3072 bits ...
     static constexpr int kL2 = 176, kL2Chunks = 42;   // 168 words: 5120 bits ...
-    static constexpr int kL3 = 344, kL3Chunks = 66;   // 264 words: 1024 bytes ...
-    static constexpr int kWords = 608;
+    static constexpr int kL3 = 344, kL3Chunks = 10;   //  40 words: up to ~120 level-3 bytes; a block with
+                                                      //  more is decoded straight from global memory
+    static constexpr int kWords = 384;
 };
 
 __device__ __forceinline__ void cp_async_16(uint32_t *dst_smem, const void *src, uint32_t valid_bytes)
@@ -312,8 +408,9 @@ __device__ __forceinline__ void stage_chunks(uint32_t *dst, const void *base, ui
 // Issue the asynchronous copies of rank block `b` into `slot` and describe the
 // result.  (a0, c0) are the block's rank-table entries, (a1, c1) those of the
 // next block (ignored for the last block, whose slices run to the stream end).
-__device__ __forceinline__ SlotSrc stage_block(const Streams &s, uint32_t b, bool last, uint32_t a0, uint32_t c0,
-                                               uint32_t a1, uint32_t c1, uint32_t *slot, int lane)
+// General version: every slice is copied by a loop over the whole warp.
+__device__ __noinline__ SlotSrc stage_block_any(const Streams &s, uint32_t b, bool last, uint32_t a0, uint32_t c0,
+                                                uint32_t a1, uint32_t c1, uint32_t *slot, int lane)
 {
     SlotSrc src;
     uint32_t e1 = min((b + 1u) * (uint32_t)kBlk, s.n);
@@ -326,15 +423,19 @@ __device__ __forceinline__ SlotSrc stage_block(const Streams &s, uint32_t b, boo
     const int at[4] = {Slot::kB2, Slot::kL1, Slot::kL2, Slot::kL3};
     const uint32_t cap[4] = {Slot::kB2Chunks, Slot::kL1Chunks, Slot::kL2Chunks, Slot::kL3Chunks};
     uint32_t org[4];
+    bool too_big = false;
     stage_chunks(slot + Slot::kB1, s.b1, s.b1_words * 4u, b * 8u, b * 8u + 8u, lane);
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
         uint32_t c_lo = lo[k] >> 7;                                   // 128 bits per chunk
         uint32_t w_hi = last ? ((bytes[k] + 3u) >> 2) : ((hi[k] + 31u) >> 5);
-        uint32_t c_hi = min((w_hi + 2u + 3u) >> 2, c_lo + cap[k]);
+        uint32_t c_need = (w_hi + 2u + 3u) >> 2;
+        uint32_t c_hi = min(c_need, c_lo + cap[k]);
+        too_big = too_big || c_need > c_lo + cap[k];
         stage_chunks(slot + at[k], base[k], bytes[k], c_lo, c_hi, lane);
         org[k] = c_lo * 128u;
     }
+    src.too_big = too_big;
     src.b2 = slot + Slot::kB2;
     src.l1 = slot + Slot::kL1;
     src.l2 = slot + Slot::kL2;
@@ -343,6 +444,91 @@ __device__ __forceinline__ SlotSrc stage_block(const Streams &s, uint32_t b, boo
     src.org_l1 = org[1];
     src.org_l2 = org[2];
     src.org_l3 = org[3] >> 3;
+    return src;
+}
+
+// Lane roles for the common case.  The bit range of every slice is a linear
+// form  ke * E + ka * a + kc * c  of the block's first element E and its
+// rank-table entries, so each lane evaluates only the slice it serves:
+//   B1: E            B2: E - a         L1: 3a        L2: 5c       L3: 8(E - a - c)
+// Two passes of 32 lanes copy up to 8 / 7 / 20 / 24 / 5 chunks of B1 / B2 /
+// L1 / L2 / L3; a block that needs more goes through stage_block_any.
+struct StageRole {
+    const char *base;     // stream base
+    uint32_t bytes;       // stream length
+    int32_t ke, ka, kc;   // coefficients of the slice's bit range
+    uint32_t idx;         // chunk of the slice this lane copies
+    uint32_t allot;       // chunks of the slice served by roles
+    uint32_t cap;         // chunks the slot can hold for the slice
+    uint32_t at;          // word offset of the slice in the slot
+};
+
+__device__ __forceinline__ StageRole make_role(const Streams &s, int slice, uint32_t idx)
+{
+    StageRole r;
+    r.idx = idx;
+    switch (slice) {
+    case 0: r = {(const char *)s.b1, s.b1_words * 4u, 1, 0, 0, idx, 8u, (uint32_t)Slot::kB1Chunks, (uint32_t)Slot::kB1}; break;
+    case 1: r = {(const char *)s.b2, s.b2_words * 4u, 1, -1, 0, idx, 7u, (uint32_t)Slot::kB2Chunks, (uint32_t)Slot::kB2}; break;
+    case 2: r = {(const char *)s.l1, s.l1_words * 4u, 0, 3, 0, idx, 20u, (uint32_t)Slot::kL1Chunks, (uint32_t)Slot::kL1}; break;
+    case 3: r = {(const char *)s.l2, s.l2_words * 4u, 0, 0, 5, idx, 24u, (uint32_t)Slot::kL2Chunks, (uint32_t)Slot::kL2}; break;
+    default: r = {(const char *)s.l3, s.l3_bytes, 8, -8, -8, idx, 5u, (uint32_t)Slot::kL3Chunks, (uint32_t)Slot::kL3}; break;
+    }
+    return r;
+}
+
+// pass A: lanes 0-7 B1, 8-31 L2[0..23];  pass B: lanes 0-19 L1, 20-26 B2, 27-31 L3
+__device__ __forceinline__ StageRole role_a(const Streams &s, int lane)
+{
+    return lane < 8 ? make_role(s, 0, lane) : make_role(s, 3, lane - 8);
+}
+__device__ __forceinline__ StageRole role_b(const Streams &s, int lane)
+{
+    return lane < 20 ? make_role(s, 2, lane) : (lane < 27 ? make_role(s, 1, lane - 20) : make_role(s, 4, lane - 27));
+}
+
+// One role's copy for a block; returns the slice's first chunk and whether the
+// slice needs more chunks than the roles serve.
+__device__ __forceinline__ uint32_t stage_role(const StageRole &r, uint32_t E0, uint32_t E1, bool last, uint32_t a0,
+                                               uint32_t c0, uint32_t a1, uint32_t c1, uint32_t *slot, bool &overflow)
+{
+    uint32_t lo = (uint32_t)(r.ke * (int32_t)E0 + r.ka * (int32_t)a0 + r.kc * (int32_t)c0);
+    uint32_t hi = (uint32_t)(r.ke * (int32_t)E1 + r.ka * (int32_t)a1 + r.kc * (int32_t)c1);
+    uint32_t c_lo = lo >> 7;
+    uint32_t w_hi = last ? ((r.bytes + 3u) >> 2) : ((hi + 31u) >> 5);
+    uint32_t spare = r.at == (uint32_t)Slot::kB1 ? 0u : 2u;
+    uint32_t c_hi = min((w_hi + spare + 3u) >> 2, c_lo + r.cap);
+    overflow = c_hi - c_lo > r.allot;
+    uint32_t c = c_lo + r.idx;
+    if (c < c_hi) {
+        uint32_t off = c * 16u;
+        uint32_t valid = r.bytes > off ? min(16u, r.bytes - off) : 0u;
+        uint32_t *d = slot + r.at + r.idx * 4u;
+        if (valid) cp_async_16(d, r.base + off, valid);
+        else *(uint4 *)d = make_uint4(0, 0, 0, 0);
+    }
+    return c_lo;
+}
+
+__device__ __forceinline__ SlotSrc stage_block(const Streams &s, const StageRole &ra, const StageRole &rb, uint32_t b,
+                                               bool last, uint32_t a0, uint32_t c0, uint32_t a1, uint32_t c1,
+                                               uint32_t *slot, int lane)
+{
+    uint32_t E0 = b * (uint32_t)kBlk, E1 = min(E0 + (uint32_t)kBlk, s.n);
+    bool ova, ovb;
+    uint32_t lo_a = stage_role(ra, E0, E1, last, a0, c0, a1, c1, slot, ova);
+    uint32_t lo_b = stage_role(rb, E0, E1, last, a0, c0, a1, c1, slot, ovb);
+    if (__any_sync(0xffffffffu, ova || ovb)) return stage_block_any(s, b, last, a0, c0, a1, c1, slot, lane);
+    SlotSrc src;
+    src.too_big = false;
+    src.b2 = slot + Slot::kB2;
+    src.l1 = slot + Slot::kL1;
+    src.l2 = slot + Slot::kL2;
+    src.l3 = slot + Slot::kL3;
+    src.org_l2 = __shfl_sync(0xffffffffu, lo_a, 8) * 128u;
+    src.org_l1 = __shfl_sync(0xffffffffu, lo_b, 0) * 128u;
+    src.org_b2 = __shfl_sync(0xffffffffu, lo_b, 20) * 128u;
+    src.org_l3 = __shfl_sync(0xffffffffu, lo_b, 27) * 16u;
     return src;
 }
 

@@ -8,8 +8,6 @@ work is split at 1024-element rank blocks (the gran=1024 prefix table), so the
 """
 from __future__ import annotations
 
-import weakref
-
 import torch
 
 from .packed import DevicePacked
@@ -20,6 +18,7 @@ FUSED_TILE = 512  # the reference's inner tile; kept for callers that test `in_f
 
 # rank tables derived per bitmap tensor, keyed by the tensor object's identity
 _views: dict = {}
+_MAX_VIEWS = 64
 
 
 def compute_row_prefixes(packed, chunk: int | None = None, device=None):
@@ -58,13 +57,13 @@ def _pick_split(in_f: int) -> int:
 
 def _view(b1, b2, l1, l2, l3, scale, out_f, in_f) -> DevicePacked:
     key = id(b1)
-    hit = _views.get(key)
-    if hit is not None:
-        ref, dp = hit
-        if ref() is b1 and dp.out_f == out_f and dp.in_f == in_f and dp.l1.data_ptr() == l1.data_ptr():
-            return dp
+    dp = _views.get(key)
+    if dp is not None and dp.b1 is b1 and dp.out_f == out_f and dp.in_f == in_f and dp.l1 is l1:
+        return dp
     dp = DevicePacked.from_device_streams(b1, b2, l1, l2, l3, scale, out_f, in_f)
-    _views[key] = (weakref.ref(b1, lambda _r, k=key: _views.pop(k, None)), dp)
+    if len(_views) >= _MAX_VIEWS:          # bounded: the views keep their streams alive
+        _views.pop(next(iter(_views)))
+    _views[key] = dp
     return dp
 
 
