@@ -101,6 +101,37 @@ int ixb_gemv(const ixb_packed *w, const int32_t *blk_q1, const int32_t *blk_q2,
              void *y_device, int y_is_f32,
              void *scratch_device, size_t scratch_bytes, ixb_stream_t stream);
 
+/*
+ * ixb_gemv for callers that cannot hand over scratch memory.  It has no
+ * counterpart in the reference.
+ *
+ * Some hosts may not allocate device memory at the point where they run a
+ * layer: a serving process that gave the whole device to its own pool at
+ * start-up, a host framework that plans every buffer ahead and rejects later
+ * allocations, or a plain C caller that only owns the input and output buffers
+ * it was handed.  For them this call takes the same arguments as ixb_gemv minus
+ * the scratch: the partial-sum slots and the completion counter live in an
+ * array of IXB_STATIC_SCRATCH_BYTES bytes that is part of the library image on
+ * every device that loads it (so that much device memory stays taken until the
+ * process exits).  The call performs no cudaMalloc/cudaFree and uses no
+ * allocating library routine.
+ *
+ *  - Shapes whose scratch need (ixb_gemv_scratch_bytes) exceeds
+ *    IXB_STATIC_SCRATCH_BYTES are rejected with IXB_E_SCRATCH.
+ *  - The first call on each device looks up the array's device address with
+ *    that device current; make that first call before starting any stream
+ *    capture.
+ *  - All calls on a device share the one array and each call reuses what the
+ *    previous one left (the counter is re-zeroed on the stream before every
+ *    launch).  Two calls whose kernels can overlap on the GPU (different
+ *    streams, no ordering) race on it: serialise them, or use ixb_gemv with
+ *    one scratch buffer per stream.
+ */
+#define IXB_STATIC_SCRATCH_BYTES (4 * 1024 * 1024)
+int ixb_gemv_static(const ixb_packed *w, const int32_t *blk_q1, const int32_t *blk_q2,
+                    const void *x_device, int64_t m_rows, const void *bias_device,
+                    void *y_device, int y_is_f32, ixb_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

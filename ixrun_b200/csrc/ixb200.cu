@@ -641,3 +641,35 @@ extern "C" int ixb_gemv(const ixb_packed *w, const int32_t *blk_q1, const int32_
     }
     return launch_check("k_gemv");
 }
+
+// ------------------------------------------------ gemv without caller scratch
+// Scratch of ixb_gemv_static: one array per device that loads this library,
+// resident until the process exits.  In host code the name below is only a
+// handle for cudaGetSymbolAddress; the kernel receives the device address.
+static __device__ __align__(256) unsigned char g_static_scratch[IXB_STATIC_SCRATCH_BYTES];
+
+extern "C" int ixb_gemv_static(const ixb_packed *w, const int32_t *blk_q1, const int32_t *blk_q2, const void *x,
+                               int64_t m_rows, const void *bias, void *y, int y_is_f32, ixb_stream_t stream)
+{
+    static void *dev_ptr[64] = {nullptr};   // device address of the array, per device ordinal
+    if (!w) return fail(IXB_E_ARG, "packed tensor is NULL");
+    size_t need = ixb_gemv_scratch_bytes(w->out_f, w->in_f, m_rows);
+    if (need == 0) return fail(IXB_E_ARG, "bad shape or m_rows");
+    if (need > (size_t)IXB_STATIC_SCRATCH_BYTES)
+        return fail(IXB_E_SCRATCH,
+                    "ixb_gemv_static: %lld x %lld with m_rows=%lld needs %zu bytes of scratch, the built-in array holds %d; "
+                    "use ixb_gemv with caller scratch",
+                    (long long)w->out_f, (long long)w->in_f, (long long)m_rows, need, IXB_STATIC_SCRATCH_BYTES);
+    int dev = -1;
+    IXB_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return fail(IXB_E_UNSUPPORTED, "device ordinal %d outside 0..63", dev);
+    if (!dev_ptr[dev]) {
+        // first call on this device: resolve the array's device address (the device is current)
+        void *p = nullptr;
+        IXB_CUDA(cudaGetSymbolAddress(&p, g_static_scratch));
+        dev_ptr[dev] = p;
+    }
+    // the ticket word must start at zero whatever an earlier call left behind
+    IXB_CUDA(cudaMemsetAsync(dev_ptr[dev], 0, 256, (cudaStream_t)stream));
+    return ixb_gemv(w, blk_q1, blk_q2, x, m_rows, bias, y, y_is_f32, dev_ptr[dev], IXB_STATIC_SCRATCH_BYTES, stream);
+}
