@@ -201,7 +201,7 @@ def run_gpu(args):
 
     # ---- timed region: K steps, device timed, max over ranks
     graph = None
-    if world == 1:
+    if world == 1 and not args.eager:
         # one CUDA graph holding the K launches keeps host launch gaps out of the device time
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
@@ -319,6 +319,7 @@ def main():
     ap.add_argument("--steps", type=int, default=400)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--eager", action="store_true", help="launch the timed steps one by one instead of one CUDA graph")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
