@@ -1,0 +1,223 @@
+"""Batch-1 decode loop for a Llama-style decoder whose linears are packed
+INT8-X layers, with the whole token step captured in one CUDA graph.
+
+The reference drives HuggingFace `generate()` around its packed modules
+(ixrun/generate.py:39-70, ixrun/engine.py:510-516) and records that whole-model
+graph capture was not possible with HF's dynamic KV cache.  This runner keeps a
+static KV cache and position tensors so that one token step is a fixed launch
+sequence: per layer RMSNorm -> q/k/v packed GEMVs -> RoPE -> cache write ->
+attention over the static cache -> o_proj GEMV -> RMSNorm -> gate/up GEMVs ->
+SwiGLU -> down GEMV.  The packed linears run the fused decode+GEMV kernel; the
+glue (norms, RoPE, attention, SwiGLU, lm_head) is plain torch for now.
+
+`weights="packed"` uses StreamingLinear (fused kernels); `weights="decoded"`
+builds the same model with the packed weights decoded to bf16 and dense
+matmuls -- the ground truth for greedy-token agreement.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+import torch.nn.functional as F
+
+from .engine import StreamingLinear
+from .packed import DevicePacked
+
+
+@dataclass
+class LlamaConfig:
+    n_layers: int = 24
+    hidden: int = 2048
+    intermediate: int = 6144
+    n_heads: int = 16
+    n_kv_heads: int = 8
+    head_dim: int = 128
+    vocab: int = 73448
+    rope_theta: float = 10000.0
+    rms_eps: float = 1e-5
+    max_seq: int = 1280
+
+
+LINEARS = ("q_proj", "k_proj", "v_proj", "o_proj", "gate_proj", "up_proj", "down_proj")
+
+
+def linear_shapes(cfg: LlamaConfig) -> dict:
+    h, hd = cfg.hidden, cfg.head_dim
+    return {
+        "q_proj": (cfg.n_heads * hd, h), "k_proj": (cfg.n_kv_heads * hd, h), "v_proj": (cfg.n_kv_heads * hd, h),
+        "o_proj": (h, cfg.n_heads * hd), "gate_proj": (cfg.intermediate, h), "up_proj": (cfg.intermediate, h),
+        "down_proj": (h, cfg.intermediate),
+    }
+
+
+class _DenseLinear(torch.nn.Module):
+    """bf16 weight decoded once from a packed dict (ground-truth path)."""
+
+    def __init__(self, packed: dict):
+        super().__init__()
+        self.weight = DevicePacked(packed).decode(kind="bf16")
+
+    def forward(self, x):
+        return F.linear(x, self.weight)
+
+
+def _rms(x, w, eps):
+    v = x.float()
+    return (v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + eps)).to(x.dtype) * w
+
+
+class PackedLlama(torch.nn.Module):
+    def __init__(self, cfg: LlamaConfig, packed_layers: list, embed: torch.Tensor, lm_head: torch.Tensor,
+                 norms: list | None = None, weights: str = "packed", device="cuda"):
+        """packed_layers[i][name] = packed dict of layer i's linear `name`;
+        embed [vocab, hidden] and lm_head [vocab, hidden] stay bf16."""
+        super().__init__()
+        if weights not in ("packed", "decoded"):
+            raise ValueError("weights must be 'packed' or 'decoded'")
+        self.cfg = cfg
+        dev = torch.device(device)
+        mk = StreamingLinear if weights == "packed" else _DenseLinear
+        self.layers = torch.nn.ModuleList()
+        max_n = 0
+        for li in range(cfg.n_layers):
+            mods = torch.nn.ModuleDict({n: mk(packed_layers[li][n]) for n in LINEARS})
+            self.layers.append(mods)
+            max_n = max(max_n, max(packed_layers[li][n]["N"] for n in LINEARS))
+        if weights == "packed":
+            # one shared decode buffer for inputs of more than 8 rows (prefill), like the streaming engine
+            self._shared = torch.empty(max_n, dtype=torch.bfloat16, device=dev)
+            for mods in self.layers:
+                for n in LINEARS:
+                    mods[n]._set_shared_buf(self._shared)
+        ones = torch.ones(cfg.hidden, dtype=torch.bfloat16, device=dev)
+        self.ln1 = [ones.clone() if norms is None else norms[i][0].to(dev) for i in range(cfg.n_layers)]
+        self.ln2 = [ones.clone() if norms is None else norms[i][1].to(dev) for i in range(cfg.n_layers)]
+        self.ln_f = ones.clone()
+        self.embed = embed.to(dev, torch.bfloat16)
+        self.lm_head = lm_head.to(dev, torch.bfloat16)
+        half = cfg.head_dim // 2
+        inv = 1.0 / (cfg.rope_theta ** (torch.arange(0, half, dtype=torch.float32) / half))
+        ang = torch.arange(cfg.max_seq, dtype=torch.float32)[:, None] * inv[None, :]
+        self.cos = ang.cos().to(dev)
+        self.sin = ang.sin().to(dev)
+        self.k_cache = torch.zeros(cfg.n_layers, cfg.max_seq, cfg.n_kv_heads, cfg.head_dim, dtype=torch.bfloat16, device=dev)
+        self.v_cache = torch.zeros_like(self.k_cache)
+        self.key_pos = torch.arange(cfg.max_seq, device=dev)
+        # static inputs / outputs of the captured step
+        self.tok = torch.zeros(1, dtype=torch.long, device=dev)
+        self.pos = torch.zeros(1, dtype=torch.long, device=dev)
+        self.logits = None
+        self.graph = None
+
+    # ------------------------------------------------------------------ core
+    def _rope(self, x, pos):
+        """x [T, heads, head_dim], pos [T] (rotate-half convention)"""
+        c = self.cos.index_select(0, pos)[:, None, :]
+        s = self.sin.index_select(0, pos)[:, None, :]
+        x1, x2 = x.float().chunk(2, dim=-1)
+        return torch.cat([x1 * c - x2 * s, x2 * c + x1 * s], dim=-1).to(x.dtype)
+
+    def _block(self, li, h, pos):
+        """h [T, hidden], pos [T] absolute positions (T = 1 in the decode step)"""
+        cfg, m = self.cfg, self.layers[li]
+        t = h.shape[0]
+        x = _rms(h, self.ln1[li], cfg.rms_eps)
+        q = m["q_proj"](x).view(t, cfg.n_heads, cfg.head_dim)
+        k = m["k_proj"](x).view(t, cfg.n_kv_heads, cfg.head_dim)
+        v = m["v_proj"](x).view(t, cfg.n_kv_heads, cfg.head_dim)
+        q, k = self._rope(q, pos), self._rope(k, pos)
+        self.k_cache[li].index_copy_(0, pos, k)
+        self.v_cache[li].index_copy_(0, pos, v)
+        # attention of the T new queries over the whole static cache, masked to keys <= query position
+        rep = cfg.n_heads // cfg.n_kv_heads
+        kk = self.k_cache[li].repeat_interleave(rep, dim=1).transpose(0, 1)      # [heads, S, d]
+        vv = self.v_cache[li].repeat_interleave(rep, dim=1).transpose(0, 1)
+        mask = self.key_pos[None, :] <= pos[:, None]                               # [T, S]
+        a = F.scaled_dot_product_attention(q.transpose(0, 1), kk, vv, attn_mask=mask[None])
+        a = a.transpose(0, 1).reshape(t, cfg.n_heads * cfg.head_dim)
+        h = h + m["o_proj"](a)
+        x = _rms(h, self.ln2[li], cfg.rms_eps)
+        return h + m["down_proj"](F.silu(m["gate_proj"](x)) * m["up_proj"](x))
+
+    def _forward(self, tok, pos):
+        h = self.embed.index_select(0, tok)
+        for li in range(self.cfg.n_layers):
+            h = self._block(li, h, pos)
+        h = _rms(h[-1:], self.ln_f, self.cfg.rms_eps)
+        return F.linear(h, self.lm_head).float()
+
+    # ------------------------------------------------------------------- API
+    @torch.no_grad()
+    def prefill(self, ids: torch.Tensor, chunk: int = 256) -> torch.Tensor:
+        """Run the prompt through the model (many rows per linear: decode +
+        dense matmul path); returns the logits of the last prompt token."""
+        logits = None
+        for s in range(0, ids.numel(), chunk):
+            part = ids[s:s + chunk].to(self.tok.device)
+            pos = torch.arange(s, s + part.numel(), device=part.device)
+            logits = self._forward(part, pos)
+        return logits
+
+    @torch.no_grad()
+    def capture(self):
+        """Capture one token step (static tok/pos in, static logits out)."""
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(2):
+                self._forward(self.tok, self.pos)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            self.logits = self._forward(self.tok, self.pos)
+        return self
+
+    @torch.no_grad()
+    def step(self, tok: torch.Tensor, pos: int) -> torch.Tensor:
+        """One decode step at absolute position `pos`; returns logits [1, vocab]
+        (a static tensor when the step is graph-captured)."""
+        self.tok.copy_(tok.reshape(1))
+        self.pos.fill_(pos)
+        if self.graph is not None:
+            self.graph.replay()
+            return self.logits
+        return self._forward(self.tok, self.pos)
+
+    @torch.no_grad()
+    def generate(self, prompt_ids: torch.Tensor, n_new: int) -> torch.Tensor:
+        """Greedy decode of n_new tokens after the prompt."""
+        logits = self.prefill(prompt_ids)
+        out = []
+        pos = prompt_ids.numel()
+        tok = logits.argmax(-1)
+        for _ in range(n_new):
+            out.append(tok.clone())
+            logits = self.step(tok, pos)
+            tok = logits.argmax(-1)
+            pos += 1
+        return torch.cat(out)
+
+
+def synthetic_llama(cfg: LlamaConfig, seed: int = 0, distinct_layers: bool = True):
+    """Random-init weights of the config: Laplace codes for every linear (one
+    tensor per linear type and layer when distinct_layers, else one per type
+    shared by all layers), N(0, 0.02) embeddings and head."""
+    from .synth import synthetic_packed
+
+    shapes = linear_shapes(cfg)
+    layers = []
+    cache = {}
+    for li in range(cfg.n_layers):
+        d = {}
+        for j, n in enumerate(LINEARS):
+            key = (li if distinct_layers else 0, n)
+            if key not in cache:
+                cache[key] = synthetic_packed(*shapes[n], seed=seed * 1000003 + key[0] * 16 + j)
+            d[n] = cache[key]
+        layers.append(d)
+    g = torch.Generator().manual_seed(seed + 17)
+    embed = (torch.randn(cfg.vocab, cfg.hidden, generator=g) * 0.02).bfloat16()
+    head = (torch.randn(cfg.vocab, cfg.hidden, generator=g) * 0.02).bfloat16()
+    return layers, embed, head
