@@ -106,6 +106,9 @@ def algorithmic_bytes(total_bytes: int) -> int:
 # ----------------------------------------------------------------- CPU arm ---
 def cpu_layer_gbs(steps: int, warmup: int, seed: int = 0):
     """Oracle port of the reference's CPU layer path on the host cores."""
+    # torchrun pins OMP_NUM_THREADS=1 for its ranks; the CPU arm is meant to use every host core
+    if os.environ.get("OMP_NUM_THREADS") == "1" and "TORCHELASTIC_RUN_ID" in os.environ:
+        os.environ["OMP_NUM_THREADS"] = str(os.cpu_count() or 1)
     from ixrun_b200.synth import laplace_codes
     from oracle import ixb_oracle as O
 
@@ -305,7 +308,7 @@ def run_gpu(args):
             line["cpu_baseline"] = {"value": gbs, "unit": UNIT, "cores": cores, "kind": "port",
                                     "sample": f"{cpu_steps} full {OUT_F}x{IN_F} layers, {dt * 1e3:.0f} ms each"}
         traffic = os.path.join(ROOT, "profiles", "gemv_traffic.json")
-        if os.path.exists(traffic):
+        if world == 1 and os.path.exists(traffic):
             with open(traffic) as f:
                 line["roofline"]["traffic"] = json.load(f).get("dram_bytes_per_launch")
         print(json.dumps(line), flush=True)
