@@ -102,6 +102,23 @@ int ixb_gemv(const ixb_packed *w, const int32_t *blk_q1, const int32_t *blk_q2,
              void *scratch_device, size_t scratch_bytes, ixb_stream_t stream);
 
 /*
+ * Fused decode + small-M GEMM on the tensor cores (tcgen05, accumulators in
+ * TMEM) for 1 <= m_rows <= 64; intended for 9..64 rows (batched decode, MTP
+ * verify), below that ixb_gemv is the better call.  Same result definition and
+ * argument meaning as ixb_gemv; products are bf16 x bf16 accumulated in fp32.
+ * Replaces, for these row counts, the reference's decode-to-bf16 followed by a
+ * dense matmul (ixrun/engine.py:171-173); the only fused decode+GEMM in the
+ * reference is the TPAB one (ixrun/tpab_gemm.py:34-94).
+ * Requires in_f % 1024 == 0.  If a tensor-core completion wait ever runs out
+ * the whole output is set to NaN instead of hanging.
+ */
+size_t ixb_gemm_scratch_bytes(int64_t out_f, int64_t in_f, int64_t m_rows);
+int ixb_gemm(const ixb_packed *w, const int32_t *blk_q1, const int32_t *blk_q2,
+             const void *x_device, int64_t m_rows, const void *bias_device,
+             void *y_device, int y_is_f32,
+             void *scratch_device, size_t scratch_bytes, ixb_stream_t stream);
+
+/*
  * ixb_gemv for callers that cannot hand over scratch memory.  It has no
  * counterpart in the reference.
  *

@@ -20,6 +20,7 @@ SYMBOLS = (
     "ixb_version", "ixb_last_error", "ixb_launch_count",
     "ixb_prefix_workspace_bytes", "ixb_prefix_tables",
     "ixb_decode", "ixb_gemv_scratch_bytes", "ixb_gemv", "ixb_gemv_static",
+    "ixb_gemm_scratch_bytes", "ixb_gemm",
 )
 
 
@@ -68,6 +69,10 @@ def lib():
     L.ixb_gemv_scratch_bytes.argtypes = [i64, i64, i64]
     L.ixb_gemv.restype = C.c_int
     L.ixb_gemv.argtypes = [C.POINTER(Packed), vp, vp, vp, i64, vp, vp, C.c_int, vp, sz, vp]
+    L.ixb_gemm_scratch_bytes.restype = sz
+    L.ixb_gemm_scratch_bytes.argtypes = [i64, i64, i64]
+    L.ixb_gemm.restype = C.c_int
+    L.ixb_gemm.argtypes = [C.POINTER(Packed), vp, vp, vp, i64, vp, vp, C.c_int, vp, sz, vp]
     L.ixb_gemv_static.restype = C.c_int
     L.ixb_gemv_static.argtypes = [C.POINTER(Packed), vp, vp, vp, i64, vp, vp, C.c_int, vp]
     _lib = L

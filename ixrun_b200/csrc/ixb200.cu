@@ -2,6 +2,7 @@
 // Built for sm_100a only.  See include/ixb200.h for the contract of each call.
 #include "../../include/ixb200.h"
 #include "ixb_common.cuh"
+#include "ixb_gemm_tc.cuh"
 
 #include <atomic>
 #include <cstdarg>
@@ -640,6 +641,57 @@ extern "C" int ixb_gemv(const ixb_packed *w, const int32_t *blk_q1, const int32_
     default: launch_gemv<8>(s, blk_q1, blk_q2, x, bias, y, y_is_f32, slots, ticket, p, st); break;
     }
     return launch_check("k_gemv");
+}
+
+// ------------------------------------------------------- tensor-core small-M GEMM
+static TcPlan make_tc_plan(uint32_t out_f, uint32_t in_f)
+{
+    TcPlan p;
+    p.n_kslab = in_f / (uint32_t)kTcSlab;
+    p.n_rowtiles = (out_f + kTcRows - 1) / kTcRows;
+    p.n_tiles = p.n_kslab * p.n_rowtiles;
+    uint32_t sms = (uint32_t)num_sms();
+    p.grid = p.n_tiles < sms ? p.n_tiles : sms;
+    if (p.grid == 0) p.grid = 1;
+    p.tiles_per_cta = (p.n_tiles + p.grid - 1) / p.grid;
+    return p;
+}
+
+extern "C" size_t ixb_gemm_scratch_bytes(int64_t out_f, int64_t in_f, int64_t m_rows)
+{
+    if (out_f <= 0 || in_f <= 0 || m_rows <= 0 || in_f % kTcSlab) return 0;
+    return 256 + (size_t)(in_f / kTcSlab) * (size_t)m_rows * (size_t)out_f * sizeof(float);
+}
+
+extern "C" int ixb_gemm(const ixb_packed *w, const int32_t *blk_q1, const int32_t *blk_q2, const void *x,
+                        int64_t m_rows, const void *bias, void *y, int y_is_f32, void *scratch, size_t scratch_bytes,
+                        ixb_stream_t stream)
+{
+    Streams s;
+    int rc = to_streams(w, &s);
+    if (rc) return rc;
+    if (!blk_q1 || !blk_q2 || !x || !y || !scratch) return fail(IXB_E_ARG, "NULL pointer argument");
+    if (m_rows < 1 || m_rows > kTcTok) return fail(IXB_E_UNSUPPORTED, "m_rows=%lld outside 1..%d", (long long)m_rows, kTcTok);
+    if (s.in_f % (uint32_t)kTcSlab) return fail(IXB_E_UNSUPPORTED, "in_f=%u is not a multiple of %d", s.in_f, kTcSlab);
+    if ((uintptr_t)x & 15u) return fail(IXB_E_ARG, "x is not 16-byte aligned");
+    if (scratch_bytes < ixb_gemm_scratch_bytes(s.out_f, s.in_f, m_rows)) return fail(IXB_E_SCRATCH, "gemm scratch too small");
+    TcPlan p = make_tc_plan(s.out_f, s.in_f);
+    cudaStream_t st = (cudaStream_t)stream;
+    static bool attr_set = false;
+    if (!attr_set) {
+        IXB_CUDA(cudaFuncSetAttribute(k_gemm_tc, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kTcSmemBytes));
+        attr_set = true;
+    }
+    uint32_t *err = (uint32_t *)scratch;
+    float *part = (float *)((char *)scratch + 256);
+    IXB_CUDA(cudaMemsetAsync(scratch, 0, 256, st));
+    k_gemm_tc<<<p.grid, kTcThreads, kTcSmemBytes, st>>>(s, blk_q1, blk_q2, (const __nv_bfloat16 *)x, (uint32_t)m_rows,
+                                                        part, err, p);
+    if ((rc = launch_check("k_gemm_tc"))) return rc;
+    uint32_t total = (uint32_t)m_rows * s.out_f;
+    k_gemm_finalize<<<(total + 255) / 256, 256, 0, st>>>(part, p.n_kslab, (uint32_t)m_rows, s.out_f,
+                                                         (const __nv_bfloat16 *)bias, y, y_is_f32, err);
+    return launch_check("k_gemm_finalize");
 }
 
 // ------------------------------------------------ gemv without caller scratch

@@ -131,3 +131,33 @@ class DevicePacked:
                                            out.data_ptr(), 1 if out.dtype == torch.float32 else 0,
                                            s.data_ptr(), s.numel(), _lib.stream_ptr(self.device)))
         return out
+
+    def gemm(self, x: torch.Tensor, bias: torch.Tensor | None = None, out: torch.Tensor | None = None,
+             out_dtype=torch.bfloat16) -> torch.Tensor:
+        """y[M, out_f] = x[M, in_f] @ W.T on the tensor cores, 1 <= M <= 64, in_f % 1024 == 0."""
+        if x.dtype != torch.bfloat16:
+            raise ValueError("activations must be bf16")
+        x2 = x.reshape(-1, self.in_f)
+        if not x2.is_contiguous():
+            x2 = x2.contiguous()
+        m = x2.shape[0]
+        if out is None:
+            out = torch.empty(m, self.out_f, dtype=out_dtype, device=self.device)
+        elif out.dtype not in (torch.bfloat16, torch.float32) or out.numel() != m * self.out_f or not out.is_contiguous():
+            raise ValueError("gemm output must be a contiguous bf16/fp32 tensor of M*out_f elements")
+        if bias is not None and (bias.dtype != torch.bfloat16 or bias.numel() != self.out_f):
+            raise ValueError("bias must be bf16 [out_f]")
+        key = ("gemm", m)
+        s = self._scratch.get(key)
+        if s is None:
+            nbytes = _lib.lib().ixb_gemm_scratch_bytes(self.out_f, self.in_f, m)
+            if nbytes == 0:
+                raise _lib.IxbError(f"tensor-core gemm needs in_f % 1024 == 0 (in_f={self.in_f})")
+            s = torch.zeros(nbytes, dtype=torch.uint8, device=self.device)
+            self._scratch[key] = s
+        with torch.cuda.device(self.device):
+            _lib.check(_lib.lib().ixb_gemm(C.byref(self.struct), self.blk_q1.data_ptr(), self.blk_q2.data_ptr(),
+                                           x2.data_ptr(), m, None if bias is None else bias.data_ptr(),
+                                           out.data_ptr(), 1 if out.dtype == torch.float32 else 0,
+                                           s.data_ptr(), s.numel(), _lib.stream_ptr(self.device)))
+        return out

@@ -180,3 +180,45 @@ def test_full_size_shapes(out_f, in_f):
     y1 = dp.gemv(x, out_dtype=torch.float32)
     y2 = dp.gemv((x * 2).contiguous(), out_dtype=torch.float32)
     assert torch.equal(y2, y1 * 2)
+
+
+@pytest.mark.parametrize("out_f,in_f,m", [(16, 1024, 16), (16, 1024, 64), (32, 2048, 5), (40, 5120, 33),
+                                          (100, 1024, 9), (512, 5120, 64), (3, 3072, 1)])
+def test_tensor_core_gemm_small_m(out_f, in_f, m):
+    """tcgen05 decode+GEMM (1..64 rows) against the oracle, and against the CUDA-core path"""
+    from ixrun_b200.packed import DevicePacked
+
+    codes = O.laplace_codes(out_f, in_f, seed=out_f * 3 + m)
+    sc = int(O.f32_to_bf16_bits(np.array([0.00123], dtype=np.float32))[0])
+    p = O.pack_codes(codes, out_f, in_f, sc)
+    dp = DevicePacked(torch_packed(p))
+    xb = O.f32_to_bf16_bits(np.random.default_rng(m).standard_normal((m, in_f)).astype(np.float32))
+    ref = O.gemm_f32(codes, sc, xb, out_f, in_f).astype(np.float64)
+    x = bits_to_bf16(xb).cuda()
+    bias = torch.randn(out_f).bfloat16().cuda()
+    y32 = dp.gemm(x, out_dtype=torch.float32)
+    assert rel_err(y32.cpu().numpy(), ref) < 2e-5
+    assert torch.equal(dp.gemm(x), y32.bfloat16())
+    assert torch.equal(dp.gemm(x, bias=bias), dp.gemm(x) + bias)
+    assert torch.equal(dp.gemm(x, out_dtype=torch.float32), y32)          # deterministic
+    if m <= 8:
+        assert rel_err(dp.gemv(x, out_dtype=torch.float32).cpu().numpy(), y32.cpu().numpy().astype(np.float64)) < 2e-5
+
+
+def test_tensor_core_gemm_extreme_levels_and_errors():
+    from ixrun_b200 import _lib
+    from ixrun_b200.packed import DevicePacked
+
+    out_f, in_f, m = 24, 1024, 16
+    n = out_f * in_f
+    rng = np.random.default_rng(1)
+    sc = int(O.f32_to_bf16_bits(np.array([0.0123], dtype=np.float32))[0])
+    xb = O.f32_to_bf16_bits(rng.standard_normal((m, in_f)).astype(np.float32))
+    for codes in (rng.choice(np.r_[-127:-15, 16:128], size=n).astype(np.int8),            # all level 3
+                  np.where(np.arange(n) % 2 == 0, 1, 100).astype(np.int8)):               # alternating 1 / 3
+        dp = DevicePacked(torch_packed(O.pack_codes(codes, out_f, in_f, sc)))
+        ref = O.gemm_f32(codes, sc, xb, out_f, in_f).astype(np.float64)
+        assert rel_err(dp.gemm(bits_to_bf16(xb).cuda(), out_dtype=torch.float32).cpu().numpy(), ref) < 2e-5
+    dp = DevicePacked(torch_packed(O.pack_codes(O.laplace_codes(8, 96, 0), 8, 96, sc)))
+    with pytest.raises(_lib.IxbError):
+        dp.gemm(torch.zeros(16, 96).bfloat16().cuda())                                    # in_f % 1024 != 0
