@@ -24,7 +24,8 @@ from .quantize import int8x_quantize
 
 __all__ = ["Int8XEngine", "StreamingLinear", "GraphLinear", "ResourceScheduler", "GraphedCall"]
 
-FUSED_MAX_ROWS = 8
+FUSED_MAX_ROWS = 8        # rows served by the CUDA-core fused kernel
+TC_MAX_ROWS = 64          # rows served by the tensor-core fused kernel (when enabled)
 
 
 class StreamingLinear(nn.Module):
@@ -61,6 +62,9 @@ class StreamingLinear(nn.Module):
             self.register_buffer("_q1", q1, persistent=False)
             self.register_buffer("_q2", q2, persistent=False)
         self._y32 = None
+        # 9..64 rows: fused decode+GEMM on the tensor cores (needs in_f % 1024 == 0).  Off by default while
+        # decoding into the shared buffer plus a dense matmul is the faster of the two on B200.
+        self._use_tc = False
         if bias is not None:
             self.register_buffer("_bias", bias.detach().clone().to(dp.device), persistent=False)
             self._bias_bf16 = self._bias.to(torch.bfloat16)
@@ -83,6 +87,10 @@ class StreamingLinear(nn.Module):
         if self._use_fused and x.dtype == torch.bfloat16 and 1 <= rows <= FUSED_MAX_ROWS \
                 and x.shape[-1] == self.in_features:
             y = self._dp.gemv(x.reshape(rows, self.in_features), bias=self._bias_bf16)
+            return y.view(x.shape[:-1] + (self.out_features,))
+        if self._use_tc and x.dtype == torch.bfloat16 and rows <= TC_MAX_ROWS and self.in_features % 1024 == 0 \
+                and x.shape[-1] == self.in_features:
+            y = self._dp.gemm(x.reshape(rows, self.in_features), bias=self._bias_bf16)
             return y.view(x.shape[:-1] + (self.out_features,))
         w = self._decode()
         bias = self._bias.to(x.dtype) if self._bias is not None else None

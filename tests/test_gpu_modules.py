@@ -76,6 +76,13 @@ def test_streaming_linear_many_tokens_uses_decode_buffer():
     ref = oracle_y(codes, p["scale"], x, out_f, in_f).reshape(2, 16, out_f) + b.float().numpy()
     err = np.abs(y.float().cpu().numpy() - ref).max() / np.abs(ref).max()
     assert err < 5e-3
+    # the same input through the tensor-core fused kernel (opt-in)
+    sl._use_tc = True
+    y_tc = sl(x)
+    # the fused paths round the sum to bf16 and then add the bias in bf16 (ixrun/engine.py:166-168):
+    # up to one more bf16 ulp than the dense path, which adds the bias before rounding
+    assert np.abs(y_tc.float().cpu().numpy() - ref).max() / np.abs(ref).max() < 1e-2
+    assert torch.equal(y_tc.reshape(32, out_f), sl._dp.gemm(x.reshape(32, in_f)) + b.cuda())
 
 
 def test_fused_gemv_and_prefix_functions_golden(golden_dir):
