@@ -8,8 +8,11 @@ batch-1 decode step, one process per GPU.
 What is real: every packed linear of every layer with its true shape, sharded
 tensor-parallel (column-parallel in-projections / gate / up, row-parallel
 out/o/down projections), fp32 partial sums and ONE NCCL all-reduce per
-token-mixer block and per MLP block (2 per layer), residual adds and RMSNorms,
-the whole token step in one CUDA graph.  What is a stand-in: the token mixers
+token-mixer block and per MLP block (2 per layer), residual adds and RMSNorms.
+On one GPU the whole token step is one CUDA graph; on several GPUs every
+stretch of launches between two all-reduces is its own graph and the NCCL
+all-reduces are launched eagerly in between (capturing the collectives inside
+one graph stalled on this pool and is not used).  What is a stand-in: the token mixers
 themselves (gated delta rule recurrence, causal conv, softmax attention over
 the KV cache) are replaced by an elementwise gate over the projected values, so
 the reported ms/token is the packed-weight path of the model, not the full
@@ -109,20 +112,74 @@ class Stack:
             h = h + self._reduce(mlp["down_proj"].gemv((F.silu(g.float()).to(g.dtype) * u), out_dtype=torch.float32))
         return h
 
+    # -- world > 1: the collectives stay outside CUDA graphs.  Every stretch of launches between two
+    #    all-reduces becomes its own graph over the static tensors h (bf16) and y32 (fp32 partial sums).
+    def _seg_mixer(self, li):
+        is_attn, mix, _ = self.layers[li]
+        if li > 0:
+            self.h.add_(self.y32.to(torch.bfloat16))           # residual of the previous layer's MLP
+        x = self._norm(self.h)
+        if is_attn:
+            q, k, v = mix["q_proj"].gemv(x), mix["k_proj"].gemv(x), mix["v_proj"].gemv(x)
+            n_in = mix["o_proj"].in_f
+            a = q[:, :n_in] * torch.sigmoid(q[:, n_in:2 * n_in].float()).to(q.dtype) + (k.sum() + v.sum()) * 0
+            out = mix["o_proj"]
+        else:
+            qkv, z = mix["in_proj_qkv"].gemv(x), mix["in_proj_z"].gemv(x)
+            a_, b_ = mix["in_proj_a"].gemv(x), mix["in_proj_b"].gemv(x)
+            n_in = mix["out_proj"].in_f
+            a = qkv[:, -n_in:] * F.silu(z[:, :n_in].float()).to(qkv.dtype) + (a_.sum() + b_.sum()) * 0
+            out = mix["out_proj"]
+        out.gemv(a.contiguous(), out=self.y32)
+
+    def _seg_mlp(self, li):
+        _, _, mlp = self.layers[li]
+        self.h.add_(self.y32.to(torch.bfloat16))
+        x = self._norm(self.h)
+        g, u = mlp["gate_proj"].gemv(x), mlp["up_proj"].gemv(x)
+        mlp["down_proj"].gemv(F.silu(g.float()).to(g.dtype) * u, out=self.y32)
+
     def capture(self):
+        if self.world == 1:
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                for _ in range(2):
+                    self._step(self.h)
+            torch.cuda.current_stream().wait_stream(side)
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                self.out = self._step(self.h)
+            self.graph = g
+            return
+        self.y32 = torch.zeros(1, HIDDEN, dtype=torch.float32, device=self.dev)
+        self.h0 = self.h.clone()
+        segs = []
+        for li in range(len(self.layers)):
+            segs += [lambda li=li: self._seg_mixer(li), lambda li=li: self._seg_mlp(li)]
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):
-            for _ in range(2):
-                self._step(self.h)
+            for f in segs:
+                f()
         torch.cuda.current_stream().wait_stream(side)
         torch.cuda.synchronize()
-        g = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(g):
-            self.out = self._step(self.h)
-        self.graph = g
+        self.segments = []
+        for f in segs:
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                f()
+            self.segments.append(g)
+        torch.cuda.synchronize()
 
     def step(self):
+        if self.world > 1 and getattr(self, "segments", None):
+            self.h.copy_(self.h0)
+            for g in self.segments:
+                g.replay()
+                dist.all_reduce(self.y32)
+            return self.h
         if self.graph is not None:
             self.graph.replay()
             return self.out
@@ -141,19 +198,18 @@ def main():
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+        import datetime
+
+        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=120))
     t0 = time.time()
     with torch.no_grad():
         st = Stack(args.layers, world, rank, dev)
         setup = time.time() - t0
         mode = "eager"
         if not args.eager:
-            try:
-                st.capture()
-                mode = "one CUDA graph per token step"
-            except Exception as e:  # graph capture of the collective can be unavailable: time eager then
-                mode = f"eager (graph capture failed: {type(e).__name__})"
-                st.graph = None
+            st.capture()
+            mode = ("one CUDA graph per token step" if world == 1
+                    else "one CUDA graph per stretch between all-reduces; NCCL all-reduces launched eagerly")
         for _ in range(3):
             st.step()
         if world > 1:
