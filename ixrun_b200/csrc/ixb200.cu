@@ -385,7 +385,13 @@ k_gemv(Streams s, const int32_t *__restrict__ q1, const int32_t *__restrict__ q2
             // float4 index of this word's first chunk in the swizzled fp32 copy of x
             const uint32_t xstride = ((s.in_f + 1023u) / 1024u) * 1024u;
             const uint32_t xword = (k0 >> 10) * 256u + ((k0 >> 5) & 31u);
+#if defined(IXB_DEBUG_SKIP) && IXB_DEBUG_SKIP == 1
+            { float partx[M]; for (int m = 0; m < M; ++m) partx[m] = __uint_as_float(w.bit1 + w.bit2 + w.byte3 + w.m2); if (__all_sync(0xffffffffu, true)) { for (int m = 0; m < M; ++m) acc[m] += partx[m]; } __syncwarp(); cur = nxt; a0 = a1; c0 = c1; a1 = a2; c1 = c2; continue; }
+#endif
             WordCursors c = word_cursors(w);
+#if defined(IXB_DEBUG_SKIP) && IXB_DEBUG_SKIP == 2
+            { float partx[M]; for (int m = 0; m < M; ++m) partx[m] = __uint_as_float(c.b1p[3] + c.b2p[3] + c.b3p[3] + c.nn[3] + c.max_l3 + c.b1p[1] + c.b2p[2]); if (__all_sync(0xffffffffu, true)) { for (int m = 0; m < M; ++m) acc[m] += partx[m]; } __syncwarp(); cur = nxt; a0 = a1; c0 = c1; a1 = a2; c1 = c2; continue; }
+#endif
             float part[M];
 #pragma unroll
             for (int m = 0; m < M; ++m) part[m] = 0.f;

@@ -239,18 +239,17 @@ __device__ __forceinline__ void decode_word_fast(const Src &src, const WordRanks
 // bf16(code * scale) comes from one packed bf16 multiply whose upper half is
 // the (exactly rounded) product and whose lower half is 0 * scale = 0 -- read
 // as fp32 that register is the weight itself.  On sm_100 logic/shift/compare
-// instructions issue at half the rate of add/FMA and on their own pipe, so the
-// step splits its work: two of the queue shifts are written as high-half
-// multiplies and the B2 queue (kept left-aligned, next bit in the sign) is
-// advanced with an add, which balances the two pipes.
-#define IXB_ELEM_ARITH(BITMASK)                                                                   \
+// instructions issue at half the rate of add/FMA, so the two bitmaps are kept
+// bit-reversed and left-aligned: the next B1 / B2 bit is the sign bit (one
+// compare each, no mask-and-test) and both queues advance with an add.
+#define IXB_ELEM_ARITH()                                                                          \
     asm("{\n\t"                                                                                   \
         ".reg .pred p1, p2, p3;\n\t"                                                              \
-        ".reg .b32 t, f, c;\n\t"                                                                  \
-        "and.b32 t, %6, " #BITMASK ";\n\t"                                                        \
-        "setp.ne.u32 p1, t, 0;\n\t"                                                               \
+        ".reg .b32 f, c;\n\t"                                                                     \
+        "setp.lt.s32 p1, %6, 0;\n\t"                                                              \
         "setp.lt.and.s32 p2, %5, 0, !p1;\n\t"                                                     \
         "setp.ge.and.s32 p3, %5, 0, !p1;\n\t"                                                     \
+        "add.u32 %6, %6, %6;\n\t"                                                                 \
         "lop3.b32 f, %1, 7, 0x4B000000, 0xEA;\n\t"                                                \
         "sub.f32 c, f, 0f4B000003;\n\t"                                                           \
         "@p2 lop3.b32 f, %2, 31, 0x4B000000, 0xEA;\n\t"                                           \
@@ -258,14 +257,14 @@ __device__ __forceinline__ void decode_word_fast(const Src &src, const WordRanks
         "@p3 lop3.b32 f, %4, 255, 0x4B000000, 0xEA;\n\t"                                          \
         "@p3 sub.f32 c, f, 0f4B00007F;\n\t"                                                       \
         "mul.rn.bf16x2 %0, c, %7;\n\t"                                                            \
-        "@p1 mul.hi.u32 %1, %1, 0x20000000;\n\t"                                                  \
+        "@p1 shr.u32 %1, %1, 3;\n\t"                                                              \
         "@p2 shf.r.wrap.b32 %2, %2, %3, 5;\n\t"                                                   \
         "@p2 shr.u32 %3, %3, 5;\n\t"                                                              \
-        "@p3 mul.hi.u32 %4, %4, 0x01000000;\n\t"                                                  \
+        "@p3 shr.u32 %4, %4, 8;\n\t"                                                              \
         "@!p1 add.u32 %5, %5, %5;\n\t"                                                            \
         "}"                                                                                       \
-        : "=r"(wv), "+r"(q1), "+r"(q2lo), "+r"(q2hi), "+r"(q3), "+r"(mq)                          \
-        : "r"(m1), "r"(s2))
+        : "=r"(wv), "+r"(q1), "+r"(q2lo), "+r"(q2hi), "+r"(q3), "+r"(mq), "+r"(m1s)               \
+        : "r"(s2))
 
 // Table-free variant of decode_word_fast: sink(i, v) receives the fp32 bit
 // pattern of the element's weight bf16(code * scale).  `s2` holds the bf16
@@ -274,7 +273,7 @@ template <class Src, class Pre, class Sink>
 __device__ __forceinline__ void decode_word_arith(const Src &src, const WordRanks &w, const WordCursors &c,
                                                   uint32_t s2, Pre &&pre, Sink &&sink)
 {
-    const uint32_t m1 = w.m1;
+    uint32_t m1s = __brev(w.m1);                 // next B1 bit in the sign
     const uint32_t brev_m2 = __brev(w.m2);
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
@@ -287,14 +286,11 @@ __device__ __forceinline__ void decode_word_arith(const Src &src, const WordRank
         uint32_t q3 = __funnelshift_r(src.l3w(i3), src.l3w(i3 + 1), c.b3p[q] & 31u);        // 4 bytes
         uint32_t mq = brev_m2 << c.nn[q];                                                   // next B2 bit in the sign
         uint32_t wv;
-#define IXB_E(j, mask)                      \
-    IXB_ELEM_ARITH(mask);                   \
-    sink(8 * q + j, wv);
-        if (q == 0) { IXB_E(0, 0x1) IXB_E(1, 0x2) IXB_E(2, 0x4) IXB_E(3, 0x8) IXB_E(4, 0x10) IXB_E(5, 0x20) IXB_E(6, 0x40) IXB_E(7, 0x80) }
-        if (q == 1) { IXB_E(0, 0x100) IXB_E(1, 0x200) IXB_E(2, 0x400) IXB_E(3, 0x800) IXB_E(4, 0x1000) IXB_E(5, 0x2000) IXB_E(6, 0x4000) IXB_E(7, 0x8000) }
-        if (q == 2) { IXB_E(0, 0x10000) IXB_E(1, 0x20000) IXB_E(2, 0x40000) IXB_E(3, 0x80000) IXB_E(4, 0x100000) IXB_E(5, 0x200000) IXB_E(6, 0x400000) IXB_E(7, 0x800000) }
-        if (q == 3) { IXB_E(0, 0x1000000) IXB_E(1, 0x2000000) IXB_E(2, 0x4000000) IXB_E(3, 0x8000000) IXB_E(4, 0x10000000) IXB_E(5, 0x20000000) IXB_E(6, 0x40000000) IXB_E(7, 0x80000000) }
-#undef IXB_E
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            IXB_ELEM_ARITH();
+            sink(8 * q + j, wv);
+        }
     }
 }
 
