@@ -102,6 +102,32 @@ int ixb_gemv(const ixb_packed *w, const int32_t *blk_q1, const int32_t *blk_q2,
              void *scratch_device, size_t scratch_bytes, ixb_stream_t stream);
 
 /*
+ * Device-side quantiser and packer for deploy time.  Replaces int8x_quantize
+ * (ixrun/quantize.py:41-122: per-tensor scale = max|W|/127 evaluated in bf16,
+ * codes = clamp(round_half_even(W/scale), +-127), level split, LSB-first bit
+ * packing of ixrun/bitpack.py:13-61); the streams come out bit for bit as the
+ * CPU quantiser writes them.  Three steps, because the stream sizes are only
+ * known after counting:
+ *   1. ixb_quantize_codes (from a bf16 weight) or ixb_count_codes (from int8
+ *      codes, e.g. a tensor-parallel slice that keeps the unsharded scale):
+ *      writes codes / scale, the B1 bitmap and the gran=1024 rank tables and
+ *      returns counts_host[3] = {#L1, #L2, #L3}.  Synchronises the stream.
+ *   2. the caller allocates b2 (ceil((n2+n3)/32) words), l1 (ceil(3 n1/32)),
+ *      l2 (ceil(5 n2/32)), l3 (n3 bytes)
+ *   3. ixb_pack_codes fills them (they are zeroed by the call).
+ * `ws`: ixb_pack_workspace_bytes(N) bytes of device workspace.
+ */
+size_t ixb_pack_workspace_bytes(int64_t n_elements);
+int ixb_quantize_codes(const void *w_bf16_device, int64_t n_elements, void *scale_bf16_device,
+                       int8_t *codes_device, void *b1_device, int32_t *blk_q1_device, int32_t *blk_q2_device,
+                       int64_t *counts_host, void *ws_device, size_t ws_bytes, ixb_stream_t stream);
+int ixb_count_codes(const int8_t *codes_device, int64_t n_elements, void *b1_device,
+                    int32_t *blk_q1_device, int32_t *blk_q2_device, int64_t *counts_host,
+                    void *ws_device, size_t ws_bytes, ixb_stream_t stream);
+int ixb_pack_codes(const int8_t *codes_device, const ixb_packed *out, const int32_t *blk_q1_device,
+                   const int32_t *blk_q2_device, ixb_stream_t stream);
+
+/*
  * Fused decode + small-M GEMM on the tensor cores (tcgen05, accumulators in
  * TMEM) for 1 <= m_rows <= 64; intended for 9..64 rows (batched decode, MTP
  * verify), below that ixb_gemv is the better call.  Same result definition and

@@ -21,6 +21,7 @@ SYMBOLS = (
     "ixb_prefix_workspace_bytes", "ixb_prefix_tables",
     "ixb_decode", "ixb_gemv_scratch_bytes", "ixb_gemv", "ixb_gemv_static",
     "ixb_gemm_scratch_bytes", "ixb_gemm",
+    "ixb_pack_workspace_bytes", "ixb_quantize_codes", "ixb_count_codes", "ixb_pack_codes",
 )
 
 
@@ -73,6 +74,14 @@ def lib():
     L.ixb_gemm_scratch_bytes.argtypes = [i64, i64, i64]
     L.ixb_gemm.restype = C.c_int
     L.ixb_gemm.argtypes = [C.POINTER(Packed), vp, vp, vp, i64, vp, vp, C.c_int, vp, sz, vp]
+    L.ixb_pack_workspace_bytes.restype = sz
+    L.ixb_pack_workspace_bytes.argtypes = [i64]
+    L.ixb_quantize_codes.restype = C.c_int
+    L.ixb_quantize_codes.argtypes = [vp, i64, vp, vp, vp, vp, vp, C.POINTER(i64), vp, sz, vp]
+    L.ixb_count_codes.restype = C.c_int
+    L.ixb_count_codes.argtypes = [vp, i64, vp, vp, vp, C.POINTER(i64), vp, sz, vp]
+    L.ixb_pack_codes.restype = C.c_int
+    L.ixb_pack_codes.argtypes = [vp, C.POINTER(Packed), vp, vp, vp]
     L.ixb_gemv_static.restype = C.c_int
     L.ixb_gemv_static.argtypes = [C.POINTER(Packed), vp, vp, vp, i64, vp, vp, C.c_int, vp]
     _lib = L

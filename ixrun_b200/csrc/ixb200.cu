@@ -3,6 +3,7 @@
 #include "../../include/ixb200.h"
 #include "ixb_common.cuh"
 #include "ixb_gemm_tc.cuh"
+#include "ixb_pack.cuh"
 
 #include <atomic>
 #include <cstdarg>
@@ -647,6 +648,87 @@ extern "C" int ixb_gemv(const ixb_packed *w, const int32_t *blk_q1, const int32_
     default: launch_gemv<8>(s, blk_q1, blk_q2, x, bias, y, y_is_f32, slots, ticket, p, st); break;
     }
     return launch_check("k_gemv");
+}
+
+// ------------------------------------------------------------ quantise + pack
+extern "C" size_t ixb_pack_workspace_bytes(int64_t n_elements)
+{
+    size_t nb = (size_t)((n_elements + kBlk - 1) / kBlk);
+    return 256 + 4 * nb * sizeof(int32_t);
+}
+
+// workspace layout: [0] absmax bits, [1..2] unused, [64..] cnt1 | a_blk | cnt2 | c_blk (nb int32 each)
+static int counts_and_tables(int mode, const void *w, int8_t *codes, uint32_t n, uint32_t *b1, void *scale,
+                             int32_t *blk_q1, int32_t *blk_q2, int64_t *counts_host, void *ws, size_t ws_bytes,
+                             cudaStream_t st)
+{
+    if (ws_bytes < ixb_pack_workspace_bytes(n)) return fail(IXB_E_SCRATCH, "pack workspace too small");
+    uint32_t nb = (n + kBlk - 1) / kBlk;
+    uint32_t *absmax = (uint32_t *)ws;
+    int32_t *cnt1 = (int32_t *)((char *)ws + 256), *cnt2 = cnt1 + nb;
+    int rc;
+    if (mode == 0) {
+        IXB_CUDA(cudaMemsetAsync(absmax, 0, 4, st));
+        k_absmax<<<(unsigned)min(1024u, (n + 255) / 256), 256, 0, st>>>((const uint16_t *)w, n, absmax);
+        if ((rc = launch_check("k_absmax"))) return rc;
+        k_codes_and_counts<0><<<(nb + 7) / 8, 256, 0, st>>>((const uint16_t *)w, absmax, codes, n, b1, cnt1, cnt2,
+                                                            (__nv_bfloat16 *)scale);
+    } else {
+        k_codes_and_counts<1><<<(nb + 7) / 8, 256, 0, st>>>(nullptr, absmax, codes, n, b1, cnt1, cnt2, nullptr);
+    }
+    if ((rc = launch_check("k_codes_and_counts"))) return rc;
+    k_excl_scan<<<1, 1024, 0, st>>>(cnt1, blk_q1, nb);
+    if ((rc = launch_check("k_excl_scan"))) return rc;
+    k_excl_scan<<<1, 1024, 0, st>>>(cnt2, blk_q2, nb);
+    if ((rc = launch_check("k_excl_scan"))) return rc;
+    // totals = last prefix + last count; the caller sizes the streams from them
+    int32_t last[4];
+    IXB_CUDA(cudaMemcpyAsync(&last[0], blk_q1 + nb - 1, 4, cudaMemcpyDeviceToHost, st));
+    IXB_CUDA(cudaMemcpyAsync(&last[1], cnt1 + nb - 1, 4, cudaMemcpyDeviceToHost, st));
+    IXB_CUDA(cudaMemcpyAsync(&last[2], blk_q2 + nb - 1, 4, cudaMemcpyDeviceToHost, st));
+    IXB_CUDA(cudaMemcpyAsync(&last[3], cnt2 + nb - 1, 4, cudaMemcpyDeviceToHost, st));
+    IXB_CUDA(cudaStreamSynchronize(st));
+    counts_host[0] = (int64_t)last[0] + last[1];
+    counts_host[1] = (int64_t)last[2] + last[3];
+    counts_host[2] = (int64_t)n - counts_host[0] - counts_host[1];
+    return IXB_OK;
+}
+
+extern "C" int ixb_quantize_codes(const void *w_bf16, int64_t n_elements, void *scale_bf16, int8_t *codes,
+                                  void *b1, int32_t *blk_q1, int32_t *blk_q2, int64_t *counts_host, void *ws,
+                                  size_t ws_bytes, ixb_stream_t stream)
+{
+    if (!w_bf16 || !scale_bf16 || !codes || !b1 || !blk_q1 || !blk_q2 || !counts_host || !ws)
+        return fail(IXB_E_ARG, "NULL pointer argument");
+    if (n_elements <= 0 || n_elements > 800000000LL) return fail(IXB_E_ARG, "bad element count %lld", (long long)n_elements);
+    return counts_and_tables(0, w_bf16, codes, (uint32_t)n_elements, (uint32_t *)b1, scale_bf16, blk_q1, blk_q2,
+                             counts_host, ws, ws_bytes, (cudaStream_t)stream);
+}
+
+extern "C" int ixb_count_codes(const int8_t *codes, int64_t n_elements, void *b1, int32_t *blk_q1, int32_t *blk_q2,
+                               int64_t *counts_host, void *ws, size_t ws_bytes, ixb_stream_t stream)
+{
+    if (!codes || !b1 || !blk_q1 || !blk_q2 || !counts_host || !ws) return fail(IXB_E_ARG, "NULL pointer argument");
+    if (n_elements <= 0 || n_elements > 800000000LL) return fail(IXB_E_ARG, "bad element count %lld", (long long)n_elements);
+    return counts_and_tables(1, nullptr, (int8_t *)codes, (uint32_t)n_elements, (uint32_t *)b1, nullptr, blk_q1, blk_q2,
+                             counts_host, ws, ws_bytes, (cudaStream_t)stream);
+}
+
+extern "C" int ixb_pack_codes(const int8_t *codes, const ixb_packed *out, const int32_t *blk_q1, const int32_t *blk_q2,
+                              ixb_stream_t stream)
+{
+    Streams s;
+    int rc = to_streams(out, &s);
+    if (rc) return rc;
+    if (!codes || !blk_q1 || !blk_q2) return fail(IXB_E_ARG, "NULL pointer argument");
+    cudaStream_t st = (cudaStream_t)stream;
+    if (s.b2_words) IXB_CUDA(cudaMemsetAsync((void *)s.b2, 0, (size_t)s.b2_words * 4, st));
+    if (s.l1_words) IXB_CUDA(cudaMemsetAsync((void *)s.l1, 0, (size_t)s.l1_words * 4, st));
+    if (s.l2_words) IXB_CUDA(cudaMemsetAsync((void *)s.l2, 0, (size_t)s.l2_words * 4, st));
+    uint32_t nb = (s.n + kBlk - 1) / kBlk;
+    k_pack<<<(nb + 7) / 8, 256, 0, st>>>(codes, s.n, blk_q1, blk_q2, (uint32_t *)s.b2, (uint32_t *)s.l1,
+                                         (uint32_t *)s.l2, (uint8_t *)s.l3);
+    return launch_check("k_pack");
 }
 
 // ------------------------------------------------------- tensor-core small-M GEMM

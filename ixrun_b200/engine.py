@@ -36,14 +36,16 @@ class StreamingLinear(nn.Module):
     `_use_fused`, `_split_chunk`, `_y32`).
     """
 
-    def __init__(self, packed: dict, bias=None):
+    def __init__(self, packed, bias=None):
+        """`packed`: the reference's packed dict, or a DevicePacked already on the GPU."""
         super().__init__()
-        self.out_features = packed["out_f"]
-        self.in_features = packed["in_f"]
-        self.N = packed["N"]
-        self.level_bits = packed["level_bits"]
-        self.counts = packed["counts"]
-        dp = DevicePacked(packed)
+        dp = packed if isinstance(packed, DevicePacked) else DevicePacked(packed)
+        self.out_features = dp.out_f
+        self.in_features = dp.in_f
+        self.N = dp.N
+        self.level_bits = (3, 5, 8)
+        self.counts = dp.counts
+        self.total_bytes = dp.total_bytes
         self._dp = dp
         for key, val in (("_b1", dp.b1), ("_b2", dp.b2), ("_l1", dp.l1), ("_l2", dp.l2), ("_l3", dp.l3),
                          ("_scale", dp.scale), ("_b1_blk", dp.blk_q1), ("_b2_blk", dp.blk_q2)):
@@ -72,6 +74,13 @@ class StreamingLinear(nn.Module):
             self._bias = None
             self._bias_bf16 = None
         self._w_buf = None
+
+    @classmethod
+    def from_weight(cls, weight: torch.Tensor, bias=None):
+        """Quantise and pack a bf16 weight on the GPU (no CPU pass over the tensor)."""
+        from .gpu_pack import quantize_pack_gpu
+
+        return cls(quantize_pack_gpu(weight.detach().to("cuda", torch.bfloat16)), bias=bias)
 
     def _set_shared_buf(self, w_buf):
         self._w_buf = w_buf
@@ -251,13 +260,22 @@ class Int8XEngine:
     @staticmethod
     @torch.no_grad()
     def _deploy_streaming(model, level_bits, verbose=True, cache_path=None):
-        layer_data = Int8XEngine._load_or_quantize(model, level_bits, verbose, cache_path)
         max_n = total_bytes = 0
         layers = []
-        for name, p, bias in layer_data:
-            layers.append((name, StreamingLinear(p, bias=bias)))
-            total_bytes += p["total_bytes"]
-            max_n = max(max_n, p["N"])
+        if cache_path is None:
+            # no cache file wanted: quantise and pack every layer on the GPU, one at a time
+            if tuple(sorted(level_bits)) != (3, 5, 8):
+                raise ValueError(f"only the (3, 5, 8) scheme is supported, got {tuple(level_bits)}")
+            for name, mod in list(iter_quantizable_linears(model)):
+                sl = StreamingLinear.from_weight(mod.weight.data, bias=mod.bias.data if mod.bias is not None else None)
+                layers.append((name, sl))
+                total_bytes += sl.total_bytes
+                max_n = max(max_n, sl.N)
+        else:
+            for name, p, bias in Int8XEngine._load_or_quantize(model, level_bits, verbose, cache_path):
+                layers.append((name, StreamingLinear(p, bias=bias)))
+                total_bytes += p["total_bytes"]
+                max_n = max(max_n, p["N"])
         shared_w = torch.empty(max(max_n, 1), dtype=torch.bfloat16, device="cuda")
         for name, sl in layers:
             sl._set_shared_buf(shared_w)

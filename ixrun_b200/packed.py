@@ -51,8 +51,9 @@ class DevicePacked:
         self._init_tables()
 
     @classmethod
-    def from_device_streams(cls, b1, b2, l1, l2, l3, scale, out_f: int, in_f: int):
-        """Wrap streams that already live on the device (no copies)."""
+    def from_device_streams(cls, b1, b2, l1, l2, l3, scale, out_f: int, in_f: int, blk_q1=None, blk_q2=None):
+        """Wrap streams that already live on the device (no copies); the gran=1024 rank tables are
+        computed unless given."""
         self = cls.__new__(cls)
         self.device = b1.device
         self.out_f, self.in_f, self.N = int(out_f), int(in_f), int(out_f) * int(in_f)
@@ -60,15 +61,17 @@ class DevicePacked:
         self.total_bytes = 0
         self.b1, self.b2, self.l1, self.l2, self.l3 = b1, b2, l1, l2, l3
         self.scale = scale.reshape(()).to(torch.bfloat16)
-        self._init_tables()
+        self._init_tables(blk_q1, blk_q2)
         return self
 
     # ------------------------------------------------------------ plumbing --
-    def _init_tables(self):
+    def _init_tables(self, blk_q1=None, blk_q2=None):
         self.struct = _lib.packed_struct(self.b1, self.b2, self.l1, self.l2, self.l3, self.scale,
                                          self.out_f, self.in_f)
         self.n_blocks = (self.N + BLOCK - 1) // BLOCK
-        self.blk_q1, self.blk_q2 = self.prefix_tables(BLOCK, self.n_blocks)
+        if blk_q1 is None or blk_q2 is None:
+            blk_q1, blk_q2 = self.prefix_tables(BLOCK, self.n_blocks)
+        self.blk_q1, self.blk_q2 = blk_q1, blk_q2
         self._scratch = {}
 
     def prefix_tables(self, gran: int, n_units: int | None = None):
