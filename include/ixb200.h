@@ -128,6 +128,42 @@ int ixb_pack_codes(const int8_t *codes_device, const ixb_packed *out, const int3
                    const int32_t *blk_q2_device, ixb_stream_t stream);
 
 /*
+ * Resident re-layout "P5".  It has no counterpart in the reference, whose
+ * kernels read the (3,5,8) streams directly; it plays the role of the
+ * reference's deploy-time derived buffers (ixrun/engine.py:68-97) taken one
+ * step further: the streams stay the interchange / cache-file format, and at
+ * deploy time the int8 codes are re-laid out, losslessly, for fixed
+ * addressing:
+ *   w03, w4  one uint4 + one uint32 per 32 elements: a 5-bit field per element,
+ *            code + 15 for |code| <= 15, 15 (= code 0) for level-3 elements
+ *   esc      level-3 elements as 16-bit entries (position in a 256-element
+ *            quarter block | (code + 127) << 8), in element order
+ *   esc_off  int32 [ceil(N/256) + 1] first entry of every quarter block
+ * about 5 + 16 * P(level 3) + 0.125 bits per weight.
+ * ixb_p5_build: codes -> layout (n_esc = number of level-3 elements = counts[2];
+ *   ws: (ceil(N/256) + 1) * 4 bytes).  ixb_p5_decode: layout -> int8 codes /
+ *   bf16 weights (out_kind as ixb_decode).  ixb_p5_gemv: same contract as
+ *   ixb_gemv (result definition, bias, scratch rules), reading this layout.
+ */
+typedef struct ixb_p5 {
+    const void *w03;
+    const void *w4;
+    const void *esc_off;
+    const void *esc;
+    int64_t n_esc;
+    const void *scale;    /* one bf16 */
+    int64_t out_f;
+    int64_t in_f;
+} ixb_p5;
+int ixb_p5_build(const int8_t *codes_device, int64_t n_elements, void *w03_device, void *w4_device,
+                 int32_t *esc_off_device, void *esc_device, int64_t n_esc,
+                 void *ws_device, size_t ws_bytes, ixb_stream_t stream);
+int ixb_p5_decode(const ixb_p5 *t, void *out_device, int out_kind, ixb_stream_t stream);
+size_t ixb_p5_gemv_scratch_bytes(int64_t out_f, int64_t in_f, int64_t m_rows);
+int ixb_p5_gemv(const ixb_p5 *t, const void *x_device, int64_t m_rows, const void *bias_device,
+                void *y_device, int y_is_f32, void *scratch_device, size_t scratch_bytes, ixb_stream_t stream);
+
+/*
  * Fused decode + small-M GEMM on the tensor cores (tcgen05, accumulators in
  * TMEM) for 1 <= m_rows <= 64; intended for 9..64 rows (batched decode, MTP
  * verify), below that ixb_gemv is the better call.  Same result definition and

@@ -22,6 +22,7 @@ SYMBOLS = (
     "ixb_decode", "ixb_gemv_scratch_bytes", "ixb_gemv", "ixb_gemv_static",
     "ixb_gemm_scratch_bytes", "ixb_gemm",
     "ixb_pack_workspace_bytes", "ixb_quantize_codes", "ixb_count_codes", "ixb_pack_codes",
+    "ixb_p5_build", "ixb_p5_decode", "ixb_p5_gemv_scratch_bytes", "ixb_p5_gemv",
 )
 
 
@@ -40,6 +41,15 @@ class Packed(C.Structure):
         ("l3", C.c_void_p), ("l3_bytes", C.c_int64),
         ("scale", C.c_void_p),
         ("out_f", C.c_int64), ("in_f", C.c_int64),
+    ]
+
+
+class P5Struct(C.Structure):
+    """Mirror of ``struct ixb_p5``."""
+
+    _fields_ = [
+        ("w03", C.c_void_p), ("w4", C.c_void_p), ("esc_off", C.c_void_p), ("esc", C.c_void_p),
+        ("n_esc", C.c_int64), ("scale", C.c_void_p), ("out_f", C.c_int64), ("in_f", C.c_int64),
     ]
 
 
@@ -82,6 +92,14 @@ def lib():
     L.ixb_count_codes.argtypes = [vp, i64, vp, vp, vp, C.POINTER(i64), vp, sz, vp]
     L.ixb_pack_codes.restype = C.c_int
     L.ixb_pack_codes.argtypes = [vp, C.POINTER(Packed), vp, vp, vp]
+    L.ixb_p5_build.restype = C.c_int
+    L.ixb_p5_build.argtypes = [vp, i64, vp, vp, vp, vp, i64, vp, sz, vp]
+    L.ixb_p5_decode.restype = C.c_int
+    L.ixb_p5_decode.argtypes = [C.POINTER(P5Struct), vp, C.c_int, vp]
+    L.ixb_p5_gemv_scratch_bytes.restype = sz
+    L.ixb_p5_gemv_scratch_bytes.argtypes = [i64, i64, i64]
+    L.ixb_p5_gemv.restype = C.c_int
+    L.ixb_p5_gemv.argtypes = [C.POINTER(P5Struct), vp, i64, vp, vp, C.c_int, vp, sz, vp]
     L.ixb_gemv_static.restype = C.c_int
     L.ixb_gemv_static.argtypes = [C.POINTER(Packed), vp, vp, vp, i64, vp, vp, C.c_int, vp]
     _lib = L

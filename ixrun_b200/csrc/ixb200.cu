@@ -4,6 +4,7 @@
 #include "ixb_common.cuh"
 #include "ixb_gemm_tc.cuh"
 #include "ixb_pack.cuh"
+#include "ixb_p5.cuh"
 
 #include <atomic>
 #include <cstdarg>
@@ -729,6 +730,132 @@ extern "C" int ixb_pack_codes(const int8_t *codes, const ixb_packed *out, const 
     k_pack<<<(nb + 7) / 8, 256, 0, st>>>(codes, s.n, blk_q1, blk_q2, (uint32_t *)s.b2, (uint32_t *)s.l1,
                                          (uint32_t *)s.l2, (uint8_t *)s.l3);
     return launch_check("k_pack");
+}
+
+// ------------------------------------------------------------- resident P5 layout
+static int to_p5(const ixb_p5 *t, P5 *p)
+{
+    if (!t) return fail(IXB_E_ARG, "P5 tensor is NULL");
+    if (t->out_f <= 0 || t->in_f <= 0) return fail(IXB_E_ARG, "bad shape");
+    long long n = (long long)t->out_f * t->in_f;
+    if (n > 800000000LL) return fail(IXB_E_UNSUPPORTED, "tensor too large");
+    if (!t->w03 || !t->w4 || !t->esc_off || !t->scale) return fail(IXB_E_ARG, "NULL P5 pointer");
+    if (t->n_esc && !t->esc) return fail(IXB_E_ARG, "outlier list is NULL");
+    if (((uintptr_t)t->w03 & 15u) || ((uintptr_t)t->w4 & 3u)) return fail(IXB_E_ARG, "P5 planes are misaligned");
+    p->w03 = (const uint4 *)t->w03;
+    p->w4 = (const uint32_t *)t->w4;
+    p->esc_off = (const int32_t *)t->esc_off;
+    p->esc = (const uint16_t *)t->esc;
+    p->scale = (const __nv_bfloat16 *)t->scale;
+    p->n = (uint32_t)n;
+    p->out_f = (uint32_t)t->out_f;
+    p->in_f = (uint32_t)t->in_f;
+    return IXB_OK;
+}
+
+extern "C" int ixb_p5_build(const int8_t *codes, int64_t n_elements, void *w03, void *w4, int32_t *esc_off,
+                            void *esc, int64_t n_esc, void *ws, size_t ws_bytes, ixb_stream_t stream)
+{
+    if (!codes || !w03 || !w4 || !esc_off || !ws || (n_esc && !esc)) return fail(IXB_E_ARG, "NULL pointer argument");
+    if (n_elements <= 0 || n_elements > 800000000LL) return fail(IXB_E_ARG, "bad element count");
+    uint32_t n = (uint32_t)n_elements, nb = (n + kBlk - 1) / kBlk, nq = (n + 255u) / 256u;
+    if (ws_bytes < (size_t)(nq + 1) * 4) return fail(IXB_E_SCRATCH, "P5 workspace too small");
+    cudaStream_t st = (cudaStream_t)stream;
+    int32_t *qcnt = (int32_t *)ws;
+    int rc;
+    IXB_CUDA(cudaMemsetAsync(qcnt, 0, (size_t)(nq + 1) * 4, st));
+    k_p5_plane<<<(nb + 7) / 8, 256, 0, st>>>(codes, n, (uint4 *)w03, (uint32_t *)w4, qcnt);
+    if ((rc = launch_check("k_p5_plane"))) return rc;
+    k_excl_scan<<<1, 1024, 0, st>>>(qcnt, esc_off, nq + 1);      // entry nq = total
+    if ((rc = launch_check("k_excl_scan"))) return rc;
+    if (n_esc) {
+        k_p5_esc<<<(nq + 7) / 8, 256, 0, st>>>(codes, n, esc_off, (uint16_t *)esc);
+        if ((rc = launch_check("k_p5_esc"))) return rc;
+    }
+    return IXB_OK;
+}
+
+extern "C" int ixb_p5_decode(const ixb_p5 *t, void *out, int out_kind, ixb_stream_t stream)
+{
+    P5 p;
+    int rc = to_p5(t, &p);
+    if (rc) return rc;
+    if (!out || ((uintptr_t)out & 15u)) return fail(IXB_E_ARG, "output is NULL or not 16-byte aligned");
+    uint32_t nb = (p.n + kBlk - 1) / kBlk;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (out_kind == 0) k_p5_decode<0><<<(nb + 7) / 8, 256, 0, st>>>(p, out);
+    else if (out_kind == 1) k_p5_decode<1><<<(nb + 7) / 8, 256, 0, st>>>(p, out);
+    else return fail(IXB_E_ARG, "out_kind must be 0 or 1");
+    return launch_check("k_p5_decode");
+}
+
+struct P5Plan { uint32_t nb, grid, bpw, pmax, xstride, smem, xs; };
+
+static P5Plan make_p5_plan(uint32_t out_f, uint32_t in_f, uint32_t m_rows)
+{
+    P5Plan p;
+    unsigned long long n = (unsigned long long)out_f * in_f;
+    p.nb = (uint32_t)((n + kBlk - 1) / kBlk);
+    uint32_t sms = (uint32_t)num_sms();
+    uint32_t want = (p.nb + kP5Warps - 1) / kP5Warps;
+    p.grid = want < sms ? want : sms;
+    if (!p.grid) p.grid = 1;
+    p.bpw = (p.nb + p.grid * kP5Warps - 1) / (p.grid * kP5Warps);
+    uint32_t row_blocks = (in_f + kBlk - 1) / kBlk + 1;
+    p.pmax = (row_blocks + p.bpw - 1) / p.bpw + 1;
+    p.xstride = ((in_f + 1023u) / 1024u) * 1024u;
+    uint32_t xbytes = m_rows * p.xstride * 4u;
+    p.xs = xbytes <= 200u * 1024u;
+    p.smem = p.xs ? xbytes : 0u;
+    return p;
+}
+
+extern "C" size_t ixb_p5_gemv_scratch_bytes(int64_t out_f, int64_t in_f, int64_t m_rows)
+{
+    if (out_f <= 0 || in_f <= 0 || m_rows <= 0) return 0;
+    P5Plan p = make_p5_plan((uint32_t)out_f, (uint32_t)in_f, (uint32_t)m_rows);
+    return 256 + (size_t)m_rows * (size_t)out_f * p.pmax * sizeof(float);
+}
+
+template <int M, int XS>
+static void launch_p5(const P5 &p, const void *x, const void *bias, void *y, int y_f32, float *slots, uint32_t *ticket,
+                      const P5Plan &pl, cudaStream_t st)
+{
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaFuncSetAttribute(k_p5_gemv<M, XS>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        attr_set = true;
+    }
+    k_p5_gemv<M, XS><<<pl.grid, kP5Threads, pl.smem, st>>>(p, (const __nv_bfloat16 *)x, (const __nv_bfloat16 *)bias, y,
+                                                           y_f32, slots, ticket, pl.nb, pl.bpw, pl.pmax, pl.xstride);
+}
+
+extern "C" int ixb_p5_gemv(const ixb_p5 *t, const void *x, int64_t m_rows, const void *bias, void *y, int y_is_f32,
+                           void *scratch, size_t scratch_bytes, ixb_stream_t stream)
+{
+    P5 p;
+    int rc = to_p5(t, &p);
+    if (rc) return rc;
+    if (!x || !y || !scratch) return fail(IXB_E_ARG, "NULL pointer argument");
+    if (m_rows < 1 || m_rows > 8) return fail(IXB_E_UNSUPPORTED, "m_rows=%lld outside 1..8", (long long)m_rows);
+    if (p.in_f % 32u) return fail(IXB_E_UNSUPPORTED, "in_f=%u is not a multiple of 32", p.in_f);
+    if ((uintptr_t)x & 15u) return fail(IXB_E_ARG, "x is not 16-byte aligned");
+    if (scratch_bytes < ixb_p5_gemv_scratch_bytes(p.out_f, p.in_f, m_rows)) return fail(IXB_E_SCRATCH, "gemv scratch too small");
+    P5Plan pl = make_p5_plan(p.out_f, p.in_f, (uint32_t)m_rows);
+    uint32_t *ticket = (uint32_t *)scratch;
+    float *slots = (float *)((char *)scratch + 256);
+    cudaStream_t st = (cudaStream_t)stream;
+#define IXB_P5_CASE(MM)                                                                         \
+    case MM:                                                                                    \
+        if (pl.xs) launch_p5<MM, 1>(p, x, bias, y, y_is_f32, slots, ticket, pl, st);            \
+        else launch_p5<MM, 0>(p, x, bias, y, y_is_f32, slots, ticket, pl, st);                  \
+        break;
+    switch (m_rows) {
+        IXB_P5_CASE(1) IXB_P5_CASE(2) IXB_P5_CASE(3) IXB_P5_CASE(4)
+        IXB_P5_CASE(5) IXB_P5_CASE(6) IXB_P5_CASE(7) IXB_P5_CASE(8)
+    }
+#undef IXB_P5_CASE
+    return launch_check("k_p5_gemv");
 }
 
 // ------------------------------------------------------- tensor-core small-M GEMM
