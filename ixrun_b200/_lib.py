@@ -22,7 +22,7 @@ SYMBOLS = (
     "ixb_decode", "ixb_gemv_scratch_bytes", "ixb_gemv", "ixb_gemv_static",
     "ixb_gemm_scratch_bytes", "ixb_gemm",
     "ixb_pack_workspace_bytes", "ixb_quantize_codes", "ixb_count_codes", "ixb_pack_codes",
-    "ixb_p5_build", "ixb_p5_decode", "ixb_p5_gemv_scratch_bytes", "ixb_p5_gemv",
+    "ixb_p5_blocks", "ixb_p5_build", "ixb_p5_decode", "ixb_p5_gemv_scratch_bytes", "ixb_p5_gemv",
 )
 
 
@@ -48,8 +48,8 @@ class P5Struct(C.Structure):
     """Mirror of ``struct ixb_p5``."""
 
     _fields_ = [
-        ("w03", C.c_void_p), ("w4", C.c_void_p), ("esc_off", C.c_void_p), ("esc", C.c_void_p),
-        ("n_esc", C.c_int64), ("scale", C.c_void_p), ("out_f", C.c_int64), ("in_f", C.c_int64),
+        ("w03", C.c_void_p), ("w4", C.c_void_p), ("row_off", C.c_void_p), ("esc_col", C.c_void_p),
+        ("esc_val", C.c_void_p), ("n_esc", C.c_int64), ("scale", C.c_void_p), ("out_f", C.c_int64), ("in_f", C.c_int64),
     ]
 
 
@@ -93,7 +93,9 @@ def lib():
     L.ixb_pack_codes.restype = C.c_int
     L.ixb_pack_codes.argtypes = [vp, C.POINTER(Packed), vp, vp, vp]
     L.ixb_p5_build.restype = C.c_int
-    L.ixb_p5_build.argtypes = [vp, i64, vp, vp, vp, vp, i64, vp, sz, vp]
+    L.ixb_p5_blocks.restype = i64
+    L.ixb_p5_blocks.argtypes = [i64, i64]
+    L.ixb_p5_build.argtypes = [vp, i64, i64, vp, vp, vp, vp, vp, i64, vp, sz, vp]
     L.ixb_p5_decode.restype = C.c_int
     L.ixb_p5_decode.argtypes = [C.POINTER(P5Struct), vp, C.c_int, vp]
     L.ixb_p5_gemv_scratch_bytes.restype = sz

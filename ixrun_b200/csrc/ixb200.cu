@@ -387,13 +387,7 @@ k_gemv(Streams s, const int32_t *__restrict__ q1, const int32_t *__restrict__ q2
             // float4 index of this word's first chunk in the swizzled fp32 copy of x
             const uint32_t xstride = ((s.in_f + 1023u) / 1024u) * 1024u;
             const uint32_t xword = (k0 >> 10) * 256u + ((k0 >> 5) & 31u);
-#if defined(IXB_DEBUG_SKIP) && IXB_DEBUG_SKIP == 1
-            { float partx[M]; for (int m = 0; m < M; ++m) partx[m] = __uint_as_float(w.bit1 + w.bit2 + w.byte3 + w.m2); if (__all_sync(0xffffffffu, true)) { for (int m = 0; m < M; ++m) acc[m] += partx[m]; } __syncwarp(); cur = nxt; a0 = a1; c0 = c1; a1 = a2; c1 = c2; continue; }
-#endif
             WordCursors c = word_cursors(w);
-#if defined(IXB_DEBUG_SKIP) && IXB_DEBUG_SKIP == 2
-            { float partx[M]; for (int m = 0; m < M; ++m) partx[m] = __uint_as_float(c.b1p[3] + c.b2p[3] + c.b3p[3] + c.nn[3] + c.max_l3 + c.b1p[1] + c.b2p[2]); if (__all_sync(0xffffffffu, true)) { for (int m = 0; m < M; ++m) acc[m] += partx[m]; } __syncwarp(); cur = nxt; a0 = a1; c0 = c1; a1 = a2; c1 = c2; continue; }
-#endif
             float part[M];
 #pragma unroll
             for (int m = 0; m < M; ++m) part[m] = 0.f;
@@ -739,38 +733,53 @@ static int to_p5(const ixb_p5 *t, P5 *p)
     if (t->out_f <= 0 || t->in_f <= 0) return fail(IXB_E_ARG, "bad shape");
     long long n = (long long)t->out_f * t->in_f;
     if (n > 800000000LL) return fail(IXB_E_UNSUPPORTED, "tensor too large");
-    if (!t->w03 || !t->w4 || !t->esc_off || !t->scale) return fail(IXB_E_ARG, "NULL P5 pointer");
-    if (t->n_esc && !t->esc) return fail(IXB_E_ARG, "outlier list is NULL");
+    if (t->in_f > 65536) return fail(IXB_E_UNSUPPORTED, "in_f=%lld does not fit the 16-bit outlier columns", (long long)t->in_f);
+    if (!t->w03 || !t->w4 || !t->row_off || !t->scale) return fail(IXB_E_ARG, "NULL P5 pointer");
+    if (t->n_esc && (!t->esc_col || !t->esc_val)) return fail(IXB_E_ARG, "outlier list is NULL");
     if (((uintptr_t)t->w03 & 15u) || ((uintptr_t)t->w4 & 3u)) return fail(IXB_E_ARG, "P5 planes are misaligned");
     p->w03 = (const uint4 *)t->w03;
     p->w4 = (const uint32_t *)t->w4;
-    p->esc_off = (const int32_t *)t->esc_off;
-    p->esc = (const uint16_t *)t->esc;
+    p->row_off = (const int32_t *)t->row_off;
+    p->esc_col = (const uint16_t *)t->esc_col;
+    p->esc_val = (const uint8_t *)t->esc_val;
     p->scale = (const __nv_bfloat16 *)t->scale;
-    p->n = (uint32_t)n;
     p->out_f = (uint32_t)t->out_f;
     p->in_f = (uint32_t)t->in_f;
+    p->rt = (p->out_f + kP5TileRows - 1) / kP5TileRows;
+    p->kb = (p->in_f + kP5TileCols - 1) / kP5TileCols;
     return IXB_OK;
 }
 
-extern "C" int ixb_p5_build(const int8_t *codes, int64_t n_elements, void *w03, void *w4, int32_t *esc_off,
-                            void *esc, int64_t n_esc, void *ws, size_t ws_bytes, ixb_stream_t stream)
+extern "C" int64_t ixb_p5_blocks(int64_t out_f, int64_t in_f)
 {
-    if (!codes || !w03 || !w4 || !esc_off || !ws || (n_esc && !esc)) return fail(IXB_E_ARG, "NULL pointer argument");
-    if (n_elements <= 0 || n_elements > 800000000LL) return fail(IXB_E_ARG, "bad element count");
-    uint32_t n = (uint32_t)n_elements, nb = (n + kBlk - 1) / kBlk, nq = (n + 255u) / 256u;
-    if (ws_bytes < (size_t)(nq + 1) * 4) return fail(IXB_E_SCRATCH, "P5 workspace too small");
+    if (out_f <= 0 || in_f <= 0) return 0;
+    return ((out_f + kP5TileRows - 1) / kP5TileRows) * ((in_f + kP5TileCols - 1) / kP5TileCols);
+}
+
+extern "C" int ixb_p5_build(const int8_t *codes, int64_t out_f, int64_t in_f, void *w03, void *w4, int32_t *row_off,
+                            void *esc_col, void *esc_val, int64_t n_esc, void *ws, size_t ws_bytes, ixb_stream_t stream)
+{
+    if (!codes || !w03 || !w4 || !row_off || !ws || (n_esc && (!esc_col || !esc_val)))
+        return fail(IXB_E_ARG, "NULL pointer argument");
+    if (out_f <= 0 || in_f <= 0 || out_f * in_f > 800000000LL) return fail(IXB_E_ARG, "bad shape");
+    if (in_f > 65536) return fail(IXB_E_UNSUPPORTED, "in_f=%lld does not fit the 16-bit outlier columns", (long long)in_f);
+    if (((uintptr_t)w03 & 15u) || ((uintptr_t)w4 & 3u)) return fail(IXB_E_ARG, "P5 planes are misaligned");
+    if (ws_bytes < (size_t)(out_f + 1) * 4) return fail(IXB_E_SCRATCH, "P5 workspace too small");
+    uint32_t rt = (uint32_t)((out_f + kP5TileRows - 1) / kP5TileRows), kb = (uint32_t)((in_f + kP5TileCols - 1) / kP5TileCols);
+    uint32_t nb = rt * kb;
     cudaStream_t st = (cudaStream_t)stream;
-    int32_t *qcnt = (int32_t *)ws;
+    int32_t *row_cnt = (int32_t *)ws;
     int rc;
-    IXB_CUDA(cudaMemsetAsync(qcnt, 0, (size_t)(nq + 1) * 4, st));
-    k_p5_plane<<<(nb + 7) / 8, 256, 0, st>>>(codes, n, (uint4 *)w03, (uint32_t *)w4, qcnt);
+    IXB_CUDA(cudaMemsetAsync(row_cnt, 0, (size_t)(out_f + 1) * 4, st));
+    k_p5_plane<<<(nb + 7) / 8, 256, 0, st>>>(codes, (uint32_t)out_f, (uint32_t)in_f, rt, kb, (uint4 *)w03, (uint32_t *)w4,
+                                             row_cnt);
     if ((rc = launch_check("k_p5_plane"))) return rc;
-    k_excl_scan<<<1, 1024, 0, st>>>(qcnt, esc_off, nq + 1);      // entry nq = total
+    k_excl_scan<<<1, 1024, 0, st>>>(row_cnt, row_off, (uint32_t)out_f + 1);      // entry out_f = total
     if ((rc = launch_check("k_excl_scan"))) return rc;
     if (n_esc) {
-        k_p5_esc<<<(nq + 7) / 8, 256, 0, st>>>(codes, n, esc_off, (uint16_t *)esc);
-        if ((rc = launch_check("k_p5_esc"))) return rc;
+        k_p5_csr<<<((uint32_t)out_f + 7) / 8, 256, 0, st>>>(codes, (uint32_t)out_f, (uint32_t)in_f, row_off,
+                                                            (uint16_t *)esc_col, (uint8_t *)esc_val);
+        if ((rc = launch_check("k_p5_csr"))) return rc;
     }
     return IXB_OK;
 }
@@ -780,33 +789,40 @@ extern "C" int ixb_p5_decode(const ixb_p5 *t, void *out, int out_kind, ixb_strea
     P5 p;
     int rc = to_p5(t, &p);
     if (rc) return rc;
-    if (!out || ((uintptr_t)out & 15u)) return fail(IXB_E_ARG, "output is NULL or not 16-byte aligned");
-    uint32_t nb = (p.n + kBlk - 1) / kBlk;
+    if (!out) return fail(IXB_E_ARG, "output is NULL");
+    if (out_kind != 0 && out_kind != 1) return fail(IXB_E_ARG, "out_kind must be 0 or 1");
+    uint32_t nb = p.rt * p.kb;
     cudaStream_t st = (cudaStream_t)stream;
-    if (out_kind == 0) k_p5_decode<0><<<(nb + 7) / 8, 256, 0, st>>>(p, out);
-    else if (out_kind == 1) k_p5_decode<1><<<(nb + 7) / 8, 256, 0, st>>>(p, out);
-    else return fail(IXB_E_ARG, "out_kind must be 0 or 1");
-    return launch_check("k_p5_decode");
+    if (out_kind == 0) k_p5_decode_plane<0><<<(nb + 7) / 8, 256, 0, st>>>(p, out);
+    else k_p5_decode_plane<1><<<(nb + 7) / 8, 256, 0, st>>>(p, out);
+    if ((rc = launch_check("k_p5_decode_plane"))) return rc;
+    if (t->n_esc) {
+        if (out_kind == 0) k_p5_decode_esc<0><<<(p.out_f + 7) / 8, 256, 0, st>>>(p, out);
+        else k_p5_decode_esc<1><<<(p.out_f + 7) / 8, 256, 0, st>>>(p, out);
+        rc = launch_check("k_p5_decode_esc");
+    }
+    return rc;
 }
 
-struct P5Plan { uint32_t nb, grid, bpw, pmax, xstride, smem, xs; };
+struct P5Plan { uint32_t nb, grid, bpw, xstride, smem, xs; size_t osum_bytes, slot_bytes; };
 
 static P5Plan make_p5_plan(uint32_t out_f, uint32_t in_f, uint32_t m_rows)
 {
     P5Plan p;
-    unsigned long long n = (unsigned long long)out_f * in_f;
-    p.nb = (uint32_t)((n + kBlk - 1) / kBlk);
+    uint32_t rt = (out_f + kP5TileRows - 1) / kP5TileRows, kb = (in_f + kP5TileCols - 1) / kP5TileCols;
+    p.nb = rt * kb;
     uint32_t sms = (uint32_t)num_sms();
     uint32_t want = (p.nb + kP5Warps - 1) / kP5Warps;
     p.grid = want < sms ? want : sms;
     if (!p.grid) p.grid = 1;
     p.bpw = (p.nb + p.grid * kP5Warps - 1) / (p.grid * kP5Warps);
-    uint32_t row_blocks = (in_f + kBlk - 1) / kBlk + 1;
-    p.pmax = (row_blocks + p.bpw - 1) / p.bpw + 1;
-    p.xstride = ((in_f + 1023u) / 1024u) * 1024u;
-    uint32_t xbytes = m_rows * p.xstride * 4u;
-    p.xs = xbytes <= 200u * 1024u;
-    p.smem = p.xs ? xbytes : 0u;
+    p.xstride = kb * kP5TileCols + 8u;
+    uint32_t parts = kP5Warps * 2u * 32u * (uint32_t)sizeof(float4);
+    uint32_t xbytes = m_rows * p.xstride * 2u;
+    p.xs = parts + xbytes <= 216u * 1024u;
+    p.smem = parts + (p.xs ? xbytes : 0u);
+    p.osum_bytes = (((size_t)m_rows * out_f * sizeof(float)) + 255u) & ~(size_t)255u;
+    p.slot_bytes = (size_t)p.grid * 2u * 32u * sizeof(float4);
     return p;
 }
 
@@ -814,20 +830,20 @@ extern "C" size_t ixb_p5_gemv_scratch_bytes(int64_t out_f, int64_t in_f, int64_t
 {
     if (out_f <= 0 || in_f <= 0 || m_rows <= 0) return 0;
     P5Plan p = make_p5_plan((uint32_t)out_f, (uint32_t)in_f, (uint32_t)m_rows);
-    return 256 + (size_t)m_rows * (size_t)out_f * p.pmax * sizeof(float);
+    return 256 + p.osum_bytes + p.slot_bytes;
 }
 
-template <int M, int XS>
-static void launch_p5(const P5 &p, const void *x, const void *bias, void *y, int y_f32, float *slots, uint32_t *ticket,
-                      const P5Plan &pl, cudaStream_t st)
+template <int XS>
+static void launch_p5(const P5 &p, const void *x, uint32_t m_rows, const void *bias, void *y, int y_f32, const float *osum,
+                      float4 *slots, uint32_t *ticket, const P5Plan &pl, cudaStream_t st)
 {
     static bool attr_set = false;
     if (!attr_set) {
-        cudaFuncSetAttribute(k_p5_gemv<M, XS>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        cudaFuncSetAttribute(k_p5_mma<XS>, cudaFuncAttributeMaxDynamicSharedMemorySize, 216 * 1024);
         attr_set = true;
     }
-    k_p5_gemv<M, XS><<<pl.grid, kP5Threads, pl.smem, st>>>(p, (const __nv_bfloat16 *)x, (const __nv_bfloat16 *)bias, y,
-                                                           y_f32, slots, ticket, pl.nb, pl.bpw, pl.pmax, pl.xstride);
+    k_p5_mma<XS><<<pl.grid, kP5Threads, pl.smem, st>>>(p, (const __nv_bfloat16 *)x, m_rows, (const __nv_bfloat16 *)bias, y,
+                                                       y_f32, osum, slots, ticket, pl.nb, pl.bpw, pl.xstride);
 }
 
 extern "C" int ixb_p5_gemv(const ixb_p5 *t, const void *x, int64_t m_rows, const void *bias, void *y, int y_is_f32,
@@ -838,24 +854,33 @@ extern "C" int ixb_p5_gemv(const ixb_p5 *t, const void *x, int64_t m_rows, const
     if (rc) return rc;
     if (!x || !y || !scratch) return fail(IXB_E_ARG, "NULL pointer argument");
     if (m_rows < 1 || m_rows > 8) return fail(IXB_E_UNSUPPORTED, "m_rows=%lld outside 1..8", (long long)m_rows);
-    if (p.in_f % 32u) return fail(IXB_E_UNSUPPORTED, "in_f=%u is not a multiple of 32", p.in_f);
     if ((uintptr_t)x & 15u) return fail(IXB_E_ARG, "x is not 16-byte aligned");
+    if ((uintptr_t)scratch & 15u) return fail(IXB_E_ARG, "scratch is not 16-byte aligned");
     if (scratch_bytes < ixb_p5_gemv_scratch_bytes(p.out_f, p.in_f, m_rows)) return fail(IXB_E_SCRATCH, "gemv scratch too small");
     P5Plan pl = make_p5_plan(p.out_f, p.in_f, (uint32_t)m_rows);
+    if (!pl.xs && (p.in_f % kP5TileCols))
+        return fail(IXB_E_UNSUPPORTED, "in_f=%u: activations too large for shared memory need in_f %% 64 == 0", p.in_f);
     uint32_t *ticket = (uint32_t *)scratch;
-    float *slots = (float *)((char *)scratch + 256);
+    float *osum = (float *)((char *)scratch + 256);
+    float4 *slots = (float4 *)((char *)scratch + 256 + pl.osum_bytes);
     cudaStream_t st = (cudaStream_t)stream;
-#define IXB_P5_CASE(MM)                                                                         \
-    case MM:                                                                                    \
-        if (pl.xs) launch_p5<MM, 1>(p, x, bias, y, y_is_f32, slots, ticket, pl, st);            \
-        else launch_p5<MM, 0>(p, x, bias, y, y_is_f32, slots, ticket, pl, st);                  \
+    {
+        uint32_t blocks = (p.out_f + 7u) / 8u, cap = (uint32_t)num_sms() * 8u;
+        if (blocks > cap) blocks = cap;
+#define IXB_P5_OUT(MM)                                                                                        \
+    case MM:                                                                                                  \
+        k_p5_outliers<MM><<<blocks, 256, 0, st>>>(p, (const __nv_bfloat16 *)x, 0u, osum);                     \
         break;
-    switch (m_rows) {
-        IXB_P5_CASE(1) IXB_P5_CASE(2) IXB_P5_CASE(3) IXB_P5_CASE(4)
-        IXB_P5_CASE(5) IXB_P5_CASE(6) IXB_P5_CASE(7) IXB_P5_CASE(8)
+        switch (m_rows) {
+            IXB_P5_OUT(1) IXB_P5_OUT(2) IXB_P5_OUT(3) IXB_P5_OUT(4)
+            IXB_P5_OUT(5) IXB_P5_OUT(6) IXB_P5_OUT(7) IXB_P5_OUT(8)
+        }
+#undef IXB_P5_OUT
+        if ((rc = launch_check("k_p5_outliers"))) return rc;
     }
-#undef IXB_P5_CASE
-    return launch_check("k_p5_gemv");
+    if (pl.xs) launch_p5<1>(p, x, (uint32_t)m_rows, bias, y, y_is_f32, osum, slots, ticket, pl, st);
+    else launch_p5<0>(p, x, (uint32_t)m_rows, bias, y, y_is_f32, osum, slots, ticket, pl, st);
+    return launch_check("k_p5_mma");
 }
 
 // ------------------------------------------------------- tensor-core small-M GEMM

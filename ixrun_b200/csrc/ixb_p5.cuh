@@ -2,385 +2,453 @@
 //
 // The reference's (3,5,8) streams (ixrun/quantize.py:80-96) are kept as the
 // on-disk / interchange format.  At deploy time they can be transcoded, on the
-// GPU and losslessly on the int8 codes, into a layout with fixed addressing:
+// GPU and losslessly on the int8 codes, into a layout with fixed addressing in
+// which nothing but a short outlier list is data dependent:
 //
-//   plane   every element owns a 5-bit field, 32 fields = 160 bits per bitmap
-//           word, stored as one uint4 + one uint32 per 32 elements.  Levels 1
-//           and 2 (|code| <= 15) store code + 15; a level-3 element stores 15
-//           (code 0, weight 0) as a placeholder.
-//   esc     the level-3 elements as a sparse list per 256-element quarter
-//           block: 16-bit entries  (position in quarter : 8) | (code + 127) << 8,
-//           in element order, with an int32 offset table per quarter block.
+//   plane   every element owns a 5-bit field: code + 15 for |code| <= 15
+//           (levels 1 and 2), 15 (code 0, weight 0) as a placeholder for a
+//           level-3 element.  The matrix is cut into tiles of 16 rows x 64
+//           columns ("blocks", 1024 elements, padded with placeholders at the
+//           ragged edges); one warp owns a block, a lane 32 of its fields in
+//           five 32-bit words (one uint4 + one uint32), ordered so that after
+//           one mask, one subtract and one multiply per PAIR of elements the
+//           lane's registers ARE the A fragments of four
+//           mma.sync.m16n8k16 (bf16) instructions -- see p5_elem().
+//   esc     the level-3 elements as a CSR list: row_off[out_f + 1], and per
+//           entry a 16-bit column and an 8-bit code + 127, sorted by column.
 //
-// Size: 5 + 16 * P(level 3) + 0.125 bits per weight, i.e. 5.60 bpw for the
-// benchmark distribution against 5.44 for the reference streams.  Nothing is
-// data dependent any more except the short outlier list, so a warp decodes 1024
-// weights with ~4 instructions per weight instead of ~34.
+// Size: 5 + 24 * P(level 3) bits per weight (+ 4 bytes per row), i.e. ~5.72 bpw
+// for the benchmark distribution against 5.44 for the reference streams.
+//
+// y = W x then is: a sparse pass over the outliers (k_p5_outliers, fp32 FMAs,
+// one warp per row) followed by the plane pass (k_p5_mma), which turns fields
+// into bf16 weights bf16(code * scale) -- the reference's dequantised weights,
+// bit for bit (ixrun/quantize.py:201-204) -- and feeds them to the tensor cores
+// with the activations as the B operand: up to 8 activation rows cost the same
+// as one.  Products are exact, accumulation is fp32.
 #pragma once
 #include "ixb_common.cuh"
 
 namespace ixb {
 
+constexpr int kP5TileRows = 16;
+constexpr int kP5TileCols = 64;
+
 struct P5 {
-    const uint4 *w03;          // [nb * 32] fields 0..24 and the low 3 bits of field 25 of every word
-    const uint32_t *w4;        // [nb * 32] the remaining 32 bits
-    const int32_t *esc_off;    // [nq + 1] first outlier entry of every 256-element quarter block
-    const uint16_t *esc;       // [n3] outlier entries
+    const uint4 *w03;          // [nb * 32] plane words 0..3 of every lane of every block
+    const uint32_t *w4;        // [nb * 32] plane word 4
+    const int32_t *row_off;    // [out_f + 1] first outlier entry of every row
+    const uint16_t *esc_col;   // [n_esc] column of the entry
+    const uint8_t *esc_val;    // [n_esc] code + 127
     const __nv_bfloat16 *scale;
-    uint32_t n, out_f, in_f;
+    uint32_t out_f, in_f;
+    uint32_t rt, kb;           // row tiles, column blocks per row tile; nb = rt * kb
 };
 
-// ------------------------------------------------------------------ build ---
-// codes -> plane words + outlier count per quarter block (one warp per 1024 block, lane = word)
-__global__ void __launch_bounds__(256)
-k_p5_plane(const int8_t *__restrict__ codes, uint32_t n, uint4 *w03, uint32_t *w4, int32_t *qcnt)
+// ----------------------------------------------------------- field layout ---
+// Lane l of a block: g = l >> 2, t = l & 3.  Its 16 pairs p = 4 j + q (j = 0..3 the mma, q = 0..3 the A register):
+//   row    = 16 R + g + 8 (q & 1)
+//   column = 64 kb + 16 t + 4 j + 2 (q >> 1) + h          (h = 0 low half, 1 high half of the register)
+// i.e. the k index of mma j is permuted so that a lane needs the 16 consecutive activations 16 t .. 16 t + 15.
+// Pair p < 15 lives in word p / 3 at bit 5 (p % 3) (low element) and 16 + 5 (p % 3) (high element);
+// pair 15 is spread over the spare bits: bit i of its low / high field is bit 15 / 31 of word i.
+__device__ __forceinline__ void p5_elem(int lane, int p, int h, uint32_t &row_in_tile, uint32_t &col_in_tile)
 {
-    uint32_t nb = (n + kBlk - 1) / kBlk;
-    uint32_t b = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-    int lane = threadIdx.x & 31;
-    if (b >= nb) return;
-    uint32_t e0 = (b * 32u + lane) * 32u;
-    uint32_t w[5] = {0, 0, 0, 0, 0};
-    uint32_t n_esc = 0;
-#pragma unroll
-    for (int i = 0; i < 32; ++i) {
-        int c = e0 + i < n ? (int)codes[e0 + i] : 0;
-        bool out = c > 15 || c < -15;
-        n_esc += out;
-        uint32_t f = out ? 15u : (uint32_t)(c + 15);
-        const int bit = 5 * i, k = bit >> 5, s = bit & 31;
-        w[k] |= f << s;
-        if (s > 27) w[k + 1] |= f >> (32 - s);
-    }
-    w03[b * 32u + lane] = make_uint4(w[0], w[1], w[2], w[3]);
-    w4[b * 32u + lane] = w[4];
-    // 8 lanes share a quarter block
-    n_esc += __shfl_xor_sync(0xffffffffu, n_esc, 1);
-    n_esc += __shfl_xor_sync(0xffffffffu, n_esc, 2);
-    n_esc += __shfl_xor_sync(0xffffffffu, n_esc, 4);
-    uint32_t q = b * 4u + (lane >> 3);
-    if ((lane & 7) == 0 && q * 256u < n) qcnt[q] = (int32_t)n_esc;
+    int g = lane >> 2, t = lane & 3, j = p >> 2, q = p & 3;
+    row_in_tile = (uint32_t)(g + 8 * (q & 1));
+    col_in_tile = (uint32_t)(16 * t + 4 * j + 2 * (q >> 1) + h);
 }
 
-// outlier entries, in element order (one warp per quarter block, lane = 8 elements)
-__global__ void __launch_bounds__(256)
-k_p5_esc(const int8_t *__restrict__ codes, uint32_t n, const int32_t *__restrict__ esc_off, uint16_t *esc)
+__device__ __forceinline__ void p5_put(uint32_t (&w)[5], int p, int h, uint32_t f)
 {
-    uint32_t nq = (n + 255u) / 256u;
-    uint32_t q = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-    int lane = threadIdx.x & 31;
-    if (q >= nq) return;
-    uint32_t e0 = q * 256u + lane * 8u;
-    int c[8];
-    uint32_t cnt = 0;
+    if (p < 15) {
+        w[p / 3] |= f << (5 * (p % 3) + 16 * h);
+    } else {
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-        c[i] = e0 + i < n ? (int)codes[e0 + i] : 0;
-        cnt += (c[i] > 15 || c[i] < -15);
+        for (int i = 0; i < 5; ++i) w[i] |= ((f >> i) & 1u) << (15 + 16 * h);
     }
-    uint32_t at = (uint32_t)esc_off[q] + warp_incl_scan(cnt, lane) - cnt;
+}
+
+__device__ __forceinline__ uint32_t p5_get(const uint32_t (&w)[5], int p, int h)
+{
+    if (p < 15) return (w[p / 3] >> (5 * (p % 3) + 16 * h)) & 31u;
+    uint32_t f = 0;
 #pragma unroll
-    for (int i = 0; i < 8; ++i)
-        if (c[i] > 15 || c[i] < -15) esc[at++] = (uint16_t)((lane * 8u + i) | ((uint32_t)(c[i] + 127) << 8));
+    for (int i = 0; i < 5; ++i) f |= ((w[i] >> (15 + 16 * h)) & 1u) << i;
+    return f;
+}
+
+// ------------------------------------------------------------------ build ---
+// codes [out_f, in_f] -> plane words, and the number of outliers of every row (row_cnt, zeroed by the caller)
+__global__ void __launch_bounds__(256)
+k_p5_plane(const int8_t *__restrict__ codes, uint32_t out_f, uint32_t in_f, uint32_t rt, uint32_t kb,
+           uint4 *w03, uint32_t *w4, int32_t *row_cnt)
+{
+    uint32_t b = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    int lane = threadIdx.x & 31;
+    if (b >= rt * kb) return;
+    uint32_t R = b / kb, kbi = b - R * kb;
+    int g = lane >> 2, t = lane & 3;
+    uint32_t w[5] = {0, 0, 0, 0, 0};
+    uint32_t n_out[2] = {0, 0};
+#pragma unroll
+    for (int p = 0; p < 16; ++p) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            uint32_t r, c;
+            p5_elem(lane, p, h, r, c);
+            uint32_t row = R * kP5TileRows + r, col = kbi * kP5TileCols + c;
+            int code = (row < out_f && col < in_f) ? (int)codes[(size_t)row * in_f + col] : 0;
+            bool out = code > 15 || code < -15;
+            n_out[(p & 1)] += out;                  // q & 1 selects row g / g + 8
+            p5_put(w, p, h, out ? 15u : (uint32_t)(code + 15));
+        }
+    }
+    w03[(size_t)b * 32u + lane] = make_uint4(w[0], w[1], w[2], w[3]);
+    w4[(size_t)b * 32u + lane] = w[4];
+#pragma unroll
+    for (int s = 0; s < 2; ++s) {
+        uint32_t v = n_out[s];
+        v += __shfl_xor_sync(0xffffffffu, v, 1);
+        v += __shfl_xor_sync(0xffffffffu, v, 2);
+        uint32_t row = R * kP5TileRows + g + 8 * s;
+        if (t == 0 && v && row < out_f) atomicAdd(row_cnt + row, (int32_t)v);     // integer count: order does not matter
+    }
+}
+
+// outlier entries of every row in column order (one warp per row)
+__global__ void __launch_bounds__(256)
+k_p5_csr(const int8_t *__restrict__ codes, uint32_t out_f, uint32_t in_f, const int32_t *__restrict__ row_off,
+         uint16_t *esc_col, uint8_t *esc_val)
+{
+    uint32_t row = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    int lane = threadIdx.x & 31;
+    if (row >= out_f) return;
+    uint32_t at = (uint32_t)row_off[row];
+    const int8_t *src = codes + (size_t)row * in_f;
+    for (uint32_t k0 = 0; k0 < in_f; k0 += 32) {
+        uint32_t k = k0 + lane;
+        int c = k < in_f ? (int)src[k] : 0;
+        bool out = c > 15 || c < -15;
+        uint32_t m = __ballot_sync(0xffffffffu, out);
+        if (out) {
+            uint32_t i = at + __popc(m & ((1u << lane) - 1u));
+            esc_col[i] = (uint16_t)k;
+            esc_val[i] = (uint8_t)(c + 127);
+        }
+        at += __popc(m);
+    }
 }
 
 // ---------------------------------------------------------------- decode ----
-// field i of a word's 160-bit string, as an integer 0..31
-__device__ __forceinline__ uint32_t p5_field(const uint32_t (&w)[5], int i)
-{
-    const int bit = 5 * i, k = bit >> 5, s = bit & 31;
-    uint32_t v = w[k] >> s;
-    if (s > 27) v |= w[k + 1] << (32 - s);
-    return v & 31u;
-}
-
-// P5 -> int8 codes (OUT 0) or bf16 weights (OUT 1); one warp per block
+// plane -> int8 codes (OUT 0) or bf16 weights (OUT 1), row major [out_f, in_f]; outliers come out as 0 here
 template <int OUT>
-__global__ void __launch_bounds__(256) k_p5_decode(P5 p, void *out)
+__global__ void __launch_bounds__(256) k_p5_decode_plane(P5 p, void *out)
 {
-    uint32_t nb = (p.n + kBlk - 1) / kBlk;
     uint32_t b = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     int lane = threadIdx.x & 31;
-    if (b >= nb) return;
+    if (b >= p.rt * p.kb) return;
+    uint32_t R = b / p.kb, kbi = b - R * p.kb;
     float sc = __bfloat162float(*p.scale);
-    uint4 a = p.w03[b * 32u + lane];
-    uint32_t w[5] = {a.x, a.y, a.z, a.w, p.w4[b * 32u + lane]};
-    uint32_t e0 = (b * 32u + lane) * 32u;
-    uint32_t r[OUT == 0 ? 8 : 16];
+    uint4 a = p.w03[(size_t)b * 32u + lane];
+    uint32_t w[5] = {a.x, a.y, a.z, a.w, p.w4[(size_t)b * 32u + lane]};
 #pragma unroll
-    for (int i = 0; i < (OUT == 0 ? 8 : 16); ++i) r[i] = 0;
+    for (int pr = 0; pr < 16; ++pr) {
 #pragma unroll
-    for (int i = 0; i < 32; ++i) {
-        int c = (int)p5_field(w, i) - 15;
-        if (OUT == 0) r[i >> 2] |= (uint32_t)(c & 0xff) << (8 * (i & 3));
-        else r[i >> 1] |= (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn((float)c * sc)) << (16 * (i & 1));
-    }
-    if (e0 + 32u <= p.n) {
-        uint4 *o = (uint4 *)((char *)out + (size_t)e0 * (OUT == 0 ? 1 : 2));
-#pragma unroll
-        for (int j = 0; j < (OUT == 0 ? 2 : 4); ++j) o[j] = make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
-    } else {
-        for (uint32_t i = 0; e0 + i < p.n; ++i) {
-            if (OUT == 0) ((int8_t *)out)[e0 + i] = (int8_t)((r[i >> 2] >> (8 * (i & 3))) & 0xff);
-            else ((uint16_t *)out)[e0 + i] = (uint16_t)((r[i >> 1] >> (16 * (i & 1))) & 0xffff);
+        for (int h = 0; h < 2; ++h) {
+            uint32_t r, c;
+            p5_elem(lane, pr, h, r, c);
+            uint32_t row = R * kP5TileRows + r, col = kbi * kP5TileCols + c;
+            if (row >= p.out_f || col >= p.in_f) continue;
+            int code = (int)p5_get(w, pr, h) - 15;
+            size_t o = (size_t)row * p.in_f + col;
+            if (OUT == 0) ((int8_t *)out)[o] = (int8_t)code;
+            else ((__nv_bfloat16 *)out)[o] = __float2bfloat16_rn((float)code * sc);
         }
-    }
-    __syncwarp();
-    // the block's outliers overwrite their placeholders (all plane stores of this warp are done)
-    uint32_t q0 = b * 4u, nq = (p.n + 255u) / 256u;
-    int32_t o0 = p.esc_off[q0], o1 = p.esc_off[min(q0 + 1, nq)], o2 = p.esc_off[min(q0 + 2, nq)],
-            o3 = p.esc_off[min(q0 + 3, nq)], o4 = p.esc_off[min(q0 + 4, nq)];
-    for (int32_t j = o0 + lane; j < o4; j += 32) {
-        uint32_t ent = p.esc[j];
-        uint32_t quarter = (uint32_t)(j >= o1) + (uint32_t)(j >= o2) + (uint32_t)(j >= o3);
-        uint32_t e = b * (uint32_t)kBlk + quarter * 256u + (ent & 255u);
-        int c = (int)(ent >> 8) - 127;
-        if (OUT == 0) ((int8_t *)out)[e] = (int8_t)c;
-        else ((__nv_bfloat16 *)out)[e] = __float2bfloat16_rn((float)c * sc);
     }
 }
 
-// ------------------------------------------------------------------ gemv ----
+// the outliers overwrite their placeholders (launched after k_p5_decode_plane on the same stream)
+template <int OUT>
+__global__ void __launch_bounds__(256) k_p5_decode_esc(P5 p, void *out)
+{
+    uint32_t row = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    int lane = threadIdx.x & 31;
+    if (row >= p.out_f) return;
+    float sc = __bfloat162float(*p.scale);
+    for (int32_t j = p.row_off[row] + lane; j < p.row_off[row + 1]; j += 32) {
+        int code = (int)p.esc_val[j] - 127;
+        size_t o = (size_t)row * p.in_f + p.esc_col[j];
+        if (OUT == 0) ((int8_t *)out)[o] = (int8_t)code;
+        else ((__nv_bfloat16 *)out)[o] = __float2bfloat16_rn((float)code * sc);
+    }
+}
+
+// -------------------------------------------------------------- outliers ----
+// osum[m][row] = sum over the row's outliers of x[m0 + m][col] * bf16(code * scale), m < MC   (one warp per row)
+template <int MC>
+__global__ void __launch_bounds__(256)
+k_p5_outliers(P5 p, const __nv_bfloat16 *__restrict__ x, uint32_t m0, float *__restrict__ osum)
+{
+    const int lane = threadIdx.x & 31;
+    const uint32_t n_warps = (gridDim.x * blockDim.x) >> 5;
+    uint32_t sb = (uint32_t)__bfloat16_as_ushort(*p.scale);
+    const uint32_t s2 = sb | (sb << 16);
+    const unsigned short *xu = (const unsigned short *)x;
+    for (uint32_t row = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; row < p.out_f; row += n_warps) {
+        float acc[MC];
+#pragma unroll
+        for (int m = 0; m < MC; ++m) acc[m] = 0.f;
+        const int32_t end = __ldg(p.row_off + row + 1);
+        for (int32_t j = __ldg(p.row_off + row) + lane; j < end; j += 32) {
+            uint32_t col = __ldg(p.esc_col + j);
+            float cf = (float)((int)__ldg(p.esc_val + j) - 127);
+            uint32_t wv;       // upper half: bf16(code * scale); lower half: bf16(0 * scale) = 0
+            asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(wv) : "r"(__float_as_uint(cf)), "r"(s2));
+#pragma unroll
+            for (int m = 0; m < MC; ++m) {
+                float xf = __uint_as_float((uint32_t)__ldg(xu + (size_t)(m0 + m) * p.in_f + col) << 16);
+                acc[m] = fmaf(xf, __uint_as_float(wv), acc[m]);
+            }
+        }
+#pragma unroll
+        for (int m = 0; m < MC; ++m) {
+            float v = warp_sum(acc[m]);
+            if (lane == 0) osum[(size_t)(m0 + m) * p.out_f + row] = v;
+        }
+    }
+}
+
+// ------------------------------------------------------------- plane pass ---
 constexpr int kP5Threads = 1024;
 constexpr int kP5Warps = kP5Threads / 32;
 
-// One field of a register-resident word, straight to the fp32 bit pattern of bf16(code * scale):
-// the field is masked into the mantissa of 2^23 (it sits at bit SH <= 18 of SRC), one FFMA turns that
-// into the exact float code, one packed bf16 multiply rounds code * scale like the reference does.
-#define IXB_P5_W(SRC, SH, OUT)                                                                              \
-    {                                                                                                       \
-        uint32_t f_ = ((SRC) & (31u << (SH))) | 0x4B000000u;                                                \
-        float c_ = fmaf(__uint_as_float(f_), 1.0f / (float)(1u << (SH)), -(8388608.0f / (float)(1u << (SH)) + 15.0f)); \
-        asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(OUT) : "r"(__float_as_uint(c_)), "r"(s2));                   \
-    }
-
-// XS = 1: activations as swizzled fp32 in shared memory; XS = 0: bf16 straight from global memory (L1/L2)
-template <int M, int XS>
-__global__ void __launch_bounds__(kP5Threads, 1)
-k_p5_gemv(P5 p, const __nv_bfloat16 *__restrict__ x, const __nv_bfloat16 *__restrict__ bias, void *y, int y_f32,
-          float *slots, uint32_t *ticket, uint32_t nb, uint32_t bpw, uint32_t pmax, uint32_t xstride)
+// (SRC & 0x001F001F) | 0x43004300: the two fields of a pair as the bf16 values 128 + field
+__device__ __forceinline__ uint32_t p5_pair_raw(uint32_t src, uint32_t magic)
 {
-    extern __shared__ __align__(16) float p5_xs[];     // M rows of x as fp32, swizzled like in k_gemv
+    uint32_t v;
+    asm("lop3.b32 %0, %1, 0x001F001F, %2, 0xEA;" : "=r"(v) : "r"(src), "r"(magic));
+    return v;
+}
+// (SRC & MASK) | ACC
+__device__ __forceinline__ uint32_t p5_and_or(uint32_t src, uint32_t mask, uint32_t acc)
+{
+    uint32_t v;
+    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(v) : "r"(src), "r"(mask), "r"(acc));
+    return v;
+}
+// two bf16 values 128 + field -> two bf16 weights bf16((field - 15) * scale): the subtraction is exact,
+// the multiplication rounds once, like the reference's bf16 product code * scale
+__device__ __forceinline__ uint32_t p5_pair_weight(uint32_t v, uint32_t one2, uint32_t neg2, uint32_t s2)
+{
+    uint32_t d, w;
+    asm("fma.rn.bf16x2 %0, %1, %2, %3;" : "=r"(d) : "r"(v), "r"(one2), "r"(neg2));
+    asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(w) : "r"(d), "r"(s2));
+    return w;
+}
+
+__device__ __forceinline__ void p5_mma(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                       uint32_t b1)
+{
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// Final value of a row tile's C fragment image: lane (g, t) holds rows g, g + 8 and activation rows 2 t, 2 t + 1.
+__device__ __forceinline__ void p5_store_tile(const P5 &p, uint32_t R, int lane, const float (&c)[4], uint32_t m_rows,
+                                              const float *__restrict__ osum, const __nv_bfloat16 *__restrict__ bias,
+                                              void *y, int y_f32)
+{
+    const int g = lane >> 2, t = lane & 3;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        uint32_t m = 2u * t + (i & 1), row = R * kP5TileRows + g + 8 * (i >> 1);
+        if (m >= m_rows || row >= p.out_f) continue;
+        size_t o = (size_t)m * p.out_f + row;
+        float v = c[i] + osum[o];
+        if (y_f32) {
+            ((float *)y)[o] = bias ? v + __bfloat162float(bias[row]) : v;
+        } else {
+            __nv_bfloat16 hv = __float2bfloat16_rn(v);
+            if (bias) hv = __hadd(hv, bias[row]);
+            ((__nv_bfloat16 *)y)[o] = hv;
+        }
+    }
+}
+
+// One warp = one contiguous run of bpw blocks in (row tile, column block) order; a CTA = 32 consecutive runs.
+// Row tiles that a run covers completely are written straight to y.  Partial tiles go to shared memory, are
+// summed per CTA in warp order, and tiles shared between CTAs go through cta_slots and are finished, in CTA
+// order, by whichever CTA takes the last ticket -- no floating-point atomics anywhere, so results are
+// reproducible.  XS = 1: activations staged in shared memory (bf16, padded rows); XS = 0: read from global.
+template <int XS>
+__global__ void __launch_bounds__(kP5Threads, 1)
+k_p5_mma(P5 p, const __nv_bfloat16 *__restrict__ x, uint32_t m_rows, const __nv_bfloat16 *__restrict__ bias, void *y,
+         int y_f32, const float *__restrict__ osum, float4 *cta_slots, uint32_t *ticket, uint32_t nb, uint32_t bpw,
+         uint32_t xstride)
+{
+    extern __shared__ __align__(16) unsigned char p5_smem[];
+    float4 *parts = (float4 *)p5_smem;                                  // [warp][2][32 lanes]
+    __nv_bfloat16 *xs = (__nv_bfloat16 *)(p5_smem + kP5Warps * 2 * 32 * sizeof(float4));   // [m_rows][xstride]
     __shared__ uint32_t is_last;
-    uint32_t s2;
-    {
-        uint32_t sb = (uint32_t)__bfloat16_as_ushort(*p.scale);
-        s2 = sb | (sb << 16);
-        if (XS) {
-            for (uint32_t i = threadIdx.x; i < (uint32_t)M * p.in_f; i += blockDim.x) {
-                uint32_t m = i / p.in_f, k = i - m * p.in_f;
-                uint32_t pos = ((k >> 10) * 8u + ((k & 31u) >> 2)) * 128u + ((k >> 5) & 31u) * 4u + (k & 3u);
-                p5_xs[m * xstride + pos] = __bfloat162float(x[i]);
+
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    const int g = lane >> 2, t = lane & 3;
+    const uint32_t KB = p.kb;
+    uint32_t sb = (uint32_t)__bfloat16_as_ushort(*p.scale);
+    const uint32_t s2 = sb | (sb << 16);
+    uint32_t magic, one2, neg2;
+    // opaque to the optimiser, so that they stay in registers as LOP3 / HFMA2 operands
+    asm volatile("mov.b32 %0, 0x43004300;" : "=r"(magic));
+    asm volatile("mov.b32 %0, 0x3F803F80;" : "=r"(one2));
+    asm volatile("mov.b32 %0, 0xC30FC30F;" : "=r"(neg2));              // -143, -143
+
+    if (XS) {
+        // rows of x, zero padded up to kb * 64 columns, row stride xstride elements (16 bytes more than a multiple of 128)
+        const uint32_t chunks = KB * (kP5TileCols / 8);
+        for (uint32_t i = threadIdx.x; i < m_rows * chunks; i += blockDim.x) {
+            uint32_t m = i / chunks, k8 = (i - m * chunks) * 8u;
+            uint4 v;
+            if ((p.in_f & 7u) == 0 && k8 + 8u <= p.in_f) {
+                v = *(const uint4 *)(x + (size_t)m * p.in_f + k8);
+            } else {
+                unsigned short e[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+                    e[j] = k8 + j < p.in_f ? __bfloat16_as_ushort(x[(size_t)m * p.in_f + k8 + j]) : (unsigned short)0;
+                v = make_uint4(e[0] | ((uint32_t)e[1] << 16), e[2] | ((uint32_t)e[3] << 16), e[4] | ((uint32_t)e[5] << 16),
+                               e[6] | ((uint32_t)e[7] << 16));
             }
+            *(uint4 *)(xs + (size_t)m * xstride + k8) = v;
         }
     }
     __syncthreads();
 
-    const int lane = threadIdx.x & 31;
-    const uint32_t gw = blockIdx.x * kP5Warps + (threadIdx.x >> 5);
-    const uint32_t b_begin = gw * bpw;
+    const uint32_t cta_blocks = bpw * kP5Warps;
+    const uint32_t cb0 = blockIdx.x * cta_blocks;
+    const uint32_t cb1 = min(cb0 + cta_blocks, nb);
+    const uint32_t b_begin = cb0 + wid * bpw;
     const uint32_t b_end = min(b_begin + bpw, nb);
-    const uint32_t nq = (p.n + 255u) / 256u;
-
-    auto emit = [&](uint32_t row, const float (&acc)[M]) {
-        uint32_t fb = (uint32_t)(((unsigned long long)row * p.in_f) >> 10);
-        uint32_t lb = (uint32_t)((((unsigned long long)(row + 1) * p.in_f) - 1) >> 10);
-        bool whole = fb >= b_begin && lb < b_end;
-#pragma unroll
-        for (int m = 0; m < M; ++m) {
-            float v = warp_sum(acc[m]);
-            if (lane == 0) {
-                if (whole) {
-                    size_t o = (size_t)m * p.out_f + row;
-                    if (y_f32) {
-                        ((float *)y)[o] = bias ? v + __bfloat162float(bias[row]) : v;
-                    } else {
-                        __nv_bfloat16 h = __float2bfloat16_rn(v);
-                        if (bias) h = __hadd(h, bias[row]);
-                        ((__nv_bfloat16 *)y)[o] = h;
-                    }
-                } else {
-                    slots[((size_t)m * p.out_f + row) * pmax + (gw - fb / bpw)] = v;
-                }
-            }
-        }
-    };
 
     if (b_begin < b_end) {
-        float acc[M];
-#pragma unroll
-        for (int m = 0; m < M; ++m) acc[m] = 0.f;
-        // row and in-row offset of the current block's first element (warp uniform, kept incrementally)
-        uint32_t blk_row = (uint32_t)(((unsigned long long)b_begin * kBlk) / p.in_f);
-        uint32_t blk_k = (uint32_t)((unsigned long long)b_begin * kBlk - (unsigned long long)blk_row * p.in_f);
+        float c[4] = {0.f, 0.f, 0.f, 0.f};
+        uint32_t R = b_begin / KB, kbi = b_begin - R * KB;
+        const uint32_t R_first = R;
+        bool from_start = kbi == 0;                  // the current tile's first block belongs to this run
+        // this lane's activations: row min(g, m_rows - 1) (rows beyond m_rows only feed unused C columns)
+        const uint32_t xrow = min((uint32_t)g, m_rows - 1u);
+        const __nv_bfloat16 *xl = XS ? xs + (size_t)xrow * xstride + 16 * t : x + (size_t)xrow * p.in_f + 16 * t;
 
-        // plane words and outlier offsets of the next two blocks are in flight while one is used
-        auto load_w03 = [&](uint32_t b) { return b < b_end ? p.w03[b * 32u + lane] : make_uint4(0, 0, 0, 0); };
-        auto load_w4 = [&](uint32_t b) { return b < b_end ? p.w4[b * 32u + lane] : 0u; };
-        // lanes 0..4 hold esc_off[4b .. 4b+4]
-        auto load_off = [&](uint32_t b) {
-            return (b < b_end && lane < 5) ? __ldg(p.esc_off + min(b * 4u + (uint32_t)lane, nq)) : 0;
-        };
-        uint4 p1_03 = load_w03(b_begin), p2_03 = load_w03(b_begin + 1);
-        uint32_t p1_4 = load_w4(b_begin), p2_4 = load_w4(b_begin + 1);
-        int32_t p1_off = load_off(b_begin), p2_off = load_off(b_begin + 1);
+        const uint4 *p03 = p.w03 + (size_t)b_begin * 32u + lane;
+        const uint32_t *p4 = p.w4 + (size_t)b_begin * 32u + lane;
+        // the plane words of the next two blocks are in flight while one is used
+        uint4 n1_03 = p03[0];
+        uint32_t n1_4 = p4[0];
+        uint32_t o2 = b_begin + 1 < b_end ? 32u : 0u;
+        uint4 n2_03 = p03[o2];
+        uint32_t n2_4 = p4[o2];
 
         for (uint32_t b = b_begin; b < b_end; ++b) {
-            const uint4 a = p1_03;
-            const uint32_t w4 = p1_4;
-            const int32_t off = p1_off;
-            p1_03 = p2_03; p1_4 = p2_4; p1_off = p2_off;
-            p2_03 = load_w03(b + 2); p2_4 = load_w4(b + 2); p2_off = load_off(b + 2);
-
-            const uint32_t blk_e0 = b * (uint32_t)kBlk;
-            const uint32_t blk_cnt = min((uint32_t)kBlk, p.n - blk_e0);          // elements in this block
-            const bool one_row = blk_k + blk_cnt <= p.in_f;
-            // this lane's word: element offset in the block 32*lane; row / column only needed per path
-            const bool valid = 32u * lane < blk_cnt;
-            uint32_t k0 = blk_k + 32u * lane, lrow = blk_row;
-            if (!one_row) while (k0 >= p.in_f) { k0 -= p.in_f; ++lrow; }
-
-            // five source words plus their halves shifted down by 16 (fields at bit 19..31 are taken from those)
-            const uint32_t w0 = a.x, w1 = a.y, w2 = a.z, w3 = a.w;
-            const uint32_t h0 = __funnelshift_r(w0, w1, 16), h1 = __funnelshift_r(w1, w2, 16),
-                           h2 = __funnelshift_r(w2, w3, 16), h3 = __funnelshift_r(w3, w4, 16), h4 = w4 >> 16;
-            const uint32_t xword = (k0 >> 10) * 256u + ((k0 >> 5) & 31u);
-            float part[M];
-#pragma unroll
-            for (int m = 0; m < M; ++m) part[m] = 0.f;
-            if (valid) {
-#pragma unroll
-                for (int g = 0; g < 8; ++g) {       // 4 elements per step: one float4 of x per row
-                    float4 xv[M];
-#pragma unroll
-                    for (int m = 0; m < M; ++m) {
-                        if (XS) {
-                            xv[m] = ((const float4 *)(p5_xs + (size_t)m * xstride))[xword + 32 * g];
-                        } else {
-                            uint2 r = __ldg((const uint2 *)(x + (size_t)m * p.in_f + k0) + g);
-                            xv[m] = make_float4(__uint_as_float(r.x << 16), __uint_as_float(r.x & 0xffff0000u),
-                                                __uint_as_float(r.y << 16), __uint_as_float(r.y & 0xffff0000u));
-                        }
-                    }
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        const int i = 4 * g + j, bit = 5 * i, k = bit >> 5, s = bit & 31;
-                        uint32_t wv;
-                        if (s <= 18) {
-                            const uint32_t src = k == 0 ? w0 : k == 1 ? w1 : k == 2 ? w2 : k == 3 ? w3 : w4;
-                            IXB_P5_W(src, s, wv)
-                        } else {
-                            const uint32_t src = k == 0 ? h0 : k == 1 ? h1 : k == 2 ? h2 : k == 3 ? h3 : h4;
-                            IXB_P5_W(src, s - 16, wv)
-                        }
-                        const float wt = __uint_as_float(wv);
-#pragma unroll
-                        for (int m = 0; m < M; ++m) {
-                            const float xf = j == 0 ? xv[m].x : j == 1 ? xv[m].y : j == 2 ? xv[m].z : xv[m].w;
-                            part[m] = fmaf(xf, wt, part[m]);
-                        }
-                    }
-                }
+            const uint4 a = n1_03;
+            const uint32_t w4 = n1_4;
+            n1_03 = n2_03;
+            n1_4 = n2_4;
+            {
+                uint32_t nxt = min(b + 2, b_end - 1) - b_begin;
+                n2_03 = p03[(size_t)nxt * 32u];
+                n2_4 = p4[(size_t)nxt * 32u];
             }
+            // activations 64 kbi + 16 t .. + 15 of this lane's row
+            const uint4 x0 = *(const uint4 *)(xl + (size_t)kbi * kP5TileCols);
+            const uint4 x1 = *(const uint4 *)(xl + (size_t)kbi * kP5TileCols + 8);
 
-            // ---- level-3 outliers of this block (lane j takes entries j, j+32, ...)
-            const int32_t o0 = __shfl_sync(0xffffffffu, off, 0), o1 = __shfl_sync(0xffffffffu, off, 1),
-                          o2 = __shfl_sync(0xffffffffu, off, 2), o3 = __shfl_sync(0xffffffffu, off, 3),
-                          o4 = __shfl_sync(0xffffffffu, off, 4);
-            // contribution of this lane's outlier entries that lie in row r (any row when the block has one row)
-            auto outliers = [&](uint32_t r, uint32_t r_k0, bool any_row, float (&dst)[M]) {
-                // r_k0: in-row offset of the block's first element if it were in row r (may be "negative")
-                for (int32_t j = o0 + lane; j < o4; j += 32) {
-                    uint32_t ent = __ldg(p.esc + j);
-                    uint32_t quarter = (uint32_t)(j >= o1) + (uint32_t)(j >= o2) + (uint32_t)(j >= o3);
-                    uint32_t kk = r_k0 + quarter * 256u + (ent & 255u);          // column if the entry is in row r
-                    if (!any_row && kk >= p.in_f) continue;                       // wraps for other rows
-                    float cf = (float)((int)(ent >> 8) - 127);
-                    uint32_t wv;
-                    asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(wv) : "r"(__float_as_uint(cf)), "r"(s2));
-                    uint32_t pos = ((kk >> 10) * 8u + ((kk & 31u) >> 2)) * 128u + ((kk >> 5) & 31u) * 4u + (kk & 3u);
+            const uint32_t w[5] = {a.x, a.y, a.z, a.w, w4};
+            uint32_t f[16];
 #pragma unroll
-                    for (int m = 0; m < M; ++m) {
-                        float xf = XS ? p5_xs[(size_t)m * xstride + pos] : __bfloat162float(x[(size_t)m * p.in_f + kk]);
-                        dst[m] = fmaf(xf, __uint_as_float(wv), dst[m]);
-                    }
-                }
-            };
-            if (one_row) {
-                // the usual case: the whole block belongs to blk_row
-                if (o4 > o0) outliers(blk_row, blk_k, true, part);
-#pragma unroll
-                for (int m = 0; m < M; ++m) acc[m] += part[m];
-                if (blk_k + blk_cnt == p.in_f || blk_e0 + blk_cnt >= p.n) {      // the row ends with this block
-                    emit(blk_row, acc);
-#pragma unroll
-                    for (int m = 0; m < M; ++m) acc[m] = 0.f;
-                }
-            } else {
-                // the block covers the tail of blk_row and one or more following rows
-                uint32_t r = blk_row, r_k0 = blk_k;                               // r_k0 wraps below zero for later rows
-                uint32_t covered = 0;
-                while (covered < blk_cnt) {
-                    if (valid && lrow == r) {
-#pragma unroll
-                        for (int m = 0; m < M; ++m) acc[m] += part[m];
-                    }
-                    outliers(r, r_k0, false, acc);
-                    uint32_t in_row = min(p.in_f - (r == blk_row ? blk_k : 0u), blk_cnt - covered);
-                    covered += in_row;
-                    bool row_done = (r == blk_row ? blk_k : 0u) + in_row == p.in_f || blk_e0 + covered >= p.n;
-                    if (row_done) {
-                        emit(r, acc);
-#pragma unroll
-                        for (int m = 0; m < M; ++m) acc[m] = 0.f;
-                    }
-                    ++r;
-                    r_k0 -= p.in_f;
-                }
+            for (int k = 0; k < 5; ++k) {
+                f[3 * k] = p5_pair_raw(w[k], magic);
+                f[3 * k + 1] = p5_pair_raw(w[k] >> 5, magic);
+                f[3 * k + 2] = p5_pair_raw(w[k] >> 10, magic);
             }
-            // advance the block position
-            blk_k += blk_cnt;
-            while (blk_k >= p.in_f) { blk_k -= p.in_f; ++blk_row; }
+            {
+                uint32_t v = p5_and_or(w[0] >> 15, 0x00010001u, magic);
+                v = p5_and_or(w[1] >> 14, 0x00020002u, v);
+                v = p5_and_or(w[2] >> 13, 0x00040004u, v);
+                v = p5_and_or(w[3] >> 12, 0x00080008u, v);
+                f[15] = p5_and_or(w[4] >> 11, 0x00100010u, v);
+            }
+#pragma unroll
+            for (int i = 0; i < 16; ++i) f[i] = p5_pair_weight(f[i], one2, neg2, s2);
+            p5_mma(c, f[0], f[1], f[2], f[3], x0.x, x0.y);
+            p5_mma(c, f[4], f[5], f[6], f[7], x0.z, x0.w);
+            p5_mma(c, f[8], f[9], f[10], f[11], x1.x, x1.y);
+            p5_mma(c, f[12], f[13], f[14], f[15], x1.z, x1.w);
+
+            if (++kbi == KB) {
+                // the tile is complete within this run, or this was its last part
+                if (from_start) p5_store_tile(p, R, lane, c, m_rows, osum, bias, y, y_f32);
+                else parts[(wid * 2 + (R == R_first ? 0 : 1)) * 32 + lane] = make_float4(c[0], c[1], c[2], c[3]);
+                c[0] = c[1] = c[2] = c[3] = 0.f;
+                kbi = 0;
+                ++R;
+                from_start = true;
+            }
         }
-        // run ended inside a row: hand the partial sum over
-        uint32_t end_e = min(b_end * (uint32_t)kBlk, p.n);
-        if (end_e < p.n && blk_k != 0) emit(blk_row, acc);
+        if (kbi != 0) parts[(wid * 2 + (R == R_first ? 0 : 1)) * 32 + lane] = make_float4(c[0], c[1], c[2], c[3]);
+    }
+    __syncthreads();
+
+    // ---- per CTA: sum the parts of every tile that more than one run of this CTA (or another CTA) touched
+    if (cb0 < cb1) {
+        const uint32_t Rc0 = cb0 / KB, Rc1 = (cb1 - 1) / KB;
+        for (uint32_t R = Rc0 + wid; R <= Rc1; R += kP5Warps) {
+            const uint32_t t0 = R * KB, t1 = t0 + KB;                   // the tile's blocks
+            const bool inside = t0 >= cb0 && t1 <= cb1;
+            const uint32_t wlo = (max(t0, cb0) - cb0) / bpw, whi = (min(t1, cb1) - 1 - cb0) / bpw;
+            if (inside && wlo == whi) continue;                          // one run had all of it and wrote y itself
+            float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (uint32_t w = wlo; w <= whi; ++w) {
+                uint32_t rf = (cb0 + w * bpw) / KB;
+                float4 v = parts[(w * 2 + (R == rf ? 0 : 1)) * 32 + lane];
+                s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+            }
+            if (inside) {
+                const float cc[4] = {s.x, s.y, s.z, s.w};
+                p5_store_tile(p, R, lane, cc, m_rows, osum, bias, y, y_f32);
+            } else {
+                cta_slots[((size_t)blockIdx.x * 2 + (R == Rc0 ? 0 : 1)) * 32 + lane] = s;
+            }
+        }
     }
 
-    // ---- last CTA sums the rows that were shared between runs (same scheme as k_gemv)
+    // ---- the CTA that takes the last ticket finishes the tiles shared between CTAs
     __threadfence();
     __syncthreads();
     if (threadIdx.x == 0) {
-        uint32_t t = atomicAdd(ticket, 1u);
-        is_last = (t == gridDim.x - 1);
+        uint32_t tk = atomicAdd(ticket, 1u);
+        is_last = (tk == gridDim.x - 1);
     }
     __syncthreads();
     if (!is_last) return;
     __threadfence();
-    uint32_t n_runs = (nb + bpw - 1) / bpw;
-    for (uint32_t g = 1 + threadIdx.x; g < n_runs; g += blockDim.x) {
-        unsigned long long e = (unsigned long long)g * bpw * kBlk;
-        uint32_t row = (uint32_t)(e / p.in_f);
-        unsigned long long row_e0 = (unsigned long long)row * p.in_f;
-        if (e == row_e0) continue;
-        unsigned long long prev = (unsigned long long)(g - 1) * bpw * kBlk;
-        if (prev > row_e0) continue;
-        uint32_t fb = (uint32_t)(row_e0 >> 10);
-        uint32_t lb = (uint32_t)((row_e0 + p.in_f - 1) >> 10);
-        uint32_t np = lb / bpw - fb / bpw + 1;
-        for (int m = 0; m < M; ++m) {
-            const float *sl = slots + ((size_t)m * p.out_f + row) * pmax;
-            float v = 0.f;
-            for (uint32_t q = 0; q < np; ++q) v += __ldcg(sl + q);
-            size_t o = (size_t)m * p.out_f + row;
-            if (y_f32) {
-                ((float *)y)[o] = bias ? v + __bfloat162float(bias[row]) : v;
-            } else {
-                __nv_bfloat16 h = __float2bfloat16_rn(v);
-                if (bias) h = __hadd(h, bias[row]);
-                ((__nv_bfloat16 *)y)[o] = h;
-            }
+    for (uint32_t cta = 1 + wid; cta < gridDim.x; cta += kP5Warps) {
+        unsigned long long e = (unsigned long long)cta * cta_blocks;    // first block of this CTA
+        if (e >= nb) continue;
+        uint32_t R = (uint32_t)(e / KB);
+        uint32_t t0 = R * KB, t1 = min(t0 + KB, nb);
+        if (e == t0) continue;                                           // the tile starts with the CTA
+        if ((unsigned long long)(cta - 1) * cta_blocks > t0) continue;   // an earlier boundary in this tile does it
+        uint32_t clo = t0 / cta_blocks, chi = (t1 - 1) / cta_blocks;
+        float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (uint32_t cc = clo; cc <= chi; ++cc) {
+            uint32_t rf = (uint32_t)(((unsigned long long)cc * cta_blocks) / KB);
+            const float4 *sl = cta_slots + ((size_t)cc * 2 + (R == rf ? 0 : 1)) * 32 + lane;
+            float4 v = make_float4(__ldcg(&sl->x), __ldcg(&sl->y), __ldcg(&sl->z), __ldcg(&sl->w));
+            s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
         }
+        const float cc4[4] = {s.x, s.y, s.z, s.w};
+        p5_store_tile(p, R, lane, cc4, m_rows, osum, bias, y, y_f32);
     }
     if (threadIdx.x == 0) *ticket = 0;
 }

@@ -10,7 +10,7 @@ from oracle import ixb_oracle as O
 pytestmark = pytest.mark.gpu
 
 SHAPES = [(64, 5120), (48, 5120), (40, 17408), (96, 2176), (7, 4352), (33, 96), (1, 32), (3, 1024), (300, 512),
-          (10, 96)]
+          (10, 96), (5, 100), (17, 72), (512, 17408), (16, 64)]
 
 
 def bits_to_bf16(a):
@@ -39,7 +39,7 @@ def test_p5_roundtrip_is_lossless(out_f, in_f):
     assert np.array_equal(w, O.codes_to_bf16(codes, sc_bits))
 
 
-@pytest.mark.parametrize("out_f,in_f", [s for s in SHAPES if s[1] % 32 == 0])
+@pytest.mark.parametrize("out_f,in_f", SHAPES)
 @pytest.mark.parametrize("m", [1, 2, 5, 8])
 def test_p5_gemv_matches_oracle(out_f, in_f, m):
     codes, scale, p5 = make(out_f, in_f, out_f * 5 + in_f + m)
@@ -82,3 +82,23 @@ def test_p5_extreme_level_mixes_and_from_packed(golden_dir):
     assert np.array_equal(p5.decode(kind="codes").cpu().numpy().reshape(-1), g["codes"])
     y = p5.gemv(bits_to_bf16(g["x_bits"]).cuda(), out_dtype=torch.float32).cpu().numpy()
     assert rel_err(y, g["y_f32"].astype(np.float64)) < 2e-5
+
+
+@pytest.mark.parametrize("out_f,in_f", [(5120, 17408), (17408, 5120)])
+def test_p5_full_size_agrees_with_the_stream_kernel(out_f, in_f):
+    """Benchmark shapes: the GEMV on the resident layout against the fused kernel on the reference's streams
+    (itself checked against the oracle), the decoded codes against the stream decoder, twice for reproducibility."""
+    from ixrun_b200.p5 import P5Packed
+    from ixrun_b200.packed import DevicePacked
+    from ixrun_b200.synth import synthetic_packed
+
+    dp = DevicePacked(synthetic_packed(out_f, in_f, seed=3))
+    p5 = P5Packed.from_packed(dp)
+    assert torch.equal(p5.decode(kind="codes"), dp.decode(kind="codes"))
+    for m in (1, 8):
+        x = torch.randn(m, in_f, device="cuda").bfloat16()
+        ref = dp.gemv(x, out_dtype=torch.float32)
+        y = p5.gemv(x, out_dtype=torch.float32)
+        assert float((y - ref).abs().max() / ref.abs().max()) < 2e-5
+        assert torch.equal(p5.gemv(x, out_dtype=torch.float32), y)
+    assert p5.resident_bytes < 1.08 * dp.total_bytes
