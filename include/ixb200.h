@@ -136,9 +136,10 @@ int ixb_pack_codes(const int8_t *codes_device, const ixb_packed *out, const int3
  * addressing:
  *   w03, w4  a 5-bit field per element (code + 15 for |code| <= 15, 15 = code 0
  *            for level-3 elements), one uint4 + one uint32 per 32 elements; the
- *            matrix is cut into tiles of 16 rows x 64 columns (ixb_p5_blocks of
- *            them, ragged edges padded) whose fields are ordered as the
- *            tensor-core A fragments that the GEMV consumes
+ *            matrix is cut into tiles of 16 rows x 64 columns (ragged edges
+ *            padded) whose fields are ordered as the tensor-core A fragments
+ *            that the GEMV consumes; ixb_p5_blocks = number of tiles + 4 blocks
+ *            of slack that the GEMV's prefetch may read but never interprets
  *   row_off  int32 [out_f + 1], esc_col uint16 [n_esc], esc_val uint8 [n_esc]:
  *            the level-3 elements as a CSR list (column, code + 127)
  * about 5 + 24 * P(level 3) bits per weight; in_f <= 65536.

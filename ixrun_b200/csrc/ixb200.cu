@@ -753,7 +753,7 @@ static int to_p5(const ixb_p5 *t, P5 *p)
 extern "C" int64_t ixb_p5_blocks(int64_t out_f, int64_t in_f)
 {
     if (out_f <= 0 || in_f <= 0) return 0;
-    return ((out_f + kP5TileRows - 1) / kP5TileRows) * ((in_f + kP5TileCols - 1) / kP5TileCols);
+    return ((out_f + kP5TileRows - 1) / kP5TileRows) * ((in_f + kP5TileCols - 1) / kP5TileCols) + kP5SlackBlocks;
 }
 
 extern "C" int ixb_p5_build(const int8_t *codes, int64_t out_f, int64_t in_f, void *w03, void *w4, int32_t *row_off,
@@ -804,7 +804,7 @@ extern "C" int ixb_p5_decode(const ixb_p5 *t, void *out, int out_kind, ixb_strea
     return rc;
 }
 
-struct P5Plan { uint32_t nb, grid, bpw, xstride, smem, xs; size_t osum_bytes, slot_bytes; };
+struct P5Plan { uint32_t nb, grid, xstride, smem, xs; size_t osum_bytes, slot_bytes; };
 
 static P5Plan make_p5_plan(uint32_t out_f, uint32_t in_f, uint32_t m_rows)
 {
@@ -815,7 +815,6 @@ static P5Plan make_p5_plan(uint32_t out_f, uint32_t in_f, uint32_t m_rows)
     uint32_t want = (p.nb + kP5Warps - 1) / kP5Warps;
     p.grid = want < sms ? want : sms;
     if (!p.grid) p.grid = 1;
-    p.bpw = (p.nb + p.grid * kP5Warps - 1) / (p.grid * kP5Warps);
     p.xstride = kb * kP5TileCols + 8u;
     uint32_t parts = kP5Warps * 2u * 32u * (uint32_t)sizeof(float4);
     uint32_t xbytes = m_rows * p.xstride * 2u;
@@ -830,7 +829,7 @@ extern "C" size_t ixb_p5_gemv_scratch_bytes(int64_t out_f, int64_t in_f, int64_t
 {
     if (out_f <= 0 || in_f <= 0 || m_rows <= 0) return 0;
     P5Plan p = make_p5_plan((uint32_t)out_f, (uint32_t)in_f, (uint32_t)m_rows);
-    return 256 + p.osum_bytes + p.slot_bytes;
+    return 1024 + p.osum_bytes + p.slot_bytes;
 }
 
 template <int XS>
@@ -843,7 +842,7 @@ static void launch_p5(const P5 &p, const void *x, uint32_t m_rows, const void *b
         attr_set = true;
     }
     k_p5_mma<XS><<<pl.grid, kP5Threads, pl.smem, st>>>(p, (const __nv_bfloat16 *)x, m_rows, (const __nv_bfloat16 *)bias, y,
-                                                       y_f32, osum, slots, ticket, pl.nb, pl.bpw, pl.xstride);
+                                                       y_f32, osum, slots, ticket, pl.nb, pl.xstride);
 }
 
 extern "C" int ixb_p5_gemv(const ixb_p5 *t, const void *x, int64_t m_rows, const void *bias, void *y, int y_is_f32,
@@ -861,8 +860,8 @@ extern "C" int ixb_p5_gemv(const ixb_p5 *t, const void *x, int64_t m_rows, const
     if (!pl.xs && (p.in_f % kP5TileCols))
         return fail(IXB_E_UNSUPPORTED, "in_f=%u: activations too large for shared memory need in_f %% 64 == 0", p.in_f);
     uint32_t *ticket = (uint32_t *)scratch;
-    float *osum = (float *)((char *)scratch + 256);
-    float4 *slots = (float4 *)((char *)scratch + 256 + pl.osum_bytes);
+    float *osum = (float *)((char *)scratch + 1024);          // the first 1024 bytes hold the tile tickets (grid + 1 words)
+    float4 *slots = (float4 *)((char *)scratch + 1024 + pl.osum_bytes);
     cudaStream_t st = (cudaStream_t)stream;
     {
         uint32_t blocks = (p.out_f + 7u) / 8u, cap = (uint32_t)num_sms() * 8u;

@@ -33,6 +33,7 @@ namespace ixb {
 
 constexpr int kP5TileRows = 16;
 constexpr int kP5TileCols = 64;
+constexpr int kP5SlackBlocks = 4;    // readable blocks behind the planes (the GEMV's prefetch runs past the end)
 
 struct P5 {
     const uint4 *w03;          // [nb * 32] plane words 0..3 of every lane of every block
@@ -200,15 +201,26 @@ k_p5_outliers(P5 p, const __nv_bfloat16 *__restrict__ x, uint32_t m0, float *__r
 #pragma unroll
         for (int m = 0; m < MC; ++m) acc[m] = 0.f;
         const int32_t end = __ldg(p.row_off + row + 1);
-        for (int32_t j = __ldg(p.row_off + row) + lane; j < end; j += 32) {
-            uint32_t col = __ldg(p.esc_col + j);
-            float cf = (float)((int)__ldg(p.esc_val + j) - 127);
-            uint32_t wv;       // upper half: bf16(code * scale); lower half: bf16(0 * scale) = 0
-            asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(wv) : "r"(__float_as_uint(cf)), "r"(s2));
+        for (int32_t j0 = __ldg(p.row_off + row) + lane; j0 < end; j0 += 128) {
+            // four entries per lane in flight: all entry loads, then all activation loads, then the FMAs
+            uint32_t col[4], val[4];
 #pragma unroll
-            for (int m = 0; m < MC; ++m) {
-                float xf = __uint_as_float((uint32_t)__ldg(xu + (size_t)(m0 + m) * p.in_f + col) << 16);
-                acc[m] = fmaf(xf, __uint_as_float(wv), acc[m]);
+            for (int u = 0; u < 4; ++u) {
+                int32_t j = j0 + 32 * u;
+                bool ok = j < end;
+                col[u] = ok ? (uint32_t)__ldg(p.esc_col + j) : 0u;
+                val[u] = ok ? (uint32_t)__ldg(p.esc_val + j) : 127u;      // code 0
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                float cf = (float)((int)val[u] - 127);
+                uint32_t wv;       // upper half: bf16(code * scale); lower half: bf16(0 * scale) = 0
+                asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(wv) : "r"(__float_as_uint(cf)), "r"(s2));
+#pragma unroll
+                for (int m = 0; m < MC; ++m) {
+                    float xf = __uint_as_float((uint32_t)__ldg(xu + (size_t)(m0 + m) * p.in_f + col[u]) << 16);
+                    acc[m] = fmaf(xf, __uint_as_float(wv), acc[m]);
+                }
             }
         }
 #pragma unroll
@@ -277,25 +289,35 @@ __device__ __forceinline__ void p5_store_tile(const P5 &p, uint32_t R, int lane,
     }
 }
 
-// One warp = one contiguous run of bpw blocks in (row tile, column block) order; a CTA = 32 consecutive runs.
-// Row tiles that a run covers completely are written straight to y.  Partial tiles go to shared memory, are
-// summed per CTA in warp order, and tiles shared between CTAs go through cta_slots and are finished, in CTA
-// order, by whichever CTA takes the last ticket -- no floating-point atomics anywhere, so results are
-// reproducible.  XS = 1: activations staged in shared memory (bf16, padded rows); XS = 0: read from global.
+// first element of part i when n elements are cut into `parts` nearly equal contiguous parts, and its inverse
+__device__ __forceinline__ uint32_t p5_part_begin(uint32_t i, uint32_t n, uint32_t parts)
+{
+    return (uint32_t)(((unsigned long long)i * n) / parts);
+}
+__device__ __forceinline__ uint32_t p5_part_of(uint32_t pos, uint32_t n, uint32_t parts)
+{
+    return (uint32_t)((((unsigned long long)pos + 1u) * parts - 1u) / n);     // largest i with part_begin(i) <= pos
+}
+
+// The nb blocks, in (row tile, column block) order, are cut into gridDim.x nearly equal contiguous CTA ranges
+// and every CTA range into 32 warp runs.  Row tiles that a run covers completely are written straight to y.
+// Partial tiles go to shared memory and are summed per CTA in warp order; a tile shared between CTAs goes
+// through cta_slots, and the CTA that arrives last at the tile's ticket sums the slots in CTA order -- no
+// floating-point atomics anywhere, so results are reproducible.  tickets[] (gridDim.x + 1 words) must be zero
+// before the first launch and is left zero.  XS = 1: activations staged in shared memory (bf16, padded rows);
+// XS = 0: read from global memory.
 template <int XS>
 __global__ void __launch_bounds__(kP5Threads, 1)
 k_p5_mma(P5 p, const __nv_bfloat16 *__restrict__ x, uint32_t m_rows, const __nv_bfloat16 *__restrict__ bias, void *y,
-         int y_f32, const float *__restrict__ osum, float4 *cta_slots, uint32_t *ticket, uint32_t nb, uint32_t bpw,
-         uint32_t xstride)
+         int y_f32, const float *__restrict__ osum, float4 *cta_slots, uint32_t *tickets, uint32_t nb, uint32_t xstride)
 {
     extern __shared__ __align__(16) unsigned char p5_smem[];
     float4 *parts = (float4 *)p5_smem;                                  // [warp][2][32 lanes]
     __nv_bfloat16 *xs = (__nv_bfloat16 *)(p5_smem + kP5Warps * 2 * 32 * sizeof(float4));   // [m_rows][xstride]
-    __shared__ uint32_t is_last;
 
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
     const int g = lane >> 2, t = lane & 3;
-    const uint32_t KB = p.kb;
+    const uint32_t KB = p.kb, G = gridDim.x;
     uint32_t sb = (uint32_t)__bfloat16_as_ushort(*p.scale);
     const uint32_t s2 = sb | (sb << 16);
     uint32_t magic, one2, neg2;
@@ -325,44 +347,30 @@ k_p5_mma(P5 p, const __nv_bfloat16 *__restrict__ x, uint32_t m_rows, const __nv_
     }
     __syncthreads();
 
-    const uint32_t cta_blocks = bpw * kP5Warps;
-    const uint32_t cb0 = blockIdx.x * cta_blocks;
-    const uint32_t cb1 = min(cb0 + cta_blocks, nb);
-    const uint32_t b_begin = cb0 + wid * bpw;
-    const uint32_t b_end = min(b_begin + bpw, nb);
+    const uint32_t cb0 = p5_part_begin(blockIdx.x, nb, G), cb1 = p5_part_begin(blockIdx.x + 1, nb, G);
+    const uint32_t L = cb1 - cb0;
+    const uint32_t b_begin = cb0 + p5_part_begin(wid, L, kP5Warps), b_end = cb0 + p5_part_begin(wid + 1, L, kP5Warps);
 
     if (b_begin < b_end) {
         float c[4] = {0.f, 0.f, 0.f, 0.f};
-        uint32_t R = b_begin / KB, kbi = b_begin - R * KB;
+        uint32_t R = b_begin / KB;
         const uint32_t R_first = R;
-        bool from_start = kbi == 0;                  // the current tile's first block belongs to this run
-        // this lane's activations: row min(g, m_rows - 1) (rows beyond m_rows only feed unused C columns)
+        bool from_start = b_begin == R * KB;          // the current tile's first block belongs to this run
+        // this lane's activations: row min(g, m_rows - 1) (rows beyond m_rows only feed unused C columns);
+        // xo walks through the row in steps of 64 elements and wraps at the end of a tile
         const uint32_t xrow = min((uint32_t)g, m_rows - 1u);
         const __nv_bfloat16 *xl = XS ? xs + (size_t)xrow * xstride + 16 * t : x + (size_t)xrow * p.in_f + 16 * t;
+        const uint32_t xo_end = KB * kP5TileCols;
+        uint32_t xo = (b_begin - R * KB) * kP5TileCols;
 
-        const uint4 *p03 = p.w03 + (size_t)b_begin * 32u + lane;
-        const uint32_t *p4 = p.w4 + (size_t)b_begin * 32u + lane;
-        // the plane words of the next two blocks are in flight while one is used
-        uint4 n1_03 = p03[0];
-        uint32_t n1_4 = p4[0];
-        uint32_t o2 = b_begin + 1 < b_end ? 32u : 0u;
-        uint4 n2_03 = p03[o2];
-        uint32_t n2_4 = p4[o2];
-
-        for (uint32_t b = b_begin; b < b_end; ++b) {
-            const uint4 a = n1_03;
-            const uint32_t w4 = n1_4;
-            n1_03 = n2_03;
-            n1_4 = n2_4;
-            {
-                uint32_t nxt = min(b + 2, b_end - 1) - b_begin;
-                n2_03 = p03[(size_t)nxt * 32u];
-                n2_4 = p4[(size_t)nxt * 32u];
-            }
-            // activations 64 kbi + 16 t .. + 15 of this lane's row
-            const uint4 x0 = *(const uint4 *)(xl + (size_t)kbi * kP5TileCols);
-            const uint4 x1 = *(const uint4 *)(xl + (size_t)kbi * kP5TileCols + 8);
-
+        auto flush_tile = [&](bool whole) {
+            if (whole) p5_store_tile(p, R, lane, c, m_rows, osum, bias, y, y_f32);
+            else parts[(wid * 2 + (R == R_first ? 0 : 1)) * 32 + lane] = make_float4(c[0], c[1], c[2], c[3]);
+            c[0] = c[1] = c[2] = c[3] = 0.f;
+        };
+        auto process = [&](const uint4 a, const uint32_t w4) {
+            const uint4 x0 = *(const uint4 *)(xl + xo);
+            const uint4 x1 = *(const uint4 *)(xl + xo + 8);
             const uint32_t w[5] = {a.x, a.y, a.z, a.w, w4};
             uint32_t f[16];
 #pragma unroll
@@ -384,73 +392,86 @@ k_p5_mma(P5 p, const __nv_bfloat16 *__restrict__ x, uint32_t m_rows, const __nv_
             p5_mma(c, f[4], f[5], f[6], f[7], x0.z, x0.w);
             p5_mma(c, f[8], f[9], f[10], f[11], x1.x, x1.y);
             p5_mma(c, f[12], f[13], f[14], f[15], x1.z, x1.w);
-
-            if (++kbi == KB) {
-                // the tile is complete within this run, or this was its last part
-                if (from_start) p5_store_tile(p, R, lane, c, m_rows, osum, bias, y, y_f32);
-                else parts[(wid * 2 + (R == R_first ? 0 : 1)) * 32 + lane] = make_float4(c[0], c[1], c[2], c[3]);
-                c[0] = c[1] = c[2] = c[3] = 0.f;
-                kbi = 0;
+            xo += kP5TileCols;
+            if (xo == xo_end) {                      // the tile is complete, or this was its last part
+                flush_tile(from_start);
+                xo = 0;
                 ++R;
                 from_start = true;
             }
+        };
+        // two blocks' plane words in flight; the registers alternate by unrolling, not by copying.  The loads
+        // run up to two blocks past the end of the run: the planes are allocated with that much slack.
+        uint32_t idx = b_begin * 32u + lane;
+        uint4 a0 = p.w03[idx], a1 = p.w03[idx + 32u];
+        uint32_t e0 = p.w4[idx], e1 = p.w4[idx + 32u];
+        idx += 64u;
+        uint32_t left = b_end - b_begin;
+        while (true) {
+            {
+                const uint4 a = a0;
+                const uint32_t e = e0;
+                a0 = p.w03[idx];
+                e0 = p.w4[idx];
+                process(a, e);
+                if (--left == 0) break;
+            }
+            {
+                const uint4 a = a1;
+                const uint32_t e = e1;
+                a1 = p.w03[idx + 32u];
+                e1 = p.w4[idx + 32u];
+                idx += 64u;
+                process(a, e);
+                if (--left == 0) break;
+            }
         }
-        if (kbi != 0) parts[(wid * 2 + (R == R_first ? 0 : 1)) * 32 + lane] = make_float4(c[0], c[1], c[2], c[3]);
+        if (xo != 0) flush_tile(false);
     }
     __syncthreads();
 
     // ---- per CTA: sum the parts of every tile that more than one run of this CTA (or another CTA) touched
-    if (cb0 < cb1) {
+    if (L) {
         const uint32_t Rc0 = cb0 / KB, Rc1 = (cb1 - 1) / KB;
         for (uint32_t R = Rc0 + wid; R <= Rc1; R += kP5Warps) {
             const uint32_t t0 = R * KB, t1 = t0 + KB;                   // the tile's blocks
             const bool inside = t0 >= cb0 && t1 <= cb1;
-            const uint32_t wlo = (max(t0, cb0) - cb0) / bpw, whi = (min(t1, cb1) - 1 - cb0) / bpw;
+            const uint32_t wlo = p5_part_of(max(t0, cb0) - cb0, L, kP5Warps), whi = p5_part_of(min(t1, cb1) - 1 - cb0, L, kP5Warps);
             if (inside && wlo == whi) continue;                          // one run had all of it and wrote y itself
             float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
             for (uint32_t w = wlo; w <= whi; ++w) {
-                uint32_t rf = (cb0 + w * bpw) / KB;
+                uint32_t wb = p5_part_begin(w, L, kP5Warps);
+                if (wb == p5_part_begin(w + 1, L, kP5Warps)) continue;  // a warp without blocks
+                uint32_t rf = (cb0 + wb) / KB;
                 float4 v = parts[(w * 2 + (R == rf ? 0 : 1)) * 32 + lane];
                 s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
             }
             if (inside) {
                 const float cc[4] = {s.x, s.y, s.z, s.w};
                 p5_store_tile(p, R, lane, cc, m_rows, osum, bias, y, y_f32);
-            } else {
-                cta_slots[((size_t)blockIdx.x * 2 + (R == Rc0 ? 0 : 1)) * 32 + lane] = s;
+                continue;
             }
+            // shared with other CTAs: publish this CTA's sum, take a ticket; the last one finishes the tile
+            cta_slots[((size_t)blockIdx.x * 2 + (R == Rc0 ? 0 : 1)) * 32 + lane] = s;
+            __threadfence();
+            __syncwarp();
+            const uint32_t clo = p5_part_of(t0, nb, G), chi = p5_part_of(t1 - 1, nb, G);
+            uint32_t prev = 0;
+            if (lane == 0) prev = atomicAdd(tickets + clo + 1, 1u);
+            prev = __shfl_sync(0xffffffffu, prev, 0);
+            if (prev != chi - clo) continue;
+            __threadfence();
+            float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (uint32_t cc = clo; cc <= chi; ++cc) {
+                uint32_t rf = p5_part_begin(cc, nb, G) / KB;
+                const float4 *sl = cta_slots + ((size_t)cc * 2 + (R == rf ? 0 : 1)) * 32 + lane;
+                z.x += __ldcg(&sl->x); z.y += __ldcg(&sl->y); z.z += __ldcg(&sl->z); z.w += __ldcg(&sl->w);
+            }
+            const float cc4[4] = {z.x, z.y, z.z, z.w};
+            p5_store_tile(p, R, lane, cc4, m_rows, osum, bias, y, y_f32);
+            if (lane == 0) tickets[clo + 1] = 0;
         }
     }
-
-    // ---- the CTA that takes the last ticket finishes the tiles shared between CTAs
-    __threadfence();
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        uint32_t tk = atomicAdd(ticket, 1u);
-        is_last = (tk == gridDim.x - 1);
-    }
-    __syncthreads();
-    if (!is_last) return;
-    __threadfence();
-    for (uint32_t cta = 1 + wid; cta < gridDim.x; cta += kP5Warps) {
-        unsigned long long e = (unsigned long long)cta * cta_blocks;    // first block of this CTA
-        if (e >= nb) continue;
-        uint32_t R = (uint32_t)(e / KB);
-        uint32_t t0 = R * KB, t1 = min(t0 + KB, nb);
-        if (e == t0) continue;                                           // the tile starts with the CTA
-        if ((unsigned long long)(cta - 1) * cta_blocks > t0) continue;   // an earlier boundary in this tile does it
-        uint32_t clo = t0 / cta_blocks, chi = (t1 - 1) / cta_blocks;
-        float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (uint32_t cc = clo; cc <= chi; ++cc) {
-            uint32_t rf = (uint32_t)(((unsigned long long)cc * cta_blocks) / KB);
-            const float4 *sl = cta_slots + ((size_t)cc * 2 + (R == rf ? 0 : 1)) * 32 + lane;
-            float4 v = make_float4(__ldcg(&sl->x), __ldcg(&sl->y), __ldcg(&sl->z), __ldcg(&sl->w));
-            s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
-        }
-        const float cc4[4] = {s.x, s.y, s.z, s.w};
-        p5_store_tile(p, R, lane, cc4, m_rows, osum, bias, y, y_f32);
-    }
-    if (threadIdx.x == 0) *ticket = 0;
 }
 
 }  // namespace ixb
