@@ -136,36 +136,38 @@ int ixb_pack_codes(const int8_t *codes_device, const ixb_packed *out, const int3
  * addressing:
  *   w03, w4  a 5-bit field per element (code + 15 for |code| <= 15, 15 = code 0
  *            for level-3 elements), one uint4 + one uint32 per 32 elements; the
- *            matrix is cut into tiles of 16 rows x 64 columns (ragged edges
- *            padded) whose fields are ordered as the tensor-core A fragments
- *            that the GEMV consumes; ixb_p5_blocks = number of tiles + 4 blocks
- *            of slack that the GEMV's prefetch may read but never interprets
- *   row_off  int32 [out_f + 1], esc_col uint16 [n_esc], esc_val uint8 [n_esc]:
- *            the level-3 elements as a CSR list (column, code + 127)
- * about 5 + 24 * P(level 3) bits per weight; in_f <= 65536.
- * ixb_p5_build: int8 codes [out_f, in_f] -> layout (n_esc = number of level-3
- *   elements = counts[2]; planes of ixb_p5_blocks * 512 and * 128 bytes;
- *   ws: (out_f + 1) * 4 bytes).  ixb_p5_decode: layout -> int8 codes / bf16
- *   weights (out_kind as ixb_decode).  ixb_p5_gemv: same contract as ixb_gemv
- *   (result definition, bias, scratch rules; scratch 16-byte aligned), reading
- *   this layout: a sparse pass over the outliers, then the plane on the tensor
- *   cores (mma.sync, bf16 x bf16 products, fp32 accumulation) -- 1..8
- *   activation rows cost the same.
+ *            matrix is cut into blocks of 16 rows x 64 columns (ixb_p5_blocks of
+ *            them, ragged edges padded) whose fields are ordered as the
+ *            tensor-core A fragments that the GEMV consumes
+ *   esc      the level-3 elements of every block as uint32 entries: the weight
+ *            bf16(code * scale) in the low half, its position in the block's
+ *            fragment image in the high half; blk_off: int32 first entry of
+ *            every block
+ * about 5 + 32 * P(level 3) bits per weight.  Buffer sizes, with the slack
+ * that the GEMV's prefetch may read but never interprets (B = ixb_p5_blocks):
+ *   w03 (B + 4) * 512 bytes, w4 (B + 4) * 128 bytes, blk_off (B + 5) * 4 bytes,
+ *   esc (n_esc + 64) * 4 bytes.
+ * ixb_p5_build: int8 codes [out_f, in_f] + the bf16 scale -> layout (n_esc =
+ *   number of level-3 elements = counts[2]; ws: (B + 5) * 4 bytes).
+ * ixb_p5_decode: layout -> int8 codes / bf16 weights (out_kind as ixb_decode).
+ * ixb_p5_gemv: same contract as ixb_gemv (result definition, bias, scratch
+ *   rules; scratch 16-byte aligned), reading this layout on the tensor cores
+ *   (mma.sync, bf16 x bf16 products, fp32 accumulation) in one kernel --
+ *   1..8 activation rows cost the same.
  */
 typedef struct ixb_p5 {
     const void *w03;
     const void *w4;
-    const void *row_off;
-    const void *esc_col;
-    const void *esc_val;
+    const void *blk_off;
+    const void *esc;
     int64_t n_esc;
     const void *scale;    /* one bf16 */
     int64_t out_f;
     int64_t in_f;
 } ixb_p5;
 int64_t ixb_p5_blocks(int64_t out_f, int64_t in_f);
-int ixb_p5_build(const int8_t *codes_device, int64_t out_f, int64_t in_f, void *w03_device, void *w4_device,
-                 int32_t *row_off_device, void *esc_col_device, void *esc_val_device, int64_t n_esc,
+int ixb_p5_build(const int8_t *codes_device, const void *scale_device, int64_t out_f, int64_t in_f, void *w03_device,
+                 void *w4_device, int32_t *blk_off_device, void *esc_device, int64_t n_esc,
                  void *ws_device, size_t ws_bytes, ixb_stream_t stream);
 int ixb_p5_decode(const ixb_p5 *t, void *out_device, int out_kind, ixb_stream_t stream);
 size_t ixb_p5_gemv_scratch_bytes(int64_t out_f, int64_t in_f, int64_t m_rows);

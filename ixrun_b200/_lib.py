@@ -48,8 +48,8 @@ class P5Struct(C.Structure):
     """Mirror of ``struct ixb_p5``."""
 
     _fields_ = [
-        ("w03", C.c_void_p), ("w4", C.c_void_p), ("row_off", C.c_void_p), ("esc_col", C.c_void_p),
-        ("esc_val", C.c_void_p), ("n_esc", C.c_int64), ("scale", C.c_void_p), ("out_f", C.c_int64), ("in_f", C.c_int64),
+        ("w03", C.c_void_p), ("w4", C.c_void_p), ("blk_off", C.c_void_p), ("esc", C.c_void_p),
+        ("n_esc", C.c_int64), ("scale", C.c_void_p), ("out_f", C.c_int64), ("in_f", C.c_int64),
     ]
 
 
@@ -95,7 +95,7 @@ def lib():
     L.ixb_p5_build.restype = C.c_int
     L.ixb_p5_blocks.restype = i64
     L.ixb_p5_blocks.argtypes = [i64, i64]
-    L.ixb_p5_build.argtypes = [vp, i64, i64, vp, vp, vp, vp, vp, i64, vp, sz, vp]
+    L.ixb_p5_build.argtypes = [vp, vp, i64, i64, vp, vp, vp, vp, i64, vp, sz, vp]
     L.ixb_p5_decode.restype = C.c_int
     L.ixb_p5_decode.argtypes = [C.POINTER(P5Struct), vp, C.c_int, vp]
     L.ixb_p5_gemv_scratch_bytes.restype = sz

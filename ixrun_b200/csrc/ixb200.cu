@@ -733,15 +733,12 @@ static int to_p5(const ixb_p5 *t, P5 *p)
     if (t->out_f <= 0 || t->in_f <= 0) return fail(IXB_E_ARG, "bad shape");
     long long n = (long long)t->out_f * t->in_f;
     if (n > 800000000LL) return fail(IXB_E_UNSUPPORTED, "tensor too large");
-    if (t->in_f > 65536) return fail(IXB_E_UNSUPPORTED, "in_f=%lld does not fit the 16-bit outlier columns", (long long)t->in_f);
-    if (!t->w03 || !t->w4 || !t->row_off || !t->scale) return fail(IXB_E_ARG, "NULL P5 pointer");
-    if (t->n_esc && (!t->esc_col || !t->esc_val)) return fail(IXB_E_ARG, "outlier list is NULL");
+    if (!t->w03 || !t->w4 || !t->blk_off || !t->esc || !t->scale) return fail(IXB_E_ARG, "NULL P5 pointer");
     if (((uintptr_t)t->w03 & 15u) || ((uintptr_t)t->w4 & 3u)) return fail(IXB_E_ARG, "P5 planes are misaligned");
     p->w03 = (const uint4 *)t->w03;
     p->w4 = (const uint32_t *)t->w4;
-    p->row_off = (const int32_t *)t->row_off;
-    p->esc_col = (const uint16_t *)t->esc_col;
-    p->esc_val = (const uint8_t *)t->esc_val;
+    p->blk_off = (const int32_t *)t->blk_off;
+    p->esc = (const uint32_t *)t->esc;
     p->scale = (const __nv_bfloat16 *)t->scale;
     p->out_f = (uint32_t)t->out_f;
     p->in_f = (uint32_t)t->in_f;
@@ -753,33 +750,37 @@ static int to_p5(const ixb_p5 *t, P5 *p)
 extern "C" int64_t ixb_p5_blocks(int64_t out_f, int64_t in_f)
 {
     if (out_f <= 0 || in_f <= 0) return 0;
-    return ((out_f + kP5TileRows - 1) / kP5TileRows) * ((in_f + kP5TileCols - 1) / kP5TileCols) + kP5SlackBlocks;
+    return ((out_f + kP5TileRows - 1) / kP5TileRows) * ((in_f + kP5TileCols - 1) / kP5TileCols);
 }
 
-extern "C" int ixb_p5_build(const int8_t *codes, int64_t out_f, int64_t in_f, void *w03, void *w4, int32_t *row_off,
-                            void *esc_col, void *esc_val, int64_t n_esc, void *ws, size_t ws_bytes, ixb_stream_t stream)
+extern "C" int ixb_p5_build(const int8_t *codes, const void *scale, int64_t out_f, int64_t in_f, void *w03, void *w4,
+                            int32_t *blk_off, void *esc, int64_t n_esc, void *ws, size_t ws_bytes, ixb_stream_t stream)
 {
-    if (!codes || !w03 || !w4 || !row_off || !ws || (n_esc && (!esc_col || !esc_val)))
-        return fail(IXB_E_ARG, "NULL pointer argument");
+    if (!codes || !scale || !w03 || !w4 || !blk_off || !esc || !ws) return fail(IXB_E_ARG, "NULL pointer argument");
     if (out_f <= 0 || in_f <= 0 || out_f * in_f > 800000000LL) return fail(IXB_E_ARG, "bad shape");
-    if (in_f > 65536) return fail(IXB_E_UNSUPPORTED, "in_f=%lld does not fit the 16-bit outlier columns", (long long)in_f);
+    if (n_esc < 0) return fail(IXB_E_ARG, "bad outlier count");
     if (((uintptr_t)w03 & 15u) || ((uintptr_t)w4 & 3u)) return fail(IXB_E_ARG, "P5 planes are misaligned");
-    if (ws_bytes < (size_t)(out_f + 1) * 4) return fail(IXB_E_SCRATCH, "P5 workspace too small");
     uint32_t rt = (uint32_t)((out_f + kP5TileRows - 1) / kP5TileRows), kb = (uint32_t)((in_f + kP5TileCols - 1) / kP5TileCols);
-    uint32_t nb = rt * kb;
+    uint32_t nb = rt * kb, n_off = nb + 1 + kP5SlackBlocks;
+    if (ws_bytes < (size_t)n_off * 4) return fail(IXB_E_SCRATCH, "P5 workspace too small");
     cudaStream_t st = (cudaStream_t)stream;
-    int32_t *row_cnt = (int32_t *)ws;
+    int32_t *blk_cnt = (int32_t *)ws;
     int rc;
-    IXB_CUDA(cudaMemsetAsync(row_cnt, 0, (size_t)(out_f + 1) * 4, st));
+    // slack behind the planes and the entries is zero (it is read, never interpreted); the counts of the slack
+    // blocks are zero so that their offsets repeat the total
+    IXB_CUDA(cudaMemsetAsync(blk_cnt, 0, (size_t)n_off * 4, st));
+    IXB_CUDA(cudaMemsetAsync((char *)w03 + (size_t)nb * 512, 0, (size_t)kP5SlackBlocks * 512, st));
+    IXB_CUDA(cudaMemsetAsync((char *)w4 + (size_t)nb * 128, 0, (size_t)kP5SlackBlocks * 128, st));
+    IXB_CUDA(cudaMemsetAsync((char *)esc + (size_t)n_esc * 4, 0, (size_t)kP5SlackEntries * 4, st));
     k_p5_plane<<<(nb + 7) / 8, 256, 0, st>>>(codes, (uint32_t)out_f, (uint32_t)in_f, rt, kb, (uint4 *)w03, (uint32_t *)w4,
-                                             row_cnt);
+                                             blk_cnt);
     if ((rc = launch_check("k_p5_plane"))) return rc;
-    k_excl_scan<<<1, 1024, 0, st>>>(row_cnt, row_off, (uint32_t)out_f + 1);      // entry out_f = total
+    k_excl_scan<<<1, 1024, 0, st>>>(blk_cnt, blk_off, n_off);      // entry nb (and the slack) = total
     if ((rc = launch_check("k_excl_scan"))) return rc;
     if (n_esc) {
-        k_p5_csr<<<((uint32_t)out_f + 7) / 8, 256, 0, st>>>(codes, (uint32_t)out_f, (uint32_t)in_f, row_off,
-                                                            (uint16_t *)esc_col, (uint8_t *)esc_val);
-        if ((rc = launch_check("k_p5_csr"))) return rc;
+        k_p5_esc<<<(nb + 7) / 8, 256, 0, st>>>(codes, (uint32_t)out_f, (uint32_t)in_f, rt, kb, blk_off,
+                                               (const __nv_bfloat16 *)scale, (uint32_t *)esc);
+        if ((rc = launch_check("k_p5_esc"))) return rc;
     }
     return IXB_OK;
 }
@@ -797,14 +798,14 @@ extern "C" int ixb_p5_decode(const ixb_p5 *t, void *out, int out_kind, ixb_strea
     else k_p5_decode_plane<1><<<(nb + 7) / 8, 256, 0, st>>>(p, out);
     if ((rc = launch_check("k_p5_decode_plane"))) return rc;
     if (t->n_esc) {
-        if (out_kind == 0) k_p5_decode_esc<0><<<(p.out_f + 7) / 8, 256, 0, st>>>(p, out);
-        else k_p5_decode_esc<1><<<(p.out_f + 7) / 8, 256, 0, st>>>(p, out);
+        if (out_kind == 0) k_p5_decode_esc<0><<<(nb + 7) / 8, 256, 0, st>>>(p, out);
+        else k_p5_decode_esc<1><<<(nb + 7) / 8, 256, 0, st>>>(p, out);
         rc = launch_check("k_p5_decode_esc");
     }
     return rc;
 }
 
-struct P5Plan { uint32_t nb, grid, xstride, smem, xs; size_t osum_bytes, slot_bytes; };
+struct P5Plan { uint32_t nb, grid, xstride, smem, xs; size_t slot_bytes; };
 
 static P5Plan make_p5_plan(uint32_t out_f, uint32_t in_f, uint32_t m_rows)
 {
@@ -816,11 +817,9 @@ static P5Plan make_p5_plan(uint32_t out_f, uint32_t in_f, uint32_t m_rows)
     p.grid = want < sms ? want : sms;
     if (!p.grid) p.grid = 1;
     p.xstride = kb * kP5TileCols + 8u;
-    uint32_t parts = kP5Warps * 2u * 32u * (uint32_t)sizeof(float4);
     uint32_t xbytes = m_rows * p.xstride * 2u;
-    p.xs = parts + xbytes <= 216u * 1024u;
-    p.smem = parts + (p.xs ? xbytes : 0u);
-    p.osum_bytes = (((size_t)m_rows * out_f * sizeof(float)) + 255u) & ~(size_t)255u;
+    p.xs = (uint32_t)kP5SmemFixed + xbytes <= 216u * 1024u;
+    p.smem = (uint32_t)kP5SmemFixed + (p.xs ? xbytes : 0u);
     p.slot_bytes = (size_t)p.grid * 2u * 32u * sizeof(float4);
     return p;
 }
@@ -829,12 +828,12 @@ extern "C" size_t ixb_p5_gemv_scratch_bytes(int64_t out_f, int64_t in_f, int64_t
 {
     if (out_f <= 0 || in_f <= 0 || m_rows <= 0) return 0;
     P5Plan p = make_p5_plan((uint32_t)out_f, (uint32_t)in_f, (uint32_t)m_rows);
-    return 1024 + p.osum_bytes + p.slot_bytes;
+    return 1024 + p.slot_bytes;
 }
 
 template <int XS>
-static void launch_p5(const P5 &p, const void *x, uint32_t m_rows, const void *bias, void *y, int y_f32, const float *osum,
-                      float4 *slots, uint32_t *ticket, const P5Plan &pl, cudaStream_t st)
+static void launch_p5(const P5 &p, const void *x, uint32_t m_rows, const void *bias, void *y, int y_f32, float4 *slots,
+                      uint32_t *tickets, const P5Plan &pl, cudaStream_t st)
 {
     static bool attr_set = false;
     if (!attr_set) {
@@ -842,7 +841,7 @@ static void launch_p5(const P5 &p, const void *x, uint32_t m_rows, const void *b
         attr_set = true;
     }
     k_p5_mma<XS><<<pl.grid, kP5Threads, pl.smem, st>>>(p, (const __nv_bfloat16 *)x, m_rows, (const __nv_bfloat16 *)bias, y,
-                                                       y_f32, osum, slots, ticket, pl.nb, pl.xstride);
+                                                       y_f32, slots, tickets, pl.nb, pl.xstride);
 }
 
 extern "C" int ixb_p5_gemv(const ixb_p5 *t, const void *x, int64_t m_rows, const void *bias, void *y, int y_is_f32,
@@ -859,26 +858,11 @@ extern "C" int ixb_p5_gemv(const ixb_p5 *t, const void *x, int64_t m_rows, const
     P5Plan pl = make_p5_plan(p.out_f, p.in_f, (uint32_t)m_rows);
     if (!pl.xs && (p.in_f % kP5TileCols))
         return fail(IXB_E_UNSUPPORTED, "in_f=%u: activations too large for shared memory need in_f %% 64 == 0", p.in_f);
-    uint32_t *ticket = (uint32_t *)scratch;
-    float *osum = (float *)((char *)scratch + 1024);          // the first 1024 bytes hold the tile tickets (grid + 1 words)
-    float4 *slots = (float4 *)((char *)scratch + 1024 + pl.osum_bytes);
+    uint32_t *tickets = (uint32_t *)scratch;                  // the first 1024 bytes hold the tile tickets (grid + 1 words)
+    float4 *slots = (float4 *)((char *)scratch + 1024);
     cudaStream_t st = (cudaStream_t)stream;
-    {
-        uint32_t blocks = (p.out_f + 7u) / 8u, cap = (uint32_t)num_sms() * 8u;
-        if (blocks > cap) blocks = cap;
-#define IXB_P5_OUT(MM)                                                                                        \
-    case MM:                                                                                                  \
-        k_p5_outliers<MM><<<blocks, 256, 0, st>>>(p, (const __nv_bfloat16 *)x, 0u, osum);                     \
-        break;
-        switch (m_rows) {
-            IXB_P5_OUT(1) IXB_P5_OUT(2) IXB_P5_OUT(3) IXB_P5_OUT(4)
-            IXB_P5_OUT(5) IXB_P5_OUT(6) IXB_P5_OUT(7) IXB_P5_OUT(8)
-        }
-#undef IXB_P5_OUT
-        if ((rc = launch_check("k_p5_outliers"))) return rc;
-    }
-    if (pl.xs) launch_p5<1>(p, x, (uint32_t)m_rows, bias, y, y_is_f32, osum, slots, ticket, pl, st);
-    else launch_p5<0>(p, x, (uint32_t)m_rows, bias, y, y_is_f32, osum, slots, ticket, pl, st);
+    if (pl.xs) launch_p5<1>(p, x, (uint32_t)m_rows, bias, y, y_is_f32, slots, tickets, pl, st);
+    else launch_p5<0>(p, x, (uint32_t)m_rows, bias, y, y_is_f32, slots, tickets, pl, st);
     return launch_check("k_p5_mma");
 }
 

@@ -14,18 +14,22 @@
 //           one mask, one subtract and one multiply per PAIR of elements the
 //           lane's registers ARE the A fragments of four
 //           mma.sync.m16n8k16 (bf16) instructions -- see p5_elem().
-//   esc     the level-3 elements as a CSR list: row_off[out_f + 1], and per
-//           entry a 16-bit column and an 8-bit code + 127, sorted by column.
+//   esc     the level-3 elements of every block as 32-bit entries
+//           (slot << 16) | bf16(code * scale): the weight itself, and the
+//           byte offset of the 16-bit A-fragment slot it belongs to in a
+//           1024-slot image of the block (p5_slot()); blk_off[nb + 1] gives
+//           the first entry of every block.
 //
-// Size: 5 + 24 * P(level 3) bits per weight (+ 4 bytes per row), i.e. ~5.72 bpw
+// Size: 5 + 32 * P(level 3) bits per weight + 4 bytes per block, i.e. ~6.0 bpw
 // for the benchmark distribution against 5.44 for the reference streams.
 //
-// y = W x then is: a sparse pass over the outliers (k_p5_outliers, fp32 FMAs,
-// one warp per row) followed by the plane pass (k_p5_mma), which turns fields
-// into bf16 weights bf16(code * scale) -- the reference's dequantised weights,
-// bit for bit (ixrun/quantize.py:201-204) -- and feeds them to the tensor cores
-// with the activations as the B operand: up to 8 activation rows cost the same
-// as one.  Products are exact, accumulation is fp32.
+// y = W x is one kernel (k_p5_mma): a warp turns a block's fields into bf16
+// weights bf16(code * scale) -- the reference's dequantised weights, bit for
+// bit (ixrun/quantize.py:201-204) -- which are the A operand of four mma.sync
+// with the activations as B; the block's outliers are scattered into a zeroed
+// fragment image in shared memory that feeds four more mma.sync.  Up to 8
+// activation rows cost the same as one.  Products are exact, accumulation is
+// fp32.
 #pragma once
 #include "ixb_common.cuh"
 
@@ -33,14 +37,14 @@ namespace ixb {
 
 constexpr int kP5TileRows = 16;
 constexpr int kP5TileCols = 64;
-constexpr int kP5SlackBlocks = 4;    // readable blocks behind the planes (the GEMV's prefetch runs past the end)
+constexpr int kP5SlackBlocks = 4;    // readable blocks behind the planes and offsets (the GEMV's prefetch runs past the end)
+constexpr int kP5SlackEntries = 64;  // readable entries behind the outlier list
 
 struct P5 {
-    const uint4 *w03;          // [nb * 32] plane words 0..3 of every lane of every block
-    const uint32_t *w4;        // [nb * 32] plane word 4
-    const int32_t *row_off;    // [out_f + 1] first outlier entry of every row
-    const uint16_t *esc_col;   // [n_esc] column of the entry
-    const uint8_t *esc_val;    // [n_esc] code + 127
+    const uint4 *w03;          // [(nb + slack) * 32] plane words 0..3 of every lane of every block
+    const uint32_t *w4;        // [(nb + slack) * 32] plane word 4
+    const int32_t *blk_off;    // [nb + 1 + slack] first outlier entry of every block (the slack repeats the total)
+    const uint32_t *esc;       // [n_esc + slack] outlier entries
     const __nv_bfloat16 *scale;
     uint32_t out_f, in_f;
     uint32_t rt, kb;           // row tiles, column blocks per row tile; nb = rt * kb
@@ -79,19 +83,25 @@ __device__ __forceinline__ uint32_t p5_get(const uint32_t (&w)[5], int p, int h)
     return f;
 }
 
+// Byte offset of element (lane, pair p, half h) in the block's fragment image: 64 uint4, uint4 (p >> 2) * 32 + lane
+// holds the lane's A registers of mma p >> 2, so that a lane reads its four registers with one conflict-free load.
+__device__ __forceinline__ uint32_t p5_slot(int lane, int p, int h)
+{
+    return (uint32_t)((((p >> 2) * 32 + lane) * 4 + (p & 3)) * 4 + 2 * h);
+}
+
 // ------------------------------------------------------------------ build ---
-// codes [out_f, in_f] -> plane words, and the number of outliers of every row (row_cnt, zeroed by the caller)
+// codes [out_f, in_f] -> plane words and the number of outliers of every block (one warp per block)
 __global__ void __launch_bounds__(256)
 k_p5_plane(const int8_t *__restrict__ codes, uint32_t out_f, uint32_t in_f, uint32_t rt, uint32_t kb,
-           uint4 *w03, uint32_t *w4, int32_t *row_cnt)
+           uint4 *w03, uint32_t *w4, int32_t *blk_cnt)
 {
     uint32_t b = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     int lane = threadIdx.x & 31;
     if (b >= rt * kb) return;
     uint32_t R = b / kb, kbi = b - R * kb;
-    int g = lane >> 2, t = lane & 3;
     uint32_t w[5] = {0, 0, 0, 0, 0};
-    uint32_t n_out[2] = {0, 0};
+    uint32_t n_out = 0;
 #pragma unroll
     for (int p = 0; p < 16; ++p) {
 #pragma unroll
@@ -101,43 +111,43 @@ k_p5_plane(const int8_t *__restrict__ codes, uint32_t out_f, uint32_t in_f, uint
             uint32_t row = R * kP5TileRows + r, col = kbi * kP5TileCols + c;
             int code = (row < out_f && col < in_f) ? (int)codes[(size_t)row * in_f + col] : 0;
             bool out = code > 15 || code < -15;
-            n_out[(p & 1)] += out;                  // q & 1 selects row g / g + 8
+            n_out += out;
             p5_put(w, p, h, out ? 15u : (uint32_t)(code + 15));
         }
     }
     w03[(size_t)b * 32u + lane] = make_uint4(w[0], w[1], w[2], w[3]);
     w4[(size_t)b * 32u + lane] = w[4];
-#pragma unroll
-    for (int s = 0; s < 2; ++s) {
-        uint32_t v = n_out[s];
-        v += __shfl_xor_sync(0xffffffffu, v, 1);
-        v += __shfl_xor_sync(0xffffffffu, v, 2);
-        uint32_t row = R * kP5TileRows + g + 8 * s;
-        if (t == 0 && v && row < out_f) atomicAdd(row_cnt + row, (int32_t)v);     // integer count: order does not matter
-    }
+    n_out = warp_incl_scan(n_out, lane);
+    if (lane == 31) blk_cnt[b] = (int32_t)n_out;
 }
 
-// outlier entries of every row in column order (one warp per row)
+// outlier entries of every block, in (lane, pair, half) order (one warp per block)
 __global__ void __launch_bounds__(256)
-k_p5_csr(const int8_t *__restrict__ codes, uint32_t out_f, uint32_t in_f, const int32_t *__restrict__ row_off,
-         uint16_t *esc_col, uint8_t *esc_val)
+k_p5_esc(const int8_t *__restrict__ codes, uint32_t out_f, uint32_t in_f, uint32_t rt, uint32_t kb,
+         const int32_t *__restrict__ blk_off, const __nv_bfloat16 *__restrict__ scale, uint32_t *esc)
 {
-    uint32_t row = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    uint32_t b = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     int lane = threadIdx.x & 31;
-    if (row >= out_f) return;
-    uint32_t at = (uint32_t)row_off[row];
-    const int8_t *src = codes + (size_t)row * in_f;
-    for (uint32_t k0 = 0; k0 < in_f; k0 += 32) {
-        uint32_t k = k0 + lane;
-        int c = k < in_f ? (int)src[k] : 0;
-        bool out = c > 15 || c < -15;
-        uint32_t m = __ballot_sync(0xffffffffu, out);
-        if (out) {
-            uint32_t i = at + __popc(m & ((1u << lane) - 1u));
-            esc_col[i] = (uint16_t)k;
-            esc_val[i] = (uint8_t)(c + 127);
+    if (b >= rt * kb) return;
+    uint32_t R = b / kb, kbi = b - R * kb;
+    float sc = __bfloat162float(*scale);
+    int code[32];
+    uint32_t n_out = 0;
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+        uint32_t r, c;
+        p5_elem(lane, i >> 1, i & 1, r, c);
+        uint32_t row = R * kP5TileRows + r, col = kbi * kP5TileCols + c;
+        code[i] = (row < out_f && col < in_f) ? (int)codes[(size_t)row * in_f + col] : 0;
+        n_out += (code[i] > 15 || code[i] < -15);
+    }
+    uint32_t at = (uint32_t)blk_off[b] + warp_incl_scan(n_out, lane) - n_out;
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+        if (code[i] > 15 || code[i] < -15) {
+            uint32_t wbits = __bfloat16_as_ushort(__float2bfloat16_rn((float)code[i] * sc));
+            esc[at++] = (p5_slot(lane, i >> 1, i & 1) << 16) | wbits;
         }
-        at += __popc(m);
     }
 }
 
@@ -169,64 +179,33 @@ __global__ void __launch_bounds__(256) k_p5_decode_plane(P5 p, void *out)
     }
 }
 
-// the outliers overwrite their placeholders (launched after k_p5_decode_plane on the same stream)
+// The outliers overwrite their placeholders (launched after k_p5_decode_plane on the same stream; one warp per
+// block).  An entry carries the bf16 weight w = bf16(code * scale).  The code is recovered from it exactly:
+// neighbouring codes differ by scale >= |code * scale| / 127, which is more than one bf16 ulp (2^-7 relative),
+// so no two codes share a weight, and w / scale is within 0.25 of the code.
 template <int OUT>
 __global__ void __launch_bounds__(256) k_p5_decode_esc(P5 p, void *out)
 {
-    uint32_t row = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    uint32_t b = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     int lane = threadIdx.x & 31;
-    if (row >= p.out_f) return;
+    if (b >= p.rt * p.kb) return;
+    uint32_t R = b / p.kb, kbi = b - R * p.kb;
     float sc = __bfloat162float(*p.scale);
-    for (int32_t j = p.row_off[row] + lane; j < p.row_off[row + 1]; j += 32) {
-        int code = (int)p.esc_val[j] - 127;
-        size_t o = (size_t)row * p.in_f + p.esc_col[j];
-        if (OUT == 0) ((int8_t *)out)[o] = (int8_t)code;
-        else ((__nv_bfloat16 *)out)[o] = __float2bfloat16_rn((float)code * sc);
-    }
-}
-
-// -------------------------------------------------------------- outliers ----
-// osum[m][row] = sum over the row's outliers of x[m0 + m][col] * bf16(code * scale), m < MC   (one warp per row)
-template <int MC>
-__global__ void __launch_bounds__(256)
-k_p5_outliers(P5 p, const __nv_bfloat16 *__restrict__ x, uint32_t m0, float *__restrict__ osum)
-{
-    const int lane = threadIdx.x & 31;
-    const uint32_t n_warps = (gridDim.x * blockDim.x) >> 5;
-    uint32_t sb = (uint32_t)__bfloat16_as_ushort(*p.scale);
-    const uint32_t s2 = sb | (sb << 16);
-    const unsigned short *xu = (const unsigned short *)x;
-    for (uint32_t row = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; row < p.out_f; row += n_warps) {
-        float acc[MC];
-#pragma unroll
-        for (int m = 0; m < MC; ++m) acc[m] = 0.f;
-        const int32_t end = __ldg(p.row_off + row + 1);
-        for (int32_t j0 = __ldg(p.row_off + row) + lane; j0 < end; j0 += 128) {
-            // four entries per lane in flight: all entry loads, then all activation loads, then the FMAs
-            uint32_t col[4], val[4];
-#pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                int32_t j = j0 + 32 * u;
-                bool ok = j < end;
-                col[u] = ok ? (uint32_t)__ldg(p.esc_col + j) : 0u;
-                val[u] = ok ? (uint32_t)__ldg(p.esc_val + j) : 127u;      // code 0
-            }
-#pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                float cf = (float)((int)val[u] - 127);
-                uint32_t wv;       // upper half: bf16(code * scale); lower half: bf16(0 * scale) = 0
-                asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(wv) : "r"(__float_as_uint(cf)), "r"(s2));
-#pragma unroll
-                for (int m = 0; m < MC; ++m) {
-                    float xf = __uint_as_float((uint32_t)__ldg(xu + (size_t)(m0 + m) * p.in_f + col[u]) << 16);
-                    acc[m] = fmaf(xf, __uint_as_float(wv), acc[m]);
-                }
-            }
-        }
-#pragma unroll
-        for (int m = 0; m < MC; ++m) {
-            float v = warp_sum(acc[m]);
-            if (lane == 0) osum[(size_t)(m0 + m) * p.out_f + row] = v;
+    for (int32_t j = p.blk_off[b] + lane; j < p.blk_off[b + 1]; j += 32) {
+        uint32_t ent = p.esc[j];
+        uint32_t slot = ent >> 16;                       // ((mma * 32 + lane) * 4 + q) * 4 + 2 h
+        int h = (slot >> 1) & 1, q = (slot >> 2) & 3, ln = (slot >> 4) & 31, j4 = slot >> 9;
+        uint32_t r, c;
+        p5_elem(ln, 4 * j4 + q, h, r, c);
+        uint32_t row = R * kP5TileRows + r, col = kbi * kP5TileCols + c;
+        if (row >= p.out_f || col >= p.in_f) continue;
+        size_t o = (size_t)row * p.in_f + col;
+        __nv_bfloat16 wv = __ushort_as_bfloat16((unsigned short)(ent & 0xffffu));
+        if (OUT == 1) {
+            ((__nv_bfloat16 *)out)[o] = wv;
+        } else {
+            int best = __float2int_rn(__bfloat162float(wv) / sc);
+            ((int8_t *)out)[o] = (int8_t)best;
         }
     }
 }
@@ -234,6 +213,7 @@ k_p5_outliers(P5 p, const __nv_bfloat16 *__restrict__ x, uint32_t m0, float *__r
 // ------------------------------------------------------------- plane pass ---
 constexpr int kP5Threads = 1024;
 constexpr int kP5Warps = kP5Threads / 32;
+constexpr int kP5SmemFixed = kP5Warps * (2 * 32 * 16 + 4 * 32 * 16);   // partial sums + outlier fragment images
 
 // (SRC & 0x001F001F) | 0x43004300: the two fields of a pair as the bf16 values 128 + field
 __device__ __forceinline__ uint32_t p5_pair_raw(uint32_t src, uint32_t magic)
@@ -269,8 +249,7 @@ __device__ __forceinline__ void p5_mma(float (&c)[4], uint32_t a0, uint32_t a1, 
 
 // Final value of a row tile's C fragment image: lane (g, t) holds rows g, g + 8 and activation rows 2 t, 2 t + 1.
 __device__ __forceinline__ void p5_store_tile(const P5 &p, uint32_t R, int lane, const float (&c)[4], uint32_t m_rows,
-                                              const float *__restrict__ osum, const __nv_bfloat16 *__restrict__ bias,
-                                              void *y, int y_f32)
+                                              const __nv_bfloat16 *__restrict__ bias, void *y, int y_f32)
 {
     const int g = lane >> 2, t = lane & 3;
 #pragma unroll
@@ -278,7 +257,7 @@ __device__ __forceinline__ void p5_store_tile(const P5 &p, uint32_t R, int lane,
         uint32_t m = 2u * t + (i & 1), row = R * kP5TileRows + g + 8 * (i >> 1);
         if (m >= m_rows || row >= p.out_f) continue;
         size_t o = (size_t)m * p.out_f + row;
-        float v = c[i] + osum[o];
+        float v = c[i];
         if (y_f32) {
             ((float *)y)[o] = bias ? v + __bfloat162float(bias[row]) : v;
         } else {
@@ -309,11 +288,12 @@ __device__ __forceinline__ uint32_t p5_part_of(uint32_t pos, uint32_t n, uint32_
 template <int XS>
 __global__ void __launch_bounds__(kP5Threads, 1)
 k_p5_mma(P5 p, const __nv_bfloat16 *__restrict__ x, uint32_t m_rows, const __nv_bfloat16 *__restrict__ bias, void *y,
-         int y_f32, const float *__restrict__ osum, float4 *cta_slots, uint32_t *tickets, uint32_t nb, uint32_t xstride)
+         int y_f32, float4 *cta_slots, uint32_t *tickets, uint32_t nb, uint32_t xstride)
 {
     extern __shared__ __align__(16) unsigned char p5_smem[];
-    float4 *parts = (float4 *)p5_smem;                                  // [warp][2][32 lanes]
-    __nv_bfloat16 *xs = (__nv_bfloat16 *)(p5_smem + kP5Warps * 2 * 32 * sizeof(float4));   // [m_rows][xstride]
+    float4 *parts = (float4 *)p5_smem;                                  // [warp][2][32 lanes] partial tile sums
+    uint4 *images = (uint4 *)(p5_smem + kP5Warps * 2 * 32 * sizeof(float4));             // [warp][4 mma][32 lanes]
+    __nv_bfloat16 *xs = (__nv_bfloat16 *)(p5_smem + kP5SmemFixed);                       // [m_rows][xstride]
 
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
     const int g = lane >> 2, t = lane & 3;
@@ -364,11 +344,18 @@ k_p5_mma(P5 p, const __nv_bfloat16 *__restrict__ x, uint32_t m_rows, const __nv_
         uint32_t xo = (b_begin - R * KB) * kP5TileCols;
 
         auto flush_tile = [&](bool whole) {
-            if (whole) p5_store_tile(p, R, lane, c, m_rows, osum, bias, y, y_f32);
+            if (whole) p5_store_tile(p, R, lane, c, m_rows, bias, y, y_f32);
             else parts[(wid * 2 + (R == R_first ? 0 : 1)) * 32 + lane] = make_float4(c[0], c[1], c[2], c[3]);
             c[0] = c[1] = c[2] = c[3] = 0.f;
         };
-        auto process = [&](const uint4 a, const uint32_t w4) {
+        uint4 *img = images + wid * 4 * 32;                      // this warp's fragment image, all zero between blocks
+        const uint32_t img_s = (uint32_t)__cvta_generic_to_shared(img);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) img[q * 32 + lane] = make_uint4(0, 0, 0, 0);
+        __syncwarp();
+
+        auto process = [&](const uint4 a, const uint32_t w4, const uint32_t ent0, const uint32_t ent1, const int32_t o_lo,
+                           const int32_t o_hi) {
             const uint4 x0 = *(const uint4 *)(xl + xo);
             const uint4 x1 = *(const uint4 *)(xl + xo + 8);
             const uint32_t w[5] = {a.x, a.y, a.z, a.w, w4};
@@ -392,6 +379,27 @@ k_p5_mma(P5 p, const __nv_bfloat16 *__restrict__ x, uint32_t m_rows, const __nv_
             p5_mma(c, f[4], f[5], f[6], f[7], x0.z, x0.w);
             p5_mma(c, f[8], f[9], f[10], f[11], x1.x, x1.y);
             p5_mma(c, f[12], f[13], f[14], f[15], x1.z, x1.w);
+            const int32_t cnt = o_hi - o_lo;
+            if (cnt > 0) {
+                // the block's outliers: entry j goes to lane j % 32 (two were prefetched, the rest is rare), which
+                // drops the weight into its slot of the image; then every lane takes its four A registers per mma
+                // from the image and clears them again
+                if (lane < cnt) asm volatile("st.shared.u16 [%0], %1;" ::"r"(img_s + (ent0 >> 16)), "h"((unsigned short)ent0));
+                if (lane + 32 < cnt) asm volatile("st.shared.u16 [%0], %1;" ::"r"(img_s + (ent1 >> 16)), "h"((unsigned short)ent1));
+                for (int32_t j = 64 + lane; j < cnt; j += 32) {
+                    uint32_t e = __ldg(p.esc + o_lo + j);
+                    asm volatile("st.shared.u16 [%0], %1;" ::"r"(img_s + (e >> 16)), "h"((unsigned short)e));
+                }
+                __syncwarp();
+                const uint4 q0 = img[lane], q1 = img[32 + lane], q2 = img[64 + lane], q3 = img[96 + lane];
+#pragma unroll
+                for (int q = 0; q < 4; ++q) img[q * 32 + lane] = make_uint4(0, 0, 0, 0);
+                __syncwarp();
+                p5_mma(c, q0.x, q0.y, q0.z, q0.w, x0.x, x0.y);
+                p5_mma(c, q1.x, q1.y, q1.z, q1.w, x0.z, x0.w);
+                p5_mma(c, q2.x, q2.y, q2.z, q2.w, x1.x, x1.y);
+                p5_mma(c, q3.x, q3.y, q3.z, q3.w, x1.z, x1.w);
+            }
             xo += kP5TileCols;
             if (xo == xo_end) {                      // the tile is complete, or this was its last part
                 flush_tile(from_start);
@@ -400,32 +408,47 @@ k_p5_mma(P5 p, const __nv_bfloat16 *__restrict__ x, uint32_t m_rows, const __nv_
                 from_start = true;
             }
         };
-        // two blocks' plane words in flight; the registers alternate by unrolling, not by copying.  The loads
-        // run up to two blocks past the end of the run: the planes are allocated with that much slack.
+        // Two blocks' plane words and one block's first 64 outlier entries are in flight; the registers alternate
+        // by unrolling, not by copying.  The loads run up to two blocks past the end of the run: planes, offsets
+        // and entries are allocated with that much slack.
         uint32_t idx = b_begin * 32u + lane;
         uint4 a0 = p.w03[idx], a1 = p.w03[idx + 32u];
         uint32_t e0 = p.w4[idx], e1 = p.w4[idx + 32u];
         idx += 64u;
+        const int32_t *offp = p.blk_off + b_begin;
+        int32_t oa = __ldg(offp), ob = __ldg(offp + 1), oc = __ldg(offp + 2);       // off[b], off[b + 1], off[b + 2]
+        offp += 3;
+        uint32_t n0 = __ldg(p.esc + oa + lane), n1 = __ldg(p.esc + oa + 32 + lane);  // entries of block b
         uint32_t left = b_end - b_begin;
         while (true) {
             {
                 const uint4 a = a0;
-                const uint32_t e = e0;
+                const uint32_t e = e0, t0 = n0, t1 = n1;
+                const int32_t lo = oa, hi = ob;
                 a0 = p.w03[idx];
                 e0 = p.w4[idx];
-                process(a, e);
+                n0 = __ldg(p.esc + ob + lane);
+                n1 = __ldg(p.esc + ob + 32 + lane);
+                oa = ob; ob = oc; oc = __ldg(offp);
+                process(a, e, t0, t1, lo, hi);
                 if (--left == 0) break;
             }
             {
                 const uint4 a = a1;
-                const uint32_t e = e1;
+                const uint32_t e = e1, t0 = n0, t1 = n1;
+                const int32_t lo = oa, hi = ob;
                 a1 = p.w03[idx + 32u];
                 e1 = p.w4[idx + 32u];
                 idx += 64u;
-                process(a, e);
+                n0 = __ldg(p.esc + ob + lane);
+                n1 = __ldg(p.esc + ob + 32 + lane);
+                oa = ob; ob = oc; oc = __ldg(offp + 1);
+                offp += 2;
+                process(a, e, t0, t1, lo, hi);
                 if (--left == 0) break;
             }
         }
+        __syncwarp();
         if (xo != 0) flush_tile(false);
     }
     __syncthreads();
@@ -448,7 +471,7 @@ k_p5_mma(P5 p, const __nv_bfloat16 *__restrict__ x, uint32_t m_rows, const __nv_
             }
             if (inside) {
                 const float cc[4] = {s.x, s.y, s.z, s.w};
-                p5_store_tile(p, R, lane, cc, m_rows, osum, bias, y, y_f32);
+                p5_store_tile(p, R, lane, cc, m_rows, bias, y, y_f32);
                 continue;
             }
             // shared with other CTAs: publish this CTA's sum, take a ticket; the last one finishes the tile
@@ -468,7 +491,7 @@ k_p5_mma(P5 p, const __nv_bfloat16 *__restrict__ x, uint32_t m_rows, const __nv_
                 z.x += __ldcg(&sl->x); z.y += __ldcg(&sl->y); z.z += __ldcg(&sl->z); z.w += __ldcg(&sl->w);
             }
             const float cc4[4] = {z.x, z.y, z.z, z.w};
-            p5_store_tile(p, R, lane, cc4, m_rows, osum, bias, y, y_f32);
+            p5_store_tile(p, R, lane, cc4, m_rows, bias, y, y_f32);
             if (lane == 0) tickets[clo + 1] = 0;
         }
     }

@@ -2,8 +2,8 @@
 
 The (3,5,8) streams remain the interchange format.  ``P5Packed.from_packed``
 transcodes them on the GPU (decode to int8 codes, re-pack as a plane of fixed
-5-bit fields in tensor-core fragment order + a CSR list of the level-3
-values); the int8 codes, and therefore every weight the reference would decode,
+5-bit fields in tensor-core fragment order + the level-3 weights of every
+block as a short list); the int8 codes, and therefore every weight the reference would decode,
 are preserved exactly.  The GEMV on this layout needs ~3 instructions per
 weight instead of ~34 and costs the same for 1..8 activation rows.
 """
@@ -32,25 +32,22 @@ class P5Packed:
         if n_esc is None:
             n_esc = int((c.to(torch.int16).abs() > 15).sum().item())
         L = _lib.lib()
-        if in_f > 65536:
-            raise _lib.IxbError(f"in_f={in_f} does not fit the 16-bit outlier columns of the P5 layout")
         nb = int(L.ixb_p5_blocks(self.out_f, self.in_f))
-        self.w03 = torch.empty(nb * 32 * 4, dtype=torch.int32, device=dev)
-        self.w4 = torch.empty(nb * 32, dtype=torch.int32, device=dev)
-        self.row_off = torch.empty(self.out_f + 1, dtype=torch.int32, device=dev)
-        self.esc_col = torch.empty(max(n_esc, 1), dtype=torch.int16, device=dev)
-        self.esc_val = torch.empty(max(n_esc, 1), dtype=torch.uint8, device=dev)
+        # sizes include the slack that the GEMV's prefetch may read (4 blocks, 64 entries)
+        self.w03 = torch.empty((nb + 4) * 32 * 4, dtype=torch.int32, device=dev)
+        self.w4 = torch.empty((nb + 4) * 32, dtype=torch.int32, device=dev)
+        self.blk_off = torch.empty(nb + 5, dtype=torch.int32, device=dev)
+        self.esc = torch.empty(n_esc + 64, dtype=torch.int32, device=dev)
         self.n_esc = n_esc
         self.scale = scale.detach().to(dev, torch.bfloat16).reshape(()).contiguous()
-        ws = torch.empty((self.out_f + 1) * 4, dtype=torch.uint8, device=dev)
+        ws = torch.empty((nb + 5) * 4, dtype=torch.uint8, device=dev)
         with torch.cuda.device(dev):
-            _lib.check(L.ixb_p5_build(c.data_ptr(), self.out_f, self.in_f, self.w03.data_ptr(), self.w4.data_ptr(),
-                                      self.row_off.data_ptr(), self.esc_col.data_ptr(), self.esc_val.data_ptr(), n_esc,
+            _lib.check(L.ixb_p5_build(c.data_ptr(), self.scale.data_ptr(), self.out_f, self.in_f, self.w03.data_ptr(),
+                                      self.w4.data_ptr(), self.blk_off.data_ptr(), self.esc.data_ptr(), n_esc,
                                       ws.data_ptr(), ws.numel(), _lib.stream_ptr(dev)))
-        self.struct = _lib.P5Struct(self.w03.data_ptr(), self.w4.data_ptr(), self.row_off.data_ptr(),
-                                    self.esc_col.data_ptr(), self.esc_val.data_ptr(), n_esc, self.scale.data_ptr(),
-                                    self.out_f, self.in_f)
-        self.resident_bytes = 4 * (self.w03.numel() + self.w4.numel() + self.row_off.numel()) + 3 * n_esc + 2
+        self.struct = _lib.P5Struct(self.w03.data_ptr(), self.w4.data_ptr(), self.blk_off.data_ptr(),
+                                    self.esc.data_ptr(), n_esc, self.scale.data_ptr(), self.out_f, self.in_f)
+        self.resident_bytes = 4 * (nb * 160 + nb + 1 + n_esc) + 2
         self._scratch = {}
 
     @classmethod

@@ -101,4 +101,4 @@ def test_p5_full_size_agrees_with_the_stream_kernel(out_f, in_f):
         y = p5.gemv(x, out_dtype=torch.float32)
         assert float((y - ref).abs().max() / ref.abs().max()) < 2e-5
         assert torch.equal(p5.gemv(x, out_dtype=torch.float32), y)
-    assert p5.resident_bytes < 1.08 * dp.total_bytes
+    assert p5.resident_bytes < 1.12 * dp.total_bytes
