@@ -177,7 +177,8 @@ def run_gpu(args):
         full_bytes = packed["total_bytes"]
     alg_bytes = algorithmic_bytes(full_bytes)
     alg_bytes_rank = packed["total_bytes"] + 2 * in_loc + 2 * OUT_F
-    layers = [StreamingLinear(packed) for _ in range(COPIES)]
+    layers = [StreamingLinear(packed, resident=args.layout) for _ in range(COPIES)]
+    resident_bytes = layers[0]._p5.resident_bytes if args.layout == "p5" else packed["total_bytes"]
     g = torch.Generator().manual_seed(1)
     x_host = torch.randn(1, IN_F, generator=g).bfloat16()[:, rank * in_loc:(rank + 1) * in_loc].contiguous().pin_memory()
     x = x_host.to(dev)
@@ -187,11 +188,11 @@ def run_gpu(args):
     def step(i):
         lay = layers[i % COPIES]
         if world > 1:
-            lay._dp.gemv(x, out=y32)
+            lay.matvec(x, out=y32)
             dist.all_reduce(y32)
             y16.copy_(y32)
         else:
-            lay._dp.gemv(x, out=y16)
+            lay.matvec(x, out=y16)
 
     def barrier():
         if world > 1:
@@ -247,7 +248,7 @@ def run_gpu(args):
     for i in range(reps):
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a.record()
-        layers[i % COPIES]._dp.gemv(x, out=y16)
+        layers[i % COPIES].matvec(x, out=y16)
         b.record()
         b.synchronize()
         kt.append(a.elapsed_time(b))
@@ -262,7 +263,7 @@ def run_gpu(args):
     def e2e_step(i):
         xd = x_host.to(dev, non_blocking=True)
         if world > 1:
-            layers[i % COPIES]._dp.gemv(xd, out=y32)
+            layers[i % COPIES].matvec(xd, out=y32)
             dist.all_reduce(y32)
             y_host.copy_(y32.to(torch.bfloat16), non_blocking=True)
         else:
@@ -289,12 +290,16 @@ def run_gpu(args):
         "config": {
             "workload": f"down_proj {OUT_F}x{IN_F} batch 1 fused decode+GEMV, (3,5,8) codes ~ round(Laplace(0,4.4))",
             "algorithmic_bytes_per_step": alg_bytes,
-            "l2": f"timed steps rotate over {COPIES} device copies of the packed streams ({COPIES * full_bytes // world / 1e6:.0f} MB per GPU)",
+            "layout": ("resident P5 re-layout of the same int8 codes (5-bit plane in mma fragment order + level-3 weight list), "
+                       "built on the GPU at deploy time from the reference's packed streams" if args.layout == "p5"
+                       else "the reference's (3,5,8) streams read directly"),
+            "resident_bytes_per_gpu": resident_bytes,
+            "l2": f"timed steps rotate over {COPIES} device copies of the weights ({COPIES * resident_bytes / 1e6:.0f} MB per GPU)",
             "parallelism": "single GPU" if world == 1 else f"tp{world}: column shards of in_f, one NCCL all-reduce of y per step",
             "timed_with": "CUDA events around one graph replay of K launches" if graph is not None else "CUDA events around K eager steps",
         },
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "traffic": None, "peak_source": peak_src, "kernel": "k_gemv<1>",
+                     "traffic": None, "peak_source": peak_src, "kernel": "k_p5_mma<1>" if args.layout == "p5" else "k_gemv<1>",
                      "algorithmic_bytes_per_launch": alg_bytes_rank, "launch_ms": k_ms},
         "e2e": {"value": alg_bytes / e2e_s / 1e9, "unit": UNIT, "h2d_bytes_per_step": 2 * in_loc,
                 "d2h_bytes_per_step": 2 * OUT_F, "ms_per_step": e2e_s * 1e3, "steps": e2e_steps},
@@ -310,7 +315,7 @@ def run_gpu(args):
         traffic = os.path.join(ROOT, "profiles", "gemv_traffic.json")
         if world == 1 and os.path.exists(traffic):
             with open(traffic) as f:
-                line["roofline"]["traffic"] = json.load(f).get("dram_bytes_per_launch")
+                line["roofline"]["traffic"] = json.load(f).get(line["roofline"]["kernel"], {}).get("dram_bytes_per_launch")
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
@@ -323,6 +328,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--eager", action="store_true", help="launch the timed steps one by one instead of one CUDA graph")
+    ap.add_argument("--layout", default="p5", choices=["p5", "streams"],
+                    help="resident weight layout: the P5 re-layout (default) or the reference's streams read directly")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

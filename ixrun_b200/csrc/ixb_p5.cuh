@@ -152,7 +152,8 @@ k_p5_esc(const int8_t *__restrict__ codes, uint32_t out_f, uint32_t in_f, uint32
 }
 
 // ---------------------------------------------------------------- decode ----
-// plane -> int8 codes (OUT 0) or bf16 weights (OUT 1), row major [out_f, in_f]; outliers come out as 0 here
+// plane -> int8 codes (OUT 0) or bf16 weights (OUT 1), row major [out_f, in_f]; outliers come out as 0 here.
+// A lane holds 16 consecutive columns of two rows: one or two 16-byte stores per row.
 template <int OUT>
 __global__ void __launch_bounds__(256) k_p5_decode_plane(P5 p, void *out)
 {
@@ -163,18 +164,30 @@ __global__ void __launch_bounds__(256) k_p5_decode_plane(P5 p, void *out)
     float sc = __bfloat162float(*p.scale);
     uint4 a = p.w03[(size_t)b * 32u + lane];
     uint32_t w[5] = {a.x, a.y, a.z, a.w, p.w4[(size_t)b * 32u + lane]};
+    const bool vec = (OUT == 0 ? (p.in_f & 15u) == 0 : (p.in_f & 7u) == 0) && ((uintptr_t)out & 15u) == 0;
 #pragma unroll
-    for (int pr = 0; pr < 16; ++pr) {
+    for (int s = 0; s < 2; ++s) {                    // row g, row g + 8
+        uint32_t row = R * kP5TileRows + (lane >> 2) + 8 * s, col0 = kbi * kP5TileCols + 16 * (lane & 3);
+        if (row >= p.out_f || col0 >= p.in_f) continue;
+        uint32_t r[OUT == 0 ? 4 : 8];
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
-            uint32_t r, c;
-            p5_elem(lane, pr, h, r, c);
-            uint32_t row = R * kP5TileRows + r, col = kbi * kP5TileCols + c;
-            if (row >= p.out_f || col >= p.in_f) continue;
-            int code = (int)p5_get(w, pr, h) - 15;
-            size_t o = (size_t)row * p.in_f + col;
-            if (OUT == 0) ((int8_t *)out)[o] = (int8_t)code;
-            else ((__nv_bfloat16 *)out)[o] = __float2bfloat16_rn((float)code * sc);
+        for (int i = 0; i < (OUT == 0 ? 4 : 8); ++i) r[i] = 0;
+#pragma unroll
+        for (int c = 0; c < 16; ++c) {               // column col0 + c = pair 4 (c >> 2) + 2 ((c >> 1) & 1) + s, half c & 1
+            int code = (int)p5_get(w, 4 * (c >> 2) + 2 * ((c >> 1) & 1) + s, c & 1) - 15;
+            if (OUT == 0) r[c >> 2] |= (uint32_t)(code & 0xff) << (8 * (c & 3));
+            else r[c >> 1] |= (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn((float)code * sc)) << (16 * (c & 1));
+        }
+        size_t o = (size_t)row * p.in_f + col0;
+        if (vec && col0 + 16u <= p.in_f) {
+            uint4 *dst = (uint4 *)((char *)out + o * (OUT == 0 ? 1 : 2));
+            dst[0] = make_uint4(r[0], r[1], r[2], r[3]);
+            if (OUT == 1) dst[1] = make_uint4(r[4], r[5], r[6], r[7]);
+        } else {
+            for (uint32_t c = 0; c < 16u && col0 + c < p.in_f; ++c) {
+                if (OUT == 0) ((int8_t *)out)[o + c] = (int8_t)((r[c >> 2] >> (8 * (c & 3))) & 0xff);
+                else ((uint16_t *)out)[o + c] = (uint16_t)((r[c >> 1] >> (16 * (c & 1))) & 0xffff);
+            }
         }
     }
 }
@@ -211,7 +224,7 @@ __global__ void __launch_bounds__(256) k_p5_decode_esc(P5 p, void *out)
 }
 
 // ------------------------------------------------------------- plane pass ---
-constexpr int kP5Threads = 1024;
+constexpr int kP5Threads = 768;
 constexpr int kP5Warps = kP5Threads / 32;
 constexpr int kP5SmemFixed = kP5Warps * (2 * 32 * 16 + 4 * 32 * 16);   // partial sums + outlier fragment images
 
@@ -332,7 +345,7 @@ k_p5_mma(P5 p, const __nv_bfloat16 *__restrict__ x, uint32_t m_rows, const __nv_
     const uint32_t b_begin = cb0 + p5_part_begin(wid, L, kP5Warps), b_end = cb0 + p5_part_begin(wid + 1, L, kP5Warps);
 
     if (b_begin < b_end) {
-        float c[4] = {0.f, 0.f, 0.f, 0.f};
+        float c[4] = {0.f, 0.f, 0.f, 0.f}, c2[4] = {0.f, 0.f, 0.f, 0.f};       // plane / outlier accumulators
         uint32_t R = b_begin / KB;
         const uint32_t R_first = R;
         bool from_start = b_begin == R * KB;          // the current tile's first block belongs to this run
@@ -344,6 +357,11 @@ k_p5_mma(P5 p, const __nv_bfloat16 *__restrict__ x, uint32_t m_rows, const __nv_
         uint32_t xo = (b_begin - R * KB) * kP5TileCols;
 
         auto flush_tile = [&](bool whole) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                c[i] += c2[i];
+                c2[i] = 0.f;
+            }
             if (whole) p5_store_tile(p, R, lane, c, m_rows, bias, y, y_f32);
             else parts[(wid * 2 + (R == R_first ? 0 : 1)) * 32 + lane] = make_float4(c[0], c[1], c[2], c[3]);
             c[0] = c[1] = c[2] = c[3] = 0.f;
@@ -379,26 +397,30 @@ k_p5_mma(P5 p, const __nv_bfloat16 *__restrict__ x, uint32_t m_rows, const __nv_
             p5_mma(c, f[4], f[5], f[6], f[7], x0.z, x0.w);
             p5_mma(c, f[8], f[9], f[10], f[11], x1.x, x1.y);
             p5_mma(c, f[12], f[13], f[14], f[15], x1.z, x1.w);
-            const int32_t cnt = o_hi - o_lo;
-            if (cnt > 0) {
-                // the block's outliers: entry j goes to lane j % 32 (two were prefetched, the rest is rare), which
-                // drops the weight into its slot of the image; then every lane takes its four A registers per mma
-                // from the image and clears them again
-                if (lane < cnt) asm volatile("st.shared.u16 [%0], %1;" ::"r"(img_s + (ent0 >> 16)), "h"((unsigned short)ent0));
-                if (lane + 32 < cnt) asm volatile("st.shared.u16 [%0], %1;" ::"r"(img_s + (ent1 >> 16)), "h"((unsigned short)ent1));
-                for (int32_t j = 64 + lane; j < cnt; j += 32) {
-                    uint32_t e = __ldg(p.esc + o_lo + j);
-                    asm volatile("st.shared.u16 [%0], %1;" ::"r"(img_s + (e >> 16)), "h"((unsigned short)e));
+            {
+                // The block's outliers: entry j goes to lane j % 32 (two were prefetched, more than 64 per block
+                // is rare), which drops the weight into its slot of the image.  Then every lane takes its four A
+                // registers per mma from the image and clears them.
+                const int32_t rel = (int32_t)lane - (o_hi - o_lo);          // < 0: this lane has a first entry
+                const uint32_t s0 = img_s + (ent0 >> 16), s1 = img_s + (ent1 >> 16);
+                if (rel < 0) asm volatile("st.shared.u16 [%0], %1;" ::"r"(s0), "h"((unsigned short)ent0));
+                if (rel < -32) asm volatile("st.shared.u16 [%0], %1;" ::"r"(s1), "h"((unsigned short)ent1));
+                const bool many = o_hi - o_lo > 64;                          // warp uniform
+                if (many) {
+                    for (int32_t j = 64 + lane; j < o_hi - o_lo; j += 32) {
+                        uint32_t e = __ldg(p.esc + o_lo + j);
+                        asm volatile("st.shared.u16 [%0], %1;" ::"r"(img_s + (e >> 16)), "h"((unsigned short)e));
+                    }
                 }
                 __syncwarp();
                 const uint4 q0 = img[lane], q1 = img[32 + lane], q2 = img[64 + lane], q3 = img[96 + lane];
 #pragma unroll
                 for (int q = 0; q < 4; ++q) img[q * 32 + lane] = make_uint4(0, 0, 0, 0);
-                __syncwarp();
-                p5_mma(c, q0.x, q0.y, q0.z, q0.w, x0.x, x0.y);
-                p5_mma(c, q1.x, q1.y, q1.z, q1.w, x0.z, x0.w);
-                p5_mma(c, q2.x, q2.y, q2.z, q2.w, x1.x, x1.y);
-                p5_mma(c, q3.x, q3.y, q3.z, q3.w, x1.z, x1.w);
+                __syncwarp();                // the image is clear before any lane writes the next block's entries
+                p5_mma(c2, q0.x, q0.y, q0.z, q0.w, x0.x, x0.y);
+                p5_mma(c2, q1.x, q1.y, q1.z, q1.w, x0.z, x0.w);
+                p5_mma(c2, q2.x, q2.y, q2.z, q2.w, x1.x, x1.y);
+                p5_mma(c2, q3.x, q3.y, q3.z, q3.w, x1.z, x1.w);
             }
             xo += kP5TileCols;
             if (xo == xo_end) {                      // the tile is complete, or this was its last part

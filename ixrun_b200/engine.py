@@ -36,9 +36,18 @@ class StreamingLinear(nn.Module):
     `_use_fused`, `_split_chunk`, `_y32`).
     """
 
-    def __init__(self, packed, bias=None):
-        """`packed`: the reference's packed dict, or a DevicePacked already on the GPU."""
+    def __init__(self, packed, bias=None, resident: str | None = None, keep_streams: bool = True):
+        """`packed`: the reference's packed dict, or a DevicePacked already on the GPU.
+
+        resident: "p5" (default; environment variable IXB200_RESIDENT overrides the default) re-lays the codes
+        out at construction as the P5 plane + outlier list and runs inputs of up to 8 rows on it; "streams" keeps
+        to the reference's (3,5,8) streams and the fused kernel that reads them directly.
+        keep_streams=False frees the stream buffers once the P5 layout exists (larger inputs then decode from
+        P5); the reference-named buffers `_b1 .. _l3` are gone in that case."""
         super().__init__()
+        resident = resident or os.environ.get("IXB200_RESIDENT", "p5")
+        if resident not in ("p5", "streams"):
+            raise ValueError("resident must be 'p5' or 'streams'")
         dp = packed if isinstance(packed, DevicePacked) else DevicePacked(packed)
         self.out_features = dp.out_f
         self.in_features = dp.in_f
@@ -74,13 +83,38 @@ class StreamingLinear(nn.Module):
             self._bias = None
             self._bias_bf16 = None
         self._w_buf = None
+        self._p5 = None
+        if resident == "p5":
+            from .p5 import P5Packed
+
+            self._p5 = P5Packed.from_packed(dp)
+            if not keep_streams:
+                for key in ("_b1", "_b2", "_l1", "_l2", "_l3", "_b1_blk", "_b2_blk", "_q1", "_q2"):
+                    if hasattr(self, key):
+                        delattr(self, key)
+                self._dp = None
+                self._use_fused = False
 
     @classmethod
-    def from_weight(cls, weight: torch.Tensor, bias=None):
+    def from_weight(cls, weight: torch.Tensor, bias=None, **kw):
         """Quantise and pack a bf16 weight on the GPU (no CPU pass over the tensor)."""
         from .gpu_pack import quantize_pack_gpu
 
-        return cls(quantize_pack_gpu(weight.detach().to("cuda", torch.bfloat16)), bias=bias)
+        return cls(quantize_pack_gpu(weight.detach().to("cuda", torch.bfloat16)), bias=bias, **kw)
+
+    @property
+    def resident_bytes(self) -> int:
+        """Bytes of weight data this layer keeps on the device."""
+        n = self._p5.resident_bytes if self._p5 is not None else 0
+        if self._dp is not None:
+            n += self.total_bytes
+        return n
+
+    def matvec(self, x, out=None, out_dtype=torch.bfloat16):
+        """y[M, out_f] for 1..8 bf16 rows on the resident layout, without bias (used by the runners and bench)."""
+        if self._p5 is not None:
+            return self._p5.gemv(x, out=out, out_dtype=out_dtype)
+        return self._dp.gemv(x, out=out, out_dtype=out_dtype)
 
     def _set_shared_buf(self, w_buf):
         self._w_buf = w_buf
@@ -89,10 +123,15 @@ class StreamingLinear(nn.Module):
         """Decode the packed weight into the shared buffer -> bf16 [out, in]."""
         if self._w_buf is None:
             raise RuntimeError("no decode buffer set (call _set_shared_buf)")
-        return self._dp.decode(out=self._w_buf[: self.N], kind="bf16")
+        src = self._dp if self._dp is not None else self._p5
+        return src.decode(out=self._w_buf[: self.N], kind="bf16")
 
     def forward(self, x):
         rows = x.numel() // self.in_features
+        if self._p5 is not None and x.dtype == torch.bfloat16 and 1 <= rows <= FUSED_MAX_ROWS \
+                and x.shape[-1] == self.in_features:
+            y = self._p5.gemv(x.reshape(rows, self.in_features), bias=self._bias_bf16)
+            return y.view(x.shape[:-1] + (self.out_features,))
         if self._use_fused and x.dtype == torch.bfloat16 and 1 <= rows <= FUSED_MAX_ROWS \
                 and x.shape[-1] == self.in_features:
             y = self._dp.gemv(x.reshape(rows, self.in_features), bias=self._bias_bf16)

@@ -53,7 +53,7 @@ def shard_shape(name, rows, cols, mode, world):
 
 
 class Stack:
-    def __init__(self, n_layers: int, world: int, rank: int, dev):
+    def __init__(self, n_layers: int, world: int, rank: int, dev, layout: str = "p5"):
         self.world, self.dev = world, dev
         cache = {}
 
@@ -63,10 +63,16 @@ class Stack:
             key = (name, r, c)
             if key not in cache:
                 cache[key] = synthetic_packed(r, c, seed=seed * 131 + rank)
-            return DevicePacked(cache[key], dev)        # separate device copy per layer
+            dp = DevicePacked(cache[key], dev)          # separate device copy per layer
+            if layout == "p5":
+                from .p5 import P5Packed
+
+                return P5Packed.from_packed(dp)         # the streams are dropped, the re-layout stays resident
+            return dp
 
         self.layers = []
         self.packed_bytes = 0
+        self.resident_bytes = 0
         self.n_weights = 0
         for li in range(n_layers):
             kind = ATTN if li % 4 == 3 else GDN
@@ -75,6 +81,7 @@ class Stack:
             self.layers.append((kind is ATTN, mix, mlp))
             for dp in list(mix.values()) + list(mlp.values()):
                 self.packed_bytes += dp.total_bytes
+                self.resident_bytes += getattr(dp, "resident_bytes", dp.total_bytes)
                 self.n_weights += dp.N
         self.norm_w = torch.ones(HIDDEN, dtype=torch.bfloat16, device=dev)
         self.h = torch.randn(1, HIDDEN, device=dev).bfloat16()
@@ -191,6 +198,8 @@ def main():
     ap.add_argument("--layers", type=int, default=64)
     ap.add_argument("--tokens", type=int, default=16)
     ap.add_argument("--eager", action="store_true")
+    ap.add_argument("--layout", default="p5", choices=["p5", "streams"],
+                    help="resident weight layout: the P5 re-layout or the reference's streams read directly")
     args = ap.parse_args()
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -203,7 +212,7 @@ def main():
         dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=120))
     t0 = time.time()
     with torch.no_grad():
-        st = Stack(args.layers, world, rank, dev)
+        st = Stack(args.layers, world, rank, dev, layout=args.layout)
         setup = time.time() - t0
         mode = "eager"
         if not args.eager:
@@ -232,6 +241,7 @@ def main():
             "n_gpus": world, "parallelism": f"tp{world}", "mode": mode, "ms_per_token": ms,
             "all_reduces_per_token": st.n_allreduce if world > 1 else 0,
             "packed_weights_per_rank": st.n_weights, "packed_GB_per_rank": st.packed_bytes / 1e9,
+            "layout": args.layout, "resident_GB_per_rank": st.resident_bytes / 1e9,
             "tokens_timed": args.tokens, "setup_s": setup,
             "note": "packed-weight path only; token mixers are elementwise stand-ins",
         }), flush=True)
