@@ -372,24 +372,44 @@ k_p5_mma(P5 p, const __nv_bfloat16 *__restrict__ x, uint32_t m_rows, const __nv_
         for (int q = 0; q < 4; ++q) img[q * 32 + lane] = make_uint4(0, 0, 0, 0);
         __syncwarp();
 
-        auto process = [&](const uint4 a, const uint32_t w4, const uint32_t ent0, const uint32_t ent1, const int32_t o_lo,
-                           const int32_t o_hi) {
+        // One block.  Everything it consumes was loaded by earlier steps into the register set it is given
+        // (plane words two blocks ahead, outlier offsets two blocks ahead, the first 64 entries one block ahead);
+        // the step reloads each set right after its last use, so the sets alternate by unrolling with no copies.
+        //   a, w4      plane words of this block           -> reloaded with those of block + 2
+        //   olo, ohi   blk_off[block], blk_off[block + 1]  -> reloaded with those of block + 2
+        //   ent0, ent1 entries olo + lane, olo + 32 + lane of this block
+        //   nlo        blk_off[block + 1]; nent0, nent1 receive the next block's first entries
+        auto step = [&](uint4 &a, uint32_t &w4, int32_t &olo, int32_t &ohi, const uint32_t ent0, const uint32_t ent1,
+                        const int32_t nlo, uint32_t &nent0, uint32_t &nent1, const uint32_t blk) {
+            {
+                const uint32_t *ne = p.esc + nlo + lane;
+                nent0 = __ldg(ne);
+                nent1 = __ldg(ne + 32);
+            }
+            const int32_t lo0 = olo, cnt = ohi - olo;
+            olo = __ldg(p.blk_off + blk + 2u);       // a whole step ahead of their first use
+            ohi = __ldg(p.blk_off + blk + 3u);
             const uint4 x0 = *(const uint4 *)(xl + xo);
             const uint4 x1 = *(const uint4 *)(xl + xo + 8);
-            const uint32_t w[5] = {a.x, a.y, a.z, a.w, w4};
             uint32_t f[16];
-#pragma unroll
-            for (int k = 0; k < 5; ++k) {
-                f[3 * k] = p5_pair_raw(w[k], magic);
-                f[3 * k + 1] = p5_pair_raw(w[k] >> 5, magic);
-                f[3 * k + 2] = p5_pair_raw(w[k] >> 10, magic);
-            }
             {
+                const uint32_t w[5] = {a.x, a.y, a.z, a.w, w4};
+#pragma unroll
+                for (int k = 0; k < 5; ++k) {
+                    f[3 * k] = p5_pair_raw(w[k], magic);
+                    f[3 * k + 1] = p5_pair_raw(w[k] >> 5, magic);
+                    f[3 * k + 2] = p5_pair_raw(w[k] >> 10, magic);
+                }
                 uint32_t v = p5_and_or(w[0] >> 15, 0x00010001u, magic);
                 v = p5_and_or(w[1] >> 14, 0x00020002u, v);
                 v = p5_and_or(w[2] >> 13, 0x00040004u, v);
                 v = p5_and_or(w[3] >> 12, 0x00080008u, v);
                 f[15] = p5_and_or(w[4] >> 11, 0x00100010u, v);
+            }
+            {
+                const uint32_t i2 = (blk + 2u) * 32u + lane;
+                a = p.w03[i2];
+                w4 = p.w4[i2];
             }
 #pragma unroll
             for (int i = 0; i < 16; ++i) f[i] = p5_pair_weight(f[i], one2, neg2, s2);
@@ -401,15 +421,16 @@ k_p5_mma(P5 p, const __nv_bfloat16 *__restrict__ x, uint32_t m_rows, const __nv_
                 // The block's outliers: entry j goes to lane j % 32 (two were prefetched, more than 64 per block
                 // is rare), which drops the weight into its slot of the image.  Then every lane takes its four A
                 // registers per mma from the image and clears them.
-                const int32_t rel = (int32_t)lane - (o_hi - o_lo);          // < 0: this lane has a first entry
-                const uint32_t s0 = img_s + (ent0 >> 16), s1 = img_s + (ent1 >> 16);
-                if (rel < 0) asm volatile("st.shared.u16 [%0], %1;" ::"r"(s0), "h"((unsigned short)ent0));
-                if (rel < -32) asm volatile("st.shared.u16 [%0], %1;" ::"r"(s1), "h"((unsigned short)ent1));
-                const bool many = o_hi - o_lo > 64;                          // warp uniform
-                if (many) {
-                    for (int32_t j = 64 + lane; j < o_hi - o_lo; j += 32) {
-                        uint32_t e = __ldg(p.esc + o_lo + j);
-                        asm volatile("st.shared.u16 [%0], %1;" ::"r"(img_s + (e >> 16)), "h"((unsigned short)e));
+                const int32_t rel = (int32_t)lane - cnt;                      // < 0: this lane has a first entry
+                asm volatile("{\n\t.reg .pred p0, p1;\n\tsetp.lt.s32 p0, %4, 0;\n\tsetp.lt.s32 p1, %4, -32;\n\t"
+                             "@p0 st.shared.u16 [%0], %1;\n\t@p1 st.shared.u16 [%2], %3;\n\t}"
+                             ::"r"(img_s + (ent0 >> 16)), "h"((unsigned short)ent0), "r"(img_s + (ent1 >> 16)),
+                             "h"((unsigned short)ent1), "r"(rel)
+                             : "memory");
+                if (cnt > 64) {                                               // warp uniform
+                    for (int32_t j = 64 + lane; j < cnt; j += 32) {
+                        uint32_t e = __ldg(p.esc + lo0 + j);
+                        asm volatile("st.shared.u16 [%0], %1;" ::"r"(img_s + (e >> 16)), "h"((unsigned short)e) : "memory");
                     }
                 }
                 __syncwarp();
@@ -430,45 +451,29 @@ k_p5_mma(P5 p, const __nv_bfloat16 *__restrict__ x, uint32_t m_rows, const __nv_
                 from_start = true;
             }
         };
-        // Two blocks' plane words and one block's first 64 outlier entries are in flight; the registers alternate
-        // by unrolling, not by copying.  The loads run up to two blocks past the end of the run: planes, offsets
-        // and entries are allocated with that much slack.
-        uint32_t idx = b_begin * 32u + lane;
-        uint4 a0 = p.w03[idx], a1 = p.w03[idx + 32u];
-        uint32_t e0 = p.w4[idx], e1 = p.w4[idx + 32u];
-        idx += 64u;
-        const int32_t *offp = p.blk_off + b_begin;
-        int32_t oa = __ldg(offp), ob = __ldg(offp + 1), oc = __ldg(offp + 2);       // off[b], off[b + 1], off[b + 2]
-        offp += 3;
-        uint32_t n0 = __ldg(p.esc + oa + lane), n1 = __ldg(p.esc + oa + 32 + lane);  // entries of block b
-        uint32_t left = b_end - b_begin;
-        while (true) {
-            {
-                const uint4 a = a0;
-                const uint32_t e = e0, t0 = n0, t1 = n1;
-                const int32_t lo = oa, hi = ob;
-                a0 = p.w03[idx];
-                e0 = p.w4[idx];
-                n0 = __ldg(p.esc + ob + lane);
-                n1 = __ldg(p.esc + ob + 32 + lane);
-                oa = ob; ob = oc; oc = __ldg(offp);
-                process(a, e, t0, t1, lo, hi);
-                if (--left == 0) break;
-            }
-            {
-                const uint4 a = a1;
-                const uint32_t e = e1, t0 = n0, t1 = n1;
-                const int32_t lo = oa, hi = ob;
-                a1 = p.w03[idx + 32u];
-                e1 = p.w4[idx + 32u];
-                idx += 64u;
-                n0 = __ldg(p.esc + ob + lane);
-                n1 = __ldg(p.esc + ob + 32 + lane);
-                oa = ob; ob = oc; oc = __ldg(offp + 1);
-                offp += 2;
-                process(a, e, t0, t1, lo, hi);
-                if (--left == 0) break;
-            }
+        // The loads run up to two blocks past the end of the run: planes, offsets and entries are allocated with
+        // that much slack.
+        uint4 aA, aB;
+        uint32_t eA, eB, nA0, nA1, nB0, nB1;
+        int32_t loA, hiA, loB, hiB;
+        {
+            const uint32_t i0 = b_begin * 32u + lane;
+            aA = p.w03[i0];
+            eA = p.w4[i0];
+            aB = p.w03[i0 + 32u];
+            eB = p.w4[i0 + 32u];
+            loA = __ldg(p.blk_off + b_begin);
+            hiA = __ldg(p.blk_off + b_begin + 1);
+            loB = hiA;
+            hiB = __ldg(p.blk_off + b_begin + 2);
+            nA0 = __ldg(p.esc + loA + lane);
+            nA1 = __ldg(p.esc + loA + 32 + lane);
+        }
+        for (uint32_t b = b_begin;;) {
+            step(aA, eA, loA, hiA, nA0, nA1, loB, nB0, nB1, b);
+            if (++b == b_end) break;
+            step(aB, eB, loB, hiB, nB0, nB1, loA, nA0, nA1, b);
+            if (++b == b_end) break;
         }
         __syncwarp();
         if (xo != 0) flush_tile(false);
