@@ -18,6 +18,7 @@ import os
 
 import torch
 
+from .p5 import P5Packed
 from .packed import DevicePacked
 from .synth import synthetic_packed
 
@@ -50,12 +51,17 @@ def time_us(fn, reps: int, flush: torch.Tensor | None, warm: int = 3):
     return ts[len(ts) // 2]
 
 
-def run_case(dp: DevicePacked, total_bytes: int, kernel: str, rows: int, reps: int, flush, wdense=None):
+def run_case(dp: DevicePacked, total_bytes: int, kernel: str, rows: int, reps: int, flush, wdense=None, p5=None):
     out_f, in_f = dp.out_f, dp.in_f
     x = torch.randn(rows, in_f, device=dp.device).bfloat16()
     y = torch.empty(rows, out_f, dtype=torch.bfloat16, device=dp.device)
     if kernel == "gemv":
         fn = lambda: dp.gemv(x, out=y)
+    elif kernel == "p5":
+        fn = lambda: p5.gemv(x, out=y)
+    elif kernel == "p5decode":
+        w = torch.empty(out_f * in_f, dtype=torch.bfloat16, device=dp.device)
+        fn = lambda: p5.decode(out=w)
     elif kernel == "gemm":
         fn = lambda: dp.gemm(x, out=y)
     elif kernel == "decode":
@@ -77,7 +83,9 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--shape", default="5120x17408")
     ap.add_argument("--rows", type=int, default=1)
-    ap.add_argument("--kernel", default="gemv", choices=["gemv", "gemm", "decode", "dense"])
+    ap.add_argument("--kernel", default="gemv", choices=["gemv", "p5", "p5decode", "gemm", "decode", "dense"],
+                    help="gemv/gemm/decode: kernels on the reference's streams; p5/p5decode: on the resident P5 re-layout; "
+                         "dense: bf16 matmul on decoded weights")
     ap.add_argument("--reps", type=int, default=30)
     ap.add_argument("--no-flush", action="store_true")
     ap.add_argument("--sweep", action="store_true")
@@ -88,18 +96,21 @@ def main():
         p = synthetic_packed(out_f, in_f, seed=1)
         dp = DevicePacked(p)
         wd = dp.decode(kind="bf16").clone() if args.kernel == "dense" else None
-        print(json.dumps(run_case(dp, p["total_bytes"], args.kernel, args.rows, args.reps, flush, wd)), flush=True)
+        p5 = P5Packed.from_packed(dp) if args.kernel.startswith("p5") else None
+        print(json.dumps(run_case(dp, p["total_bytes"], args.kernel, args.rows, args.reps, flush, wd, p5)), flush=True)
         return
     for out_f, in_f in SWEEP_SHAPES:
         p = synthetic_packed(out_f, in_f, seed=1)
         dp = DevicePacked(p)
         wd = dp.decode(kind="bf16").clone()
+        p5 = P5Packed.from_packed(dp)
         big = out_f * in_f > 50e6
         for rows in ([1, 2, 4, 8, 16, 32, 64] if big else [1]):
-            kernels = (["gemv"] if rows <= 8 else []) + (["gemm"] if rows >= 8 and in_f % 1024 == 0 else []) + ["dense"]
+            kernels = (["p5", "gemv"] if rows <= 8 else []) + (["gemm"] if rows >= 8 and in_f % 1024 == 0 else []) + ["dense"]
             for k in kernels:
-                print(json.dumps(run_case(dp, p["total_bytes"], k, rows, args.reps, flush, wd)), flush=True)
+                print(json.dumps(run_case(dp, p["total_bytes"], k, rows, args.reps, flush, wd, p5)), flush=True)
         print(json.dumps(run_case(dp, p["total_bytes"], "decode", 1, args.reps, flush)), flush=True)
+        print(json.dumps(run_case(dp, p["total_bytes"], "p5decode", 1, args.reps, flush, None, p5)), flush=True)
 
 
 if __name__ == "__main__":
