@@ -794,6 +794,10 @@ extern "C" int ixb_p5_decode(const ixb_p5 *t, void *out, int out_kind, ixb_strea
     if (out_kind != 0 && out_kind != 1) return fail(IXB_E_ARG, "out_kind must be 0 or 1");
     uint32_t nb = p.rt * p.kb;
     cudaStream_t st = (cudaStream_t)stream;
+    if (out_kind == 1 && (p.in_f & 7u) == 0 && ((uintptr_t)out & 15u) == 0) {
+        k_p5_decode_bf16<<<(nb + 7) / 8, 256, 0, st>>>(p, (__nv_bfloat16 *)out);       // plane and outliers in one pass
+        return launch_check("k_p5_decode_bf16");
+    }
     if (out_kind == 0) k_p5_decode_plane<0><<<(nb + 7) / 8, 256, 0, st>>>(p, out);
     else k_p5_decode_plane<1><<<(nb + 7) / 8, 256, 0, st>>>(p, out);
     if ((rc = launch_check("k_p5_decode_plane"))) return rc;

@@ -260,6 +260,73 @@ __device__ __forceinline__ void p5_mma(float (&c)[4], uint32_t a0, uint32_t a1, 
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+// layout -> bf16 weights with the GEMV's own conversion (three instructions per pair of elements) and its outlier
+// image, so every weight is stored once, in 16-byte pieces; needs in_f % 8 == 0 and a 16-byte aligned output
+__global__ void __launch_bounds__(256) k_p5_decode_bf16(P5 p, __nv_bfloat16 *out)
+{
+    __shared__ uint4 images[8 * 128];                // one 2 KB fragment image per warp
+    uint32_t b = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    int lane = threadIdx.x & 31;
+    if (b >= p.rt * p.kb) return;                    // whole warps leave together
+    uint4 *img = images + (threadIdx.x >> 5) * 128;
+#pragma unroll
+    for (int q = 0; q < 4; ++q) img[q * 32 + lane] = make_uint4(0, 0, 0, 0);
+    __syncwarp();
+    {
+        const uint32_t img_s = (uint32_t)__cvta_generic_to_shared(img);
+        const int32_t lo = __ldg(p.blk_off + b), hi = __ldg(p.blk_off + b + 1);
+        for (int32_t j = lo + lane; j < hi; j += 32) {
+            uint32_t e = __ldg(p.esc + j);
+            asm volatile("st.shared.u16 [%0], %1;" ::"r"(img_s + (e >> 16)), "h"((unsigned short)e) : "memory");
+        }
+    }
+    __syncwarp();
+    uint32_t R = b / p.kb, kbi = b - R * p.kb;
+    uint32_t sb = (uint32_t)__bfloat16_as_ushort(*p.scale);
+    const uint32_t s2 = sb | (sb << 16), magic = 0x43004300u, one2 = 0x3F803F80u, neg2 = 0xC30FC30Fu;
+    uint4 a = p.w03[(size_t)b * 32u + lane];
+    const uint32_t w[5] = {a.x, a.y, a.z, a.w, p.w4[(size_t)b * 32u + lane]};
+    uint32_t f[16];
+#pragma unroll
+    for (int k = 0; k < 5; ++k) {
+        f[3 * k] = p5_pair_raw(w[k], magic);
+        f[3 * k + 1] = p5_pair_raw(w[k] >> 5, magic);
+        f[3 * k + 2] = p5_pair_raw(w[k] >> 10, magic);
+    }
+    {
+        uint32_t v = p5_and_or(w[0] >> 15, 0x00010001u, magic);
+        v = p5_and_or(w[1] >> 14, 0x00020002u, v);
+        v = p5_and_or(w[2] >> 13, 0x00040004u, v);
+        v = p5_and_or(w[3] >> 12, 0x00080008u, v);
+        f[15] = p5_and_or(w[4] >> 11, 0x00100010u, v);
+    }
+#pragma unroll
+    for (int i = 0; i < 16; ++i) f[i] = p5_pair_weight(f[i], one2, neg2, s2);
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {                    // placeholders are +0.0, so OR-ing the outlier weights in is exact
+        const uint4 v = img[q * 32 + lane];
+        f[4 * q] |= v.x;
+        f[4 * q + 1] |= v.y;
+        f[4 * q + 2] |= v.z;
+        f[4 * q + 3] |= v.w;
+    }
+    // pair 4 j + q: row g + 8 (q & 1), columns 4 j + 2 (q >> 1) + {0, 1} of the lane's 16
+    const uint32_t col0 = kbi * kP5TileCols + 16 * (lane & 3);
+#pragma unroll
+    for (int s = 0; s < 2; ++s) {
+        uint32_t row = R * kP5TileRows + (lane >> 2) + 8 * s;
+        if (row >= p.out_f || col0 >= p.in_f) continue;
+        __nv_bfloat16 *dst = out + (size_t)row * p.in_f + col0;
+        const uint32_t r[8] = {f[0 + s], f[2 + s], f[4 + s], f[6 + s], f[8 + s], f[10 + s], f[12 + s], f[14 + s]};
+        if (col0 + 16u <= p.in_f) {
+            ((uint4 *)dst)[0] = make_uint4(r[0], r[1], r[2], r[3]);
+            ((uint4 *)dst)[1] = make_uint4(r[4], r[5], r[6], r[7]);
+        } else {
+            for (uint32_t c = 0; col0 + c < p.in_f; ++c) ((uint16_t *)dst)[c] = (uint16_t)(r[c >> 1] >> (16 * (c & 1)));
+        }
+    }
+}
+
 // Final value of a row tile's C fragment image: lane (g, t) holds rows g, g + 8 and activation rows 2 t, 2 t + 1.
 __device__ __forceinline__ void p5_store_tile(const P5 &p, uint32_t R, int lane, const float (&c)[4], uint32_t m_rows,
                                               const __nv_bfloat16 *__restrict__ bias, void *y, int y_f32)

@@ -123,7 +123,7 @@ class StreamingLinear(nn.Module):
         """Decode the packed weight into the shared buffer -> bf16 [out, in]."""
         if self._w_buf is None:
             raise RuntimeError("no decode buffer set (call _set_shared_buf)")
-        src = self._dp if self._dp is not None else self._p5
+        src = self._p5 if self._p5 is not None else self._dp       # the P5 decoder is the faster of the two
         return src.decode(out=self._w_buf[: self.N], kind="bf16")
 
     def forward(self, x):
