@@ -178,7 +178,7 @@ def run_gpu(args):
     alg_bytes = algorithmic_bytes(full_bytes)
     alg_bytes_rank = packed["total_bytes"] + 2 * in_loc + 2 * OUT_F
     layers = [StreamingLinear(packed, resident=args.layout) for _ in range(COPIES)]
-    resident_bytes = layers[0]._p5.resident_bytes if args.layout == "p5" else packed["total_bytes"]
+    resident_bytes = layers[0]._p5.resident_bytes if args.layout in ("p5", "p6") else packed["total_bytes"]
     g = torch.Generator().manual_seed(1)
     x_host = torch.randn(1, IN_F, generator=g).bfloat16()[:, rank * in_loc:(rank + 1) * in_loc].contiguous().pin_memory()
     x = x_host.to(dev)
@@ -302,16 +302,14 @@ def run_gpu(args):
         "config": {
             "workload": f"down_proj {OUT_F}x{IN_F} batch 1 fused decode+GEMV, (3,5,8) codes ~ round(Laplace(0,4.4))",
             "algorithmic_bytes_per_step": alg_bytes,
-            "layout": ("resident P5 re-layout of the same int8 codes (5-bit plane in mma fragment order + level-3 weight list), "
-                       "built on the GPU at deploy time from the reference's packed streams" if args.layout == "p5"
-                       else "the reference's (3,5,8) streams read directly"),
+            "layout": LAYOUT_TEXT[args.layout],
             "resident_bytes_per_gpu": resident_bytes,
             "l2": f"timed steps rotate over {COPIES} device copies of the weights ({COPIES * resident_bytes / 1e6:.0f} MB per GPU)",
             "parallelism": "single GPU" if world == 1 else f"tp{world}: column shards of in_f, one NCCL all-reduce of y per step",
             "timed_with": "CUDA events around one graph replay of K launches" if graph is not None else "CUDA events around K eager steps",
         },
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "traffic": None, "peak_source": peak_src, "kernel": "k_p5_mma<1>" if args.layout == "p5" else "k_gemv<1>",
+                     "traffic": None, "peak_source": peak_src, "kernel": LAYOUT_KERNEL[args.layout],
                      "algorithmic_bytes_per_launch": alg_bytes_rank, "launch_ms": k_ms},
         "e2e": {"value": alg_bytes / e2e_s / 1e9, "unit": UNIT, "h2d_bytes_per_step": 2 * in_loc,
                 "d2h_bytes_per_step": 2 * OUT_F, "ms_per_step": e2e_s * 1e3, "steps": e2e_steps,
@@ -335,6 +333,18 @@ def run_gpu(args):
         dist.destroy_process_group()
 
 
+DEFAULT_LAYOUT = "p5"
+LAYOUT_KERNEL = {"p5": "k_p5_mma<1>", "p6": "k_p6_mma<1>", "streams": "k_gemv<1>"}
+LAYOUT_TEXT = {
+    "p5": ("resident P5 re-layout of the same int8 codes (5-bit plane in mma fragment order + level-3 weight list), "
+           "built on the GPU at deploy time from the reference's packed streams"),
+    "p6": ("resident P6 re-layout of the same int8 codes (6-bit plane in mma fragment order whose fields are part of "
+           "the bf16 number 1 + code/32, + a weight list for codes outside -16..31), built on the GPU at deploy time "
+           "from the reference's packed streams"),
+    "streams": "the reference's (3,5,8) streams read directly",
+}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -342,8 +352,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--eager", action="store_true", help="launch the timed steps one by one instead of one CUDA graph")
-    ap.add_argument("--layout", default="p5", choices=["p5", "streams"],
-                    help="resident weight layout: the P5 re-layout (default) or the reference's streams read directly")
+    ap.add_argument("--layout", default=DEFAULT_LAYOUT, choices=["p5", "p6", "streams"],
+                    help="resident weight layout: the P5 or P6 re-layout, or the reference's streams read directly")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -175,6 +175,59 @@ int ixb_p5_gemv(const ixb_p5 *t, const void *x_device, int64_t m_rows, const voi
                 void *y_device, int y_is_f32, void *scratch_device, size_t scratch_bytes, ixb_stream_t stream);
 
 /*
+ * Resident re-layout "P6": the same idea as P5 with one more plane bit per
+ * weight and a cheaper conversion.  No counterpart in the reference (it plays
+ * the role of its deploy-time derived buffers, ixrun/engine.py:68-97).
+ *   plane    a 6-bit field per element, blocks of 16 rows x 64 columns as in
+ *            P5, 768 contiguous bytes per block.  The field is bits 7..2 of the
+ *            low byte of the bf16 number 1 + code / 32 (codes -16 .. 31), so the
+ *            GEMV needs a shift, a mask and ONE fused multiply-add per pair of
+ *            weights to obtain bf16(code * scale) -- the reference's
+ *            dequantised weight (ixrun/quantize.py:201-204), rounded once
+ *   esc      every other code as a uint32 entry: bf16(code * scale) in the high
+ *            half, row in tile, block index mod 64 and column in block below;
+ *            blk_off: int32 first entry of every block
+ * about 6 + 32 * P(code outside -16 .. 31) bits per weight.  Buffer sizes
+ * (B = ixb_p5_blocks): plane (B + 5) * 768 bytes, blk_off (B + 1) * 4 bytes,
+ * esc (n_esc + 64) * 4 bytes; plane and esc 16-byte aligned.
+ * ixb_p6_build: int8 codes [out_f, in_f] + the bf16 scale -> layout (n_esc =
+ *   number of codes outside -16 .. 31; ws: (B + 1) * 4 bytes).
+ * ixb_p6_decode: layout -> int8 codes / bf16 weights (out_kind as ixb_decode).
+ * ixb_p6_gemv: same contract as ixb_gemv / ixb_p5_gemv (result definition,
+ *   bias, scratch rules; scratch 16-byte aligned, zero before the first call),
+ *   1..8 activation rows in one kernel: plane on the tensor cores (mma.sync,
+ *   exact bf16 x bf16 products, fp32 accumulation), outliers on the CUDA cores.
+ */
+typedef struct ixb_p6 {
+    const void *plane;
+    const void *blk_off;
+    const void *esc;
+    int64_t n_esc;
+    const void *scale;    /* one bf16 */
+    int64_t out_f;
+    int64_t in_f;
+} ixb_p6;
+int ixb_p6_build(const int8_t *codes_device, const void *scale_device, int64_t out_f, int64_t in_f, void *plane_device,
+                 int32_t *blk_off_device, void *esc_device, int64_t n_esc, void *ws_device, size_t ws_bytes,
+                 ixb_stream_t stream);
+int ixb_p6_decode(const ixb_p6 *t, void *out_device, int out_kind, ixb_stream_t stream);
+size_t ixb_p6_gemv_scratch_bytes(int64_t out_f, int64_t in_f, int64_t m_rows);
+int ixb_p6_gemv(const ixb_p6 *t, const void *x_device, int64_t m_rows, const void *bias_device,
+                void *y_device, int y_is_f32, void *scratch_device, size_t scratch_bytes, ixb_stream_t stream);
+/*
+ * Programmatic dependent launch for ixb_p6_gemv (process-wide switch, off by
+ * default; returns the previous setting).  No counterpart in the reference,
+ * whose per-layer kernels run strictly one after the other.  When on, an
+ * ixb_p6_gemv launch may start while the kernel ahead of it in the stream is
+ * still finishing: it fetches its first weight blocks and outlier entries, then
+ * waits for that kernel to complete before it reads x or writes y or the
+ * scratch.  Turn it on only once the layouts it will read are complete (after
+ * deployment and a synchronise): a layout still being built by the kernel just
+ * ahead in the stream would be read too early.
+ */
+int ixb_set_pdl(int on);
+
+/*
  * Fused decode + small-M GEMM on the tensor cores (tcgen05, accumulators in
  * TMEM) for 1 <= m_rows <= 64; intended for 9..64 rows (batched decode, MTP
  * verify), below that ixb_gemv is the better call.  Same result definition and

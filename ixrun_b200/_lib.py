@@ -23,6 +23,7 @@ SYMBOLS = (
     "ixb_gemm_scratch_bytes", "ixb_gemm",
     "ixb_pack_workspace_bytes", "ixb_quantize_codes", "ixb_count_codes", "ixb_pack_codes",
     "ixb_p5_blocks", "ixb_p5_build", "ixb_p5_decode", "ixb_p5_gemv_scratch_bytes", "ixb_p5_gemv",
+    "ixb_p6_build", "ixb_p6_decode", "ixb_p6_gemv_scratch_bytes", "ixb_p6_gemv", "ixb_set_pdl",
 )
 
 
@@ -49,6 +50,15 @@ class P5Struct(C.Structure):
 
     _fields_ = [
         ("w03", C.c_void_p), ("w4", C.c_void_p), ("blk_off", C.c_void_p), ("esc", C.c_void_p),
+        ("n_esc", C.c_int64), ("scale", C.c_void_p), ("out_f", C.c_int64), ("in_f", C.c_int64),
+    ]
+
+
+class P6Struct(C.Structure):
+    """Mirror of ``struct ixb_p6``."""
+
+    _fields_ = [
+        ("plane", C.c_void_p), ("blk_off", C.c_void_p), ("esc", C.c_void_p),
         ("n_esc", C.c_int64), ("scale", C.c_void_p), ("out_f", C.c_int64), ("in_f", C.c_int64),
     ]
 
@@ -102,6 +112,16 @@ def lib():
     L.ixb_p5_gemv_scratch_bytes.argtypes = [i64, i64, i64]
     L.ixb_p5_gemv.restype = C.c_int
     L.ixb_p5_gemv.argtypes = [C.POINTER(P5Struct), vp, i64, vp, vp, C.c_int, vp, sz, vp]
+    L.ixb_p6_build.restype = C.c_int
+    L.ixb_p6_build.argtypes = [vp, vp, i64, i64, vp, vp, vp, i64, vp, sz, vp]
+    L.ixb_p6_decode.restype = C.c_int
+    L.ixb_p6_decode.argtypes = [C.POINTER(P6Struct), vp, C.c_int, vp]
+    L.ixb_p6_gemv_scratch_bytes.restype = sz
+    L.ixb_p6_gemv_scratch_bytes.argtypes = [i64, i64, i64]
+    L.ixb_p6_gemv.restype = C.c_int
+    L.ixb_p6_gemv.argtypes = [C.POINTER(P6Struct), vp, i64, vp, vp, C.c_int, vp, sz, vp]
+    L.ixb_set_pdl.restype = C.c_int
+    L.ixb_set_pdl.argtypes = [C.c_int]
     L.ixb_gemv_static.restype = C.c_int
     L.ixb_gemv_static.argtypes = [C.POINTER(Packed), vp, vp, vp, i64, vp, vp, C.c_int, vp]
     _lib = L

@@ -16,7 +16,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 SO = os.path.join(HERE, "libixb200.so")
 SOURCES = ["ixb200.cu"]
-HEADERS = ["ixb_common.cuh", os.path.join("..", "..", "include", "ixb200.h")]
+HEADERS = sorted(f for f in os.listdir(CSRC) if f.endswith(".cuh")) + [os.path.join("..", "..", "include", "ixb200.h")]
 
 
 def nvcc_path() -> str:
@@ -41,6 +41,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
         nvcc_path(), "-O3", "-std=c++17", "-lineinfo",
         "-gencode", "arch=compute_100a,code=sm_100a",
         "-Xcompiler", "-fPIC", "-shared",
+    ] + ([f"-D{d}" for d in os.environ.get("IXB200_DEFINES", "").split()]) + [
         "-o", SO,
     ] + [os.path.join(CSRC, f) for f in SOURCES]
     if verbose:

@@ -5,6 +5,7 @@
 #include "ixb_gemm_tc.cuh"
 #include "ixb_pack.cuh"
 #include "ixb_p5.cuh"
+#include "ixb_p6.cuh"
 
 #include <atomic>
 #include <cstdarg>
@@ -869,6 +870,166 @@ extern "C" int ixb_p5_gemv(const ixb_p5 *t, const void *x, int64_t m_rows, const
     else launch_p5<0>(p, x, (uint32_t)m_rows, bias, y, y_is_f32, slots, tickets, pl, st);
     return launch_check("k_p5_mma");
 }
+
+// ------------------------------------------------------------- resident P6 layout
+static int to_p6(const ixb_p6 *t, P6 *p)
+{
+    if (!t) return fail(IXB_E_ARG, "P6 tensor is NULL");
+    if (t->out_f <= 0 || t->in_f <= 0) return fail(IXB_E_ARG, "bad shape");
+    long long n = (long long)t->out_f * t->in_f;
+    if (n > 800000000LL) return fail(IXB_E_UNSUPPORTED, "tensor too large");
+    if (!t->plane || !t->blk_off || !t->esc || !t->scale) return fail(IXB_E_ARG, "NULL P6 pointer");
+    if (((uintptr_t)t->plane & 15u) || ((uintptr_t)t->esc & 15u)) return fail(IXB_E_ARG, "P6 plane or entries are misaligned");
+    p->plane = (const unsigned char *)t->plane;
+    p->blk_off = (const int32_t *)t->blk_off;
+    p->esc = (const uint32_t *)t->esc;
+    p->scale = (const __nv_bfloat16 *)t->scale;
+    p->out_f = (uint32_t)t->out_f;
+    p->in_f = (uint32_t)t->in_f;
+    p->rt = (p->out_f + kP5TileRows - 1) / kP5TileRows;
+    p->kb = (p->in_f + kP5TileCols - 1) / kP5TileCols;
+    return IXB_OK;
+}
+
+extern "C" int ixb_p6_build(const int8_t *codes, const void *scale, int64_t out_f, int64_t in_f, void *plane,
+                            int32_t *blk_off, void *esc, int64_t n_esc, void *ws, size_t ws_bytes, ixb_stream_t stream)
+{
+    if (!codes || !scale || !plane || !blk_off || !esc || !ws) return fail(IXB_E_ARG, "NULL pointer argument");
+    if (out_f <= 0 || in_f <= 0 || out_f * in_f > 800000000LL) return fail(IXB_E_ARG, "bad shape");
+    if (n_esc < 0) return fail(IXB_E_ARG, "bad outlier count");
+    if (((uintptr_t)plane & 15u) || ((uintptr_t)esc & 15u)) return fail(IXB_E_ARG, "P6 plane or entries are misaligned");
+    uint32_t rt = (uint32_t)((out_f + kP5TileRows - 1) / kP5TileRows), kb = (uint32_t)((in_f + kP5TileCols - 1) / kP5TileCols);
+    uint32_t nb = rt * kb, n_off = nb + 1;
+    if (ws_bytes < (size_t)n_off * 4) return fail(IXB_E_SCRATCH, "P6 workspace too small");
+    cudaStream_t st = (cudaStream_t)stream;
+    int32_t *blk_cnt = (int32_t *)ws;
+    int rc;
+    // the slack behind the plane and the entries is zero: it is read, never interpreted
+    IXB_CUDA(cudaMemsetAsync(blk_cnt, 0, (size_t)n_off * 4, st));
+    IXB_CUDA(cudaMemsetAsync((char *)plane + (size_t)nb * kP6BlockBytes, 0, (size_t)kP6SlackBlocks * kP6BlockBytes, st));
+    IXB_CUDA(cudaMemsetAsync((char *)esc + (size_t)n_esc * 4, 0, (size_t)kP6SlackEntries * 4, st));
+    k_p6_plane<<<(nb + 7) / 8, 256, 0, st>>>(codes, (uint32_t)out_f, (uint32_t)in_f, rt, kb, (unsigned char *)plane, blk_cnt);
+    if ((rc = launch_check("k_p6_plane"))) return rc;
+    k_excl_scan<<<1, 1024, 0, st>>>(blk_cnt, blk_off, n_off);      // entry nb = total
+    if ((rc = launch_check("k_excl_scan"))) return rc;
+    if (n_esc) {
+        k_p6_esc<<<(nb + 7) / 8, 256, 0, st>>>(codes, (uint32_t)out_f, (uint32_t)in_f, rt, kb, blk_off,
+                                               (const __nv_bfloat16 *)scale, (uint32_t *)esc);
+        if ((rc = launch_check("k_p6_esc"))) return rc;
+    }
+    return IXB_OK;
+}
+
+extern "C" int ixb_p6_decode(const ixb_p6 *t, void *out, int out_kind, ixb_stream_t stream)
+{
+    P6 p;
+    int rc = to_p6(t, &p);
+    if (rc) return rc;
+    if (!out) return fail(IXB_E_ARG, "NULL output");
+    if (out_kind != 0 && out_kind != 1) return fail(IXB_E_ARG, "out_kind must be 0 (int8 codes) or 1 (bf16 weights)");
+    cudaStream_t st = (cudaStream_t)stream;
+    uint32_t nb = p.rt * p.kb;
+    if (out_kind == 0) k_p6_decode_plane<0><<<(nb + 7) / 8, 256, 0, st>>>(p, out);
+    else k_p6_decode_plane<1><<<(nb + 7) / 8, 256, 0, st>>>(p, out);
+    if ((rc = launch_check("k_p6_decode_plane"))) return rc;
+    if (t->n_esc) {
+        if (out_kind == 0) k_p6_decode_esc<0><<<(nb + 7) / 8, 256, 0, st>>>(p, out);
+        else k_p6_decode_esc<1><<<(nb + 7) / 8, 256, 0, st>>>(p, out);
+        rc = launch_check("k_p6_decode_esc");
+    }
+    return rc;
+}
+
+struct P6Plan { uint32_t nb, grid, xstride, smem, xs; size_t slot_bytes; };
+
+static P6Plan make_p6_plan(uint32_t out_f, uint32_t in_f, uint32_t m_rows)
+{
+    P6Plan p;
+    uint32_t rt = (out_f + kP5TileRows - 1) / kP5TileRows, kb = (in_f + kP5TileCols - 1) / kP5TileCols;
+    p.nb = rt * kb;
+    uint32_t sms = (uint32_t)num_sms();
+    uint32_t want = (p.nb + kP6Warps - 1) / kP6Warps;
+    p.grid = want < sms ? want : sms;
+    if (!p.grid) p.grid = 1;
+    p.xstride = kb * kP5TileCols + 8u;
+    uint32_t xbytes = m_rows * p.xstride * 2u;
+    p.xs = (uint32_t)kP6SmemFixed + xbytes <= 227u * 1024u;
+    p.smem = (uint32_t)kP6SmemFixed + (p.xs ? xbytes : 0u);
+    p.slot_bytes = (size_t)p.grid * 2u * 32u * sizeof(float4);
+    return p;
+}
+
+extern "C" size_t ixb_p6_gemv_scratch_bytes(int64_t out_f, int64_t in_f, int64_t m_rows)
+{
+    if (out_f <= 0 || in_f <= 0 || m_rows <= 0) return 0;
+    P6Plan p = make_p6_plan((uint32_t)out_f, (uint32_t)in_f, (uint32_t)m_rows);
+    return 1024 + p.slot_bytes;
+}
+
+// Programmatic dependent launch for the P6 GEMV (off by default).  When on, a launch may begin before the kernel
+// ahead of it in the stream has finished: it fetches its first weight blocks and outlier entries, then waits for that
+// kernel to complete before it touches the activations, y or the scratch.
+static int g_p6_pdl = 0;
+
+extern "C" int ixb_set_pdl(int on)
+{
+    int prev = g_p6_pdl;
+    g_p6_pdl = on ? 1 : 0;
+    return prev;
+}
+
+template <int XS>
+static cudaError_t launch_p6(const P6 &p, const void *x, uint32_t m_rows, const void *bias, void *y, int y_f32,
+                             float4 *slots, uint32_t *tickets, const P6Plan &pl, cudaStream_t st)
+{
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaFuncSetAttribute(k_p6_mma<XS>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        attr_set = true;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(pl.grid);
+    cfg.blockDim = dim3(kP6Threads);
+    cfg.dynamicSmemBytes = pl.smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = g_p6_pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, k_p6_mma<XS>, p, (const __nv_bfloat16 *)x, m_rows, (const __nv_bfloat16 *)bias, y, y_f32,
+                              slots, tickets, pl.nb, pl.xstride, pl.nb / pl.grid, pl.nb % pl.grid);
+}
+
+extern "C" int ixb_p6_gemv(const ixb_p6 *t, const void *x, int64_t m_rows, const void *bias, void *y, int y_is_f32,
+                           void *scratch, size_t scratch_bytes, ixb_stream_t stream)
+{
+    P6 p;
+    int rc = to_p6(t, &p);
+    if (rc) return rc;
+    if (!x || !y || !scratch) return fail(IXB_E_ARG, "NULL pointer argument");
+    if (m_rows < 1 || m_rows > 8) return fail(IXB_E_UNSUPPORTED, "m_rows=%lld outside 1..8", (long long)m_rows);
+    if ((uintptr_t)x & 15u) return fail(IXB_E_ARG, "x is not 16-byte aligned");
+    if ((uintptr_t)scratch & 15u) return fail(IXB_E_ARG, "scratch is not 16-byte aligned");
+    if (scratch_bytes < ixb_p6_gemv_scratch_bytes(p.out_f, p.in_f, m_rows)) return fail(IXB_E_SCRATCH, "gemv scratch too small");
+    P6Plan pl = make_p6_plan(p.out_f, p.in_f, (uint32_t)m_rows);
+    if (!pl.xs && (p.in_f % kP5TileCols))
+        return fail(IXB_E_UNSUPPORTED, "in_f=%u: activations too large for shared memory need in_f %% 64 == 0", p.in_f);
+    uint32_t *tickets = (uint32_t *)scratch;                  // the first 1024 bytes hold the tile tickets (grid + 1 words)
+    float4 *slots = (float4 *)((char *)scratch + 1024);
+    cudaStream_t st = (cudaStream_t)stream;
+    cudaError_t e = pl.xs ? launch_p6<1>(p, x, (uint32_t)m_rows, bias, y, y_is_f32, slots, tickets, pl, st)
+                          : launch_p6<0>(p, x, (uint32_t)m_rows, bias, y, y_is_f32, slots, tickets, pl, st);
+    if (e != cudaSuccess) return fail(IXB_E_CUDA, "k_p6_mma launch: %s", cudaGetErrorString(e));
+    return launch_check("k_p6_mma");
+}
+
+#ifdef IXB_P6_TRACE
+extern "C" int ixb_p6_trace(long long *host_out, int n)
+{
+    return (int)cudaMemcpyFromSymbol(host_out, p6_trace, (size_t)n * 8);
+}
+#endif
 
 // ------------------------------------------------------- tensor-core small-M GEMM
 static TcPlan make_tc_plan(uint32_t out_f, uint32_t in_f)

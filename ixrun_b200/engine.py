@@ -39,15 +39,15 @@ class StreamingLinear(nn.Module):
     def __init__(self, packed, bias=None, resident: str | None = None, keep_streams: bool = True):
         """`packed`: the reference's packed dict, or a DevicePacked already on the GPU.
 
-        resident: "p5" (default; environment variable IXB200_RESIDENT overrides the default) re-lays the codes
-        out at construction as the P5 plane + outlier list and runs inputs of up to 8 rows on it; "streams" keeps
+        resident: "p5" (default; environment variable IXB200_RESIDENT overrides the default) or "p6" re-lays the
+        codes out at construction as a plane + outlier list and runs inputs of up to 8 rows on it; "streams" keeps
         to the reference's (3,5,8) streams and the fused kernel that reads them directly.
         keep_streams=False frees the stream buffers once the P5 layout exists (larger inputs then decode from
         P5); the reference-named buffers `_b1 .. _l3` are gone in that case."""
         super().__init__()
         resident = resident or os.environ.get("IXB200_RESIDENT", "p5")
-        if resident not in ("p5", "streams"):
-            raise ValueError("resident must be 'p5' or 'streams'")
+        if resident not in ("p5", "p6", "streams"):
+            raise ValueError("resident must be 'p5', 'p6' or 'streams'")
         dp = packed if isinstance(packed, DevicePacked) else DevicePacked(packed)
         self.out_features = dp.out_f
         self.in_features = dp.in_f
@@ -84,10 +84,12 @@ class StreamingLinear(nn.Module):
             self._bias_bf16 = None
         self._w_buf = None
         self._p5 = None
-        if resident == "p5":
-            from .p5 import P5Packed
-
-            self._p5 = P5Packed.from_packed(dp)
+        if resident in ("p5", "p6"):            # `_p5` names the resident re-layout, whichever of the two it is
+            if resident == "p5":
+                from .p5 import P5Packed as Resident
+            else:
+                from .p6 import P6Packed as Resident
+            self._p5 = Resident.from_packed(dp)
             if not keep_streams:
                 for key in ("_b1", "_b2", "_l1", "_l2", "_l3", "_b1_blk", "_b2_blk", "_q1", "_q2"):
                     if hasattr(self, key):

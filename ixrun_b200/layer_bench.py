@@ -19,6 +19,7 @@ import os
 import torch
 
 from .p5 import P5Packed
+from .p6 import P6Packed
 from .packed import DevicePacked
 from .synth import synthetic_packed
 
@@ -57,9 +58,9 @@ def run_case(dp: DevicePacked, total_bytes: int, kernel: str, rows: int, reps: i
     y = torch.empty(rows, out_f, dtype=torch.bfloat16, device=dp.device)
     if kernel == "gemv":
         fn = lambda: dp.gemv(x, out=y)
-    elif kernel == "p5":
+    elif kernel in ("p5", "p6"):
         fn = lambda: p5.gemv(x, out=y)
-    elif kernel == "p5decode":
+    elif kernel in ("p5decode", "p6decode"):
         w = torch.empty(out_f * in_f, dtype=torch.bfloat16, device=dp.device)
         fn = lambda: p5.decode(out=w)
     elif kernel == "gemm":
@@ -79,16 +80,59 @@ def run_case(dp: DevicePacked, total_bytes: int, kernel: str, rows: int, reps: i
             "Gelem_per_s": round(out_f * in_f / us / 1e3, 1)}
 
 
+def run_graph_case(dp: DevicePacked, total_bytes: int, kernel: str, rows: int, reps: int, first, pdl=False):
+    """Device time per launch with the launches back to back in a CUDA graph, over 4 copies of the layer."""
+    cls = P5Packed if kernel == "p5" else P6Packed
+    copies = [first] + [cls.from_packed(dp) for _ in range(3)]
+    x = torch.randn(rows, dp.in_f, device=dp.device).bfloat16()
+    y = torch.empty(rows, dp.out_f, dtype=torch.bfloat16, device=dp.device)
+    for c in copies:
+        c.gemv(x, out=y)
+    torch.cuda.synchronize()
+    if pdl:
+        from .p6 import set_pdl
+        set_pdl(True)
+    n = 20
+    st = torch.cuda.Stream()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(st):
+        with torch.cuda.graph(g, stream=st):
+            for i in range(n):
+                copies[i % 4].gemv(x, out=y)
+    ts = []
+    for _ in range(max(reps, 5)):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        g.replay()
+        b.record()
+        b.synchronize()
+        ts.append(a.elapsed_time(b) * 1e3 / n)
+    ts.sort()
+    us = ts[len(ts) // 2]
+    alg = total_bytes + 2 * dp.in_f * rows + 2 * dp.out_f * rows
+    gbs = alg / us / 1e3
+    if pdl:
+        set_pdl(False)
+    return {"shape": f"{dp.out_f}x{dp.in_f}", "rows": rows, "kernel": kernel + (" (graph, pdl)" if pdl else " (graph)"), "us": round(us, 2),
+            "us_min": round(ts[0], 2), "packed_GBps": round(gbs, 1), "frac_of_measured_hbm_peak": round(gbs / _peak(), 4),
+            "resident_bytes": first.resident_bytes}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--shape", default="5120x17408")
     ap.add_argument("--rows", type=int, default=1)
-    ap.add_argument("--kernel", default="gemv", choices=["gemv", "p5", "p5decode", "gemm", "decode", "dense"],
-                    help="gemv/gemm/decode: kernels on the reference's streams; p5/p5decode: on the resident P5 re-layout; "
+    ap.add_argument("--kernel", default="gemv", choices=["gemv", "p5", "p5decode", "p6", "p6decode", "gemm", "decode", "dense"],
+                    help="gemv/gemm/decode: kernels on the reference's streams; p5/p5decode, p6/p6decode: on the resident "
+                         "P5 / P6 re-layout; "
                          "dense: bf16 matmul on decoded weights")
     ap.add_argument("--reps", type=int, default=30)
     ap.add_argument("--no-flush", action="store_true")
     ap.add_argument("--sweep", action="store_true")
+    ap.add_argument("--pdl", action="store_true", help="p6 with --graph: programmatic dependent launch between the launches")
+    ap.add_argument("--graph", action="store_true",
+                    help="p5/p6: time 20 launches captured in one CUDA graph, rotating over 4 copies of the layer "
+                         "(no host launch gaps, weights never served from L2)")
     args = ap.parse_args()
     flush = None if args.no_flush else torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
     if not args.sweep:
@@ -97,6 +141,12 @@ def main():
         dp = DevicePacked(p)
         wd = dp.decode(kind="bf16").clone() if args.kernel == "dense" else None
         p5 = P5Packed.from_packed(dp) if args.kernel.startswith("p5") else None
+        if args.kernel.startswith("p6"):
+            p5 = P6Packed.from_packed(dp)
+        if args.graph and args.kernel in ("p5", "p6"):
+            print(json.dumps(run_graph_case(dp, p["total_bytes"], args.kernel, args.rows, args.reps, p5,
+                                            pdl=args.pdl and args.kernel == "p6")), flush=True)
+            return
         print(json.dumps(run_case(dp, p["total_bytes"], args.kernel, args.rows, args.reps, flush, wd, p5)), flush=True)
         return
     for out_f, in_f in SWEEP_SHAPES:

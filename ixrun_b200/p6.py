@@ -1,0 +1,106 @@
+"""Resident re-layout "P6" of a packed tensor (see ``csrc/ixb_p6.cuh``).
+
+Same role as :mod:`ixrun_b200.p5`: the (3,5,8) streams remain the interchange
+format and ``P6Packed.from_packed`` transcodes them on the GPU, keeping every
+int8 code.  P6 spends 6 plane bits per weight on a field that *is* part of the
+bf16 number ``1 + code/32`` (codes -16..31), so one fused multiply-add per pair
+of weights yields the reference's ``bf16(code * scale)``; every other code goes
+to a short list that the GEMV adds on the CUDA cores.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from . import _lib
+from .packed import DevicePacked
+
+__all__ = ["P6Packed", "set_pdl"]
+
+
+def set_pdl(on: bool) -> bool:
+    """Programmatic dependent launch for the P6 GEMV (process-wide; returns the previous setting).
+
+    When on, a GEMV launch may begin fetching its weights while the kernel ahead of it in the stream finishes; it
+    still waits for that kernel before touching activations, output or scratch.  Turn it on after deployment, once
+    the device has been synchronised: a layout still being built would be read too early."""
+    return bool(_lib.lib().ixb_set_pdl(1 if on else 0))
+
+CODE_MIN, CODE_MAX = -16, 31     # codes that the plane holds
+SLACK_BLOCKS, SLACK_ENTRIES, BLOCK_BYTES = 5, 64, 768
+
+
+class P6Packed:
+    def __init__(self, codes: torch.Tensor, scale: torch.Tensor, out_f: int, in_f: int, total_bytes: int = 0):
+        """codes: int8 [out_f*in_f] on a CUDA device; scale: bf16 scalar."""
+        if not codes.is_cuda or codes.dtype != torch.int8 or codes.numel() != out_f * in_f:
+            raise ValueError("P6Packed needs out_f*in_f int8 codes on a CUDA device")
+        dev = codes.device
+        self.device, self.out_f, self.in_f, self.N = dev, int(out_f), int(in_f), int(out_f) * int(in_f)
+        self.total_bytes = int(total_bytes)          # the reference format's byte count of this tensor
+        c = codes.contiguous().reshape(-1)
+        n_esc = int(((c < CODE_MIN) | (c > CODE_MAX)).sum().item())
+        L = _lib.lib()
+        nb = int(L.ixb_p5_blocks(self.out_f, self.in_f))
+        # sizes include the slack that the GEMV's prefetch may read
+        self.plane = torch.empty((nb + SLACK_BLOCKS) * BLOCK_BYTES // 4, dtype=torch.int32, device=dev)
+        self.blk_off = torch.empty(nb + 1, dtype=torch.int32, device=dev)
+        self.esc = torch.empty(n_esc + SLACK_ENTRIES, dtype=torch.int32, device=dev)
+        self.n_esc = n_esc
+        self.scale = scale.detach().to(dev, torch.bfloat16).reshape(()).contiguous()
+        ws = torch.empty((nb + 1) * 4, dtype=torch.uint8, device=dev)
+        with torch.cuda.device(dev):
+            _lib.check(L.ixb_p6_build(c.data_ptr(), self.scale.data_ptr(), self.out_f, self.in_f, self.plane.data_ptr(),
+                                      self.blk_off.data_ptr(), self.esc.data_ptr(), n_esc,
+                                      ws.data_ptr(), ws.numel(), _lib.stream_ptr(dev)))
+        self.struct = _lib.P6Struct(self.plane.data_ptr(), self.blk_off.data_ptr(), self.esc.data_ptr(), n_esc,
+                                    self.scale.data_ptr(), self.out_f, self.in_f)
+        self.resident_bytes = nb * BLOCK_BYTES + 4 * (nb + 1 + n_esc) + 2
+        self._scratch = {}
+
+    @classmethod
+    def from_packed(cls, packed):
+        """From the reference's packed dict or a DevicePacked: decode the streams to codes, re-lay out."""
+        dp = packed if isinstance(packed, DevicePacked) else DevicePacked(packed)
+        codes = dp.decode(kind="codes").reshape(-1)
+        return cls(codes, dp.scale, dp.out_f, dp.in_f, total_bytes=dp.total_bytes)
+
+    def decode(self, out: torch.Tensor | None = None, kind: str = "bf16") -> torch.Tensor:
+        dtype = {"bf16": torch.bfloat16, "codes": torch.int8}[kind]
+        if out is None:
+            out = torch.empty(self.N, dtype=dtype, device=self.device)
+        flat = out.reshape(-1)
+        if flat.dtype != dtype or flat.numel() < self.N or not flat.is_contiguous():
+            raise ValueError("decode output must be a contiguous tensor of the right dtype and size")
+        with torch.cuda.device(self.device):
+            _lib.check(_lib.lib().ixb_p6_decode(C.byref(self.struct), flat.data_ptr(), 0 if kind == "codes" else 1,
+                                                _lib.stream_ptr(self.device)))
+        return flat[: self.N].view(self.out_f, self.in_f)
+
+    def gemv(self, x: torch.Tensor, bias: torch.Tensor | None = None, out: torch.Tensor | None = None,
+             out_dtype=torch.bfloat16) -> torch.Tensor:
+        """y[M, out_f] = x[M, in_f] @ W.T, 1 <= M <= 8."""
+        if x.dtype != torch.bfloat16:
+            raise ValueError("activations must be bf16")
+        x2 = x.reshape(-1, self.in_f)
+        if not x2.is_contiguous():
+            x2 = x2.contiguous()
+        m = x2.shape[0]
+        if out is None:
+            out = torch.empty(m, self.out_f, dtype=out_dtype, device=self.device)
+        elif out.dtype not in (torch.bfloat16, torch.float32) or out.numel() != m * self.out_f or not out.is_contiguous():
+            raise ValueError("gemv output must be a contiguous bf16/fp32 tensor of M*out_f elements")
+        if bias is not None and (bias.dtype != torch.bfloat16 or bias.numel() != self.out_f):
+            raise ValueError("bias must be bf16 [out_f]")
+        s = self._scratch.get(m)
+        if s is None:
+            s = torch.zeros(_lib.lib().ixb_p6_gemv_scratch_bytes(self.out_f, self.in_f, m), dtype=torch.uint8,
+                            device=self.device)
+            self._scratch[m] = s
+        with torch.cuda.device(self.device):
+            _lib.check(_lib.lib().ixb_p6_gemv(C.byref(self.struct), x2.data_ptr(), m,
+                                              None if bias is None else bias.data_ptr(), out.data_ptr(),
+                                              1 if out.dtype == torch.float32 else 0, s.data_ptr(), s.numel(),
+                                              _lib.stream_ptr(self.device)))
+        return out

@@ -1,0 +1,143 @@
+"""Resident P6 layout: lossless on the codes, GEMV equal to the oracle."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import ixb_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+SHAPES = [(64, 5120), (48, 5120), (40, 17408), (96, 2176), (7, 4352), (33, 96), (1, 32), (3, 1024), (300, 512),
+          (10, 96), (5, 100), (17, 72), (512, 17408), (16, 64)]
+
+
+def bits_to_bf16(a):
+    return torch.from_numpy(np.ascontiguousarray(a).view(np.int16)).view(torch.bfloat16)
+
+
+def rel_err(y, ref):
+    return float(np.abs(y.astype(np.float64) - ref).max() / max(float(np.abs(ref).max()), 1e-30))
+
+
+def make(out_f, in_f, seed, codes=None):
+    from ixrun_b200.p6 import P6Packed
+
+    if codes is None:
+        codes = O.laplace_codes(out_f, in_f, seed)
+    scale = torch.tensor(0.00251, dtype=torch.bfloat16)
+    return codes, scale, P6Packed(torch.from_numpy(codes).cuda(), scale, out_f, in_f)
+
+
+@pytest.mark.parametrize("out_f,in_f", SHAPES)
+def test_p6_roundtrip_is_lossless(out_f, in_f):
+    codes, scale, p6 = make(out_f, in_f, out_f + in_f)
+    assert np.array_equal(p6.decode(kind="codes").cpu().numpy().reshape(-1), codes)
+    sc_bits = int(scale.view(torch.int16).item()) & 0xFFFF
+    w = p6.decode(kind="bf16").cpu().view(torch.int16).numpy().view(np.uint16).reshape(-1)
+    assert np.array_equal(w, O.codes_to_bf16(codes, sc_bits))
+
+
+@pytest.mark.parametrize("out_f,in_f", SHAPES)
+@pytest.mark.parametrize("m", [1, 2, 5, 8])
+def test_p6_gemv_matches_oracle(out_f, in_f, m):
+    codes, scale, p6 = make(out_f, in_f, out_f * 5 + in_f + m)
+    sc_bits = int(scale.view(torch.int16).item()) & 0xFFFF
+    xb = O.f32_to_bf16_bits(np.random.default_rng(m).standard_normal((m, in_f)).astype(np.float32))
+    ref = O.gemm_f32(codes, sc_bits, xb, out_f, in_f).astype(np.float64)
+    x = bits_to_bf16(xb).cuda()
+    bias = torch.randn(out_f).bfloat16().cuda()
+    y32 = p6.gemv(x, out_dtype=torch.float32)
+    assert rel_err(y32.cpu().numpy(), ref) < 2e-5
+    assert torch.equal(p6.gemv(x), y32.bfloat16())
+    assert torch.equal(p6.gemv(x, bias=bias), p6.gemv(x) + bias)
+    assert torch.equal(p6.gemv(x, out_dtype=torch.float32), y32)
+
+
+def test_p6_extreme_level_mixes_and_from_packed(golden_dir):
+    from ixrun_b200.p6 import P6Packed
+
+    out_f, in_f = 8, 1024
+    n = out_f * in_f
+    rng = np.random.default_rng(0)
+    xb = O.f32_to_bf16_bits(rng.standard_normal((2, in_f)).astype(np.float32))
+    for codes in (rng.choice(np.r_[-127:-16, 32:128], size=n).astype(np.int8),
+                  rng.integers(-16, 32, size=n).astype(np.int8),
+                  rng.integers(-3, 4, size=n).astype(np.int8),
+                  np.where(np.arange(n) % 2 == 0, 1, 100).astype(np.int8),
+                  np.zeros(n, dtype=np.int8)):
+        c, scale, p6 = make(out_f, in_f, 0, codes=codes)
+        assert np.array_equal(p6.decode(kind="codes").cpu().numpy().reshape(-1), codes)
+        sc_bits = int(scale.view(torch.int16).item()) & 0xFFFF
+        ref = O.gemm_f32(codes, sc_bits, xb, out_f, in_f).astype(np.float64)
+        y = p6.gemv(bits_to_bf16(xb).cuda(), out_dtype=torch.float32).cpu().numpy()
+        assert float(np.abs(y - ref).max()) <= 2e-5 * max(float(np.abs(ref).max()), 1e-30)
+    # from the reference's packed streams (fixture written by the reference's own quantiser)
+    g = dict(np.load(os.path.join(golden_dir, "heavy_64x1024.npz")))
+    packed = {"level_bits": (3, 5, 8), "out_f": 64, "in_f": 1024, "N": 65536, "scale": bits_to_bf16(g["scale_bits"]).reshape(()),
+              "bitmaps": [torch.from_numpy(g["b1"]), torch.from_numpy(g["b2"])],
+              "streams": [torch.from_numpy(g["l1"]), torch.from_numpy(g["l2"]), torch.from_numpy(g["l3"])],
+              "counts": [int(c) for c in g["counts"]], "total_bytes": int(g["total_bytes"][0])}
+    p6 = P6Packed.from_packed(packed)
+    assert np.array_equal(p6.decode(kind="codes").cpu().numpy().reshape(-1), g["codes"])
+    y = p6.gemv(bits_to_bf16(g["x_bits"]).cuda(), out_dtype=torch.float32).cpu().numpy()
+    assert rel_err(y, g["y_f32"].astype(np.float64)) < 2e-5
+
+
+@pytest.mark.parametrize("out_f,in_f", [(5120, 17408), (17408, 5120)])
+def test_p6_full_size_agrees_with_the_stream_kernel(out_f, in_f):
+    """Benchmark shapes: the GEMV on the resident layout against the fused kernel on the reference's streams
+    (itself checked against the oracle), the decoded codes against the stream decoder, twice for reproducibility."""
+    from ixrun_b200.p6 import P6Packed
+    from ixrun_b200.packed import DevicePacked
+    from ixrun_b200.synth import synthetic_packed
+
+    dp = DevicePacked(synthetic_packed(out_f, in_f, seed=3))
+    p6 = P6Packed.from_packed(dp)
+    assert torch.equal(p6.decode(kind="codes"), dp.decode(kind="codes"))
+    for m in (1, 8):
+        x = torch.randn(m, in_f, device="cuda").bfloat16()
+        ref = dp.gemv(x, out_dtype=torch.float32)
+        y = p6.gemv(x, out_dtype=torch.float32)
+        assert float((y - ref).abs().max() / ref.abs().max()) < 2e-5
+        assert torch.equal(p6.gemv(x, out_dtype=torch.float32), y)
+    assert p6.resident_bytes < 1.2 * dp.total_bytes
+
+
+def test_p6_programmatic_dependent_launch_gives_the_same_result():
+    """Back-to-back launches with programmatic dependent launch on (eagerly and replayed from a CUDA graph):
+    every launch must still see the activations written just before it and produce the bits of a plain launch."""
+    from ixrun_b200.p6 import set_pdl
+
+    out_f, in_f = 512, 5120
+    _, _, a = make(out_f, in_f, 11)
+    _, _, b = make(in_f, out_f, 12)
+    x = torch.randn(1, in_f, device="cuda").bfloat16()
+    h_ref = a.gemv(x)
+    y_ref = b.gemv(h_ref)
+    torch.cuda.synchronize()
+    prev = set_pdl(True)
+    try:
+        h = torch.empty_like(h_ref)
+        y = torch.empty_like(y_ref)
+        for _ in range(3):
+            h.zero_()
+            y.zero_()
+            a.gemv(x, out=h)
+            b.gemv(h, out=y)          # reads what the launch just ahead of it wrote
+            assert torch.equal(h, h_ref) and torch.equal(y, y_ref)
+        st = torch.cuda.Stream()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(st):
+            with torch.cuda.graph(g, stream=st):
+                for _ in range(4):
+                    a.gemv(x, out=h)
+                    b.gemv(h, out=y)
+        h.zero_()
+        y.zero_()
+        g.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(h, h_ref) and torch.equal(y, y_ref)
+    finally:
+        set_pdl(prev)
