@@ -202,6 +202,13 @@ def run_gpu(args):
     for i in range(max(args.warmup, 3)):
         step(i)
     barrier()
+    pdl = args.layout == "p6" and not args.no_pdl
+    if pdl:
+        # deployment is complete and the device idle: from here on a GEMV launch may fetch its first weight blocks
+        # while the kernel ahead of it in the stream finishes (it still waits for that kernel before it reads x)
+        from ixrun_b200.p6 import set_pdl
+
+        set_pdl(True)
 
     # ---- timed region: K steps, device timed, max over ranks
     graph = None
@@ -307,6 +314,7 @@ def run_gpu(args):
             "l2": f"timed steps rotate over {COPIES} device copies of the weights ({COPIES * resident_bytes / 1e6:.0f} MB per GPU)",
             "parallelism": "single GPU" if world == 1 else f"tp{world}: column shards of in_f, one NCCL all-reduce of y per step",
             "timed_with": "CUDA events around one graph replay of K launches" if graph is not None else "CUDA events around K eager steps",
+            "programmatic_dependent_launch": bool(pdl),
         },
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "traffic": None, "peak_source": peak_src, "kernel": LAYOUT_KERNEL[args.layout],
@@ -333,7 +341,7 @@ def run_gpu(args):
         dist.destroy_process_group()
 
 
-DEFAULT_LAYOUT = "p5"
+DEFAULT_LAYOUT = "p6"
 LAYOUT_KERNEL = {"p5": "k_p5_mma<1>", "p6": "k_p6_mma<1>", "streams": "k_gemv<1>"}
 LAYOUT_TEXT = {
     "p5": ("resident P5 re-layout of the same int8 codes (5-bit plane in mma fragment order + level-3 weight list), "
@@ -352,6 +360,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--eager", action="store_true", help="launch the timed steps one by one instead of one CUDA graph")
+    ap.add_argument("--no-pdl", action="store_true",
+                    help="layout p6: launch the GEMVs without programmatic dependent launch")
     ap.add_argument("--layout", default=DEFAULT_LAYOUT, choices=["p5", "p6", "streams"],
                     help="resident weight layout: the P5 or P6 re-layout, or the reference's streams read directly")
     args = ap.parse_args()

@@ -1024,13 +1024,6 @@ extern "C" int ixb_p6_gemv(const ixb_p6 *t, const void *x, int64_t m_rows, const
     return launch_check("k_p6_mma");
 }
 
-#ifdef IXB_P6_TRACE
-extern "C" int ixb_p6_trace(long long *host_out, int n)
-{
-    return (int)cudaMemcpyFromSymbol(host_out, p6_trace, (size_t)n * 8);
-}
-#endif
-
 // ------------------------------------------------------- tensor-core small-M GEMM
 static TcPlan make_tc_plan(uint32_t out_f, uint32_t in_f)
 {

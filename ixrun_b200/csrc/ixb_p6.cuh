@@ -287,13 +287,6 @@ __device__ __forceinline__ uint32_t p6_part_of(uint32_t pos, uint32_t q, uint32_
 // last arriver sums the slots in CTA order.  tickets[] (gridDim.x + 1 words) must be zero before the first
 // launch and is left zero.  XS = 1: activations staged in shared memory (bf16, padded rows); XS = 0: read from
 // global memory.
-#ifdef IXB_P6_TRACE
-__device__ long long p6_trace[160 * 24 * 8];
-__device__ __forceinline__ long long p6_gtime() { long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; }
-#define P6_STAMP(k) do { if (lane == 0) p6_trace[(blockIdx.x * 24 + wid) * 8 + (k)] = p6_gtime(); } while (0)
-#else
-#define P6_STAMP(k) do { } while (0)
-#endif
 
 template <int XS>
 __global__ void __launch_bounds__(kP6Threads, 1)
@@ -306,7 +299,6 @@ k_p6_mma(P6 p, const __nv_bfloat16 *__restrict__ x, uint32_t m_rows, const __nv_
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
     const int g = lane >> 2, t = lane & 3;
     const uint32_t KB = p.kb;
-    P6_STAMP(0);
     unsigned char *wsm = p6_smem + wid * kP6WarpSmem;
     float *oacc = (float *)(wsm + kP6RingBytes);                       // [16 rows][32 lanes] outlier sums, zero between passes
     uint32_t *estage = (uint32_t *)(wsm + kP6RingBytes + 2048);        // the run's first kP6StageEntries outlier entries
@@ -346,9 +338,7 @@ k_p6_mma(P6 p, const __nv_bfloat16 *__restrict__ x, uint32_t m_rows, const __nv_
         c2 = b2 ^ 0x80008000u;
         asm volatile("mov.b32 %0, 0x3F003F00;" : "=r"(e2));            // opaque, so that it stays a register operand
     }
-    P6_STAMP(1);
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    P6_STAMP(2);
     if (XS) {
         // whole 16-byte chunks by cp.async; ragged ends are written with plain stores
         const uint32_t chunks = KB * (kP5TileCols / 8);
@@ -386,7 +376,6 @@ k_p6_mma(P6 p, const __nv_bfloat16 *__restrict__ x, uint32_t m_rows, const __nv_
     cp_async_commit();
     cp_async_wait<1>();                              // group A has landed for this thread
     __syncthreads();                                 // ... and for the CTA
-    P6_STAMP(3);
 
     if (active) {
         float c[4] = {0.f, 0.f, 0.f, 0.f};
@@ -521,10 +510,8 @@ k_p6_mma(P6 p, const __nv_bfloat16 *__restrict__ x, uint32_t m_rows, const __nv_
             ++R;
         }
     }
-    P6_STAMP(4);
     cp_async_wait<0>();
     __syncthreads();
-    P6_STAMP(5);
 
     // ---- per CTA: sum the parts of every tile that more than one run of this CTA (or another CTA) touched
     if (L) {
@@ -568,7 +555,6 @@ k_p6_mma(P6 p, const __nv_bfloat16 *__restrict__ x, uint32_t m_rows, const __nv_
             if (lane == 0) tickets[clo + 1] = 0;
         }
     }
-    P6_STAMP(6);
 }
 
 }  // namespace ixb

@@ -39,13 +39,13 @@ class StreamingLinear(nn.Module):
     def __init__(self, packed, bias=None, resident: str | None = None, keep_streams: bool = True):
         """`packed`: the reference's packed dict, or a DevicePacked already on the GPU.
 
-        resident: "p5" (default; environment variable IXB200_RESIDENT overrides the default) or "p6" re-lays the
+        resident: "p6" (default; environment variable IXB200_RESIDENT overrides the default) or "p5" re-lays the
         codes out at construction as a plane + outlier list and runs inputs of up to 8 rows on it; "streams" keeps
         to the reference's (3,5,8) streams and the fused kernel that reads them directly.
         keep_streams=False frees the stream buffers once the P5 layout exists (larger inputs then decode from
         P5); the reference-named buffers `_b1 .. _l3` are gone in that case."""
         super().__init__()
-        resident = resident or os.environ.get("IXB200_RESIDENT", "p5")
+        resident = resident or os.environ.get("IXB200_RESIDENT", "p6")
         if resident not in ("p5", "p6", "streams"):
             raise ValueError("resident must be 'p5', 'p6' or 'streams'")
         dp = packed if isinstance(packed, DevicePacked) else DevicePacked(packed)

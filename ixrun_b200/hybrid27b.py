@@ -53,7 +53,7 @@ def shard_shape(name, rows, cols, mode, world):
 
 
 class Stack:
-    def __init__(self, n_layers: int, world: int, rank: int, dev, layout: str = "p5"):
+    def __init__(self, n_layers: int, world: int, rank: int, dev, layout: str = "p6"):
         self.world, self.dev = world, dev
         cache = {}
 
@@ -68,6 +68,10 @@ class Stack:
                 from .p5 import P5Packed
 
                 return P5Packed.from_packed(dp)         # the streams are dropped, the re-layout stays resident
+            if layout == "p6":
+                from .p6 import P6Packed
+
+                return P6Packed.from_packed(dp)
             return dp
 
         self.layers = []
@@ -198,8 +202,10 @@ def main():
     ap.add_argument("--layers", type=int, default=64)
     ap.add_argument("--tokens", type=int, default=16)
     ap.add_argument("--eager", action="store_true")
-    ap.add_argument("--layout", default="p5", choices=["p5", "streams"],
-                    help="resident weight layout: the P5 re-layout or the reference's streams read directly")
+    ap.add_argument("--layout", default="p6", choices=["p6", "p5", "streams"],
+                    help="resident weight layout: the P6 or P5 re-layout, or the reference's streams read directly")
+    ap.add_argument("--no-pdl", action="store_true",
+                    help="layout p6: launch the GEMVs without programmatic dependent launch")
     args = ap.parse_args()
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -213,6 +219,11 @@ def main():
     t0 = time.time()
     with torch.no_grad():
         st = Stack(args.layers, world, rank, dev, layout=args.layout)
+        torch.cuda.synchronize()
+        if args.layout == "p6" and not args.no_pdl:
+            from .p6 import set_pdl
+
+            set_pdl(True)                               # every layout is complete: GEMVs may overlap their neighbours' tails
         setup = time.time() - t0
         mode = "eager"
         if not args.eager:
