@@ -10,6 +10,7 @@ and the teacher-forced greedy-token agreement between the two.
 from __future__ import annotations
 
 import argparse
+import os
 import json
 import time
 
@@ -25,6 +26,8 @@ def main():
     ap.add_argument("--new", type=int, default=256)
     ap.add_argument("--shared-layer-weights", action="store_true",
                     help="generate one tensor per linear type and reuse it in every layer (faster set-up)")
+    ap.add_argument("--no-pdl", action="store_true",
+                    help="launch the packed GEMVs without programmatic dependent launch")
     args = ap.parse_args()
     cfg = LlamaConfig(n_layers=args.layers, max_seq=args.prompt + args.new)
     t0 = time.time()
@@ -36,6 +39,11 @@ def main():
     setup_s = time.time() - t0
     prompt = torch.randint(0, cfg.vocab, (args.prompt,), generator=torch.Generator().manual_seed(1))
     lp, ld = packed.prefill(prompt), dense.prefill(prompt)
+    torch.cuda.synchronize()
+    if not args.no_pdl and os.environ.get("IXB200_RESIDENT", "p6") == "p6":
+        from .p6 import set_pdl
+
+        set_pdl(True)               # every layout is complete: a GEMV may fetch weights while its predecessor finishes
     packed.capture()
     dense.capture()
 
@@ -74,6 +82,7 @@ def main():
         "model": f"llama-style {args.layers}L h{cfg.hidden} ffn{cfg.intermediate} {cfg.n_heads}q/{cfg.n_kv_heads}kv vocab{cfg.vocab}",
         "packed_linears": len(layers) * 7, "packed_weights": n_weights, "packed_MB": packed_bytes / 1e6,
         "prompt": args.prompt, "new_tokens": args.new, "mode": "one CUDA graph per token step",
+        "resident_layout": os.environ.get("IXB200_RESIDENT", "p6"), "programmatic_dependent_launch": not args.no_pdl,
         "ms_per_token_packed": ms_packed, "ms_per_token_decoded_bf16": ms_dense,
         "greedy_agreement_teacher_forced": agree / args.new, "steps_with_exact_top1_tie": ties,
         "free_running_prefix_match": int((toks_packed == toks_dense).long().cumprod(0).sum().item()),
