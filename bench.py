@@ -185,12 +185,23 @@ def run_gpu(args):
     y32 = torch.empty(1, OUT_F, dtype=torch.float32, device=dev)
     y16 = torch.empty(1, OUT_F, dtype=torch.bfloat16, device=dev)
 
+    # several GPUs: the fp32 partial outputs are summed by one kernel of this library over peer memory
+    # (graph-capturable); --nccl keeps the eager NCCL all-reduce
+    ar = None
+    if world > 1 and not args.nccl:
+        from ixrun_b200.parallel import PeerAllReduce
+
+        ar = PeerAllReduce(OUT_F, dev)
+
     def step(i):
         lay = layers[i % COPIES]
         if world > 1:
             lay.matvec(x, out=y32)
-            dist.all_reduce(y32)
-            y16.copy_(y32)
+            if ar is not None:
+                ar(y32, out=y16)
+            else:
+                dist.all_reduce(y32)
+                y16.copy_(y32)
         else:
             lay.matvec(x, out=y16)
 
@@ -212,7 +223,7 @@ def run_gpu(args):
 
     # ---- timed region: K steps, device timed, max over ranks
     graph = None
-    if world == 1 and not args.eager:
+    if (world == 1 or ar is not None) and not args.eager:
         # one CUDA graph holding the K launches keeps host launch gaps out of the device time
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
@@ -245,7 +256,7 @@ def run_gpu(args):
         t = torch.tensor([ms], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t.item())
-    launches = args.steps if graph is not None else _lib.lib().ixb_launch_count() - launches0
+    launches = args.steps * (2 if ar is not None else 1) if graph is not None else _lib.lib().ixb_launch_count() - launches0
     ms_per_step = ms / args.steps
     value = alg_bytes / (ms_per_step * 1e-3) / 1e9
 
@@ -259,7 +270,7 @@ def run_gpu(args):
         b.record()
         b.synchronize()
         kt.append(a.elapsed_time(b))
-    k_ms = float(np.mean(kt)) if graph is None else ms_per_step
+    k_ms = ms_per_step if (graph is not None and world == 1) else float(np.mean(kt))
     peak, peak_src = measured_peak()
     achieved = alg_bytes_rank / (k_ms * 1e-3) / 1e9
 
@@ -281,7 +292,10 @@ def run_gpu(args):
             torch.cuda.current_stream().synchronize()
             return
         xd = x_host.to(dev, non_blocking=True)
-        if world > 1:
+        if world > 1 and ar is not None:
+            layers[i % COPIES].matvec(xd, out=y32)
+            y_host.copy_(ar(y32, out=y16), non_blocking=True)
+        elif world > 1:
             layers[i % COPIES].matvec(xd, out=y32)
             dist.all_reduce(y32)
             y_host.copy_(y32.to(torch.bfloat16), non_blocking=True)
@@ -312,9 +326,12 @@ def run_gpu(args):
             "layout": LAYOUT_TEXT[args.layout],
             "resident_bytes_per_gpu": resident_bytes,
             "l2": f"timed steps rotate over {COPIES} device copies of the weights ({COPIES * resident_bytes / 1e6:.0f} MB per GPU)",
-            "parallelism": "single GPU" if world == 1 else f"tp{world}: column shards of in_f, one NCCL all-reduce of y per step",
+            "parallelism": ("single GPU" if world == 1 else
+                            f"tp{world}: column shards of in_f, fp32 partial outputs summed per step by " +
+                            ("one kernel over peer memory (ixb_allreduce)" if ar is not None else "one NCCL all-reduce")),
             "timed_with": "CUDA events around one graph replay of K launches" if graph is not None else "CUDA events around K eager steps",
             "programmatic_dependent_launch": bool(pdl),
+            "peer_allreduce_timed_out": (ar.timed_out() if ar is not None else None),
         },
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "traffic": None, "peak_source": peak_src, "kernel": LAYOUT_KERNEL[args.layout],
@@ -360,6 +377,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--eager", action="store_true", help="launch the timed steps one by one instead of one CUDA graph")
+    ap.add_argument("--nccl", action="store_true",
+                    help="several GPUs: eager NCCL all-reduce instead of the one-kernel all-reduce over peer memory")
     ap.add_argument("--no-pdl", action="store_true",
                     help="layout p6: launch the GEMVs without programmatic dependent launch")
     ap.add_argument("--layout", default=DEFAULT_LAYOUT, choices=["p5", "p6", "streams"],

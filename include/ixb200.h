@@ -228,6 +228,28 @@ int ixb_p6_gemv(const ixb_p6 *t, const void *x_device, int64_t m_rows, const voi
 int ixb_set_pdl(int on);
 
 /*
+ * One-shot all-reduce (sum, fp32) over peer memory for the partial outputs of
+ * row-parallel packed linears.  No counterpart in the reference, which is
+ * single-GPU; it stands where a tensor-parallel ixrun would call its
+ * collective after o_proj / down_proj (ixrun/engine.py:135-168 per shard).
+ * Every rank owns one buffer of ixb_allreduce_bytes(world, n_max) bytes that
+ * all ranks can address (peer pointers, e.g. torch symmetric memory), zeroed
+ * and followed by a barrier before the first call.  peer_buffers: host array
+ * of `world` device pointers, entry r = rank r's buffer as seen from this
+ * rank.  Every rank must make the same sequence of calls with the same n.
+ *   x: this rank's n fp32 partial sums (n a multiple of 4, n <= n_max)
+ *   y: n sums over the ranks, added in rank order (the same bits on every
+ *      rank), + bias (bf16, after rounding for bf16 output), bf16 or fp32
+ * One kernel: peer stores of data then flags, a bounded wait on the local
+ * flags (on a time-out the last word of the buffer becomes non-zero and the
+ * result is wrong; the kernel never hangs), local sum.  Graph-capturable;
+ * follows ixb_set_pdl.  world in {1, 2, 4, 8}.
+ */
+size_t ixb_allreduce_bytes(int world, int64_t n_max);
+int ixb_allreduce(const void *x_device_f32, int64_t n, void *const *peer_buffers, int rank, int world, int64_t n_max,
+                  const void *bias_device, void *y_device, int y_is_f32, ixb_stream_t stream);
+
+/*
  * Fused decode + small-M GEMM on the tensor cores (tcgen05, accumulators in
  * TMEM) for 1 <= m_rows <= 64; intended for 9..64 rows (batched decode, MTP
  * verify), below that ixb_gemv is the better call.  Same result definition and

@@ -24,6 +24,7 @@ SYMBOLS = (
     "ixb_pack_workspace_bytes", "ixb_quantize_codes", "ixb_count_codes", "ixb_pack_codes",
     "ixb_p5_blocks", "ixb_p5_build", "ixb_p5_decode", "ixb_p5_gemv_scratch_bytes", "ixb_p5_gemv",
     "ixb_p6_build", "ixb_p6_decode", "ixb_p6_gemv_scratch_bytes", "ixb_p6_gemv", "ixb_set_pdl",
+    "ixb_allreduce_bytes", "ixb_allreduce",
 )
 
 
@@ -122,6 +123,10 @@ def lib():
     L.ixb_p6_gemv.argtypes = [C.POINTER(P6Struct), vp, i64, vp, vp, C.c_int, vp, sz, vp]
     L.ixb_set_pdl.restype = C.c_int
     L.ixb_set_pdl.argtypes = [C.c_int]
+    L.ixb_allreduce_bytes.restype = sz
+    L.ixb_allreduce_bytes.argtypes = [C.c_int, i64]
+    L.ixb_allreduce.restype = C.c_int
+    L.ixb_allreduce.argtypes = [vp, i64, C.POINTER(C.c_void_p), C.c_int, C.c_int, i64, vp, vp, C.c_int, vp]
     L.ixb_gemv_static.restype = C.c_int
     L.ixb_gemv_static.argtypes = [C.POINTER(Packed), vp, vp, vp, i64, vp, vp, C.c_int, vp]
     _lib = L

@@ -6,6 +6,7 @@
 #include "ixb_pack.cuh"
 #include "ixb_p5.cuh"
 #include "ixb_p6.cuh"
+#include "ixb_allreduce.cuh"
 
 #include <atomic>
 #include <cstdarg>
@@ -929,6 +930,10 @@ extern "C" int ixb_p6_decode(const ixb_p6 *t, void *out, int out_kind, ixb_strea
     if (out_kind != 0 && out_kind != 1) return fail(IXB_E_ARG, "out_kind must be 0 (int8 codes) or 1 (bf16 weights)");
     cudaStream_t st = (cudaStream_t)stream;
     uint32_t nb = p.rt * p.kb;
+    if (out_kind == 1 && (p.in_f & 7u) == 0 && ((uintptr_t)out & 15u) == 0) {
+        k_p6_decode_bf16<<<(nb + 7) / 8, 256, 0, st>>>(p, (__nv_bfloat16 *)out);       // plane and outliers in one pass
+        return launch_check("k_p6_decode_bf16");
+    }
     if (out_kind == 0) k_p6_decode_plane<0><<<(nb + 7) / 8, 256, 0, st>>>(p, out);
     else k_p6_decode_plane<1><<<(nb + 7) / 8, 256, 0, st>>>(p, out);
     if ((rc = launch_check("k_p6_decode_plane"))) return rc;
@@ -940,7 +945,7 @@ extern "C" int ixb_p6_decode(const ixb_p6 *t, void *out, int out_kind, ixb_strea
     return rc;
 }
 
-struct P6Plan { uint32_t nb, grid, xstride, smem, xs; size_t slot_bytes; };
+struct P6Plan { uint32_t nb, grid, xstride, smem, xs, cq, cr, unit; size_t slot_bytes; };
 
 static P6Plan make_p6_plan(uint32_t out_f, uint32_t in_f, uint32_t m_rows)
 {
@@ -951,6 +956,22 @@ static P6Plan make_p6_plan(uint32_t out_f, uint32_t in_f, uint32_t m_rows)
     uint32_t want = (p.nb + kP6Warps - 1) / kP6Warps;
     p.grid = want < sms ? want : sms;
     if (!p.grid) p.grid = 1;
+    p.unit = 1;
+    {
+        // Balanced to one block, row tiles at CTA boundaries are finished across CTAs: slot store, fence, ticket and
+        // slot loads, about 3.4 us at the end of the kernel, worth about 170 blocks of streaming (11.5 us for the 588
+        // blocks per CTA of the 5120 x 17408 layer).  Whole row tiles per CTA avoid that at the price of imbalance.
+        const uint32_t tgrid = rt < sms ? rt : sms;
+        const uint32_t shared_cost = (p.nb + p.grid - 1) / p.grid + 170u;
+        const uint32_t tiles_cost = ((rt + tgrid - 1) / tgrid) * kb;
+        if (tiles_cost <= shared_cost) {
+            p.grid = tgrid;
+            p.unit = kb;
+        }
+    }
+    const uint32_t units = p.nb / p.unit;
+    p.cq = units / p.grid;
+    p.cr = units % p.grid;
     p.xstride = kb * kP5TileCols + 8u;
     uint32_t xbytes = m_rows * p.xstride * 2u;
     p.xs = (uint32_t)kP6SmemFixed + xbytes <= 227u * 1024u;
@@ -998,7 +1019,7 @@ static cudaError_t launch_p6(const P6 &p, const void *x, uint32_t m_rows, const 
     cfg.attrs = attr;
     cfg.numAttrs = g_p6_pdl ? 1 : 0;
     return cudaLaunchKernelEx(&cfg, k_p6_mma<XS>, p, (const __nv_bfloat16 *)x, m_rows, (const __nv_bfloat16 *)bias, y, y_f32,
-                              slots, tickets, pl.nb, pl.xstride, pl.nb / pl.grid, pl.nb % pl.grid);
+                              slots, tickets, pl.nb, pl.xstride, pl.cq, pl.cr, pl.unit);
 }
 
 extern "C" int ixb_p6_gemv(const ixb_p6 *t, const void *x, int64_t m_rows, const void *bias, void *y, int y_is_f32,
@@ -1022,6 +1043,65 @@ extern "C" int ixb_p6_gemv(const ixb_p6 *t, const void *x, int64_t m_rows, const
                           : launch_p6<0>(p, x, (uint32_t)m_rows, bias, y, y_is_f32, slots, tickets, pl, st);
     if (e != cudaSuccess) return fail(IXB_E_CUDA, "k_p6_mma launch: %s", cudaGetErrorString(e));
     return launch_check("k_p6_mma");
+}
+
+// ------------------------------------------------------- one-shot all-reduce over peer memory
+extern "C" size_t ixb_allreduce_bytes(int world, int64_t n_max)
+{
+    if (world < 1 || world > kArMaxWorld || n_max <= 0 || (n_max & 3)) return 0;
+    // slots, flags [world][ctas], epoch [ctas], one error word; rounded up to 256 bytes
+    size_t b = ar_slots_bytes(world, n_max) + ((size_t)world * ar_ctas(n_max) + ar_ctas(n_max) + 1) * 4;
+    return (b + 255) & ~(size_t)255;
+}
+
+template <int W>
+static cudaError_t launch_ar(const ArPeers &peers, const void *x, int rank, uint32_t n, uint32_t n_max, const void *bias,
+                             void *y, int y_f32, uint32_t *epoch, uint32_t *err, cudaStream_t st)
+{
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(ar_ctas(n_max));
+    cfg.blockDim = dim3(kArThreads);
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = g_p6_pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, k_allreduce_oneshot<W>, peers, (const float *)x, rank, n, n_max,
+                              (const __nv_bfloat16 *)bias, y, y_f32, epoch, err);
+}
+
+extern "C" int ixb_allreduce(const void *x, int64_t n, void *const *peer_buffers, int rank, int world, int64_t n_max,
+                             const void *bias, void *y, int y_is_f32, ixb_stream_t stream)
+{
+    if (!x || !y || !peer_buffers) return fail(IXB_E_ARG, "NULL pointer argument");
+    if (world < 1 || world > kArMaxWorld || rank < 0 || rank >= world) return fail(IXB_E_ARG, "bad rank/world");
+    if (n <= 0 || n > n_max || (n & 3) || (n_max & 3)) return fail(IXB_E_ARG, "n must be a multiple of 4 and at most n_max");
+    if (((uintptr_t)x & 15u) || ((uintptr_t)y & 7u)) return fail(IXB_E_ARG, "x / y are misaligned");
+    ArPeers peers;
+    const size_t sb = ar_slots_bytes(world, n_max);
+    const uint32_t ctas = ar_ctas(n_max);
+    for (int r = 0; r < world; ++r) {
+        if (!peer_buffers[r] || ((uintptr_t)peer_buffers[r] & 15u)) return fail(IXB_E_ARG, "peer buffer %d is NULL or misaligned", r);
+        peers.slots[r] = (float *)peer_buffers[r];
+        peers.flags[r] = (uint32_t *)((char *)peer_buffers[r] + sb);
+    }
+    for (int r = world; r < kArMaxWorld; ++r) {
+        peers.slots[r] = nullptr;
+        peers.flags[r] = nullptr;
+    }
+    uint32_t *epoch = peers.flags[rank] + (size_t)world * ctas, *err = epoch + ctas;
+    cudaStream_t st = (cudaStream_t)stream;
+    cudaError_t e;
+    switch (world) {
+    case 1: e = launch_ar<1>(peers, x, rank, (uint32_t)n, (uint32_t)n_max, bias, y, y_is_f32, epoch, err, st); break;
+    case 2: e = launch_ar<2>(peers, x, rank, (uint32_t)n, (uint32_t)n_max, bias, y, y_is_f32, epoch, err, st); break;
+    case 4: e = launch_ar<4>(peers, x, rank, (uint32_t)n, (uint32_t)n_max, bias, y, y_is_f32, epoch, err, st); break;
+    case 8: e = launch_ar<8>(peers, x, rank, (uint32_t)n, (uint32_t)n_max, bias, y, y_is_f32, epoch, err, st); break;
+    default: return fail(IXB_E_UNSUPPORTED, "world=%d: supported sizes are 1, 2, 4, 8", world);
+    }
+    if (e != cudaSuccess) return fail(IXB_E_CUDA, "k_allreduce_oneshot launch: %s", cudaGetErrorString(e));
+    return launch_check("k_allreduce_oneshot");
 }
 
 // ------------------------------------------------------- tensor-core small-M GEMM

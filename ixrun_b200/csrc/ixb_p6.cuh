@@ -279,8 +279,83 @@ __device__ __forceinline__ uint32_t p6_part_of(uint32_t pos, uint32_t q, uint32_
     return pos < big ? pos / (q + 1u) : r + (pos - big) / q;      // q > 0 whenever pos >= big
 }
 
-// The nb blocks, in (row tile, column block) order, are cut into gridDim.x contiguous CTA ranges (cq, cr = nb / and
-// % gridDim.x) and every CTA range into kP6Warps runs.  A run is walked segment by segment (its part of one row
+// layout -> bf16 weights in one pass, with the GEMV's own conversion (shift, mask, one fma per pair of elements): the
+// block's outliers are dropped into a zeroed image of the lanes' registers in shared memory first and OR-ed over the
+// placeholders (+0.0), so every weight is stored once, in 16-byte pieces; needs in_f % 8 == 0 and a 16-byte aligned
+// output.  One warp per block.
+__global__ void __launch_bounds__(256) k_p6_decode_bf16(P6 p, __nv_bfloat16 *out)
+{
+    __shared__ uint4 images[8 * 128];                // per warp: [4 mma][32 lanes] the lane's four A registers
+    uint32_t b = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    int lane = threadIdx.x & 31;
+    if (b >= p.rt * p.kb) return;                    // whole warps leave together
+    uint4 *img = images + (threadIdx.x >> 5) * 128;
+#pragma unroll
+    for (int q = 0; q < 4; ++q) img[q * 32 + lane] = make_uint4(0, 0, 0, 0);
+    __syncwarp();
+    {
+        const uint32_t img_s = (uint32_t)__cvta_generic_to_shared(img);
+        const int32_t lo = __ldg(p.blk_off + b), hi = __ldg(p.blk_off + b + 1);
+        for (int32_t j = lo + lane; j < hi; j += 32) {
+            const uint32_t e = __ldg(p.esc + j);
+            // element (row r, column c) of the block sits in lane 4 (r & 7) + (c >> 4), pair 4 ((c >> 2) & 3) +
+            // 2 ((c >> 1) & 1) + (r >> 3), half c & 1 (the inverse of p5_elem)
+            const uint32_t r = (e >> 12) & 15u, c = e & 63u;
+            const uint32_t ln = 4u * (r & 7u) + (c >> 4), j4 = (c >> 2) & 3u, q = 2u * ((c >> 1) & 1u) + (r >> 3);
+            const uint32_t off = ((j4 * 32u + ln) * 4u + q) * 4u + 2u * (c & 1u);
+            asm volatile("st.shared.u16 [%0], %1;" ::"r"(img_s + off), "h"((unsigned short)(e >> 16)) : "memory");
+        }
+    }
+    __syncwarp();
+    uint32_t R = b / p.kb, kbi = b - R * p.kb;
+    const float s32 = 32.f * __bfloat162float(*p.scale);
+    const uint32_t bb = (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(s32));
+    const uint32_t b2 = bb | (bb << 16), c2 = b2 ^ 0x80008000u, e2 = 0x3F003F00u;
+    const unsigned char *blk = p.plane + (size_t)b * kP6BlockBytes;
+    const uint4 a = ((const uint4 *)blk)[lane];
+    const uint2 a2 = ((const uint2 *)(blk + 512))[lane];
+    const uint32_t w[6] = {a.x, a.y, a.z, a.w, a2.x, a2.y};
+    uint32_t f[16];
+#pragma unroll
+    for (int k = 0; k < 6; ++k) {
+        f[2 * k] = p6_pair(w[k] << 2, e2, b2, c2);
+        f[2 * k + 1] = p6_pair(w[k] >> 4, e2, b2, c2);
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        uint32_t v = p5_and_or(w[i] >> 10, 0x003C003Cu, e2);
+        v = p5_and_or(w[4 + (i >> 1)] >> (6 + 2 * (i & 1)), 0x00C000C0u, v);
+        asm("fma.rn.bf16x2 %0, %1, %2, %3;" : "=r"(f[12 + i]) : "r"(v), "r"(b2), "r"(c2));
+    }
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {                    // placeholders are +0.0, so OR-ing the outlier weights in is exact
+        const uint4 v = img[q * 32 + lane];
+        f[4 * q] |= v.x;
+        f[4 * q + 1] |= v.y;
+        f[4 * q + 2] |= v.z;
+        f[4 * q + 3] |= v.w;
+    }
+    // pair 4 j + q: row g + 8 (q & 1), columns 4 j + 2 (q >> 1) + {0, 1} of the lane's 16
+    const uint32_t col0 = kbi * kP5TileCols + 16 * (lane & 3);
+#pragma unroll
+    for (int s = 0; s < 2; ++s) {
+        uint32_t row = R * kP5TileRows + (lane >> 2) + 8 * s;
+        if (row >= p.out_f || col0 >= p.in_f) continue;
+        __nv_bfloat16 *dst = out + (size_t)row * p.in_f + col0;
+        const uint32_t r[8] = {f[0 + s], f[2 + s], f[4 + s], f[6 + s], f[8 + s], f[10 + s], f[12 + s], f[14 + s]};
+        if (col0 + 16u <= p.in_f) {
+            ((uint4 *)dst)[0] = make_uint4(r[0], r[1], r[2], r[3]);
+            ((uint4 *)dst)[1] = make_uint4(r[4], r[5], r[6], r[7]);
+        } else {
+            for (uint32_t c = 0; col0 + c < p.in_f; ++c) ((uint16_t *)dst)[c] = (uint16_t)(r[c >> 1] >> (16 * (c & 1)));
+        }
+    }
+}
+
+// The nb blocks, in (row tile, column block) order, are cut into gridDim.x contiguous CTA ranges and every CTA range
+// into kP6Warps runs.  The CTA ranges are counted in units of `unit` blocks (cq, cr = units / and % gridDim.x):
+// unit = 1 balances the CTAs to one block, and row tiles at range boundaries are finished across CTAs; unit = blocks
+// per row tile gives every CTA whole row tiles, so nothing crosses CTAs (the host picks the cheaper of the two).  A run is walked segment by segment (its part of one row
 // tile): the segment's outliers are added first, from the entries staged in shared memory, then its blocks stream
 // through the warp's cp.async ring.  Row tiles that a run covers completely are written straight to y; partial
 // tiles are summed per CTA in warp order; a tile shared between CTAs goes through cta_slots and a ticket, the
@@ -291,7 +366,7 @@ __device__ __forceinline__ uint32_t p6_part_of(uint32_t pos, uint32_t q, uint32_
 template <int XS>
 __global__ void __launch_bounds__(kP6Threads, 1)
 k_p6_mma(P6 p, const __nv_bfloat16 *__restrict__ x, uint32_t m_rows, const __nv_bfloat16 *__restrict__ bias, void *y,
-         int y_f32, float4 *cta_slots, uint32_t *tickets, uint32_t nb, uint32_t xstride, uint32_t cq, uint32_t cr)
+         int y_f32, float4 *cta_slots, uint32_t *tickets, uint32_t nb, uint32_t xstride, uint32_t cq, uint32_t cr, uint32_t unit)
 {
     extern __shared__ __align__(128) unsigned char p6_smem[];
     __nv_bfloat16 *xs = (__nv_bfloat16 *)(p6_smem + kP6SmemFixed);                       // [m_rows][xstride]
@@ -304,7 +379,7 @@ k_p6_mma(P6 p, const __nv_bfloat16 *__restrict__ x, uint32_t m_rows, const __nv_
     uint32_t *estage = (uint32_t *)(wsm + kP6RingBytes + 2048);        // the run's first kP6StageEntries outlier entries
     float4 *wparts = (float4 *)(wsm + kP6RingBytes + 4096);            // partial sums of the run's first / last row tile
 
-    const uint32_t cb0 = p6_begin(blockIdx.x, cq, cr), cb1 = p6_begin(blockIdx.x + 1, cq, cr);
+    const uint32_t cb0 = p6_begin(blockIdx.x, cq, cr) * unit, cb1 = p6_begin(blockIdx.x + 1, cq, cr) * unit;
     const uint32_t L = cb1 - cb0, wq = L / kP6Warps, wr = L - wq * kP6Warps;
     const uint32_t b_begin = cb0 + p6_begin(wid, wq, wr), b_end = cb0 + p6_begin(wid + 1, wq, wr);
     const bool active = b_begin < b_end;

@@ -7,12 +7,13 @@ batch-1 decode step, one process per GPU.
 
 What is real: every packed linear of every layer with its true shape, sharded
 tensor-parallel (column-parallel in-projections / gate / up, row-parallel
-out/o/down projections), fp32 partial sums and ONE NCCL all-reduce per
+out/o/down projections), fp32 partial sums and ONE all-reduce per
 token-mixer block and per MLP block (2 per layer), residual adds and RMSNorms.
-On one GPU the whole token step is one CUDA graph; on several GPUs every
-stretch of launches between two all-reduces is its own graph and the NCCL
-all-reduces are launched eagerly in between (capturing the collectives inside
-one graph stalled on this pool and is not used).  What is a stand-in: the token mixers
+The whole token step is one CUDA graph.  On several GPUs the all-reduce is one
+kernel of this library over peer memory (parallel.PeerAllReduce) inside that
+graph; with --nccl every stretch of launches between two all-reduces is its
+own graph and NCCL all-reduces are launched eagerly in between (capturing NCCL
+inside one graph stalled on this pool).  What is a stand-in: the token mixers
 themselves (gated delta rule recurrence, causal conv, softmax attention over
 the KV cache) are replaced by an elementwise gate over the projected values, so
 the reported ms/token is the packed-weight path of the model, not the full
@@ -53,8 +54,13 @@ def shard_shape(name, rows, cols, mode, world):
 
 
 class Stack:
-    def __init__(self, n_layers: int, world: int, rank: int, dev, layout: str = "p6"):
+    def __init__(self, n_layers: int, world: int, rank: int, dev, layout: str = "p6", nccl: bool = False):
         self.world, self.dev = world, dev
+        self.ar = None
+        if world > 1 and not nccl:
+            from .parallel import PeerAllReduce
+
+            self.ar = PeerAllReduce(HIDDEN, dev)        # one kernel over peer memory per row-parallel layer
         cache = {}
 
         def mk(name, spec, seed):
@@ -97,6 +103,8 @@ class Stack:
         return (v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + 1e-6)).to(torch.bfloat16) * self.norm_w
 
     def _reduce(self, y32):
+        if self.ar is not None:
+            return self.ar(y32)
         if self.world > 1:
             dist.all_reduce(y32)
         return y32.to(torch.bfloat16)
@@ -151,7 +159,7 @@ class Stack:
         mlp["down_proj"].gemv(F.silu(g.float()).to(g.dtype) * u, out=self.y32)
 
     def capture(self):
-        if self.world == 1:
+        if self.world == 1 or self.ar is not None:
             side = torch.cuda.Stream()
             side.wait_stream(torch.cuda.current_stream())
             with torch.cuda.stream(side):
@@ -204,6 +212,9 @@ def main():
     ap.add_argument("--eager", action="store_true")
     ap.add_argument("--layout", default="p6", choices=["p6", "p5", "streams"],
                     help="resident weight layout: the P6 or P5 re-layout, or the reference's streams read directly")
+    ap.add_argument("--nccl", action="store_true",
+                    help="several GPUs: sum the partial outputs with eager NCCL all-reduces between per-stretch graphs "
+                         "instead of the one-kernel all-reduce over peer memory inside one graph per token")
     ap.add_argument("--no-pdl", action="store_true",
                     help="layout p6: launch the GEMVs without programmatic dependent launch")
     args = ap.parse_args()
@@ -218,17 +229,28 @@ def main():
         dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=120))
     t0 = time.time()
     with torch.no_grad():
-        st = Stack(args.layers, world, rank, dev, layout=args.layout)
+        st = Stack(args.layers, world, rank, dev, layout=args.layout, nccl=args.nccl)
         torch.cuda.synchronize()
         if args.layout == "p6" and not args.no_pdl:
             from .p6 import set_pdl
 
             set_pdl(True)                               # every layout is complete: GEMVs may overlap their neighbours' tails
         setup = time.time() - t0
+        ar_check = None
+        if st.ar is not None:
+            # the peer all-reduce against NCCL on one random vector (two ranks: the same bits; more: fp32 rounding)
+            v = torch.randn(1, HIDDEN, device=dev, generator=torch.Generator(device=dev).manual_seed(100 + rank))
+            got = st.ar(v, out_dtype=torch.float32)
+            ref = v.clone()
+            dist.all_reduce(ref)
+            ar_check = float((got - ref).abs().max() / ref.abs().max())
+            if ar_check > 1e-6 or st.ar.timed_out():
+                raise RuntimeError(f"peer all-reduce differs from NCCL: rel {ar_check}, timed out {st.ar.timed_out()}")
         mode = "eager"
         if not args.eager:
             st.capture()
-            mode = ("one CUDA graph per token step" if world == 1
+            mode = ("one CUDA graph per token step" if world == 1 else
+                    "one CUDA graph per token step, all-reduces as one kernel each over peer memory" if st.ar is not None
                     else "one CUDA graph per stretch between all-reduces; NCCL all-reduces launched eagerly")
         for _ in range(3):
             st.step()
@@ -254,6 +276,7 @@ def main():
             "packed_weights_per_rank": st.n_weights, "packed_GB_per_rank": st.packed_bytes / 1e9,
             "layout": args.layout, "resident_GB_per_rank": st.resident_bytes / 1e9,
             "tokens_timed": args.tokens, "setup_s": setup,
+            "peer_allreduce_vs_nccl_rel": ar_check, "peer_allreduce_timed_out": (st.ar.timed_out() if st.ar is not None else None),
             "note": "packed-weight path only; token mixers are elementwise stand-ins",
         }), flush=True)
     if world > 1:

@@ -15,7 +15,7 @@ import torch.distributed as dist
 
 from .quantize import pack_codes
 
-__all__ = ["shard_bounds", "shard_codes", "shard_packed", "RowParallelLinear", "ColumnParallelLinear"]
+__all__ = ["shard_bounds", "shard_codes", "shard_packed", "RowParallelLinear", "ColumnParallelLinear", "PeerAllReduce"]
 
 
 def shard_bounds(n: int, world: int, rank: int, multiple: int = 1) -> tuple[int, int]:
@@ -93,3 +93,72 @@ class RowParallelLinear(torch.nn.Module):
         if self.bias is not None:
             y = y + self.bias
         return y.view(x_shard.shape[:-1] + (self.out_features,))
+
+
+class PeerAllReduce:
+    """Sum of a short fp32 vector over the ranks in one kernel over peer memory (``ixb_allreduce``).
+
+    Every rank allocates one symmetric-memory buffer, exchanges the peer pointers once, and from then on a call is a
+    single launch of this library on the current stream: peer stores of the data and of flags, a bounded wait, a
+    local sum in rank order.  It can be captured in a CUDA graph together with the GEMVs around it, which the NCCL
+    all-reduce of this size could not on this pool.  world_size 1 works on one GPU (the buffer is the rank's own).
+    """
+
+    def __init__(self, n_max: int, device, group=None):
+        import ctypes as C
+
+        import torch.distributed as dist
+
+        from . import _lib
+
+        self.n_max = int(n_max)
+        self.device = torch.device(device)
+        self.world = dist.get_world_size(group) if dist.is_available() and dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if self.world > 1 else 0
+        L = _lib.lib()
+        nbytes = int(L.ixb_allreduce_bytes(self.world, self.n_max))
+        if nbytes == 0:
+            raise ValueError(f"unsupported all-reduce geometry: world={self.world}, n_max={self.n_max}")
+        if self.world > 1:
+            import torch.distributed._symmetric_memory as symm_mem
+
+            self.buf = symm_mem.empty(nbytes, dtype=torch.uint8, device=self.device)
+            self.buf.zero_()
+            grp = group if group is not None else dist.group.WORLD
+            self._hdl = symm_mem.rendezvous(self.buf, group=grp)
+            ptrs = [int(p) for p in self._hdl.buffer_ptrs]
+            torch.cuda.synchronize(self.device)
+            dist.barrier(group)                      # every rank's buffer is zero before anyone's first call
+        else:
+            self.buf = torch.zeros(nbytes, dtype=torch.uint8, device=self.device)
+            ptrs = [self.buf.data_ptr()]
+        self._ptrs = (C.c_void_p * self.world)(*ptrs)
+        self._nbytes = nbytes
+
+    def __call__(self, x: torch.Tensor, out: torch.Tensor | None = None, bias: torch.Tensor | None = None,
+                 out_dtype=torch.bfloat16) -> torch.Tensor:
+        from . import _lib
+
+        if x.dtype != torch.float32 or not x.is_contiguous() or x.numel() > self.n_max or x.numel() % 4:
+            raise ValueError("all-reduce input must be a contiguous fp32 tensor of a multiple of 4, at most n_max, values")
+        if out is None:
+            out = torch.empty(x.shape, dtype=out_dtype, device=x.device)
+        elif out.dtype not in (torch.bfloat16, torch.float32) or out.numel() != x.numel() or not out.is_contiguous():
+            raise ValueError("all-reduce output must be a contiguous bf16/fp32 tensor of the input's size")
+        if bias is not None and (bias.dtype != torch.bfloat16 or bias.numel() != x.numel()):
+            raise ValueError("bias must be bf16 with one value per element")
+        with torch.cuda.device(self.device):
+            _lib.check(_lib.lib().ixb_allreduce(x.data_ptr(), x.numel(), self._ptrs, self.rank, self.world, self.n_max,
+                                                None if bias is None else bias.data_ptr(), out.data_ptr(),
+                                                1 if out.dtype == torch.float32 else 0, _lib.stream_ptr(self.device)))
+        return out
+
+    def timed_out(self) -> bool:
+        """True if a wait inside any call so far gave up (the results since then are not to be trusted)."""
+        return bool(self._err_word().item() != 0)
+
+    def _err_word(self):
+        # layout of the buffer: slots, flags [world][ctas], epoch [ctas], error word
+        ctas = (self.n_max + 1023) // 1024
+        off = 2 * self.world * self.n_max * 4 + (self.world * ctas + ctas) * 4
+        return self.buf[off:off + 4].view(torch.int32)
