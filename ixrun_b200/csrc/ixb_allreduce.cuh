@@ -12,7 +12,7 @@
 //     1. stores its 1024 values of the local partial vector into slot (parity, r) of EVERY rank's buffer,
 //     2. fences (system scope), then stores e into flags[r][c] of every rank's buffer,
 //     3. waits until flags[s][c] >= e for every sender s in ITS OWN buffer -- a bounded wait: after
-//        kArSpinLimit polls it records an error word and goes on --
+//        kArSpinLimit polls it records an error word and goes on (and later calls stop waiting after 64 polls) --
 //     4. sums slots (parity, 0 .. W-1) of its own buffer in rank order (every rank gets the same bits), adds the
 //        bias, writes y (bf16 or fp32), and stores e into epoch[c].
 // Two parities are enough: a rank can only reach call e + 2 after every other rank has sent call e + 1, which each
@@ -45,12 +45,15 @@ k_allreduce_oneshot(ArPeers peers, const float *__restrict__ x, int rank, uint32
     __shared__ uint32_t e_s;
     const uint32_t c = blockIdx.x, ctas = gridDim.x, tid = threadIdx.x;
     asm volatile("griddepcontrol.launch_dependents;");
+    const uint32_t i = (c * kArThreads + tid) * 4u;
+    const bool valid = i < n;                              // n is a multiple of 4
+    // Nothing of this kernel may run ahead of the kernels before it: the epoch below is written by the previous
+    // all-reduce, which is only known to be complete once the kernel directly ahead (which waited for its own
+    // predecessor in turn) is complete.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     if (tid == 0) e_s = epoch[c] + 1u;
     __syncthreads();
     const uint32_t e = e_s, par = e & 1u;
-    const uint32_t i = (c * kArThreads + tid) * 4u;
-    const bool valid = i < n;                              // n is a multiple of 4
-    asm volatile("griddepcontrol.wait;" ::: "memory");
     // 1. this rank's values to every rank
     if (valid) {
         const float4 v = *(const float4 *)(x + i);
@@ -67,10 +70,12 @@ k_allreduce_oneshot(ArPeers peers, const float *__restrict__ x, int rank, uint32
     // 3. wait for every sender's flag in this rank's own buffer
     if (tid < (uint32_t)W) {
         volatile uint32_t *f = peers.flags[rank] + (size_t)tid * ctas + c;
+        // once a wait has given up, later calls give up quickly too instead of stalling for the full limit each time
+        const uint32_t limit = *(volatile uint32_t *)err ? 64u : kArSpinLimit;
         uint32_t polls = 0;
         while ((int32_t)(*f - e) < 0) {
             __nanosleep(32);
-            if (++polls > kArSpinLimit) {
+            if (++polls > limit) {
                 *err = 1u + tid;                           // sender tid never arrived: the result is wrong, not a hang
                 break;
             }
