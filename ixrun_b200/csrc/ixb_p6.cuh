@@ -386,6 +386,7 @@ k_p6_mma(P6 p, const __nv_bfloat16 *__restrict__ x, uint32_t m_rows, const __nv_
     const uint32_t ring_s = (uint32_t)__cvta_generic_to_shared(wsm);
     const uint32_t d16 = ring_s + lane * 16;
     const unsigned char *n16 = p.plane + (size_t)b_begin * kP6BlockBytes + lane * 16;    // this lane's next chunk to fetch
+    uint32_t pf_left = b_end - b_begin;                                                  // blocks of the run not yet requested
 
     // Everything up to griddepcontrol.wait reads only the layer's own (constant) buffers.  When the launch carries
     // the programmatic-stream-serialization attribute this part overlaps the tail of the kernel before it in the
@@ -398,9 +399,11 @@ k_p6_mma(P6 p, const __nv_bfloat16 *__restrict__ x, uint32_t m_rows, const __nv_
         j_end = __ldg(p.blk_off + b_end);
 #pragma unroll
         for (int s = 0; s < 3; ++s) {
-            p6_cp16(d16 + s * kP6BlockBytes, n16);
-            p6_cp16_if(d16 + s * kP6BlockBytes + 512, n16 + 512, lane < 16);
+            const bool more = pf_left != 0;               // nothing is fetched past the end of the run
+            p6_cp16_if(d16 + s * kP6BlockBytes, n16, more);
+            p6_cp16_if(d16 + s * kP6BlockBytes + 512, n16 + 512, more && lane < 16);
             n16 += kP6BlockBytes;
+            pf_left -= more ? 1u : 0u;
         }
 #pragma unroll
         for (int r = 0; r < 16; ++r) oacc[r * 32 + lane] = 0.f;
@@ -469,10 +472,12 @@ k_p6_mma(P6 p, const __nv_bfloat16 *__restrict__ x, uint32_t m_rows, const __nv_
         auto run = [&](uint32_t b0, uint32_t b1) {
             uint32_t xo = (b0 - R * KB) * (kP5TileCols * 2u);     // byte offset into the activation row
             for (uint32_t n = b1 - b0; n != 0; --n) {
-                p6_cp16(d16 + is, n16);                           // past the run end: slack or a neighbour's blocks, never used
-                p6_cp16_if(d16 + is + 512, n16 + 512, lo16);
+                const bool more = pf_left != 0;                   // the last three iterations of a run fetch nothing
+                p6_cp16_if(d16 + is, n16, more);
+                p6_cp16_if(d16 + is + 512, n16 + 512, more && lo16);
                 cp_async_commit();
                 n16 += kP6BlockBytes;
+                pf_left -= more ? 1u : 0u;
                 cp_async_wait<3>();                               // this lane's chunks of the block have landed ...
                 __syncwarp();                                     // ... and so have the other lanes'
                 const uint4 a = p6_lds128(d16 + cs);
