@@ -270,6 +270,28 @@ __device__ __forceinline__ void p6_store_tile(uint32_t out_f, uint32_t R, int la
     }
 }
 
+// one half of a lane's C fragment: row g + 8 h of the tile, activation rows 2 t and 2 t + 1
+__device__ __forceinline__ void p6_store_pair(uint32_t out_f, uint32_t R, int lane, int h, const float (&v)[2], uint32_t m_rows,
+                                              const __nv_bfloat16 *__restrict__ bias, void *y, int y_f32)
+{
+    const int g = lane >> 2, t = lane & 3;
+    const uint32_t row = R * kP5TileRows + g + 8 * h;
+    if (row >= out_f) return;
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const uint32_t m = 2u * t + i;
+        if (m >= m_rows) continue;
+        const size_t o = (size_t)m * out_f + row;
+        if (y_f32) {
+            ((float *)y)[o] = bias ? v[i] + __bfloat162float(bias[row]) : v[i];
+        } else {
+            __nv_bfloat16 hv = __float2bfloat16_rn(v[i]);
+            if (bias) hv = __hadd(hv, bias[row]);
+            ((__nv_bfloat16 *)y)[o] = hv;
+        }
+    }
+}
+
 // n elements cut into `parts` contiguous parts, the first r = n % parts of them one longer than q = n / parts:
 // first element of part i, and the part that holds element pos (no 64-bit arithmetic, no division on the way in)
 __device__ __forceinline__ uint32_t p6_begin(uint32_t i, uint32_t q, uint32_t r) { return i * q + min(i, r); }
@@ -614,11 +636,39 @@ k_p6_mma(P6 p, const __nv_bfloat16 *__restrict__ x, uint32_t m_rows, const __nv_
                 p6_store_tile(p.out_f, R, lane, cc, m_rows, bias, y, y_f32);
                 continue;
             }
-            // shared with other CTAs: publish this CTA's sum, take a ticket; the last one finishes the tile
+            const uint32_t clo = p6_part_of(t0, cq, cr), chi = p6_part_of(t1 - 1, cq, cr);
+            if (chi - clo == 1u) {
+                // Shared by exactly two CTAs (the usual case): one atomic exchange per 64-bit word carries the
+                // partial sums themselves -- no slot store, fence, ticket and slot load, a single round trip to L2.
+                // A lane swaps its two words (row g: c[0], c[1]; row g + 8: c[2], c[3]), XOR-ed with a constant so
+                // that a deposit is never the all-zero "empty" word, into the tile's area.  Whoever finds the
+                // other CTA's deposit adds it to its own values (a + b = b + a bit for bit, so it does not matter
+                // which of the two that is, word by word), stores the outputs and empties the word again.
+                unsigned long long *w2 = (unsigned long long *)(cta_slots + ((size_t)chi * 2) * 32 + lane);
+                const unsigned long long K = 0x7FC0DEAD7FC0DEADull;
+                const float mine[4] = {s.x, s.y, s.z, s.w};
+                unsigned long long got[2];
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const unsigned long long dep =
+                        ((unsigned long long)__float_as_uint(mine[2 * h + 1]) << 32 | __float_as_uint(mine[2 * h])) ^ K;
+                    got[h] = atomicExch(w2 + h, dep);
+                }
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    if (got[h] == 0ull) continue;                        // first to arrive for this word
+                    const unsigned long long o = got[h] ^ K;
+                    const float v[2] = {mine[2 * h] + __uint_as_float((uint32_t)o),
+                                        mine[2 * h + 1] + __uint_as_float((uint32_t)(o >> 32))};
+                    p6_store_pair(p.out_f, R, lane, h, v, m_rows, bias, y, y_f32);
+                    w2[h] = 0ull;
+                }
+                continue;
+            }
+            // shared by three or more CTAs: publish this CTA's sum, take a ticket; the last one finishes the tile
             cta_slots[((size_t)blockIdx.x * 2 + (R == Rc0 ? 0 : 1)) * 32 + lane] = s;
             __threadfence();
             __syncwarp();
-            const uint32_t clo = p6_part_of(t0, cq, cr), chi = p6_part_of(t1 - 1, cq, cr);
             uint32_t prev = 0;
             if (lane == 0) prev = atomicAdd(tickets + clo + 1, 1u);
             prev = __shfl_sync(0xffffffffu, prev, 0);
