@@ -216,7 +216,9 @@ constexpr int kP6StageEntries = 512;                                  // outlier
 constexpr int kP6RingBytes = kP6Slots * kP6BlockBytes;                // 3072
 // per warp: ring, per-row outlier sums [16][32] fp32, staged entries, two partial tiles [2][32] float4
 constexpr int kP6WarpSmem = kP6RingBytes + 16 * 32 * 4 + kP6StageEntries * 4 + 2 * 32 * 16;
-constexpr int kP6SmemFixed = kP6Warps * kP6WarpSmem;
+constexpr int kP6TailTiles = 32;                                      // row tiles per CTA that the barrier-free tail tracks
+constexpr int kP6TailBytes = kP6TailTiles * 12;                       // per tile: arrival counter + two words of plan
+constexpr int kP6SmemFixed = kP6Warps * kP6WarpSmem + kP6TailBytes;
 static_assert(kP6WarpSmem % 128 == 0, "per-warp shared memory keeps 128-byte alignment");
 
 __device__ __forceinline__ void p6_cp16(uint32_t dst, const void *src)
@@ -405,6 +407,29 @@ k_p6_mma(P6 p, const __nv_bfloat16 *__restrict__ x, uint32_t m_rows, const __nv_
     const uint32_t L = cb1 - cb0, wq = L / kP6Warps, wr = L - wq * kP6Warps;
     const uint32_t b_begin = cb0 + p6_begin(wid, wq, wr), b_end = cb0 + p6_begin(wid + 1, wq, wr);
     const bool active = b_begin < b_end;
+    // ---- plan of the tail, made while nothing else can run yet.  For every row tile R0 + i that this CTA touches
+    // (fast path: at most kP6TailTiles): which warps' runs meet it, whether it lies inside the CTA's range, how many
+    // partial sums will arrive (0: one run covers it and writes y itself), and the CTAs that share it.
+    uint32_t *tcnt = (uint32_t *)(p6_smem + kP6Warps * kP6WarpSmem);   // [kP6TailTiles] arrivals
+    uint32_t *tplan = tcnt + kP6TailTiles;                             // [kP6TailTiles][2]
+    const uint32_t Rc0 = cb0 / KB, Rc1 = L ? (cb1 - 1u) / KB : Rc0;
+    const bool fast_tail = L != 0 && Rc1 - Rc0 < (uint32_t)kP6TailTiles;
+    if (fast_tail && lane == 0) {
+        for (uint32_t i = wid; i <= Rc1 - Rc0; i += kP6Warps) {
+            const uint32_t t0 = (Rc0 + i) * KB, t1 = t0 + KB;
+            const uint32_t inside = t0 >= cb0 && t1 <= cb1;
+            const uint32_t wlo = p6_part_of(max(t0, cb0) - cb0, wq, wr), whi = p6_part_of(min(t1, cb1) - 1 - cb0, wq, wr);
+            const uint32_t need = inside && wlo == whi ? 0u : whi - wlo + 1u;
+            uint32_t clo = 0, span = 0;
+            if (!inside) {
+                clo = p6_part_of(t0, cq, cr);
+                span = p6_part_of(t1 - 1u, cq, cr) - clo;
+            }
+            tcnt[i] = 0;
+            tplan[2 * i] = wlo | whi << 8 | need << 16 | inside << 24;
+            tplan[2 * i + 1] = clo | span << 16;
+        }
+    }
     const uint32_t ring_s = (uint32_t)__cvta_generic_to_shared(wsm);
     const uint32_t d16 = ring_s + lane * 16;
     const unsigned char *n16 = p.plane + (size_t)b_begin * kP6BlockBytes + lane * 16;    // this lane's next chunk to fetch
@@ -476,6 +501,88 @@ k_p6_mma(P6 p, const __nv_bfloat16 *__restrict__ x, uint32_t m_rows, const __nv_
     cp_async_commit();
     cp_async_wait<1>();                              // group A has landed for this thread
     __syncthreads();                                 // ... and for the CTA
+
+    // Row tile R is complete in this CTA: sum the partial tiles of warps wlo .. whi in warp order; a tile inside the
+    // CTA's range is written to y, a tile shared with other CTAs (clo .. clo + span) is finished across them.
+    auto finish_tile = [&](uint32_t R, uint32_t wlo, uint32_t whi, bool inside, uint32_t clo, uint32_t span) {
+        const uint32_t t0 = R * KB;
+        float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (uint32_t w = wlo; w <= whi; ++w) {
+            const uint32_t wb = p6_begin(w, wq, wr);
+            if (wb == p6_begin(w + 1, wq, wr)) continue;                // a warp without blocks
+            // the run of warp w meets tile R: R is its first tile unless the run began in the tile before
+            const float4 v = ((const float4 *)(p6_smem + w * kP6WarpSmem + kP6RingBytes + 4096))[(cb0 + wb >= t0 ? 0 : 32) + lane];
+            s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+        }
+        if (inside) {
+            const float cc[4] = {s.x, s.y, s.z, s.w};
+            p6_store_tile(p.out_f, R, lane, cc, m_rows, bias, y, y_f32);
+            return;
+        }
+        const uint32_t chi = clo + span;
+        if (span == 1u) {
+            // Shared by exactly two CTAs (the usual case): one atomic exchange per 64-bit word carries the
+            // partial sums themselves -- no slot store, fence, ticket and slot load, a single round trip to L2.
+            // A lane swaps its two words (row g: c[0], c[1]; row g + 8: c[2], c[3]), XOR-ed with a constant so
+            // that a deposit is never the all-zero "empty" word, into the tile's area.  Whoever finds the
+            // other CTA's deposit adds it to its own values (a + b = b + a bit for bit, so it does not matter
+            // which of the two that is, word by word), stores the outputs and empties the word again.
+            unsigned long long *w2 = (unsigned long long *)(cta_slots + ((size_t)chi * 2) * 32 + lane);
+            const unsigned long long K = 0x7FC0DEAD7FC0DEADull;
+            const float mine[4] = {s.x, s.y, s.z, s.w};
+            unsigned long long got[2];
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const unsigned long long dep =
+                    ((unsigned long long)__float_as_uint(mine[2 * h + 1]) << 32 | __float_as_uint(mine[2 * h])) ^ K;
+                got[h] = atomicExch(w2 + h, dep);
+            }
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                if (got[h] == 0ull) continue;                            // first to arrive for this word
+                const unsigned long long o = got[h] ^ K;
+                const float v[2] = {mine[2 * h] + __uint_as_float((uint32_t)o),
+                                    mine[2 * h + 1] + __uint_as_float((uint32_t)(o >> 32))};
+                p6_store_pair(p.out_f, R, lane, h, v, m_rows, bias, y, y_f32);
+                w2[h] = 0ull;
+            }
+            return;
+        }
+        // shared by three or more CTAs: publish this CTA's sum, take a ticket; the last one finishes the tile
+        cta_slots[((size_t)blockIdx.x * 2 + (R == Rc0 ? 0 : 1)) * 32 + lane] = s;
+        __threadfence();
+        __syncwarp();
+        uint32_t prev = 0;
+        if (lane == 0) prev = atomicAdd(tickets + clo + 1, 1u);
+        prev = __shfl_sync(0xffffffffu, prev, 0);
+        if (prev != span) return;
+        // the other CTAs' slots were fenced before their tickets; they are read from L2 (ld.global.cg), which
+        // every SM shares, so nothing cached on this SM can be stale
+        float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (uint32_t cc = clo; cc <= chi; ++cc) {
+            const float4 *sl = cta_slots + ((size_t)cc * 2 + (p6_begin(cc, cq, cr) >= t0 ? 0 : 1)) * 32 + lane;
+            z.x += __ldcg(&sl->x); z.y += __ldcg(&sl->y); z.z += __ldcg(&sl->z); z.w += __ldcg(&sl->w);
+        }
+        const float cc4[4] = {z.x, z.y, z.z, z.w};
+        p6_store_tile(p.out_f, R, lane, cc4, m_rows, bias, y, y_f32);
+        if (lane == 0) tickets[clo + 1] = 0;
+    };
+    // Fast tail: a warp that leaves a partial row tile behind counts itself in; the warp that completes the count
+    // finishes the tile at once -- no CTA-wide barrier, nobody waits for an unrelated slow warp.
+    auto tile_arrive = [&](uint32_t R) {
+        const uint32_t i = R - Rc0;
+        __syncwarp();                                                    // all lanes' parts are written
+        uint32_t prev = 0;
+        if (lane == 0) {
+            __threadfence_block();
+            prev = atomicAdd(tcnt + i, 1u);
+        }
+        prev = __shfl_sync(0xffffffffu, prev, 0);
+        const uint32_t w0 = tplan[2 * i], w1 = tplan[2 * i + 1];
+        if (prev + 1u != ((w0 >> 16) & 0xffu)) return;
+        __threadfence_block();
+        finish_tile(R, w0 & 0xffu, (w0 >> 8) & 0xffu, (w0 >> 24) & 1u, w1 & 0xffffu, w1 >> 16);
+    };
 
     if (active) {
         float c[4] = {0.f, 0.f, 0.f, 0.f};
@@ -605,7 +712,10 @@ k_p6_mma(P6 p, const __nv_bfloat16 *__restrict__ x, uint32_t m_rows, const __nv_
                 c1[i] = 0.f;
             }
             if (whole) p6_store_tile(p.out_f, R, lane, c, m_rows, bias, y, y_f32);
-            else wparts[(R == R_first ? 0 : 32) + lane] = make_float4(c[0], c[1], c[2], c[3]);
+            else {
+                wparts[(R == R_first ? 0 : 32) + lane] = make_float4(c[0], c[1], c[2], c[3]);
+                if (fast_tail) tile_arrive(R);
+            }
             c[0] = c[1] = c[2] = c[3] = 0.f;
             b = seg_e;
             seg_j = seg_je;
@@ -613,76 +723,23 @@ k_p6_mma(P6 p, const __nv_bfloat16 *__restrict__ x, uint32_t m_rows, const __nv_
         }
     }
     cp_async_wait<0>();
+    if (fast_tail) return;
     __syncthreads();
 
-    // ---- per CTA: sum the parts of every tile that more than one run of this CTA (or another CTA) touched
+    // ---- more row tiles per CTA than the fast tail tracks: after a CTA-wide barrier, sum the parts of every tile
+    // that more than one run of this CTA (or another CTA) touched
     if (L) {
-        const uint32_t Rc0 = cb0 / KB, Rc1 = (cb1 - 1) / KB;
         for (uint32_t R = Rc0 + wid; R <= Rc1; R += kP6Warps) {
             const uint32_t t0 = R * KB, t1 = t0 + KB;                   // the tile's blocks
             const bool inside = t0 >= cb0 && t1 <= cb1;
             const uint32_t wlo = p6_part_of(max(t0, cb0) - cb0, wq, wr), whi = p6_part_of(min(t1, cb1) - 1 - cb0, wq, wr);
             if (inside && wlo == whi) continue;                          // one run had all of it and wrote y itself
-            float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
-            for (uint32_t w = wlo; w <= whi; ++w) {
-                const uint32_t wb = p6_begin(w, wq, wr);
-                if (wb == p6_begin(w + 1, wq, wr)) continue;            // a warp without blocks
-                // the run of warp w meets tile R: R is its first tile unless the run began in the tile before
-                const float4 v = ((const float4 *)(p6_smem + w * kP6WarpSmem + kP6RingBytes + 4096))[(cb0 + wb >= t0 ? 0 : 32) + lane];
-                s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+            uint32_t clo = 0, span = 0;
+            if (!inside) {
+                clo = p6_part_of(t0, cq, cr);
+                span = p6_part_of(t1 - 1u, cq, cr) - clo;
             }
-            if (inside) {
-                const float cc[4] = {s.x, s.y, s.z, s.w};
-                p6_store_tile(p.out_f, R, lane, cc, m_rows, bias, y, y_f32);
-                continue;
-            }
-            const uint32_t clo = p6_part_of(t0, cq, cr), chi = p6_part_of(t1 - 1, cq, cr);
-            if (chi - clo == 1u) {
-                // Shared by exactly two CTAs (the usual case): one atomic exchange per 64-bit word carries the
-                // partial sums themselves -- no slot store, fence, ticket and slot load, a single round trip to L2.
-                // A lane swaps its two words (row g: c[0], c[1]; row g + 8: c[2], c[3]), XOR-ed with a constant so
-                // that a deposit is never the all-zero "empty" word, into the tile's area.  Whoever finds the
-                // other CTA's deposit adds it to its own values (a + b = b + a bit for bit, so it does not matter
-                // which of the two that is, word by word), stores the outputs and empties the word again.
-                unsigned long long *w2 = (unsigned long long *)(cta_slots + ((size_t)chi * 2) * 32 + lane);
-                const unsigned long long K = 0x7FC0DEAD7FC0DEADull;
-                const float mine[4] = {s.x, s.y, s.z, s.w};
-                unsigned long long got[2];
-#pragma unroll
-                for (int h = 0; h < 2; ++h) {
-                    const unsigned long long dep =
-                        ((unsigned long long)__float_as_uint(mine[2 * h + 1]) << 32 | __float_as_uint(mine[2 * h])) ^ K;
-                    got[h] = atomicExch(w2 + h, dep);
-                }
-#pragma unroll
-                for (int h = 0; h < 2; ++h) {
-                    if (got[h] == 0ull) continue;                        // first to arrive for this word
-                    const unsigned long long o = got[h] ^ K;
-                    const float v[2] = {mine[2 * h] + __uint_as_float((uint32_t)o),
-                                        mine[2 * h + 1] + __uint_as_float((uint32_t)(o >> 32))};
-                    p6_store_pair(p.out_f, R, lane, h, v, m_rows, bias, y, y_f32);
-                    w2[h] = 0ull;
-                }
-                continue;
-            }
-            // shared by three or more CTAs: publish this CTA's sum, take a ticket; the last one finishes the tile
-            cta_slots[((size_t)blockIdx.x * 2 + (R == Rc0 ? 0 : 1)) * 32 + lane] = s;
-            __threadfence();
-            __syncwarp();
-            uint32_t prev = 0;
-            if (lane == 0) prev = atomicAdd(tickets + clo + 1, 1u);
-            prev = __shfl_sync(0xffffffffu, prev, 0);
-            if (prev != chi - clo) continue;
-            // the other CTAs' slots were fenced before their tickets; they are read from L2 (ld.global.cg), which
-            // every SM shares, so nothing cached on this SM can be stale
-            float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
-            for (uint32_t cc = clo; cc <= chi; ++cc) {
-                const float4 *sl = cta_slots + ((size_t)cc * 2 + (p6_begin(cc, cq, cr) >= t0 ? 0 : 1)) * 32 + lane;
-                z.x += __ldcg(&sl->x); z.y += __ldcg(&sl->y); z.z += __ldcg(&sl->z); z.w += __ldcg(&sl->w);
-            }
-            const float cc4[4] = {z.x, z.y, z.z, z.w};
-            p6_store_tile(p.out_f, R, lane, cc4, m_rows, bias, y, y_f32);
-            if (lane == 0) tickets[clo + 1] = 0;
+            finish_tile(R, wlo, whi, inside, clo, span);
         }
     }
 }
