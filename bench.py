@@ -16,6 +16,8 @@ to bf16, then matmul) on the host cores instead.
 """
 from __future__ import annotations
 
+import contextlib
+
 import argparse
 import json
 import os
@@ -34,6 +36,20 @@ COPIES = 4
 METRIC = "fused decode+GEMV packed-weight bandwidth (batch 1)"
 UNIT = "GB/s"
 
+
+
+@contextlib.contextmanager
+def _stdout_to_stderr():
+    """File descriptor 1 points at stderr inside the block (for output that native libraries write themselves)."""
+    sys.stdout.flush()
+    saved = os.dup(1)
+    os.dup2(2, 1)
+    try:
+        yield
+    finally:
+        sys.stdout.flush()
+        os.dup2(saved, 1)
+        os.close(saved)
 
 def measured_peak():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
@@ -162,8 +178,9 @@ def run_gpu(args):
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
-        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")      # NCCL's own lines must not mix with the JSON line on stdout
-        dist.init_process_group("nccl", device_id=dev)
+        with _stdout_to_stderr():        # NCCL prints its version line to stdout; stdout is for the one JSON line
+            dist.init_process_group("nccl", device_id=dev)
+            dist.barrier()
     if world != args.gpus:
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
 

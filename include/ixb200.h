@@ -240,9 +240,10 @@ int ixb_set_pdl(int on);
  *   x: this rank's n fp32 partial sums (n a multiple of 4, n <= n_max)
  *   y: n sums over the ranks, added in rank order (the same bits on every
  *      rank), + bias (bf16, after rounding for bf16 output), bf16 or fp32
- * One kernel: peer stores of data then flags, a bounded wait on the local
- * flags (on a time-out the last word of the buffer becomes non-zero and the
- * result is wrong; the kernel never hangs), local sum.  Graph-capturable;
+ * One kernel: peer stores of {value, call number} words, a bounded wait for
+ * the call number on the local copies (on a time-out the error word behind the
+ * epochs becomes non-zero and the result is wrong; the kernel never hangs),
+ * local sum.  Graph-capturable;
  * follows ixb_set_pdl.  world in {1, 2, 4, 8}.
  */
 size_t ixb_allreduce_bytes(int world, int64_t n_max);

@@ -1049,8 +1049,8 @@ extern "C" int ixb_p6_gemv(const ixb_p6 *t, const void *x, int64_t m_rows, const
 extern "C" size_t ixb_allreduce_bytes(int world, int64_t n_max)
 {
     if (world < 1 || world > kArMaxWorld || n_max <= 0 || (n_max & 3)) return 0;
-    // slots, flags [world][ctas], epoch [ctas], one error word; rounded up to 256 bytes
-    size_t b = ar_slots_bytes(world, n_max) + ((size_t)world * ar_ctas(n_max) + ar_ctas(n_max) + 1) * 4;
+    // slots, epoch [ctas], one error word; rounded up to 256 bytes
+    size_t b = ar_slots_bytes(world, n_max) + ((size_t)ar_ctas(n_max) + 1) * 4;
     return (b + 255) & ~(size_t)255;
 }
 
@@ -1083,14 +1083,10 @@ extern "C" int ixb_allreduce(const void *x, int64_t n, void *const *peer_buffers
     const uint32_t ctas = ar_ctas(n_max);
     for (int r = 0; r < world; ++r) {
         if (!peer_buffers[r] || ((uintptr_t)peer_buffers[r] & 15u)) return fail(IXB_E_ARG, "peer buffer %d is NULL or misaligned", r);
-        peers.slots[r] = (float *)peer_buffers[r];
-        peers.flags[r] = (uint32_t *)((char *)peer_buffers[r] + sb);
+        peers.slots[r] = (uint2 *)peer_buffers[r];
     }
-    for (int r = world; r < kArMaxWorld; ++r) {
-        peers.slots[r] = nullptr;
-        peers.flags[r] = nullptr;
-    }
-    uint32_t *epoch = peers.flags[rank] + (size_t)world * ctas, *err = epoch + ctas;
+    for (int r = world; r < kArMaxWorld; ++r) peers.slots[r] = nullptr;
+    uint32_t *epoch = (uint32_t *)((char *)peer_buffers[rank] + sb), *err = epoch + ctas;
     cudaStream_t st = (cudaStream_t)stream;
     cudaError_t e;
     switch (world) {

@@ -4,21 +4,25 @@
 // The reference is single-GPU; its tensor-parallel form needs one sum of out_f values per row-parallel layer.
 // A library all-reduce costs a launch of its own plus its protocol (15 .. 20 us eagerly, and it could not be
 // captured in a CUDA graph on this pool); at this size the transfer itself is a few hundred nanoseconds of
-// NVLink time, so the whole exchange is done by one small kernel with plain peer stores and loads:
+// NVLink time, so the whole exchange is done by one small kernel with plain peer stores and local loads, and the
+// data carries its own "arrived" mark, so one crossing of NVLink is all the latency there is:
 //
 //   every rank owns one buffer that all ranks can address (peer pointers):
-//     slots  [2 parities][W ranks][n_max] fp32      flags [W ranks][ctas] uint32      epoch [ctas] uint32
+//     slots  [2 parities][W ranks][n_max] x {fp32 value, uint32 epoch}      epoch [ctas] uint32      error word
 //   CTA c of rank r, call number e (epoch[c] + 1), parity e & 1:
-//     1. stores its 1024 values of the local partial vector into slot (parity, r) of EVERY rank's buffer,
-//     2. fences (system scope), then stores e into flags[r][c] of every rank's buffer,
-//     3. waits until flags[s][c] >= e for every sender s in ITS OWN buffer -- a bounded wait: after
-//        kArSpinLimit polls it records an error word and goes on (and later calls stop waiting after 64 polls) --
-//     4. sums slots (parity, 0 .. W-1) of its own buffer in rank order (every rank gets the same bits), adds the
-//        bias, writes y (bf16 or fp32), and stores e into epoch[c].
-// Two parities are enough: a rank can only reach call e + 2 after every other rank has sent call e + 1, which each
-// does after it has finished reading call e.  Nothing here is a multicast or a TMA load; NVLink carries plain
-// stores (data, flags) only, all loads are local.  The kernel takes part in programmatic dependent launch like
-// k_p6_mma (it waits for the kernel ahead of it before it reads the partial vector).
+//     1. every thread stores its four values as four 8-byte words {value, e} into slot (parity, r) of EVERY
+//        rank's buffer (an aligned 8-byte store arrives whole, so value and mark cannot be seen apart),
+//     2. then reads the same four words of every sender's slot in ITS OWN buffer until their mark is e -- a
+//        bounded wait: after kArSpinLimit polls it records an error word and goes on (later calls stop waiting
+//        after 64 polls) --
+//     3. adds the values in rank order (every rank gets the same bits), adds the bias, writes y (bf16 or
+//        fp32); thread 0 stores e into epoch[c].
+// No fences, no separate flags, no barrier after the first.  Two parities are enough: a rank can only reach call
+// e + 2 after every other rank has sent call e + 1, which each does after it has finished reading call e.
+// Nothing here is a multicast or a TMA load; NVLink carries plain stores only, all loads are local.  The kernel
+// takes part in programmatic dependent launch like k_p6_mma, but runs nothing ahead of the dependency wait: the
+// epoch is written by the previous all-reduce, which is only known to be complete once the kernel directly ahead
+// (which waited for its own predecessor in turn) is complete.
 #pragma once
 #include "ixb_common.cuh"
 
@@ -30,11 +34,10 @@ constexpr int kArPerCta = kArThreads * 4;                 // fp32 values per CTA
 constexpr uint32_t kArSpinLimit = 1u << 22;               // polls (>= 32 ns each) before a wait gives up
 
 struct ArPeers {
-    float *slots[kArMaxWorld];                            // every rank's slots, as seen from this rank
-    uint32_t *flags[kArMaxWorld];                         // every rank's flags
+    uint2 *slots[kArMaxWorld];                            // every rank's slots, as seen from this rank
 };
 
-__host__ __device__ __forceinline__ size_t ar_slots_bytes(int world, int64_t n_max) { return (size_t)2 * world * n_max * 4; }
+__host__ __device__ __forceinline__ size_t ar_slots_bytes(int world, int64_t n_max) { return (size_t)2 * world * n_max * 8; }
 __host__ __device__ __forceinline__ uint32_t ar_ctas(int64_t n_max) { return (uint32_t)((n_max + kArPerCta - 1) / kArPerCta); }
 
 template <int W>
@@ -43,56 +46,51 @@ k_allreduce_oneshot(ArPeers peers, const float *__restrict__ x, int rank, uint32
                     const __nv_bfloat16 *__restrict__ bias, void *y, int y_f32, uint32_t *epoch, uint32_t *err)
 {
     __shared__ uint32_t e_s;
-    const uint32_t c = blockIdx.x, ctas = gridDim.x, tid = threadIdx.x;
+    const uint32_t c = blockIdx.x, tid = threadIdx.x;
     asm volatile("griddepcontrol.launch_dependents;");
     const uint32_t i = (c * kArThreads + tid) * 4u;
     const bool valid = i < n;                              // n is a multiple of 4
-    // Nothing of this kernel may run ahead of the kernels before it: the epoch below is written by the previous
-    // all-reduce, which is only known to be complete once the kernel directly ahead (which waited for its own
-    // predecessor in turn) is complete.
     asm volatile("griddepcontrol.wait;" ::: "memory");
     if (tid == 0) e_s = epoch[c] + 1u;
     __syncthreads();
     const uint32_t e = e_s, par = e & 1u;
-    // 1. this rank's values to every rank
     if (valid) {
+        // 1. this rank's values, marked with the call number, to every rank
         const float4 v = *(const float4 *)(x + i);
-#pragma unroll
-        for (int r = 0; r < W; ++r) *(float4 *)(peers.slots[r] + ((size_t)(par * W + rank)) * n_max + i) = v;
-    }
-    // 2. the stores are visible system-wide before the flags that announce them
-    __threadfence_system();
-    __syncthreads();
-    if (tid < (uint32_t)W) {
-        volatile uint32_t *f = peers.flags[tid] + (size_t)rank * ctas + c;
-        *f = e;
-    }
-    // 3. wait for every sender's flag in this rank's own buffer
-    if (tid < (uint32_t)W) {
-        volatile uint32_t *f = peers.flags[rank] + (size_t)tid * ctas + c;
-        // once a wait has given up, later calls give up quickly too instead of stalling for the full limit each time
-        const uint32_t limit = *(volatile uint32_t *)err ? 64u : kArSpinLimit;
-        uint32_t polls = 0;
-        while ((int32_t)(*f - e) < 0) {
-            __nanosleep(32);
-            if (++polls > limit) {
-                *err = 1u + tid;                           // sender tid never arrived: the result is wrong, not a hang
-                break;
-            }
-        }
-    }
-    __syncthreads();
-    __threadfence_system();
-    // 4. sum in rank order
-    if (valid) {
-        const float *mine = peers.slots[rank] + (size_t)par * W * n_max + i;
-        float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+        const float in[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
         for (int r = 0; r < W; ++r) {
-            const float4 v = __ldcv((const float4 *)(mine + (size_t)r * n_max));      // written by a peer: never cached
-            s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+            volatile uint2 *dst = peers.slots[r] + ((size_t)(par * W + rank)) * n_max + i;
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                uint2 wv;
+                wv.x = __float_as_uint(in[k]);
+                wv.y = e;
+                asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(dst + k), "r"(wv.x), "r"(wv.y) : "memory");
+            }
         }
-        float o[4] = {s.x, s.y, s.z, s.w};
+        // 2. every sender's words in this rank's own buffer, once they carry this call's mark; 3. sum in rank order
+        // (once a wait has given up, later calls give up quickly too instead of stalling for the full limit each time)
+        const uint32_t limit = *(volatile uint32_t *)err ? 64u : kArSpinLimit;
+        float o[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int s = 0; s < W; ++s) {
+            const uint2 *src = peers.slots[rank] + ((size_t)(par * W + s)) * n_max + i;
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                uint32_t val, mark, polls = 0;
+                for (;;) {
+                    asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(val), "=r"(mark) : "l"(src + k) : "memory");
+                    if (mark == e) break;
+                    __nanosleep(20);
+                    if (++polls > limit) {
+                        *err = 1u + (uint32_t)s;           // sender s never arrived: the result is wrong, not a hang
+                        break;
+                    }
+                }
+                o[k] += __uint_as_float(val);
+            }
+        }
         if (y_f32) {
 #pragma unroll
             for (int k = 0; k < 4; ++k) ((float *)y)[i + k] = bias ? o[k] + __bfloat162float(bias[i + k]) : o[k];

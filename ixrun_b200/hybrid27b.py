@@ -22,6 +22,9 @@ shard-sized tensors per linear type and uses a separate device copy per layer.
 """
 from __future__ import annotations
 
+import contextlib
+import sys
+
 import argparse
 import json
 import os
@@ -43,6 +46,20 @@ ATTN = {"q_proj": (12288, HIDDEN, "col"), "k_proj": (1024, HIDDEN, "col"), "v_pr
 MLP = {"gate_proj": (FFN, HIDDEN, "col"), "up_proj": (FFN, HIDDEN, "col"), "down_proj": (HIDDEN, FFN, "row")}
 KV_HEAD_ROWS = 256      # one KV head; with more ranks than KV heads a rank still holds a whole head
 
+
+
+@contextlib.contextmanager
+def _stdout_to_stderr():
+    """File descriptor 1 points at stderr inside the block (for output that native libraries write themselves)."""
+    sys.stdout.flush()
+    saved = os.dup(1)
+    os.dup2(2, 1)
+    try:
+        yield
+    finally:
+        sys.stdout.flush()
+        os.dup2(saved, 1)
+        os.close(saved)
 
 def shard_shape(name, rows, cols, mode, world):
     if mode == "row":
@@ -226,7 +243,9 @@ def main():
     if world > 1:
         import datetime
 
-        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=120))
+        with _stdout_to_stderr():        # NCCL prints its version line to stdout; stdout is for the one JSON line
+            dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=120))
+            dist.barrier()
     t0 = time.time()
     with torch.no_grad():
         st = Stack(args.layers, world, rank, dev, layout=args.layout, nccl=args.nccl)

@@ -99,8 +99,8 @@ class PeerAllReduce:
     """Sum of a short fp32 vector over the ranks in one kernel over peer memory (``ixb_allreduce``).
 
     Every rank allocates one symmetric-memory buffer, exchanges the peer pointers once, and from then on a call is a
-    single launch of this library on the current stream: peer stores of the data and of flags, a bounded wait, a
-    local sum in rank order.  It can be captured in a CUDA graph together with the GEMVs around it, which the NCCL
+    single launch of this library on the current stream: peer stores of the data, every word marked with the call
+    number, a bounded wait for the marks, a local sum in rank order.  It can be captured in a CUDA graph together with the GEMVs around it, which the NCCL
     all-reduce of this size could not on this pool.  world_size 1 works on one GPU (the buffer is the rank's own).
     """
 
@@ -158,7 +158,7 @@ class PeerAllReduce:
         return bool(self._err_word().item() != 0)
 
     def _err_word(self):
-        # layout of the buffer: slots, flags [world][ctas], epoch [ctas], error word
+        # layout of the buffer: slots [2][world][n_max] x 8 bytes, epoch [ctas], error word
         ctas = (self.n_max + 1023) // 1024
-        off = 2 * self.world * self.n_max * 4 + (self.world * ctas + ctas) * 4
+        off = 2 * self.world * self.n_max * 8 + ctas * 4
         return self.buf[off:off + 4].view(torch.int32)
