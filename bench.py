@@ -206,10 +206,22 @@ def run_gpu(args):
     # several GPUs: the fp32 partial outputs are summed by one kernel of this library over peer memory
     # (graph-capturable); --nccl keeps the eager NCCL all-reduce
     ar = None
+    ar_note = None
     if world > 1 and not args.nccl:
         from ixrun_b200.parallel import PeerAllReduce
 
         ar = PeerAllReduce(OUT_F, dev)
+        # self-check against NCCL on one random vector per rank; on any difference beyond fp32 rounding, or a wait
+        # that gave up, every rank falls back to the NCCL all-reduce together
+        v = torch.randn(1, OUT_F, device=dev, generator=torch.Generator(device=dev).manual_seed(100 + rank))
+        got = ar(v, out_dtype=torch.float32)
+        ref = v.clone()
+        dist.all_reduce(ref)
+        bad = torch.tensor([float((got - ref).abs().max() > 1e-5 * ref.abs().max() or ar.timed_out())], device=dev)
+        dist.all_reduce(bad, op=dist.ReduceOp.MAX)
+        if bad.item() != 0:
+            ar = None
+            ar_note = "disabled: the self-check against NCCL failed"
 
     def step(i):
         lay = layers[i % COPIES]
@@ -296,18 +308,17 @@ def run_gpu(args):
     y_host = torch.empty(1, OUT_F, dtype=torch.bfloat16).pin_memory()
     e2e_steps = max(10, min(args.steps, 200))
 
-    # single GPU: the module call sits in a CUDA graph over static buffers (engine.GraphedCall), so a step is
-    # one H2D copy of x, one graph launch, one D2H copy of y and a stream synchronise
+    # single GPU: the module call sits in a CUDA graph over static buffers (engine.GraphedCall) together with the
+    # H2D copy of x and the D2H copy of y, so a step is one graph launch and a stream synchronise
     graphed = None
     if world == 1 and not args.eager:
         from ixrun_b200.engine import GraphedCall
 
-        graphed = [GraphedCall(lay, x) for lay in layers]
+        graphed = [GraphedCall(lay, x, host_io=True) for lay in layers]
 
     def e2e_step(i):
         if graphed is not None:
-            y_host.copy_(graphed[i % COPIES](x_host), non_blocking=True)
-            torch.cuda.current_stream().synchronize()
+            y_host.copy_(graphed[i % COPIES].run_host(x_host))
             return
         xd = x_host.to(dev, non_blocking=True)
         if world > 1 and ar is not None:
@@ -349,14 +360,15 @@ def run_gpu(args):
                             ("one kernel over peer memory (ixb_allreduce)" if ar is not None else "one NCCL all-reduce")),
             "timed_with": "CUDA events around one graph replay of K launches" if graph is not None else "CUDA events around K eager steps",
             "programmatic_dependent_launch": bool(pdl),
-            "peer_allreduce_timed_out": (ar.timed_out() if ar is not None else None),
+            "peer_allreduce_timed_out": (ar.timed_out() if ar is not None else ar_note),
         },
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "traffic": None, "peak_source": peak_src, "kernel": LAYOUT_KERNEL[args.layout],
                      "algorithmic_bytes_per_launch": alg_bytes_rank, "launch_ms": k_ms},
         "e2e": {"value": alg_bytes / e2e_s / 1e9, "unit": UNIT, "h2d_bytes_per_step": 2 * in_loc,
                 "d2h_bytes_per_step": 2 * OUT_F, "ms_per_step": e2e_s * 1e3, "steps": e2e_steps,
-                "call": ("engine.GraphedCall(StreamingLinear) on pinned host x -> pinned host y" if graphed is not None
+                "call": ("engine.GraphedCall(StreamingLinear, host_io=True).run_host: one graph launch holding the H2D copy of x, "
+                         "the GEMV and the D2H copy of y, then a stream synchronise" if graphed is not None
                          else "StreamingLinear.matvec on a fresh device copy of pinned host x, y copied back")},
         "gpu_launches": int(launches),
         "clocks": clocks,

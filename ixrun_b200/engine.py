@@ -177,24 +177,44 @@ class GraphedCall:
     every replay.  Call the object with new inputs of the same shapes.
     """
 
-    def __init__(self, fn, *example_inputs, warmup: int = 2):
+    def __init__(self, fn, *example_inputs, warmup: int = 2, host_io: bool = False):
+        """host_io=True also captures the copies between pinned host buffers and the static device tensors, so
+        that `run_host` is ONE graph launch per call: host-to-device copy of the inputs, the launches, device-to-host
+        copy of the (single tensor) result."""
         self.static_in = [t.clone() for t in example_inputs]
+        self.host_in = [torch.empty(t.shape, dtype=t.dtype).pin_memory() for t in example_inputs] if host_io else None
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):
-            for _ in range(warmup):
-                fn(*self.static_in)
+            for _ in range(max(warmup, 1)):
+                out = fn(*self.static_in)
         torch.cuda.current_stream().wait_stream(side)
         torch.cuda.synchronize()
+        self.host_out = torch.empty(out.shape, dtype=out.dtype).pin_memory() if host_io else None
         self.graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(self.graph):
+            if host_io:
+                for dst, src in zip(self.static_in, self.host_in):
+                    dst.copy_(src, non_blocking=True)
             self.static_out = fn(*self.static_in)
+            if host_io:
+                self.host_out.copy_(self.static_out, non_blocking=True)
 
     def __call__(self, *inputs):
         for dst, src in zip(self.static_in, inputs):
             dst.copy_(src)
         self.graph.replay()
         return self.static_out
+
+    def run_host(self, *host_inputs):
+        """Inputs from host memory, result in pinned host memory, valid on return (needs host_io=True)."""
+        if self.host_in is None:
+            raise RuntimeError("GraphedCall was built without host_io=True")
+        for dst, src in zip(self.host_in, host_inputs):
+            dst.copy_(src)                        # host memcpy into the pinned staging buffer the graph reads
+        self.graph.replay()
+        torch.cuda.current_stream().synchronize()
+        return self.host_out
 
 
 class ResourceScheduler:

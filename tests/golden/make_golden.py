@@ -20,7 +20,9 @@ import numpy as np
 import torch
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-REF = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+if len(sys.argv) < 2 and "IXRUN_REFERENCE" not in os.environ:
+    raise SystemExit("usage: make_golden.py <path to a checkout of the reference (dfytensor/ixrun)>")
+REF = sys.argv[1] if len(sys.argv) > 1 else os.environ["IXRUN_REFERENCE"]
 sys.path.insert(0, REF)
 sys.path.insert(0, os.path.join(HERE, "..", ".."))
 

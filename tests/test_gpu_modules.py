@@ -217,3 +217,19 @@ def test_graphed_layer_sequence_matches_eager():
     for _ in range(3):
         x = torch.randn(1, h).bfloat16().cuda()
         assert torch.equal(gc(x), mlp(x))
+
+
+def test_graphed_call_with_host_buffers_is_one_launch_per_call():
+    """host_io=True: the copies from and to pinned host memory are part of the graph; run_host returns the result
+    in host memory, equal to the eager module call on the same input."""
+    from ixrun_b200.engine import GraphedCall, StreamingLinear
+
+    lay = StreamingLinear(make_layer(768, 1024, 21)[1])
+    gc = GraphedCall(lay, torch.zeros(1, 1024).bfloat16().cuda(), host_io=True)
+    for i in range(3):
+        x = torch.randn(1, 1024, generator=torch.Generator().manual_seed(i)).bfloat16()
+        y = gc.run_host(x)
+        assert not y.is_cuda and y.is_pinned()
+        assert torch.equal(y, lay(x.cuda()).cpu())
+    with pytest.raises(RuntimeError):
+        GraphedCall(lay, torch.zeros(1, 1024).bfloat16().cuda()).run_host(x)
