@@ -210,18 +210,23 @@ def run_gpu(args):
     if world > 1 and not args.nccl:
         from ixrun_b200.parallel import PeerAllReduce
 
-        ar = PeerAllReduce(OUT_F, dev)
-        # self-check against NCCL on one random vector per rank; on any difference beyond fp32 rounding, or a wait
-        # that gave up, every rank falls back to the NCCL all-reduce together
-        v = torch.randn(1, OUT_F, device=dev, generator=torch.Generator(device=dev).manual_seed(100 + rank))
-        got = ar(v, out_dtype=torch.float32)
-        ref = v.clone()
-        dist.all_reduce(ref)
-        bad = torch.tensor([float((got - ref).abs().max() > 1e-5 * ref.abs().max() or ar.timed_out())], device=dev)
+        try:
+            ar = PeerAllReduce(OUT_F, dev)
+            # self-check against NCCL on one random vector per rank; on any difference beyond fp32 rounding, or a
+            # wait that gave up, every rank falls back to the NCCL all-reduce together
+            v = torch.randn(1, OUT_F, device=dev, generator=torch.Generator(device=dev).manual_seed(100 + rank))
+            got = ar(v, out_dtype=torch.float32)
+            ref = v.clone()
+            dist.all_reduce(ref)
+            bad = torch.tensor([float((got - ref).abs().max() > 1e-5 * ref.abs().max() or ar.timed_out())], device=dev)
+        except Exception as exc:       # symmetric memory not available on this box: every rank fails the same way
+            ar = None
+            ar_note = f"disabled: {type(exc).__name__}: {exc}"[:200]
+            bad = torch.tensor([1.0], device=dev)
         dist.all_reduce(bad, op=dist.ReduceOp.MAX)
         if bad.item() != 0:
             ar = None
-            ar_note = "disabled: the self-check against NCCL failed"
+            ar_note = ar_note or "disabled: the self-check against NCCL failed"
 
     def step(i):
         lay = layers[i % COPIES]
