@@ -122,11 +122,13 @@ def algorithmic_bytes(total_bytes: int) -> int:
 # ----------------------------------------------------------------- CPU arm ---
 def cpu_layer_gbs(steps: int, warmup: int, seed: int = 0):
     """Oracle port of the reference's CPU layer path on the host cores."""
-    # torchrun pins OMP_NUM_THREADS=1 for its ranks; the CPU arm is meant to use every host core
-    if os.environ.get("OMP_NUM_THREADS") == "1" and "TORCHELASTIC_RUN_ID" in os.environ:
-        os.environ["OMP_NUM_THREADS"] = str(os.cpu_count() or 1)
     from ixrun_b200.synth import laplace_codes
     from oracle import ixb_oracle as O
+
+    # torchrun pins OMP_NUM_THREADS=1 for its ranks, and the OpenMP runtime has read it by now; the CPU arm is meant
+    # to use every host core
+    if os.environ.get("OMP_NUM_THREADS") == "1" and "TORCHELASTIC_RUN_ID" in os.environ:
+        O.set_num_threads(os.cpu_count() or 1)
 
     codes = laplace_codes(OUT_F, IN_F, seed)
     sc = int(O.f32_to_bf16_bits(np.array([2.0 ** -9], dtype=np.float32))[0])

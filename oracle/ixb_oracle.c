@@ -55,6 +55,17 @@ int ixo_num_threads(void)
 #endif
 }
 
+/* the OpenMP runtime reads OMP_NUM_THREADS once, when the first library that uses it is loaded; a launcher that
+ * pins it to 1 for its worker processes is overridden here */
+void ixo_set_num_threads(int n)
+{
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
 /* ------------------------------------------------------------ quantise --- */
 
 /*

@@ -63,6 +63,11 @@ def num_threads() -> int:
     return int(lib().ixo_num_threads())
 
 
+def set_num_threads(n: int) -> None:
+    """Threads for the OpenMP loops of the oracle (overrides an OMP_NUM_THREADS read when the runtime was loaded)."""
+    lib().ixo_set_num_threads(C.c_int(int(n)))
+
+
 # ------------------------------------------------------------------ bf16 ---
 def f32_to_bf16_bits(a: np.ndarray) -> np.ndarray:
     """float32 -> bf16 bit patterns, round to nearest even."""
