@@ -30,4 +30,16 @@ def __getattr__(name):
         from . import kernels
 
         return getattr(kernels, name)
+    if name in ("P6Packed", "set_pdl"):
+        from . import p6
+
+        return getattr(p6, name)
+    if name == "P5Packed":
+        from . import p5
+
+        return p5.P5Packed
+    if name == "PeerAllReduce":
+        from . import parallel
+
+        return parallel.PeerAllReduce
     raise AttributeError(name)
