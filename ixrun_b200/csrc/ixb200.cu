@@ -1,6 +1,7 @@
 // ixb200: C-ABI entry points and kernels of the B200 INT8-X weight path.
 // Built for sm_100a only.  See include/ixb200.h for the contract of each call.
 #include "../../include/ixb200.h"
+#include <cstdlib>
 #include "ixb_common.cuh"
 #include "ixb_gemm_tc.cuh"
 #include "ixb_pack.cuh"
@@ -962,7 +963,11 @@ static P6Plan make_p6_plan(uint32_t out_f, uint32_t in_f, uint32_t m_rows)
         // slot loads, about 3.4 us at the end of the kernel, worth about 170 blocks of streaming (11.5 us for the 588
         // blocks per CTA of the 5120 x 17408 layer).  Whole row tiles per CTA avoid that at the price of imbalance.
         const uint32_t tgrid = rt < sms ? rt : sms;
-        const uint32_t shared_cost = (p.nb + p.grid - 1) / p.grid + 170u;
+        static const uint32_t handover_blocks = []() -> uint32_t {
+            const char *e = getenv("IXB200_P6_HANDOVER_BLOCKS");       // tuning knob; default from measurements on B200
+            return e && *e ? (uint32_t)atoi(e) : 170u;
+        }();
+        const uint32_t shared_cost = (p.nb + p.grid - 1) / p.grid + handover_blocks;
         const uint32_t tiles_cost = ((rt + tgrid - 1) / tgrid) * kb;
         if (tiles_cost <= shared_cost) {
             p.grid = tgrid;
