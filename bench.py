@@ -6,10 +6,16 @@ down_proj tensor (5120 x 17408), reported as packed-weight GB/s.
 One step = one pass of y = W x over the whole packed tensor.  Algorithmic bytes
 per step = the reference's `total_bytes` of the packed tensor + 2*in_f (x) +
 2*out_f (y); rank tables and padding are not counted.  Timed steps rotate over
-four device copies of the packed streams (242 MB > L2), so every step reads
-its weights from HBM.  At N > 1 the tensor is split by columns (row-parallel
-linear: each rank owns in_f/N columns of every row) and the partial outputs are
-summed with one NCCL all-reduce per step.
+enough device copies of the layer (at least 256 MB per GPU, whatever the shard
+size) that every step reads its weights from HBM.  The K steps are captured in
+one CUDA graph, which is replayed until the timed region is at least 50 ms long;
+`ms_per_step` is the device time of all replays divided by their steps.  At
+N > 1 the tensor is split by columns (row-parallel linear: each rank owns
+in_f/N columns of every row) and the partial outputs are summed by one kernel
+over peer memory per step (NCCL with --nccl); the summed output is checked
+against the unsharded layer.  Unless --no-model is given the line also carries
+`model_27b`: ms per token of the tensor-parallel 27B-class hybrid stack at the
+same N.
 
 `--impl reference` times the CPU port of the reference's own layer path (decode
 to bf16, then matmul) on the host cores instead.
@@ -32,7 +38,8 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 OUT_F, IN_F = 5120, 17408
-COPIES = 4
+MIN_ROTATING_BYTES = 256 << 20      # weights that the timed steps rotate over, per GPU (twice the L2)
+MIN_TIMED_MS = 50.0
 METRIC = "fused decode+GEMV packed-weight bandwidth (batch 1)"
 UNIT = "GB/s"
 
@@ -56,7 +63,7 @@ def measured_peak():
     if os.path.exists(path):
         with open(path) as f:
             return float(json.load(f)["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
-    return 6650.0, "fallback (6.65 TB/s, earlier measurement on this pool)"
+    return 6650.0, "fallback (6.65 TB/s, an earlier copy-bandwidth measurement on B200)"
 
 
 class ClockSampler(threading.Thread):
@@ -144,23 +151,44 @@ def cpu_layer_gbs(steps: int, warmup: int, seed: int = 0):
     return algorithmic_bytes(p["total_bytes"]) / dt / 1e9, dt, O.num_threads()
 
 
+WORKLOAD = f"down_proj {OUT_F}x{IN_F} batch 1 fused decode+GEMV, (3,5,8) codes ~ round(Laplace(0,4.4))"
+
+
 def run_reference(args):
+    """The reference's CPU layer path (decode to bf16, then matmul) on all host cores: K steps after W warm-up steps,
+    each one full 5120 x 17408 layer (about half a second), rank 0 only."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    steps = max(1, min(args.steps, 8))       # a step is a full 89 M-weight layer on the CPU (~1 s)
-    warm = max(1, min(args.warmup, 2))
+    steps, warm = max(1, args.steps), max(0, args.warmup)
+    if steps > 200:                          # the GPU arm's default step count would take minutes here
+        steps = 20
     gbs, dt, cores = cpu_layer_gbs(steps, warm)
     line = {
         "impl": "reference", "metric": METRIC, "value": gbs, "unit": UNIT, "n_gpus": args.gpus,
         "steps": steps, "warmup": warm, "ms_per_step": dt * 1e3, "higher_is_better": True,
         "scaling": "strong" if args.gpus > 1 else "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": f"down_proj {OUT_F}x{IN_F} batch 1, decode to bf16 then matmul, host cores"},
+        "config": {"workload": WORKLOAD, "algorithmic_bytes_per_step": algorithmic_bytes_full(),
+                   "path": "CPU port of the reference layer path: decode to bf16, then matmul, host cores"},
         "cpu_baseline": {"value": gbs, "unit": UNIT, "cores": cores, "kind": "port",
                          "sample": f"{steps} full {OUT_F}x{IN_F} layers"},
         "e2e": {"value": gbs, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line), flush=True)
+
+
+_FULL_BYTES = None
+
+
+def algorithmic_bytes_full() -> int:
+    global _FULL_BYTES
+    if _FULL_BYTES is None:
+        from ixrun_b200.quantize import pack_codes
+        from ixrun_b200.synth import laplace_codes
+
+        codes = laplace_codes(OUT_F, IN_F, seed=0)
+        _FULL_BYTES = algorithmic_bytes(pack_codes(codes, torch.tensor(2.0 ** -9, dtype=torch.bfloat16), OUT_F, IN_F)["total_bytes"])
+    return _FULL_BYTES
 
 
 # ----------------------------------------------------------------- GPU arm ---
@@ -169,6 +197,7 @@ def run_gpu(args):
 
     from ixrun_b200 import _lib
     from ixrun_b200.engine import StreamingLinear
+    from ixrun_b200.p6 import set_pdl
     from ixrun_b200.quantize import pack_codes
     from ixrun_b200.synth import laplace_codes
 
@@ -189,18 +218,22 @@ def run_gpu(args):
     # ---- synthetic layer, column shard of this rank
     codes = laplace_codes(OUT_F, IN_F, seed=0).reshape(OUT_F, IN_F)
     scale = torch.tensor(2.0 ** -9, dtype=torch.bfloat16)
-    full_bytes = pack_codes(codes.reshape(-1), scale, OUT_F, IN_F)["total_bytes"] if world > 1 else None
+    full_packed = pack_codes(codes.reshape(-1), scale, OUT_F, IN_F) if (world > 1 and rank == 0) or world == 1 else None
     in_loc = IN_F // world
-    shard = np.ascontiguousarray(codes[:, rank * in_loc:(rank + 1) * in_loc])
-    packed = pack_codes(shard.reshape(-1), scale, OUT_F, in_loc)
-    if full_bytes is None:
-        full_bytes = packed["total_bytes"]
-    alg_bytes = algorithmic_bytes(full_bytes)
+    if world > 1:
+        shard = np.ascontiguousarray(codes[:, rank * in_loc:(rank + 1) * in_loc])
+        packed = pack_codes(shard.reshape(-1), scale, OUT_F, in_loc)
+    else:
+        packed = full_packed
+    alg_bytes = algorithmic_bytes_full()
     alg_bytes_rank = packed["total_bytes"] + 2 * in_loc + 2 * OUT_F
-    layers = [StreamingLinear(packed, resident=args.layout) for _ in range(COPIES)]
-    resident_bytes = layers[0]._p5.resident_bytes if args.layout in ("p5", "p6") else packed["total_bytes"]
+    first = StreamingLinear(packed, resident=args.layout)
+    resident_bytes = first.resident_bytes
+    copies = max(4, -(-MIN_ROTATING_BYTES // resident_bytes) + 1)      # the rotating set exceeds twice the L2 at every N
+    layers = [first] + [StreamingLinear(packed, resident=args.layout) for _ in range(copies - 1)]
     g = torch.Generator().manual_seed(1)
-    x_host = torch.randn(1, IN_F, generator=g).bfloat16()[:, rank * in_loc:(rank + 1) * in_loc].contiguous().pin_memory()
+    x_full = torch.randn(1, IN_F, generator=g).bfloat16()
+    x_host = x_full[:, rank * in_loc:(rank + 1) * in_loc].contiguous().pin_memory()
     x = x_host.to(dev)
     y32 = torch.empty(1, OUT_F, dtype=torch.float32, device=dev)
     y16 = torch.empty(1, OUT_F, dtype=torch.bfloat16, device=dev)
@@ -221,7 +254,7 @@ def run_gpu(args):
             ref = v.clone()
             dist.all_reduce(ref)
             bad = torch.tensor([float((got - ref).abs().max() > 1e-5 * ref.abs().max() or ar.timed_out())], device=dev)
-        except Exception as exc:       # symmetric memory not available on this box: every rank fails the same way
+        except Exception as exc:       # no symmetric memory between these GPUs: every rank fails the same way
             ar = None
             ar_note = f"disabled: {type(exc).__name__}: {exc}"[:200]
             bad = torch.tensor([1.0], device=dev)
@@ -231,7 +264,7 @@ def run_gpu(args):
             ar_note = ar_note or "disabled: the self-check against NCCL failed"
 
     def step(i):
-        lay = layers[i % COPIES]
+        lay = layers[i % copies]
         if world > 1:
             lay.matvec(x, out=y32)
             if ar is not None:
@@ -250,64 +283,103 @@ def run_gpu(args):
     for i in range(max(args.warmup, 3)):
         step(i)
     barrier()
-    pdl = args.layout == "p6" and not args.no_pdl
-    if pdl:
-        # deployment is complete and the device idle: from here on a GEMV launch may fetch its first weight blocks
-        # while the kernel ahead of it in the stream finishes (it still waits for that kernel before it reads x)
-        from ixrun_b200.p6 import set_pdl
 
-        set_pdl(True)
+    # ---- the step's result against the unsharded layer (rank 0 holds it)
+    tp_check = None
+    if world > 1:
+        y_tp = y16.float().cpu()
+        if rank == 0:
+            ref_layer = StreamingLinear(full_packed, resident=args.layout)
+            y_ref = ref_layer.matvec(x_full.to(dev), out_dtype=torch.float32).cpu()
+            tp_check = {"max_rel_err_vs_unsharded": float((y_tp - y_ref).abs().max() / y_ref.abs().max()),
+                        "tolerance": "one bf16 rounding of the output (2^-8 relative to the largest element)",
+                        "exchange": "peer all-reduce kernel (ixb_allreduce)" if ar is not None else "NCCL all-reduce"}
+            del ref_layer
+        barrier()
 
-    # ---- timed region: K steps, device timed, max over ranks
-    graph = None
-    if (world == 1 or ar is not None) and not args.eager:
-        # one CUDA graph holding the K launches keeps host launch gaps out of the device time
+    use_graph = (world == 1 or ar is not None) and not args.eager
+
+    def capture():
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):
             step(0)
         torch.cuda.current_stream().wait_stream(side)
         torch.cuda.synchronize()
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
+        gr = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(gr):
             for i in range(args.steps):
                 step(i)
-        graph.replay()      # untimed: first replay uploads the graph
+        gr.replay()         # untimed: the first replay uploads the graph
         torch.cuda.synchronize()
+        return gr
+
+    def timed(gr, replays, sampler=None):
+        """Device time of `replays` replays of the K-step graph (or of K eager steps), max over ranks, in ms."""
+        barrier()
+        if sampler is not None:
+            sampler.start()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(replays):
+            if gr is not None:
+                gr.replay()
+            else:
+                for i in range(args.steps):
+                    step(i)
+        e1.record()
+        barrier()
+        ms = e0.elapsed_time(e1)
+        if world > 1:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+    def replays_for(gr):
+        """Replays that make the timed region at least MIN_TIMED_MS long (the same number on every rank)."""
+        one = timed(gr, 1)
+        return max(1, int(MIN_TIMED_MS / max(one, 1e-3)) + 1)
+
+    # ---- timed region: R replays of the K steps, programmatic dependent launch on (layout p6)
+    pdl = args.layout == "p6" and not args.no_pdl
+    launch_ms_no_pdl = None
+    if pdl and use_graph and world == 1:
+        # the same graph without programmatic dependent launch, for the record
+        g0 = capture()
+        r0 = replays_for(g0)
+        launch_ms_no_pdl = timed(g0, r0) / (r0 * args.steps)
+        del g0
+    if pdl:
+        # deployment is complete and the device idle: from here on a GEMV launch may fetch its first weight blocks
+        # while the kernel ahead of it in the stream finishes (it still waits for that kernel before it reads x)
+        set_pdl(True)
+    graph = capture() if use_graph else None
+    replays = replays_for(graph)
     launches0 = _lib.lib().ixb_launch_count()
     sampler = ClockSampler(local)
-    sampler.start()
-    barrier()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    if graph is not None:
-        graph.replay()
-    else:
-        for i in range(args.steps):
-            step(i)
-    e1.record()
-    barrier()
+    ms = timed(graph, replays, sampler)
     clocks = sampler.stop()
-    ms = e0.elapsed_time(e1)
-    if world > 1:
-        t = torch.tensor([ms], device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t.item())
-    launches = args.steps * (2 if ar is not None else 1) if graph is not None else _lib.lib().ixb_launch_count() - launches0
-    ms_per_step = ms / args.steps
+    total_steps = replays * args.steps
+    launches = total_steps * (2 if ar is not None else 1) if graph is not None else _lib.lib().ixb_launch_count() - launches0
+    ms_per_step = ms / total_steps
     value = alg_bytes / (ms_per_step * 1e-3) / 1e9
+    if clocks.get("sm_mhz"):
+        clocks["ms_per_step_x_mhz"] = ms_per_step * clocks["sm_mhz"]
 
-    # ---- dominant kernel alone (rank-local shard), CUDA events on the launching stream
-    reps = max(20, min(args.steps, 200))
+    # ---- dominant kernel alone (rank-local shard): one launch at a time, CUDA events on the launching stream
     kt = []
-    for i in range(reps):
+    for i in range(50):
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a.record()
-        layers[i % COPIES].matvec(x, out=y16)
+        layers[i % copies].matvec(x, out=y16)
         b.record()
         b.synchronize()
         kt.append(a.elapsed_time(b))
-    k_ms = ms_per_step if (graph is not None and world == 1) else float(np.mean(kt))
+    kernel_ms_eager = float(np.median(kt))
+    # roofline of the dominant kernel: at N = 1 a step IS one launch of it and the graph figure is its device time
+    # without host gaps; at N > 1 a step also holds the all-reduce, so the eagerly launched kernel is reported
+    k_ms = ms_per_step if (graph is not None and world == 1) else kernel_ms_eager
     peak, peak_src = measured_peak()
     achieved = alg_bytes_rank / (k_ms * 1e-3) / 1e9
 
@@ -321,22 +393,22 @@ def run_gpu(args):
     if world == 1 and not args.eager:
         from ixrun_b200.engine import GraphedCall
 
-        graphed = [GraphedCall(lay, x, host_io=True) for lay in layers]
+        graphed = [GraphedCall(lay, x, host_io=True) for lay in layers[:4]]
 
     def e2e_step(i):
         if graphed is not None:
-            y_host.copy_(graphed[i % COPIES].run_host(x_host))
+            y_host.copy_(graphed[i % len(graphed)].run_host(x_host))
             return
         xd = x_host.to(dev, non_blocking=True)
         if world > 1 and ar is not None:
-            layers[i % COPIES].matvec(xd, out=y32)
+            layers[i % copies].matvec(xd, out=y32)
             y_host.copy_(ar(y32, out=y16), non_blocking=True)
         elif world > 1:
-            layers[i % COPIES].matvec(xd, out=y32)
+            layers[i % copies].matvec(xd, out=y32)
             dist.all_reduce(y32)
             y_host.copy_(y32.to(torch.bfloat16), non_blocking=True)
         else:
-            y_host.copy_(layers[i % COPIES](xd), non_blocking=True)
+            y_host.copy_(layers[i % copies](xd), non_blocking=True)
         torch.cuda.current_stream().synchronize()
 
     for i in range(3):
@@ -351,34 +423,53 @@ def run_gpu(args):
         t = torch.tensor([e2e_s], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e_s = float(t.item())
+    ar_timed_out = ar.timed_out() if ar is not None else ar_note
+
+    # ---- the 27B-class hybrid stack at the same N (every rank takes part; rank 0 reports)
+    model = None
+    graph_used = graph is not None
+    if not args.no_model:
+        del layers, graphed, graph
+        torch.cuda.empty_cache()
+        from ixrun_b200 import hybrid27b
+
+        try:
+            model = hybrid27b.measure(world, rank, dev, tokens=args.model_tokens, nccl=args.nccl or (world > 1 and ar is None))
+        except Exception as exc:      # reported, not hidden: the headline metric above stands on its own
+            model = {"error": f"{type(exc).__name__}: {exc}"[:300]}
 
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
         "scaling": "strong" if world > 1 else "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {
-            "workload": f"down_proj {OUT_F}x{IN_F} batch 1 fused decode+GEMV, (3,5,8) codes ~ round(Laplace(0,4.4))",
+            "workload": WORKLOAD,
             "algorithmic_bytes_per_step": alg_bytes,
             "layout": LAYOUT_TEXT[args.layout],
             "resident_bytes_per_gpu": resident_bytes,
-            "l2": f"timed steps rotate over {COPIES} device copies of the weights ({COPIES * resident_bytes / 1e6:.0f} MB per GPU)",
+            "l2": f"timed steps rotate over {copies} device copies of the weights ({copies * resident_bytes / 1e6:.0f} MB per GPU)",
             "parallelism": ("single GPU" if world == 1 else
                             f"tp{world}: column shards of in_f, fp32 partial outputs summed per step by " +
                             ("one kernel over peer memory (ixb_allreduce)" if ar is not None else "one NCCL all-reduce")),
-            "timed_with": "CUDA events around one graph replay of K launches" if graph is not None else "CUDA events around K eager steps",
+            "timed_with": (f"CUDA events around {replays} replays of one graph of K launches" if graph_used
+                           else f"CUDA events around {replays} x K eager steps"),
+            "timed_region_ms": ms, "graph_replays": replays,
             "programmatic_dependent_launch": bool(pdl),
-            "peer_allreduce_timed_out": (ar.timed_out() if ar is not None else ar_note),
+            "peer_allreduce_timed_out": ar_timed_out,
+            "tp_check": tp_check,
         },
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "traffic": None, "peak_source": peak_src, "kernel": LAYOUT_KERNEL[args.layout],
-                     "algorithmic_bytes_per_launch": alg_bytes_rank, "launch_ms": k_ms},
+                     "algorithmic_bytes_per_launch": alg_bytes_rank, "launch_ms": k_ms,
+                     "launch_ms_no_pdl": launch_ms_no_pdl, "launch_ms_eager_median": kernel_ms_eager},
         "e2e": {"value": alg_bytes / e2e_s / 1e9, "unit": UNIT, "h2d_bytes_per_step": 2 * in_loc,
                 "d2h_bytes_per_step": 2 * OUT_F, "ms_per_step": e2e_s * 1e3, "steps": e2e_steps,
                 "call": ("engine.GraphedCall(StreamingLinear, host_io=True).run_host: one graph launch holding the H2D copy of x, "
-                         "the GEMV and the D2H copy of y, then a stream synchronise" if graphed is not None
+                         "the GEMV and the D2H copy of y, then a stream synchronise" if world == 1 and not args.eager
                          else "StreamingLinear.matvec on a fresh device copy of pinned host x, y copied back")},
         "gpu_launches": int(launches),
         "clocks": clocks,
+        "model_27b": model,
     }
     if rank == 0:
         if world == 1:
@@ -396,10 +487,8 @@ def run_gpu(args):
 
 
 DEFAULT_LAYOUT = "p6"
-LAYOUT_KERNEL = {"p5": "k_p5_mma<1>", "p6": "k_p6_mma<1>", "streams": "k_gemv<1>"}
+LAYOUT_KERNEL = {"p6": "k_p6_mma<1>", "streams": "k_gemv<1>"}
 LAYOUT_TEXT = {
-    "p5": ("resident P5 re-layout of the same int8 codes (5-bit plane in mma fragment order + level-3 weight list), "
-           "built on the GPU at deploy time from the reference's packed streams"),
     "p6": ("resident P6 re-layout of the same int8 codes (6-bit plane in mma fragment order whose fields are part of "
            "the bf16 number 1 + code/32, + a weight list for codes outside -16..31), built on the GPU at deploy time "
            "from the reference's packed streams"),
@@ -410,7 +499,7 @@ LAYOUT_TEXT = {
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=2000)
+    ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--eager", action="store_true", help="launch the timed steps one by one instead of one CUDA graph")
@@ -418,8 +507,10 @@ def main():
                     help="several GPUs: eager NCCL all-reduce instead of the one-kernel all-reduce over peer memory")
     ap.add_argument("--no-pdl", action="store_true",
                     help="layout p6: launch the GEMVs without programmatic dependent launch")
-    ap.add_argument("--layout", default=DEFAULT_LAYOUT, choices=["p5", "p6", "streams"],
-                    help="resident weight layout: the P5 or P6 re-layout, or the reference's streams read directly")
+    ap.add_argument("--layout", default=DEFAULT_LAYOUT, choices=["p6", "streams"],
+                    help="resident weight layout: the P6 re-layout, or the reference's streams read directly")
+    ap.add_argument("--no-model", action="store_true", help="skip the model_27b sub-record (27B-class hybrid stack, ms per token)")
+    ap.add_argument("--model-tokens", type=int, default=16, help="tokens timed for the model_27b sub-record")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

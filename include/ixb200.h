@@ -128,75 +128,38 @@ int ixb_pack_codes(const int8_t *codes_device, const ixb_packed *out, const int3
                    const int32_t *blk_q2_device, ixb_stream_t stream);
 
 /*
- * Resident re-layout "P5".  It has no counterpart in the reference, whose
+ * Resident re-layout "P6".  It has no counterpart in the reference, whose
  * kernels read the (3,5,8) streams directly; it plays the role of the
- * reference's deploy-time derived buffers (ixrun/engine.py:68-97) taken one
- * step further: the streams stay the interchange / cache-file format, and at
- * deploy time the int8 codes are re-laid out, losslessly, for fixed
- * addressing:
- *   w03, w4  a 5-bit field per element (code + 15 for |code| <= 15, 15 = code 0
- *            for level-3 elements), one uint4 + one uint32 per 32 elements; the
- *            matrix is cut into blocks of 16 rows x 64 columns (ixb_p5_blocks of
- *            them, ragged edges padded) whose fields are ordered as the
- *            tensor-core A fragments that the GEMV consumes
- *   esc      the level-3 elements of every block as uint32 entries: the weight
- *            bf16(code * scale) in the low half, its position in the block's
- *            fragment image in the high half; blk_off: int32 first entry of
- *            every block
- * about 5 + 32 * P(level 3) bits per weight.  Buffer sizes, with the slack
- * that the GEMV's prefetch may read but never interprets (B = ixb_p5_blocks):
- *   w03 (B + 4) * 512 bytes, w4 (B + 4) * 128 bytes, blk_off (B + 5) * 4 bytes,
- *   esc (n_esc + 64) * 4 bytes.
- * ixb_p5_build: int8 codes [out_f, in_f] + the bf16 scale -> layout (n_esc =
- *   number of level-3 elements = counts[2]; ws: (B + 5) * 4 bytes).
- * ixb_p5_decode: layout -> int8 codes / bf16 weights (out_kind as ixb_decode).
- * ixb_p5_gemv: same contract as ixb_gemv (result definition, bias, scratch
- *   rules; scratch 16-byte aligned), reading this layout on the tensor cores
- *   (mma.sync, bf16 x bf16 products, fp32 accumulation) in one kernel --
- *   1..8 activation rows cost the same.
- */
-typedef struct ixb_p5 {
-    const void *w03;
-    const void *w4;
-    const void *blk_off;
-    const void *esc;
-    int64_t n_esc;
-    const void *scale;    /* one bf16 */
-    int64_t out_f;
-    int64_t in_f;
-} ixb_p5;
-int64_t ixb_p5_blocks(int64_t out_f, int64_t in_f);
-int ixb_p5_build(const int8_t *codes_device, const void *scale_device, int64_t out_f, int64_t in_f, void *w03_device,
-                 void *w4_device, int32_t *blk_off_device, void *esc_device, int64_t n_esc,
-                 void *ws_device, size_t ws_bytes, ixb_stream_t stream);
-int ixb_p5_decode(const ixb_p5 *t, void *out_device, int out_kind, ixb_stream_t stream);
-size_t ixb_p5_gemv_scratch_bytes(int64_t out_f, int64_t in_f, int64_t m_rows);
-int ixb_p5_gemv(const ixb_p5 *t, const void *x_device, int64_t m_rows, const void *bias_device,
-                void *y_device, int y_is_f32, void *scratch_device, size_t scratch_bytes, ixb_stream_t stream);
-
-/*
- * Resident re-layout "P6": the same idea as P5 with one more plane bit per
- * weight and a cheaper conversion.  No counterpart in the reference (it plays
- * the role of its deploy-time derived buffers, ixrun/engine.py:68-97).
- *   plane    a 6-bit field per element, blocks of 16 rows x 64 columns as in
- *            P5, 768 contiguous bytes per block.  The field is bits 7..2 of the
- *            low byte of the bf16 number 1 + code / 32 (codes -16 .. 31), so the
- *            GEMV needs a shift, a mask and ONE fused multiply-add per pair of
- *            weights to obtain bf16(code * scale) -- the reference's
- *            dequantised weight (ixrun/quantize.py:201-204), rounded once
+ * reference's deploy-time derived buffers (ixrun/engine.py:68-97).  The streams
+ * stay the interchange / cache-file format; at deploy time the int8 codes they
+ * decode to are re-laid out on the GPU, losslessly, so that nothing is
+ * addressed by rank:
+ *   plane    a 6-bit field per element, blocks of 16 rows x 64 columns (ragged
+ *            edges padded), 768 contiguous bytes per block, block b =
+ *            row_tile * ceil(in_f / 64) + column_block.  The field is bits 7..2
+ *            of the low byte of the bf16 number 1 + code / 32 (codes -16 .. 31),
+ *            so the GEMV needs a shift, a mask and ONE fused multiply-add per
+ *            pair of weights to obtain bf16(code * scale) -- the reference's
+ *            dequantised weight (ixrun/quantize.py:182, ixrun/fused.py:169-170),
+ *            rounded once
  *   esc      every other code as a uint32 entry: bf16(code * scale) in the high
  *            half, row in tile, block index mod 64 and column in block below;
  *            blk_off: int32 first entry of every block
  * about 6 + 32 * P(code outside -16 .. 31) bits per weight.  Buffer sizes
- * (B = ixb_p5_blocks): plane (B + 5) * 768 bytes, blk_off (B + 1) * 4 bytes,
+ * (B = ixb_p6_blocks): plane (B + 5) * 768 bytes, blk_off (B + 1) * 4 bytes,
  * esc (n_esc + 64) * 4 bytes; plane and esc 16-byte aligned.
  * ixb_p6_build: int8 codes [out_f, in_f] + the bf16 scale -> layout (n_esc =
- *   number of codes outside -16 .. 31; ws: (B + 1) * 4 bytes).
+ *   number of codes outside -16 .. 31; entries beyond n_esc are not written;
+ *   ws: (B + 1) * 4 bytes).
  * ixb_p6_decode: layout -> int8 codes / bf16 weights (out_kind as ixb_decode).
- * ixb_p6_gemv: same contract as ixb_gemv / ixb_p5_gemv (result definition,
- *   bias, scratch rules; scratch 16-byte aligned, zero before the first call),
+ * ixb_p6_gemv: same result definition, bias and argument meaning as ixb_gemv,
  *   1..8 activation rows in one kernel: plane on the tensor cores (mma.sync,
- *   exact bf16 x bf16 products, fp32 accumulation), outliers on the CUDA cores.
+ *   exact bf16 x bf16 products, fp32 accumulation), outliers on the CUDA cores;
+ *   partial sums are added in a fixed order (reproducible, no floating-point
+ *   atomics).  Scratch: ixb_p6_gemv_scratch_bytes bytes, 16-byte aligned, zero
+ *   before the first call; every launch leaves it all zero again, so one buffer
+ *   (sized for the largest need) may serve layers of any shape one after the
+ *   other, but not two launches that can overlap on the GPU.
  */
 typedef struct ixb_p6 {
     const void *plane;
@@ -207,6 +170,7 @@ typedef struct ixb_p6 {
     int64_t out_f;
     int64_t in_f;
 } ixb_p6;
+int64_t ixb_p6_blocks(int64_t out_f, int64_t in_f);
 int ixb_p6_build(const int8_t *codes_device, const void *scale_device, int64_t out_f, int64_t in_f, void *plane_device,
                  int32_t *blk_off_device, void *esc_device, int64_t n_esc, void *ws_device, size_t ws_bytes,
                  ixb_stream_t stream);

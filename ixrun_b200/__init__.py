@@ -30,14 +30,10 @@ def __getattr__(name):
         from . import kernels
 
         return getattr(kernels, name)
-    if name in ("P6Packed", "set_pdl"):
+    if name in ("P6Packed", "set_pdl", "GemvScratch"):
         from . import p6
 
         return getattr(p6, name)
-    if name == "P5Packed":
-        from . import p5
-
-        return p5.P5Packed
     if name == "PeerAllReduce":
         from . import parallel
 

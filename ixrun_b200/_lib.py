@@ -22,8 +22,7 @@ SYMBOLS = (
     "ixb_decode", "ixb_gemv_scratch_bytes", "ixb_gemv", "ixb_gemv_static",
     "ixb_gemm_scratch_bytes", "ixb_gemm",
     "ixb_pack_workspace_bytes", "ixb_quantize_codes", "ixb_count_codes", "ixb_pack_codes",
-    "ixb_p5_blocks", "ixb_p5_build", "ixb_p5_decode", "ixb_p5_gemv_scratch_bytes", "ixb_p5_gemv",
-    "ixb_p6_build", "ixb_p6_decode", "ixb_p6_gemv_scratch_bytes", "ixb_p6_gemv", "ixb_set_pdl",
+    "ixb_p6_blocks", "ixb_p6_build", "ixb_p6_decode", "ixb_p6_gemv_scratch_bytes", "ixb_p6_gemv", "ixb_set_pdl",
     "ixb_allreduce_bytes", "ixb_allreduce",
 )
 
@@ -46,15 +45,6 @@ class Packed(C.Structure):
     ]
 
 
-class P5Struct(C.Structure):
-    """Mirror of ``struct ixb_p5``."""
-
-    _fields_ = [
-        ("w03", C.c_void_p), ("w4", C.c_void_p), ("blk_off", C.c_void_p), ("esc", C.c_void_p),
-        ("n_esc", C.c_int64), ("scale", C.c_void_p), ("out_f", C.c_int64), ("in_f", C.c_int64),
-    ]
-
-
 class P6Struct(C.Structure):
     """Mirror of ``struct ixb_p6``."""
 
@@ -73,9 +63,8 @@ def lib():
     if _build.is_stale():
         try:
             so = _build.build()
-        except Exception as e:  # no silent fallback
-            if not os.path.exists(so):
-                raise IxbError(f"libixb200.so is not built and cannot be built here: {e}") from e
+        except Exception as e:  # no silent fallback: a stale library is not loaded in place of a failed build
+            raise IxbError(f"libixb200.so is missing or older than its sources and cannot be built here: {e}") from e
     L = C.CDLL(so)
     vp, i64, sz = C.c_void_p, C.c_int64, C.c_size_t
     L.ixb_version.restype = C.c_int
@@ -103,16 +92,8 @@ def lib():
     L.ixb_count_codes.argtypes = [vp, i64, vp, vp, vp, C.POINTER(i64), vp, sz, vp]
     L.ixb_pack_codes.restype = C.c_int
     L.ixb_pack_codes.argtypes = [vp, C.POINTER(Packed), vp, vp, vp]
-    L.ixb_p5_build.restype = C.c_int
-    L.ixb_p5_blocks.restype = i64
-    L.ixb_p5_blocks.argtypes = [i64, i64]
-    L.ixb_p5_build.argtypes = [vp, vp, i64, i64, vp, vp, vp, vp, i64, vp, sz, vp]
-    L.ixb_p5_decode.restype = C.c_int
-    L.ixb_p5_decode.argtypes = [C.POINTER(P5Struct), vp, C.c_int, vp]
-    L.ixb_p5_gemv_scratch_bytes.restype = sz
-    L.ixb_p5_gemv_scratch_bytes.argtypes = [i64, i64, i64]
-    L.ixb_p5_gemv.restype = C.c_int
-    L.ixb_p5_gemv.argtypes = [C.POINTER(P5Struct), vp, i64, vp, vp, C.c_int, vp, sz, vp]
+    L.ixb_p6_blocks.restype = i64
+    L.ixb_p6_blocks.argtypes = [i64, i64]
     L.ixb_p6_build.restype = C.c_int
     L.ixb_p6_build.argtypes = [vp, vp, i64, i64, vp, vp, vp, i64, vp, sz, vp]
     L.ixb_p6_decode.restype = C.c_int

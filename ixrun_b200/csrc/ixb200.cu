@@ -5,7 +5,6 @@
 #include "ixb_common.cuh"
 #include "ixb_gemm_tc.cuh"
 #include "ixb_pack.cuh"
-#include "ixb_p5.cuh"
 #include "ixb_p6.cuh"
 #include "ixb_allreduce.cuh"
 
@@ -55,6 +54,22 @@ static int num_sms()
         cached[dev] = n;
     }
     return cached[dev];
+}
+
+// opt-in to more than 48 KB of dynamic shared memory, once per kernel instantiation and device
+template <class K>
+static cudaError_t opt_in_smem(K kernel, bool (&done)[64], int bytes)
+{
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+    if (!done[dev]) {
+        e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+        if (e != cudaSuccess) return e;
+        done[dev] = true;
+    }
+    return cudaSuccess;
 }
 
 static int to_streams(const ixb_packed *w, Streams *s)
@@ -535,11 +550,8 @@ template <int M, int XM>
 static void launch_gemv_x(const Streams &s, const int32_t *q1, const int32_t *q2, const void *x, const void *bias,
                           void *y, int y_f32, float *slots, uint32_t *ticket, const GemvPlan &p, cudaStream_t st)
 {
-    static bool attr_set = false;   // opt in to more than 48 KB of dynamic shared memory, once per instantiation
-    if (!attr_set) {
-        cudaFuncSetAttribute(k_gemv<M, XM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kGemvSmemBudget);
-        attr_set = true;
-    }
+    static bool attr_set[64] = {false};
+    (void)opt_in_smem(k_gemv<M, XM>, attr_set, (int)kGemvSmemBudget);   // on failure the launch below fails and is reported
     k_gemv<M, XM><<<p.grid, kGemvThreads, p.smem, st>>>(s, q1, q2, (const __nv_bfloat16 *)x,
                                                         (const __nv_bfloat16 *)bias, y, y_f32, slots, ticket, p);
 }
@@ -729,151 +741,13 @@ extern "C" int ixb_pack_codes(const int8_t *codes, const ixb_packed *out, const 
     return launch_check("k_pack");
 }
 
-// ------------------------------------------------------------- resident P5 layout
-static int to_p5(const ixb_p5 *t, P5 *p)
-{
-    if (!t) return fail(IXB_E_ARG, "P5 tensor is NULL");
-    if (t->out_f <= 0 || t->in_f <= 0) return fail(IXB_E_ARG, "bad shape");
-    long long n = (long long)t->out_f * t->in_f;
-    if (n > 800000000LL) return fail(IXB_E_UNSUPPORTED, "tensor too large");
-    if (!t->w03 || !t->w4 || !t->blk_off || !t->esc || !t->scale) return fail(IXB_E_ARG, "NULL P5 pointer");
-    if (((uintptr_t)t->w03 & 15u) || ((uintptr_t)t->w4 & 3u)) return fail(IXB_E_ARG, "P5 planes are misaligned");
-    p->w03 = (const uint4 *)t->w03;
-    p->w4 = (const uint32_t *)t->w4;
-    p->blk_off = (const int32_t *)t->blk_off;
-    p->esc = (const uint32_t *)t->esc;
-    p->scale = (const __nv_bfloat16 *)t->scale;
-    p->out_f = (uint32_t)t->out_f;
-    p->in_f = (uint32_t)t->in_f;
-    p->rt = (p->out_f + kP5TileRows - 1) / kP5TileRows;
-    p->kb = (p->in_f + kP5TileCols - 1) / kP5TileCols;
-    return IXB_OK;
-}
-
-extern "C" int64_t ixb_p5_blocks(int64_t out_f, int64_t in_f)
+// ------------------------------------------------------------- resident P6 layout
+extern "C" int64_t ixb_p6_blocks(int64_t out_f, int64_t in_f)
 {
     if (out_f <= 0 || in_f <= 0) return 0;
-    return ((out_f + kP5TileRows - 1) / kP5TileRows) * ((in_f + kP5TileCols - 1) / kP5TileCols);
+    return ((out_f + kTileRows - 1) / kTileRows) * ((in_f + kTileCols - 1) / kTileCols);
 }
 
-extern "C" int ixb_p5_build(const int8_t *codes, const void *scale, int64_t out_f, int64_t in_f, void *w03, void *w4,
-                            int32_t *blk_off, void *esc, int64_t n_esc, void *ws, size_t ws_bytes, ixb_stream_t stream)
-{
-    if (!codes || !scale || !w03 || !w4 || !blk_off || !esc || !ws) return fail(IXB_E_ARG, "NULL pointer argument");
-    if (out_f <= 0 || in_f <= 0 || out_f * in_f > 800000000LL) return fail(IXB_E_ARG, "bad shape");
-    if (n_esc < 0) return fail(IXB_E_ARG, "bad outlier count");
-    if (((uintptr_t)w03 & 15u) || ((uintptr_t)w4 & 3u)) return fail(IXB_E_ARG, "P5 planes are misaligned");
-    uint32_t rt = (uint32_t)((out_f + kP5TileRows - 1) / kP5TileRows), kb = (uint32_t)((in_f + kP5TileCols - 1) / kP5TileCols);
-    uint32_t nb = rt * kb, n_off = nb + 1 + kP5SlackBlocks;
-    if (ws_bytes < (size_t)n_off * 4) return fail(IXB_E_SCRATCH, "P5 workspace too small");
-    cudaStream_t st = (cudaStream_t)stream;
-    int32_t *blk_cnt = (int32_t *)ws;
-    int rc;
-    // slack behind the planes and the entries is zero (it is read, never interpreted); the counts of the slack
-    // blocks are zero so that their offsets repeat the total
-    IXB_CUDA(cudaMemsetAsync(blk_cnt, 0, (size_t)n_off * 4, st));
-    IXB_CUDA(cudaMemsetAsync((char *)w03 + (size_t)nb * 512, 0, (size_t)kP5SlackBlocks * 512, st));
-    IXB_CUDA(cudaMemsetAsync((char *)w4 + (size_t)nb * 128, 0, (size_t)kP5SlackBlocks * 128, st));
-    IXB_CUDA(cudaMemsetAsync((char *)esc + (size_t)n_esc * 4, 0, (size_t)kP5SlackEntries * 4, st));
-    k_p5_plane<<<(nb + 7) / 8, 256, 0, st>>>(codes, (uint32_t)out_f, (uint32_t)in_f, rt, kb, (uint4 *)w03, (uint32_t *)w4,
-                                             blk_cnt);
-    if ((rc = launch_check("k_p5_plane"))) return rc;
-    k_excl_scan<<<1, 1024, 0, st>>>(blk_cnt, blk_off, n_off);      // entry nb (and the slack) = total
-    if ((rc = launch_check("k_excl_scan"))) return rc;
-    if (n_esc) {
-        k_p5_esc<<<(nb + 7) / 8, 256, 0, st>>>(codes, (uint32_t)out_f, (uint32_t)in_f, rt, kb, blk_off,
-                                               (const __nv_bfloat16 *)scale, (uint32_t *)esc);
-        if ((rc = launch_check("k_p5_esc"))) return rc;
-    }
-    return IXB_OK;
-}
-
-extern "C" int ixb_p5_decode(const ixb_p5 *t, void *out, int out_kind, ixb_stream_t stream)
-{
-    P5 p;
-    int rc = to_p5(t, &p);
-    if (rc) return rc;
-    if (!out) return fail(IXB_E_ARG, "output is NULL");
-    if (out_kind != 0 && out_kind != 1) return fail(IXB_E_ARG, "out_kind must be 0 or 1");
-    uint32_t nb = p.rt * p.kb;
-    cudaStream_t st = (cudaStream_t)stream;
-    if (out_kind == 1 && (p.in_f & 7u) == 0 && ((uintptr_t)out & 15u) == 0) {
-        k_p5_decode_bf16<<<(nb + 7) / 8, 256, 0, st>>>(p, (__nv_bfloat16 *)out);       // plane and outliers in one pass
-        return launch_check("k_p5_decode_bf16");
-    }
-    if (out_kind == 0) k_p5_decode_plane<0><<<(nb + 7) / 8, 256, 0, st>>>(p, out);
-    else k_p5_decode_plane<1><<<(nb + 7) / 8, 256, 0, st>>>(p, out);
-    if ((rc = launch_check("k_p5_decode_plane"))) return rc;
-    if (t->n_esc) {
-        if (out_kind == 0) k_p5_decode_esc<0><<<(nb + 7) / 8, 256, 0, st>>>(p, out);
-        else k_p5_decode_esc<1><<<(nb + 7) / 8, 256, 0, st>>>(p, out);
-        rc = launch_check("k_p5_decode_esc");
-    }
-    return rc;
-}
-
-struct P5Plan { uint32_t nb, grid, xstride, smem, xs; size_t slot_bytes; };
-
-static P5Plan make_p5_plan(uint32_t out_f, uint32_t in_f, uint32_t m_rows)
-{
-    P5Plan p;
-    uint32_t rt = (out_f + kP5TileRows - 1) / kP5TileRows, kb = (in_f + kP5TileCols - 1) / kP5TileCols;
-    p.nb = rt * kb;
-    uint32_t sms = (uint32_t)num_sms();
-    uint32_t want = (p.nb + kP5Warps - 1) / kP5Warps;
-    p.grid = want < sms ? want : sms;
-    if (!p.grid) p.grid = 1;
-    p.xstride = kb * kP5TileCols + 8u;
-    uint32_t xbytes = m_rows * p.xstride * 2u;
-    p.xs = (uint32_t)kP5SmemFixed + xbytes <= 216u * 1024u;
-    p.smem = (uint32_t)kP5SmemFixed + (p.xs ? xbytes : 0u);
-    p.slot_bytes = (size_t)p.grid * 2u * 32u * sizeof(float4);
-    return p;
-}
-
-extern "C" size_t ixb_p5_gemv_scratch_bytes(int64_t out_f, int64_t in_f, int64_t m_rows)
-{
-    if (out_f <= 0 || in_f <= 0 || m_rows <= 0) return 0;
-    P5Plan p = make_p5_plan((uint32_t)out_f, (uint32_t)in_f, (uint32_t)m_rows);
-    return 1024 + p.slot_bytes;
-}
-
-template <int XS>
-static void launch_p5(const P5 &p, const void *x, uint32_t m_rows, const void *bias, void *y, int y_f32, float4 *slots,
-                      uint32_t *tickets, const P5Plan &pl, cudaStream_t st)
-{
-    static bool attr_set = false;
-    if (!attr_set) {
-        cudaFuncSetAttribute(k_p5_mma<XS>, cudaFuncAttributeMaxDynamicSharedMemorySize, 216 * 1024);
-        attr_set = true;
-    }
-    k_p5_mma<XS><<<pl.grid, kP5Threads, pl.smem, st>>>(p, (const __nv_bfloat16 *)x, m_rows, (const __nv_bfloat16 *)bias, y,
-                                                       y_f32, slots, tickets, pl.nb, pl.xstride);
-}
-
-extern "C" int ixb_p5_gemv(const ixb_p5 *t, const void *x, int64_t m_rows, const void *bias, void *y, int y_is_f32,
-                           void *scratch, size_t scratch_bytes, ixb_stream_t stream)
-{
-    P5 p;
-    int rc = to_p5(t, &p);
-    if (rc) return rc;
-    if (!x || !y || !scratch) return fail(IXB_E_ARG, "NULL pointer argument");
-    if (m_rows < 1 || m_rows > 8) return fail(IXB_E_UNSUPPORTED, "m_rows=%lld outside 1..8", (long long)m_rows);
-    if ((uintptr_t)x & 15u) return fail(IXB_E_ARG, "x is not 16-byte aligned");
-    if ((uintptr_t)scratch & 15u) return fail(IXB_E_ARG, "scratch is not 16-byte aligned");
-    if (scratch_bytes < ixb_p5_gemv_scratch_bytes(p.out_f, p.in_f, m_rows)) return fail(IXB_E_SCRATCH, "gemv scratch too small");
-    P5Plan pl = make_p5_plan(p.out_f, p.in_f, (uint32_t)m_rows);
-    if (!pl.xs && (p.in_f % kP5TileCols))
-        return fail(IXB_E_UNSUPPORTED, "in_f=%u: activations too large for shared memory need in_f %% 64 == 0", p.in_f);
-    uint32_t *tickets = (uint32_t *)scratch;                  // the first 1024 bytes hold the tile tickets (grid + 1 words)
-    float4 *slots = (float4 *)((char *)scratch + 1024);
-    cudaStream_t st = (cudaStream_t)stream;
-    if (pl.xs) launch_p5<1>(p, x, (uint32_t)m_rows, bias, y, y_is_f32, slots, tickets, pl, st);
-    else launch_p5<0>(p, x, (uint32_t)m_rows, bias, y, y_is_f32, slots, tickets, pl, st);
-    return launch_check("k_p5_mma");
-}
-
-// ------------------------------------------------------------- resident P6 layout
 static int to_p6(const ixb_p6 *t, P6 *p)
 {
     if (!t) return fail(IXB_E_ARG, "P6 tensor is NULL");
@@ -888,8 +762,8 @@ static int to_p6(const ixb_p6 *t, P6 *p)
     p->scale = (const __nv_bfloat16 *)t->scale;
     p->out_f = (uint32_t)t->out_f;
     p->in_f = (uint32_t)t->in_f;
-    p->rt = (p->out_f + kP5TileRows - 1) / kP5TileRows;
-    p->kb = (p->in_f + kP5TileCols - 1) / kP5TileCols;
+    p->rt = (p->out_f + kTileRows - 1) / kTileRows;
+    p->kb = (p->in_f + kTileCols - 1) / kTileCols;
     return IXB_OK;
 }
 
@@ -900,7 +774,7 @@ extern "C" int ixb_p6_build(const int8_t *codes, const void *scale, int64_t out_
     if (out_f <= 0 || in_f <= 0 || out_f * in_f > 800000000LL) return fail(IXB_E_ARG, "bad shape");
     if (n_esc < 0) return fail(IXB_E_ARG, "bad outlier count");
     if (((uintptr_t)plane & 15u) || ((uintptr_t)esc & 15u)) return fail(IXB_E_ARG, "P6 plane or entries are misaligned");
-    uint32_t rt = (uint32_t)((out_f + kP5TileRows - 1) / kP5TileRows), kb = (uint32_t)((in_f + kP5TileCols - 1) / kP5TileCols);
+    uint32_t rt = (uint32_t)((out_f + kTileRows - 1) / kTileRows), kb = (uint32_t)((in_f + kTileCols - 1) / kTileCols);
     uint32_t nb = rt * kb, n_off = nb + 1;
     if (ws_bytes < (size_t)n_off * 4) return fail(IXB_E_SCRATCH, "P6 workspace too small");
     cudaStream_t st = (cudaStream_t)stream;
@@ -916,7 +790,7 @@ extern "C" int ixb_p6_build(const int8_t *codes, const void *scale, int64_t out_
     if ((rc = launch_check("k_excl_scan"))) return rc;
     if (n_esc) {
         k_p6_esc<<<(nb + 7) / 8, 256, 0, st>>>(codes, (uint32_t)out_f, (uint32_t)in_f, rt, kb, blk_off,
-                                               (const __nv_bfloat16 *)scale, (uint32_t *)esc);
+                                               (const __nv_bfloat16 *)scale, (uint32_t *)esc, (uint32_t)n_esc);
         if ((rc = launch_check("k_p6_esc"))) return rc;
     }
     return IXB_OK;
@@ -951,7 +825,7 @@ struct P6Plan { uint32_t nb, grid, xstride, smem, xs, cq, cr, unit; size_t slot_
 static P6Plan make_p6_plan(uint32_t out_f, uint32_t in_f, uint32_t m_rows)
 {
     P6Plan p;
-    uint32_t rt = (out_f + kP5TileRows - 1) / kP5TileRows, kb = (in_f + kP5TileCols - 1) / kP5TileCols;
+    uint32_t rt = (out_f + kTileRows - 1) / kTileRows, kb = (in_f + kTileCols - 1) / kTileCols;
     p.nb = rt * kb;
     uint32_t sms = (uint32_t)num_sms();
     uint32_t want = (p.nb + kP6Warps - 1) / kP6Warps;
@@ -977,7 +851,7 @@ static P6Plan make_p6_plan(uint32_t out_f, uint32_t in_f, uint32_t m_rows)
     const uint32_t units = p.nb / p.unit;
     p.cq = units / p.grid;
     p.cr = units % p.grid;
-    p.xstride = kb * kP5TileCols + 8u;
+    p.xstride = kb * kTileCols + 8u;
     uint32_t xbytes = m_rows * p.xstride * 2u;
     p.xs = (uint32_t)kP6SmemFixed + xbytes <= 227u * 1024u;
     p.smem = (uint32_t)kP6SmemFixed + (p.xs ? xbytes : 0u);
@@ -995,24 +869,17 @@ extern "C" size_t ixb_p6_gemv_scratch_bytes(int64_t out_f, int64_t in_f, int64_t
 // Programmatic dependent launch for the P6 GEMV (off by default).  When on, a launch may begin before the kernel
 // ahead of it in the stream has finished: it fetches its first weight blocks and outlier entries, then waits for that
 // kernel to complete before it touches the activations, y or the scratch.
-static int g_p6_pdl = 0;
+static std::atomic<int> g_p6_pdl{0};
 
-extern "C" int ixb_set_pdl(int on)
-{
-    int prev = g_p6_pdl;
-    g_p6_pdl = on ? 1 : 0;
-    return prev;
-}
+extern "C" int ixb_set_pdl(int on) { return g_p6_pdl.exchange(on ? 1 : 0); }
 
 template <int XS>
 static cudaError_t launch_p6(const P6 &p, const void *x, uint32_t m_rows, const void *bias, void *y, int y_f32,
                              float4 *slots, uint32_t *tickets, const P6Plan &pl, cudaStream_t st)
 {
-    static bool attr_set = false;
-    if (!attr_set) {
-        cudaFuncSetAttribute(k_p6_mma<XS>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
-        attr_set = true;
-    }
+    static bool attr_set[64] = {false};
+    cudaError_t oe = opt_in_smem(k_p6_mma<XS>, attr_set, 227 * 1024);
+    if (oe != cudaSuccess) return oe;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(pl.grid);
     cfg.blockDim = dim3(kP6Threads);
@@ -1022,7 +889,7 @@ static cudaError_t launch_p6(const P6 &p, const void *x, uint32_t m_rows, const 
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = g_p6_pdl ? 1 : 0;
+    cfg.numAttrs = g_p6_pdl.load() ? 1 : 0;
     return cudaLaunchKernelEx(&cfg, k_p6_mma<XS>, p, (const __nv_bfloat16 *)x, m_rows, (const __nv_bfloat16 *)bias, y, y_f32,
                               slots, tickets, pl.nb, pl.xstride, pl.cq, pl.cr, pl.unit);
 }
@@ -1039,7 +906,7 @@ extern "C" int ixb_p6_gemv(const ixb_p6 *t, const void *x, int64_t m_rows, const
     if ((uintptr_t)scratch & 15u) return fail(IXB_E_ARG, "scratch is not 16-byte aligned");
     if (scratch_bytes < ixb_p6_gemv_scratch_bytes(p.out_f, p.in_f, m_rows)) return fail(IXB_E_SCRATCH, "gemv scratch too small");
     P6Plan pl = make_p6_plan(p.out_f, p.in_f, (uint32_t)m_rows);
-    if (!pl.xs && (p.in_f % kP5TileCols))
+    if (!pl.xs && (p.in_f % kTileCols))
         return fail(IXB_E_UNSUPPORTED, "in_f=%u: activations too large for shared memory need in_f %% 64 == 0", p.in_f);
     uint32_t *tickets = (uint32_t *)scratch;                  // the first 1024 bytes hold the tile tickets (grid + 1 words)
     float4 *slots = (float4 *)((char *)scratch + 1024);
@@ -1071,7 +938,7 @@ static cudaError_t launch_ar(const ArPeers &peers, const void *x, int rank, uint
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = g_p6_pdl ? 1 : 0;
+    cfg.numAttrs = g_p6_pdl.load() ? 1 : 0;
     return cudaLaunchKernelEx(&cfg, k_allreduce_oneshot<W>, peers, (const float *)x, rank, n, n_max,
                               (const __nv_bfloat16 *)bias, y, y_f32, epoch, err);
 }
@@ -1139,11 +1006,8 @@ extern "C" int ixb_gemm(const ixb_packed *w, const int32_t *blk_q1, const int32_
     if (scratch_bytes < ixb_gemm_scratch_bytes(s.out_f, s.in_f, m_rows)) return fail(IXB_E_SCRATCH, "gemm scratch too small");
     TcPlan p = make_tc_plan(s.out_f, s.in_f);
     cudaStream_t st = (cudaStream_t)stream;
-    static bool attr_set = false;
-    if (!attr_set) {
-        IXB_CUDA(cudaFuncSetAttribute(k_gemm_tc, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kTcSmemBytes));
-        attr_set = true;
-    }
+    static bool attr_set[64] = {false};
+    IXB_CUDA(opt_in_smem(k_gemm_tc, attr_set, (int)kTcSmemBytes));
     uint32_t *err = (uint32_t *)scratch;
     float *part = (float *)((char *)scratch + 256);
     IXB_CUDA(cudaMemsetAsync(scratch, 0, 256, st));

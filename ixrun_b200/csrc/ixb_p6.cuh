@@ -1,9 +1,10 @@
 // Resident re-layout "P6" of an INT8-X tensor and the kernels that run on it.
 //
-// Like P5 (ixb_p5.cuh) it is built at deploy time, on the GPU, from the int8
-// codes that the reference's (3,5,8) streams decode to (ixrun/quantize.py:80-96),
-// and keeps those codes exactly.  It trades one more plane bit per weight for a
-// conversion that costs three instructions per PAIR of weights:
+// It is built at deploy time, on the GPU, from the int8 codes that the
+// reference's (3,5,8) streams decode to (ixrun/quantize.py:80-96), and keeps
+// those codes exactly.  Nothing in it is addressed by rank: every 1024-weight
+// block (16 rows x 64 columns, one warp) sits at a fixed address, and turning it
+// into tensor-core operands costs three instructions per PAIR of weights:
 //
 //   plane   every element owns a 6-bit field F that is bits 7..2 of the low
 //           byte of the bf16 number a = 1 + code / 32:
@@ -12,10 +13,11 @@
 //           so (F << 2) | 0x3F00 IS a, and one fused multiply-add
 //           fma(a, 32 s, -32 s) = bf16(code * s) rounds the exact product once:
 //           the reference's dequantised weight bf16(f32(code) * f32(scale))
-//           (ixrun/quantize.py:201-204), bit for bit, for any scale s.
+//           (ixrun/quantize.py:182, ixrun/fused.py:169-170), bit for bit, for any scale s.
 //           Other codes ("outliers") leave the placeholder F = 32 (weight 0).
-//           Blocks of 16 rows x 64 columns as in P5 (p5_elem gives the element
-//           of lane / pair / half); a lane owns 32 fields in six 32-bit words,
+//           Blocks of 16 rows x 64 columns, ragged edges padded with
+//           placeholders (p6_elem gives the element of lane / pair / half); a
+//           lane owns 32 fields in six 32-bit words,
 //           a block is 768 contiguous bytes: 32 x uint4 (words 0..3), then
 //           32 x uint2 (words 4, 5).  Word k holds pair 2k at bits 0 / 16 and
 //           pair 2k+1 at bits 6 / 22 (low / high element); the 4 + 4 spare
@@ -39,9 +41,37 @@
 // segment of the run, while the ring keeps fetching.  Products are exact, accumulation is fp32, and no
 // floating-point atomics are used: results are reproducible.
 #pragma once
-#include "ixb_p5.cuh"
+#include "ixb_common.cuh"
 
 namespace ixb {
+
+constexpr int kTileRows = 16;      // a block: 16 rows x 64 columns = 1024 weights, one warp
+constexpr int kTileCols = 64;
+
+// Lane l of a block: g = l >> 2, t = l & 3.  Its 16 pairs p = 4 j + q (j = 0..3 the mma, q = 0..3 the A register):
+//   row    = 16 R + g + 8 (q & 1)
+//   column = 64 kb + 16 t + 4 j + 2 (q >> 1) + h          (h = 0 low half, 1 high half of the register)
+// i.e. the k index of mma j is permuted so that a lane needs the 16 consecutive activations 16 t .. 16 t + 15.
+__device__ __forceinline__ void p6_elem(int lane, int p, int h, uint32_t &row_in_tile, uint32_t &col_in_tile)
+{
+    int g = lane >> 2, t = lane & 3, j = p >> 2, q = p & 3;
+    row_in_tile = (uint32_t)(g + 8 * (q & 1));
+    col_in_tile = (uint32_t)(16 * t + 4 * j + 2 * (q >> 1) + h);
+}
+// (SRC & MASK) | ACC
+__device__ __forceinline__ uint32_t p6_and_or(uint32_t src, uint32_t mask, uint32_t acc)
+{
+    uint32_t v;
+    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(v) : "r"(src), "r"(mask), "r"(acc));
+    return v;
+}
+__device__ __forceinline__ void p6_mma(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                       uint32_t b1)
+{
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
 
 constexpr int kP6BlockBytes = 768;
 constexpr int kP6Slots = 4;                       // ring slots per warp; blocks are fetched three ahead
@@ -96,8 +126,8 @@ k_p6_plane(const int8_t *__restrict__ codes, uint32_t out_f, uint32_t in_f, uint
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
             uint32_t r, c;
-            p5_elem(lane, p, h, r, c);
-            uint32_t row = R * kP5TileRows + r, col = kbi * kP5TileCols + c;
+            p6_elem(lane, p, h, r, c);
+            uint32_t row = R * kTileRows + r, col = kbi * kTileCols + c;
             int code = (row < out_f && col < in_f) ? (int)codes[(size_t)row * in_f + col] : 0;
             bool out = code > kP6CodeMax || code < kP6CodeMin;
             n_out += out;
@@ -114,7 +144,7 @@ k_p6_plane(const int8_t *__restrict__ codes, uint32_t out_f, uint32_t in_f, uint
 // outlier entries of every block, in (lane, pair, half) order (one warp per block)
 __global__ void __launch_bounds__(256)
 k_p6_esc(const int8_t *__restrict__ codes, uint32_t out_f, uint32_t in_f, uint32_t rt, uint32_t kb,
-         const int32_t *__restrict__ blk_off, const __nv_bfloat16 *__restrict__ scale, uint32_t *esc)
+         const int32_t *__restrict__ blk_off, const __nv_bfloat16 *__restrict__ scale, uint32_t *esc, uint32_t n_esc)
 {
     uint32_t b = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     int lane = threadIdx.x & 31;
@@ -126,8 +156,8 @@ k_p6_esc(const int8_t *__restrict__ codes, uint32_t out_f, uint32_t in_f, uint32
 #pragma unroll
     for (int i = 0; i < 32; ++i) {
         uint32_t r, c;
-        p5_elem(lane, i >> 1, i & 1, r, c);
-        uint32_t row = R * kP5TileRows + r, col = kbi * kP5TileCols + c;
+        p6_elem(lane, i >> 1, i & 1, r, c);
+        uint32_t row = R * kTileRows + r, col = kbi * kTileCols + c;
         code[i] = (row < out_f && col < in_f) ? (int)codes[(size_t)row * in_f + col] : 0;
         n_out += (code[i] > kP6CodeMax || code[i] < kP6CodeMin);
     }
@@ -136,9 +166,10 @@ k_p6_esc(const int8_t *__restrict__ codes, uint32_t out_f, uint32_t in_f, uint32
     for (int i = 0; i < 32; ++i) {
         if (code[i] > kP6CodeMax || code[i] < kP6CodeMin) {
             uint32_t r, c;
-            p5_elem(lane, i >> 1, i & 1, r, c);
+            p6_elem(lane, i >> 1, i & 1, r, c);
             uint32_t wbits = __bfloat16_as_ushort(__float2bfloat16_rn((float)code[i] * sc));
-            esc[at++] = (wbits << 16) | (r << 12) | ((b & 63u) << 6) | c;
+            if (at < n_esc) esc[at] = (wbits << 16) | (r << 12) | ((b & 63u) << 6) | c;   // never beyond the caller's buffer
+            ++at;
         }
     }
 }
@@ -161,7 +192,7 @@ __global__ void __launch_bounds__(256) k_p6_decode_plane(P6 p, void *out)
     const bool vec = (OUT == 0 ? (p.in_f & 15u) == 0 : (p.in_f & 7u) == 0) && ((uintptr_t)out & 15u) == 0;
 #pragma unroll
     for (int s = 0; s < 2; ++s) {                    // row g, row g + 8
-        uint32_t row = R * kP5TileRows + (lane >> 2) + 8 * s, col0 = kbi * kP5TileCols + 16 * (lane & 3);
+        uint32_t row = R * kTileRows + (lane >> 2) + 8 * s, col0 = kbi * kTileCols + 16 * (lane & 3);
         if (row >= p.out_f || col0 >= p.in_f) continue;
         uint32_t r[OUT == 0 ? 4 : 8];
 #pragma unroll
@@ -200,7 +231,7 @@ __global__ void __launch_bounds__(256) k_p6_decode_esc(P6 p, void *out)
     float sc = __bfloat162float(*p.scale);
     for (int32_t j = p.blk_off[b] + lane; j < p.blk_off[b + 1]; j += 32) {
         uint32_t ent = p.esc[j];
-        uint32_t row = R * kP5TileRows + ((ent >> 12) & 15u), col = kbi * kP5TileCols + (ent & 63u);
+        uint32_t row = R * kTileRows + ((ent >> 12) & 15u), col = kbi * kTileCols + (ent & 63u);
         if (row >= p.out_f || col >= p.in_f) continue;
         size_t o = (size_t)row * p.in_f + col;
         __nv_bfloat16 wv = __ushort_as_bfloat16((unsigned short)(ent >> 16));
@@ -258,7 +289,7 @@ __device__ __forceinline__ void p6_store_tile(uint32_t out_f, uint32_t R, int la
     const int g = lane >> 2, t = lane & 3;
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-        uint32_t m = 2u * t + (i & 1), row = R * kP5TileRows + g + 8 * (i >> 1);
+        uint32_t m = 2u * t + (i & 1), row = R * kTileRows + g + 8 * (i >> 1);
         if (m >= m_rows || row >= out_f) continue;
         size_t o = (size_t)m * out_f + row;
         float v = c[i];
@@ -277,7 +308,7 @@ __device__ __forceinline__ void p6_store_pair(uint32_t out_f, uint32_t R, int la
                                               const __nv_bfloat16 *__restrict__ bias, void *y, int y_f32)
 {
     const int g = lane >> 2, t = lane & 3;
-    const uint32_t row = R * kP5TileRows + g + 8 * h;
+    const uint32_t row = R * kTileRows + g + 8 * h;
     if (row >= out_f) return;
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
@@ -323,7 +354,7 @@ __global__ void __launch_bounds__(256) k_p6_decode_bf16(P6 p, __nv_bfloat16 *out
         for (int32_t j = lo + lane; j < hi; j += 32) {
             const uint32_t e = __ldg(p.esc + j);
             // element (row r, column c) of the block sits in lane 4 (r & 7) + (c >> 4), pair 4 ((c >> 2) & 3) +
-            // 2 ((c >> 1) & 1) + (r >> 3), half c & 1 (the inverse of p5_elem)
+            // 2 ((c >> 1) & 1) + (r >> 3), half c & 1 (the inverse of p6_elem)
             const uint32_t r = (e >> 12) & 15u, c = e & 63u;
             const uint32_t ln = 4u * (r & 7u) + (c >> 4), j4 = (c >> 2) & 3u, q = 2u * ((c >> 1) & 1u) + (r >> 3);
             const uint32_t off = ((j4 * 32u + ln) * 4u + q) * 4u + 2u * (c & 1u);
@@ -347,8 +378,8 @@ __global__ void __launch_bounds__(256) k_p6_decode_bf16(P6 p, __nv_bfloat16 *out
     }
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-        uint32_t v = p5_and_or(w[i] >> 10, 0x003C003Cu, e2);
-        v = p5_and_or(w[4 + (i >> 1)] >> (6 + 2 * (i & 1)), 0x00C000C0u, v);
+        uint32_t v = p6_and_or(w[i] >> 10, 0x003C003Cu, e2);
+        v = p6_and_or(w[4 + (i >> 1)] >> (6 + 2 * (i & 1)), 0x00C000C0u, v);
         asm("fma.rn.bf16x2 %0, %1, %2, %3;" : "=r"(f[12 + i]) : "r"(v), "r"(b2), "r"(c2));
     }
 #pragma unroll
@@ -360,10 +391,10 @@ __global__ void __launch_bounds__(256) k_p6_decode_bf16(P6 p, __nv_bfloat16 *out
         f[4 * q + 3] |= v.w;
     }
     // pair 4 j + q: row g + 8 (q & 1), columns 4 j + 2 (q >> 1) + {0, 1} of the lane's 16
-    const uint32_t col0 = kbi * kP5TileCols + 16 * (lane & 3);
+    const uint32_t col0 = kbi * kTileCols + 16 * (lane & 3);
 #pragma unroll
     for (int s = 0; s < 2; ++s) {
-        uint32_t row = R * kP5TileRows + (lane >> 2) + 8 * s;
+        uint32_t row = R * kTileRows + (lane >> 2) + 8 * s;
         if (row >= p.out_f || col0 >= p.in_f) continue;
         __nv_bfloat16 *dst = out + (size_t)row * p.in_f + col0;
         const uint32_t r[8] = {f[0 + s], f[2 + s], f[4 + s], f[6 + s], f[8 + s], f[10 + s], f[12 + s], f[14 + s]};
@@ -383,8 +414,8 @@ __global__ void __launch_bounds__(256) k_p6_decode_bf16(P6 p, __nv_bfloat16 *out
 // tile): the segment's outliers are added first, from the entries staged in shared memory, then its blocks stream
 // through the warp's cp.async ring.  Row tiles that a run covers completely are written straight to y; partial
 // tiles are summed per CTA in warp order; a tile shared between CTAs goes through cta_slots and a ticket, the
-// last arriver sums the slots in CTA order.  tickets[] (gridDim.x + 1 words) must be zero before the first
-// launch and is left zero.  XS = 1: activations staged in shared memory (bf16, padded rows); XS = 0: read from
+// last arriver sums the slots in CTA order and clears them.  tickets[] (gridDim.x + 1 words) and cta_slots must be
+// zero before the first launch and are left zero, so one scratch buffer serves launches of any shape in turn.  XS = 1: activations staged in shared memory (bf16, padded rows); XS = 0: read from
 // global memory.
 
 template <int XS>
@@ -395,7 +426,8 @@ k_p6_mma(P6 p, const __nv_bfloat16 *__restrict__ x, uint32_t m_rows, const __nv_
     extern __shared__ __align__(128) unsigned char p6_smem[];
     __nv_bfloat16 *xs = (__nv_bfloat16 *)(p6_smem + kP6SmemFixed);                       // [m_rows][xstride]
 
-    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int wid = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0);   // the same in every lane, and known to be
     const int g = lane >> 2, t = lane & 3;
     const uint32_t KB = p.kb;
     unsigned char *wsm = p6_smem + wid * kP6WarpSmem;
@@ -466,7 +498,7 @@ k_p6_mma(P6 p, const __nv_bfloat16 *__restrict__ x, uint32_t m_rows, const __nv_
     asm volatile("griddepcontrol.wait;" ::: "memory");
     if (XS) {
         // whole 16-byte chunks by cp.async; ragged ends are written with plain stores
-        const uint32_t chunks = KB * (kP5TileCols / 8);
+        const uint32_t chunks = KB * (kTileCols / 8);
         const uint32_t xs_s = (uint32_t)__cvta_generic_to_shared(xs);
         const bool vec = (p.in_f & 7u) == 0;
         for (uint32_t m = 0; m < m_rows; ++m) {
@@ -560,8 +592,11 @@ k_p6_mma(P6 p, const __nv_bfloat16 *__restrict__ x, uint32_t m_rows, const __nv_
         // every SM shares, so nothing cached on this SM can be stale
         float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
         for (uint32_t cc = clo; cc <= chi; ++cc) {
-            const float4 *sl = cta_slots + ((size_t)cc * 2 + (p6_begin(cc, cq, cr) >= t0 ? 0 : 1)) * 32 + lane;
+            float4 *sl = cta_slots + ((size_t)cc * 2 + (p6_begin(cc, cq, cr) >= t0 ? 0 : 1)) * 32 + lane;
             z.x += __ldcg(&sl->x); z.y += __ldcg(&sl->y); z.z += __ldcg(&sl->z); z.w += __ldcg(&sl->w);
+            // the slot goes back to zero: a later launch of another shape uses the same words for its two-CTA
+            // hand-over, where any non-zero word counts as a deposit
+            __stcg(sl, make_float4(0.f, 0.f, 0.f, 0.f));
         }
         const float cc4[4] = {z.x, z.y, z.z, z.w};
         p6_store_tile(p.out_f, R, lane, cc4, m_rows, bias, y, y_f32);
@@ -599,7 +634,7 @@ k_p6_mma(P6 p, const __nv_bfloat16 *__restrict__ x, uint32_t m_rows, const __nv_
 
         // blocks [b0, b1) of row tile R: fetch block b + 3 into the slot consumed last, take block b from its slot
         auto run = [&](uint32_t b0, uint32_t b1) {
-            uint32_t xo = (b0 - R * KB) * (kP5TileCols * 2u);     // byte offset into the activation row
+            uint32_t xo = (b0 - R * KB) * (kTileCols * 2u);     // byte offset into the activation row
             for (uint32_t n = b1 - b0; n != 0; --n) {
                 const bool more = pf_left != 0;                   // the last three iterations of a run fetch nothing
                 p6_cp16_if(d16 + is, n16, more);
@@ -629,18 +664,18 @@ k_p6_mma(P6 p, const __nv_bfloat16 *__restrict__ x, uint32_t m_rows, const __nv_
                     }
 #pragma unroll
                     for (int i = 0; i < 4; ++i) {
-                        uint32_t v = p5_and_or(w[i] >> 10, 0x003C003Cu, e2);
-                        v = p5_and_or(w[4 + (i >> 1)] >> (6 + 2 * (i & 1)), 0x00C000C0u, v);
+                        uint32_t v = p6_and_or(w[i] >> 10, 0x003C003Cu, e2);
+                        v = p6_and_or(w[4 + (i >> 1)] >> (6 + 2 * (i & 1)), 0x00C000C0u, v);
                         asm("fma.rn.bf16x2 %0, %1, %2, %3;" : "=r"(f[12 + i]) : "r"(v), "r"(b2), "r"(c2));
                     }
                 }
-                p5_mma(c, f[0], f[1], f[2], f[3], x0.x, x0.y);
-                p5_mma(c1, f[4], f[5], f[6], f[7], x0.z, x0.w);
-                p5_mma(c, f[8], f[9], f[10], f[11], x1.x, x1.y);
-                p5_mma(c1, f[12], f[13], f[14], f[15], x1.z, x1.w);
+                p6_mma(c, f[0], f[1], f[2], f[3], x0.x, x0.y);
+                p6_mma(c1, f[4], f[5], f[6], f[7], x0.z, x0.w);
+                p6_mma(c, f[8], f[9], f[10], f[11], x1.x, x1.y);
+                p6_mma(c1, f[12], f[13], f[14], f[15], x1.z, x1.w);
                 is = cs;
                 cs = cs == (uint32_t)(3 * kP6BlockBytes) ? 0u : cs + (uint32_t)kP6BlockBytes;
-                xo += kP5TileCols * 2u;
+                xo += kTileCols * 2u;
             }
         };
 
@@ -649,7 +684,7 @@ k_p6_mma(P6 p, const __nv_bfloat16 *__restrict__ x, uint32_t m_rows, const __nv_
         // lanes in a fixed order and added to the C fragment (row g -> c[0], c[1]; row g + 8 -> c[2], c[3]).
         auto outlier_pass = [&](uint32_t sb, int32_t jlo, int32_t jhi) {
             if (jlo >= jhi) return;                                       // warp uniform
-            const uint32_t s64 = (sb & 63u) << 6, xcol0 = (sb - R * KB) * kP5TileCols;
+            const uint32_t s64 = (sb & 63u) << 6, xcol0 = (sb - R * KB) * kTileCols;
             for (uint32_t m = 0; m < m_rows; ++m) {
                 const __nv_bfloat16 *xm = (XS ? xs + (size_t)m * xstride : x + (size_t)m * p.in_f) + xcol0;
                 for (int32_t j = jlo + lane; j < jhi; j += 32) {

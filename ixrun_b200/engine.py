@@ -36,18 +36,24 @@ class StreamingLinear(nn.Module):
     `_use_fused`, `_split_chunk`, `_y32`).
     """
 
-    def __init__(self, packed, bias=None, resident: str | None = None, keep_streams: bool = True):
+    def __init__(self, packed, bias=None, resident: str | None = None, keep_streams: bool | None = None):
         """`packed`: the reference's packed dict, or a DevicePacked already on the GPU.
 
-        resident: "p6" (default; environment variable IXB200_RESIDENT overrides the default) or "p5" re-lays the
-        codes out at construction as a plane + outlier list and runs inputs of up to 8 rows on it; "streams" keeps
-        to the reference's (3,5,8) streams and the fused kernel that reads them directly.
-        keep_streams=False frees the stream buffers once the P5 layout exists (larger inputs then decode from
-        P5); the reference-named buffers `_b1 .. _l3` are gone in that case."""
+        resident: "p6" (default; environment variable IXB200_RESIDENT overrides the default) re-lays the codes out
+        at construction as a 6-bit plane + outlier tails and runs every input on it (up to 8 rows fused, more rows
+        through its decoder and a dense matmul); "streams" keeps to the reference's (3,5,8) streams and the fused
+        kernel that reads them directly.
+        keep_streams: with resident="p6" the stream buffers are freed once the layout exists (the default), so a
+        deployed layer holds one copy of its weights; keep_streams=True keeps them, and with them the
+        reference-named buffers `_b1 .. _l3`, `_q1/_q2`, `_b1_blk/_b2_blk` that the reference's benchmarks read."""
         super().__init__()
         resident = resident or os.environ.get("IXB200_RESIDENT", "p6")
-        if resident not in ("p5", "p6", "streams"):
-            raise ValueError("resident must be 'p5', 'p6' or 'streams'")
+        if resident not in ("p6", "streams"):
+            raise ValueError("resident must be 'p6' or 'streams'")
+        if keep_streams is None:
+            keep_streams = resident == "streams"
+        if resident == "streams" and not keep_streams:
+            raise ValueError("resident='streams' needs the streams")
         dp = packed if isinstance(packed, DevicePacked) else DevicePacked(packed)
         self.out_features = dp.out_f
         self.in_features = dp.in_f
@@ -56,25 +62,27 @@ class StreamingLinear(nn.Module):
         self.counts = dp.counts
         self.total_bytes = dp.total_bytes
         self._dp = dp
-        for key, val in (("_b1", dp.b1), ("_b2", dp.b2), ("_l1", dp.l1), ("_l2", dp.l2), ("_l3", dp.l3),
-                         ("_scale", dp.scale), ("_b1_blk", dp.blk_q1), ("_b2_blk", dp.blk_q2)):
-            self.register_buffer(key, val, persistent=False)
         self._use_triton = True
-        # the fused kernel handles any in_f that is a multiple of 32
-        self._use_fused = self.in_features % 32 == 0
+        # the fused kernel on the streams handles any in_f that is a multiple of 32
+        self._use_fused = keep_streams and self.in_features % 32 == 0
         self._split_chunk = 0
-        if self._use_fused:
-            split = _pick_split(self.in_features) if self.out_features < self.in_features else 1
-            gran = self.in_features
-            if split > 1:
-                self._split_chunk = self.in_features // split
-                gran = self._split_chunk
-            q1, q2 = dp.prefix_tables(gran, self.N // gran)
-            self.register_buffer("_q1", q1, persistent=False)
-            self.register_buffer("_q2", q2, persistent=False)
+        if keep_streams:
+            for key, val in (("_b1", dp.b1), ("_b2", dp.b2), ("_l1", dp.l1), ("_l2", dp.l2), ("_l3", dp.l3),
+                             ("_b1_blk", dp.blk_q1), ("_b2_blk", dp.blk_q2)):
+                self.register_buffer(key, val, persistent=False)
+            if self._use_fused:
+                split = _pick_split(self.in_features) if self.out_features < self.in_features else 1
+                gran = self.in_features
+                if split > 1:
+                    self._split_chunk = self.in_features // split
+                    gran = self._split_chunk
+                q1, q2 = dp.prefix_tables(gran, self.N // gran)
+                self.register_buffer("_q1", q1, persistent=False)
+                self.register_buffer("_q2", q2, persistent=False)
+        self.register_buffer("_scale", dp.scale, persistent=False)
         self._y32 = None
-        # 9..64 rows: fused decode+GEMM on the tensor cores (needs in_f % 1024 == 0).  Off by default while
-        # decoding into the shared buffer plus a dense matmul is the faster of the two on B200.
+        # 9..64 rows: fused decode+GEMM on the tensor cores straight from the streams (needs them kept and
+        # in_f % 1024 == 0).  Off by default.
         self._use_tc = False
         if bias is not None:
             self.register_buffer("_bias", bias.detach().clone().to(dp.device), persistent=False)
@@ -83,19 +91,13 @@ class StreamingLinear(nn.Module):
             self._bias = None
             self._bias_bf16 = None
         self._w_buf = None
-        self._p5 = None
-        if resident in ("p5", "p6"):            # `_p5` names the resident re-layout, whichever of the two it is
-            if resident == "p5":
-                from .p5 import P5Packed as Resident
-            else:
-                from .p6 import P6Packed as Resident
-            self._p5 = Resident.from_packed(dp)
+        self._res = None                         # the resident re-layout
+        if resident == "p6":
+            from .p6 import P6Packed
+
+            self._res = P6Packed.from_packed(dp)
             if not keep_streams:
-                for key in ("_b1", "_b2", "_l1", "_l2", "_l3", "_b1_blk", "_b2_blk", "_q1", "_q2"):
-                    if hasattr(self, key):
-                        delattr(self, key)
-                self._dp = None
-                self._use_fused = False
+                self._dp = None                  # the streams (and their rank tables) are released with it
 
     @classmethod
     def from_weight(cls, weight: torch.Tensor, bias=None, **kw):
@@ -107,15 +109,15 @@ class StreamingLinear(nn.Module):
     @property
     def resident_bytes(self) -> int:
         """Bytes of weight data this layer keeps on the device."""
-        n = self._p5.resident_bytes if self._p5 is not None else 0
+        n = self._res.resident_bytes if self._res is not None else 0
         if self._dp is not None:
             n += self.total_bytes
         return n
 
     def matvec(self, x, out=None, out_dtype=torch.bfloat16):
         """y[M, out_f] for 1..8 bf16 rows on the resident layout, without bias (used by the runners and bench)."""
-        if self._p5 is not None:
-            return self._p5.gemv(x, out=out, out_dtype=out_dtype)
+        if self._res is not None:
+            return self._res.gemv(x, out=out, out_dtype=out_dtype)
         return self._dp.gemv(x, out=out, out_dtype=out_dtype)
 
     def _set_shared_buf(self, w_buf):
@@ -125,21 +127,21 @@ class StreamingLinear(nn.Module):
         """Decode the packed weight into the shared buffer -> bf16 [out, in]."""
         if self._w_buf is None:
             raise RuntimeError("no decode buffer set (call _set_shared_buf)")
-        src = self._p5 if self._p5 is not None else self._dp       # the P5 decoder is the faster of the two
+        src = self._res if self._res is not None else self._dp       # the decoder of the resident layout is the faster of the two
         return src.decode(out=self._w_buf[: self.N], kind="bf16")
 
     def forward(self, x):
         rows = x.numel() // self.in_features
-        if self._p5 is not None and x.dtype == torch.bfloat16 and 1 <= rows <= FUSED_MAX_ROWS \
+        if self._res is not None and x.dtype == torch.bfloat16 and 1 <= rows <= FUSED_MAX_ROWS \
                 and x.shape[-1] == self.in_features:
-            y = self._p5.gemv(x.reshape(rows, self.in_features), bias=self._bias_bf16)
+            y = self._res.gemv(x.reshape(rows, self.in_features), bias=self._bias_bf16)
             return y.view(x.shape[:-1] + (self.out_features,))
         if self._use_fused and x.dtype == torch.bfloat16 and 1 <= rows <= FUSED_MAX_ROWS \
                 and x.shape[-1] == self.in_features:
             y = self._dp.gemv(x.reshape(rows, self.in_features), bias=self._bias_bf16)
             return y.view(x.shape[:-1] + (self.out_features,))
-        if self._use_tc and x.dtype == torch.bfloat16 and rows <= TC_MAX_ROWS and self.in_features % 1024 == 0 \
-                and x.shape[-1] == self.in_features:
+        if self._use_tc and self._dp is not None and x.dtype == torch.bfloat16 and rows <= TC_MAX_ROWS \
+                and self.in_features % 1024 == 0 and x.shape[-1] == self.in_features:
             y = self._dp.gemm(x.reshape(rows, self.in_features), bias=self._bias_bf16)
             return y.view(x.shape[:-1] + (self.out_features,))
         w = self._decode()
@@ -348,7 +350,7 @@ class Int8XEngine:
             print(f"[engine][streaming] {len(layers)} layers | packed GPU-resident={total_bytes / 1e6:.0f}MB | "
                   f"shared decode buf={shared_mb:.1f}MB", flush=True)
         return {"mode": "streaming", "n_layers": len(layers), "total_bytes": total_bytes,
-                "shared_gpu_MB": shared_mb}
+                "resident_bytes": sum(sl.resident_bytes for _, sl in layers), "shared_gpu_MB": shared_mb}
 
     @staticmethod
     @torch.no_grad()

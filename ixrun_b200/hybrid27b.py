@@ -87,14 +87,10 @@ class Stack:
             if key not in cache:
                 cache[key] = synthetic_packed(r, c, seed=seed * 131 + rank)
             dp = DevicePacked(cache[key], dev)          # separate device copy per layer
-            if layout == "p5":
-                from .p5 import P5Packed
-
-                return P5Packed.from_packed(dp)         # the streams are dropped, the re-layout stays resident
             if layout == "p6":
                 from .p6 import P6Packed
 
-                return P6Packed.from_packed(dp)
+                return P6Packed.from_packed(dp)         # the streams are dropped, the re-layout stays resident
             return dp
 
         self.layers = []
@@ -227,8 +223,8 @@ def main():
     ap.add_argument("--layers", type=int, default=64)
     ap.add_argument("--tokens", type=int, default=16)
     ap.add_argument("--eager", action="store_true")
-    ap.add_argument("--layout", default="p6", choices=["p6", "p5", "streams"],
-                    help="resident weight layout: the P6 or P5 re-layout, or the reference's streams read directly")
+    ap.add_argument("--layout", default="p6", choices=["p6", "streams"],
+                    help="resident weight layout: the P6 re-layout, or the reference's streams read directly")
     ap.add_argument("--nccl", action="store_true",
                     help="several GPUs: sum the partial outputs with eager NCCL all-reduces between per-stretch graphs "
                          "instead of the one-kernel all-reduce over peer memory inside one graph per token")
@@ -246,11 +242,23 @@ def main():
         with _stdout_to_stderr():        # NCCL prints its version line to stdout; stdout is for the one JSON line
             dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=120))
             dist.barrier()
+    rec = measure(world, rank, dev, tokens=args.tokens, nccl=args.nccl, layers=args.layers, layout=args.layout,
+                  eager=args.eager, pdl=not args.no_pdl)
+    if rank == 0:
+        print(json.dumps(rec), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def measure(world: int, rank: int, dev, tokens: int = 16, nccl: bool = False, layers: int = 64, layout: str = "p6",
+            eager: bool = False, pdl: bool = True) -> dict:
+    """Deploy the stack on this rank (the process group, if any, is already up) and time `tokens` decode steps.
+    Every rank must call it; the returned record is the same on every rank (max over ranks)."""
     t0 = time.time()
     with torch.no_grad():
-        st = Stack(args.layers, world, rank, dev, layout=args.layout, nccl=args.nccl)
+        st = Stack(layers, world, rank, dev, layout=layout, nccl=nccl)
         torch.cuda.synchronize()
-        if args.layout == "p6" and not args.no_pdl:
+        if layout == "p6" and pdl:
             from .p6 import set_pdl
 
             set_pdl(True)                               # every layout is complete: GEMVs may overlap their neighbours' tails
@@ -266,7 +274,7 @@ def main():
             if ar_check > 1e-6 or st.ar.timed_out():
                 raise RuntimeError(f"peer all-reduce differs from NCCL: rel {ar_check}, timed out {st.ar.timed_out()}")
         mode = "eager"
-        if not args.eager:
+        if not eager:
             st.capture()
             mode = ("one CUDA graph per token step" if world == 1 else
                     "one CUDA graph per token step, all-reduces as one kernel each over peer memory" if st.ar is not None
@@ -278,28 +286,26 @@ def main():
         torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
-        for _ in range(args.tokens):
+        for _ in range(tokens):
             st.step()
         e1.record()
         torch.cuda.synchronize()
-        ms = e0.elapsed_time(e1) / args.tokens
+        ms = e0.elapsed_time(e1) / tokens
     if world > 1:
         t = torch.tensor([ms], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t.item())
-    if rank == 0:
-        print(json.dumps({
-            "model": f"27B-class hybrid linear stack, {args.layers} layers (3 GDN : 1 attention), hidden {HIDDEN}, ffn {FFN}",
-            "n_gpus": world, "parallelism": f"tp{world}", "mode": mode, "ms_per_token": ms,
-            "all_reduces_per_token": st.n_allreduce if world > 1 else 0,
-            "packed_weights_per_rank": st.n_weights, "packed_GB_per_rank": st.packed_bytes / 1e9,
-            "layout": args.layout, "resident_GB_per_rank": st.resident_bytes / 1e9,
-            "tokens_timed": args.tokens, "setup_s": setup,
-            "peer_allreduce_vs_nccl_rel": ar_check, "peer_allreduce_timed_out": (st.ar.timed_out() if st.ar is not None else None),
-            "note": "packed-weight path only; token mixers are elementwise stand-ins",
-        }), flush=True)
-    if world > 1:
-        dist.destroy_process_group()
+    return {
+        "model": f"27B-class hybrid linear stack, {layers} layers (3 GDN : 1 attention), hidden {HIDDEN}, ffn {FFN}",
+        "n_gpus": world, "parallelism": f"tp{world}", "mode": mode, "ms_per_token": ms,
+        "all_reduces_per_token": st.n_allreduce if world > 1 else 0,
+        "packed_weights_per_rank": st.n_weights, "packed_GB_per_rank": st.packed_bytes / 1e9,
+        "packed_GBps_per_gpu": st.packed_bytes / 1e9 / (ms * 1e-3),
+        "layout": layout, "resident_GB_per_rank": st.resident_bytes / 1e9,
+        "tokens_timed": tokens, "setup_s": setup,
+        "peer_allreduce_vs_nccl_rel": ar_check, "peer_allreduce_timed_out": (st.ar.timed_out() if st.ar is not None else None),
+        "note": "packed-weight path only; token mixers are elementwise stand-ins",
+    }
 
 
 if __name__ == "__main__":

@@ -1,8 +1,7 @@
 """Resident re-layout "P6" of a packed tensor (see ``csrc/ixb_p6.cuh``).
 
-Same role as :mod:`ixrun_b200.p5`: the (3,5,8) streams remain the interchange
-format and ``P6Packed.from_packed`` transcodes them on the GPU, keeping every
-int8 code.  P6 spends 6 plane bits per weight on a field that *is* part of the
+The (3,5,8) streams remain the interchange format; ``P6Packed.from_packed``
+transcodes them on the GPU, keeping every int8 code.  P6 spends 6 plane bits per weight on a field that *is* part of the
 bf16 number ``1 + code/32`` (codes -16..31), so one fused multiply-add per pair
 of weights yields the reference's ``bf16(code * scale)``; every other code goes
 to a short list that the GEMV adds on the CUDA cores.
@@ -16,7 +15,7 @@ import torch
 from . import _lib
 from .packed import DevicePacked
 
-__all__ = ["P6Packed", "set_pdl"]
+__all__ = ["P6Packed", "set_pdl", "GemvScratch"]
 
 
 def set_pdl(on: bool) -> bool:
@@ -31,8 +30,39 @@ CODE_MIN, CODE_MAX = -16, 31     # codes that the plane holds
 SLACK_BLOCKS, SLACK_ENTRIES, BLOCK_BYTES = 5, 64, 768
 
 
+class GemvScratch:
+    """Scratch of the P6 GEMV on one device: zero between launches (every launch leaves it as it found it), so ONE
+    buffer serves every layer that runs on the same stream, whatever its shape.  Launches that may overlap on the
+    GPU (different streams without ordering) need separate instances."""
+
+    MIN_BYTES = 1 << 20
+    _per_device: dict = {}
+
+    def __init__(self, device):
+        self.device = torch.device(device)
+        self.buf = torch.zeros(0, dtype=torch.uint8, device=self.device)
+        self._retired = []      # outgrown buffers stay allocated: a captured CUDA graph may still point at them
+
+    @classmethod
+    def shared(cls, device) -> "GemvScratch":
+        device = torch.device(device)
+        key = (device.type, device.index if device.index is not None else torch.cuda.current_device())
+        s = cls._per_device.get(key)
+        if s is None:
+            s = cls._per_device[key] = cls(device)
+        return s
+
+    def reserve(self, nbytes: int) -> torch.Tensor:
+        if self.buf.numel() < nbytes:
+            if self.buf.numel():
+                self._retired.append(self.buf)
+            self.buf = torch.zeros(max(int(nbytes), self.MIN_BYTES), dtype=torch.uint8, device=self.device)
+        return self.buf
+
+
 class P6Packed:
-    def __init__(self, codes: torch.Tensor, scale: torch.Tensor, out_f: int, in_f: int, total_bytes: int = 0):
+    def __init__(self, codes: torch.Tensor, scale: torch.Tensor, out_f: int, in_f: int, total_bytes: int = 0,
+                 scratch: GemvScratch | None = None):
         """codes: int8 [out_f*in_f] on a CUDA device; scale: bf16 scalar."""
         if not codes.is_cuda or codes.dtype != torch.int8 or codes.numel() != out_f * in_f:
             raise ValueError("P6Packed needs out_f*in_f int8 codes on a CUDA device")
@@ -42,7 +72,7 @@ class P6Packed:
         c = codes.contiguous().reshape(-1)
         n_esc = int(((c < CODE_MIN) | (c > CODE_MAX)).sum().item())
         L = _lib.lib()
-        nb = int(L.ixb_p5_blocks(self.out_f, self.in_f))
+        nb = int(L.ixb_p6_blocks(self.out_f, self.in_f))
         # sizes include the slack that the GEMV's prefetch may read
         self.plane = torch.empty((nb + SLACK_BLOCKS) * BLOCK_BYTES // 4, dtype=torch.int32, device=dev)
         self.blk_off = torch.empty(nb + 1, dtype=torch.int32, device=dev)
@@ -57,14 +87,14 @@ class P6Packed:
         self.struct = _lib.P6Struct(self.plane.data_ptr(), self.blk_off.data_ptr(), self.esc.data_ptr(), n_esc,
                                     self.scale.data_ptr(), self.out_f, self.in_f)
         self.resident_bytes = nb * BLOCK_BYTES + 4 * (nb + 1 + n_esc) + 2
-        self._scratch = {}
+        self.scratch = scratch if scratch is not None else GemvScratch.shared(dev)
 
     @classmethod
-    def from_packed(cls, packed):
+    def from_packed(cls, packed, **kw):
         """From the reference's packed dict or a DevicePacked: decode the streams to codes, re-lay out."""
         dp = packed if isinstance(packed, DevicePacked) else DevicePacked(packed)
         codes = dp.decode(kind="codes").reshape(-1)
-        return cls(codes, dp.scale, dp.out_f, dp.in_f, total_bytes=dp.total_bytes)
+        return cls(codes, dp.scale, dp.out_f, dp.in_f, total_bytes=dp.total_bytes, **kw)
 
     def decode(self, out: torch.Tensor | None = None, kind: str = "bf16") -> torch.Tensor:
         dtype = {"bf16": torch.bfloat16, "codes": torch.int8}[kind]
@@ -93,14 +123,11 @@ class P6Packed:
             raise ValueError("gemv output must be a contiguous bf16/fp32 tensor of M*out_f elements")
         if bias is not None and (bias.dtype != torch.bfloat16 or bias.numel() != self.out_f):
             raise ValueError("bias must be bf16 [out_f]")
-        s = self._scratch.get(m)
-        if s is None:
-            s = torch.zeros(_lib.lib().ixb_p6_gemv_scratch_bytes(self.out_f, self.in_f, m), dtype=torch.uint8,
-                            device=self.device)
-            self._scratch[m] = s
+        L = _lib.lib()
         with torch.cuda.device(self.device):
-            _lib.check(_lib.lib().ixb_p6_gemv(C.byref(self.struct), x2.data_ptr(), m,
-                                              None if bias is None else bias.data_ptr(), out.data_ptr(),
-                                              1 if out.dtype == torch.float32 else 0, s.data_ptr(), s.numel(),
-                                              _lib.stream_ptr(self.device)))
+            s = self.scratch.reserve(L.ixb_p6_gemv_scratch_bytes(self.out_f, self.in_f, m))
+            _lib.check(L.ixb_p6_gemv(C.byref(self.struct), x2.data_ptr(), m,
+                                     None if bias is None else bias.data_ptr(), out.data_ptr(),
+                                     1 if out.dtype == torch.float32 else 0, s.data_ptr(), s.numel(),
+                                     _lib.stream_ptr(self.device)))
         return out

@@ -46,15 +46,23 @@ def test_streaming_linear_single_token(out_f, in_f):
     from ixrun_b200.engine import StreamingLinear
 
     w, p, b, codes = make_layer(out_f, in_f, 0, bias=True)
-    sl = StreamingLinear(p, bias=b)
-    assert sl._use_fused and sl.out_features == out_f and sl.in_features == in_f
-    assert sl._q1.numel() == (out_f * (in_f // sl._split_chunk) if sl._split_chunk else out_f)
     x = torch.randn(1, 1, in_f).bfloat16().cuda()
-    y = sl(x)
-    assert y.shape == (1, 1, out_f) and y.dtype == torch.bfloat16
     ref = torch.from_numpy(oracle_y(codes, p["scale"], x, out_f, in_f)).bfloat16() + b
-    # one bf16 ulp of slack for sums that sit on a rounding boundary
-    assert (y.cpu().float().reshape(-1) - ref.float().reshape(-1)).abs().max() <= 2.0 ** -7 * ref.float().abs().max()
+    # the default keeps one copy of the weights (the resident layout); keep_streams=True keeps the reference's
+    # buffers beside it; resident="streams" runs the fused kernel on the streams themselves
+    for kw in ({}, {"keep_streams": True}, {"resident": "streams"}):
+        sl = StreamingLinear(p, bias=b, **kw)
+        assert sl.out_features == out_f and sl.in_features == in_f
+        if kw:
+            assert sl._use_fused == (in_f % 32 == 0) and sl._b1.is_cuda and sl._l3.is_cuda
+            if sl._use_fused:
+                assert sl._q1.numel() == (out_f * (in_f // sl._split_chunk) if sl._split_chunk else out_f)
+        else:
+            assert not hasattr(sl, "_b1") and sl._dp is None and sl.resident_bytes == sl._res.resident_bytes
+        y = sl(x)
+        assert y.shape == (1, 1, out_f) and y.dtype == torch.bfloat16
+        # one bf16 ulp of slack for sums that sit on a rounding boundary
+        assert (y.cpu().float().reshape(-1) - ref.float().reshape(-1)).abs().max() <= 2.0 ** -7 * ref.float().abs().max()
 
 
 def test_streaming_linear_many_tokens_uses_decode_buffer():
@@ -62,7 +70,7 @@ def test_streaming_linear_many_tokens_uses_decode_buffer():
 
     out_f, in_f = 256, 1024
     w, p, b, codes = make_layer(out_f, in_f, 1, bias=True)
-    sl = StreamingLinear(p, bias=b)
+    sl = StreamingLinear(p, bias=b, keep_streams=True)
     x = torch.randn(2, 16, in_f).bfloat16().cuda()
     with pytest.raises(RuntimeError):
         sl(x)                                  # no shared buffer yet

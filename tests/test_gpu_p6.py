@@ -55,6 +55,27 @@ def test_p6_gemv_matches_oracle(out_f, in_f, m):
     assert torch.equal(p6.gemv(x, out_dtype=torch.float32), y32)
 
 
+def test_p6_one_scratch_buffer_serves_layers_of_any_shape():
+    """Layers whose row tiles are shared by three or more CTAs, by two, and by none run back to back on ONE scratch
+    buffer (the library leaves it all zero after every launch), in both orders, and still match the oracle."""
+    from ixrun_b200.p6 import GemvScratch
+
+    shapes = [(16, 17408), (256, 17408), (5120, 2176), (64, 5120), (16, 17408), (5120, 2176), (300, 512)]
+    scratch = GemvScratch("cuda")
+    cases = []
+    for i, (out_f, in_f) in enumerate(shapes):
+        codes, scale, p6 = make(out_f, in_f, 100 + i)
+        p6.scratch = scratch
+        sc_bits = int(scale.view(torch.int16).item()) & 0xFFFF
+        xb = O.f32_to_bf16_bits(np.random.default_rng(i).standard_normal((1, in_f)).astype(np.float32))
+        cases.append((p6, bits_to_bf16(xb).cuda(), O.gemm_f32(codes, sc_bits, xb, out_f, in_f).astype(np.float64)))
+    for order in (range(len(cases)), reversed(range(len(cases)))):
+        for i in order:
+            p6, x, ref = cases[i]
+            assert rel_err(p6.gemv(x, out_dtype=torch.float32).cpu().numpy(), ref) < 2e-5
+    assert int(scratch.buf.max().item()) == 0       # every launch left the scratch all zero
+
+
 def test_p6_extreme_level_mixes_and_from_packed(golden_dir):
     from ixrun_b200.p6 import P6Packed
 
@@ -85,23 +106,33 @@ def test_p6_extreme_level_mixes_and_from_packed(golden_dir):
     assert rel_err(y, g["y_f32"].astype(np.float64)) < 2e-5
 
 
-@pytest.mark.parametrize("out_f,in_f", [(5120, 17408), (17408, 5120)])
-def test_p6_full_size_agrees_with_the_stream_kernel(out_f, in_f):
-    """Benchmark shapes: the GEMV on the resident layout against the fused kernel on the reference's streams
-    (itself checked against the oracle), the decoded codes against the stream decoder, twice for reproducibility."""
+@pytest.mark.parametrize("out_f,in_f", [(5120, 17408), (17408, 5120), (5120, 5120), (1024, 5120), (2048, 2048)])
+def test_p6_full_size_against_the_oracle(out_f, in_f):
+    """The five benchmark shapes at full size, batch 1: the GEMV on the resident layout against the CPU oracle's
+    fp32-accumulated product of the same codes, the decoded codes against the codes that were packed; twice for
+    reproducibility; 8 rows against the fused kernel on the reference's streams (itself checked against the
+    oracle)."""
     from ixrun_b200.p6 import P6Packed
     from ixrun_b200.packed import DevicePacked
-    from ixrun_b200.synth import synthetic_packed
+    from ixrun_b200.synth import laplace_codes, synthetic_packed
 
     dp = DevicePacked(synthetic_packed(out_f, in_f, seed=3))
+    codes = laplace_codes(out_f, in_f, seed=3)
     p6 = P6Packed.from_packed(dp)
-    assert torch.equal(p6.decode(kind="codes"), dp.decode(kind="codes"))
-    for m in (1, 8):
-        x = torch.randn(m, in_f, device="cuda").bfloat16()
-        ref = dp.gemv(x, out_dtype=torch.float32)
-        y = p6.gemv(x, out_dtype=torch.float32)
-        assert float((y - ref).abs().max() / ref.abs().max()) < 2e-5
-        assert torch.equal(p6.gemv(x, out_dtype=torch.float32), y)
+    got = p6.decode(kind="codes")
+    assert torch.equal(got, dp.decode(kind="codes"))
+    assert np.array_equal(got.cpu().numpy().reshape(-1), codes.reshape(-1))
+    sc_bits = int(dp.scale.view(torch.int16).item()) & 0xFFFF
+    xb = O.f32_to_bf16_bits(np.random.default_rng(7).standard_normal((1, in_f)).astype(np.float32))
+    ref = O.gemm_f32(codes.reshape(-1), sc_bits, xb, out_f, in_f).astype(np.float64)
+    y = p6.gemv(bits_to_bf16(xb).cuda(), out_dtype=torch.float32)
+    assert rel_err(y.cpu().numpy(), ref) < 2e-5
+    assert torch.equal(p6.gemv(bits_to_bf16(xb).cuda(), out_dtype=torch.float32), y)
+    x8 = torch.randn(8, in_f, device="cuda").bfloat16()
+    ref8 = dp.gemv(x8, out_dtype=torch.float32)
+    y8 = p6.gemv(x8, out_dtype=torch.float32)
+    assert float((y8 - ref8).abs().max() / ref8.abs().max()) < 2e-5
+    assert torch.equal(p6.gemv(x8, out_dtype=torch.float32), y8)
     assert p6.resident_bytes < 1.2 * dp.total_bytes
 
 
