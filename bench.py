@@ -265,13 +265,13 @@ def run_gpu(args):
 
     def step(i):
         lay = layers[i % copies]
-        if world > 1:
+        if world > 1 and ar is not None:
+            # the shard GEMV's epilogue stores its partial sums into every rank's buffer; one small kernel adds them
+            ar.finish(lay._res.gemv_push(x, ar), y16)
+        elif world > 1:
             lay.matvec(x, out=y32)
-            if ar is not None:
-                ar(y32, out=y16)
-            else:
-                dist.all_reduce(y32)
-                y16.copy_(y32)
+            dist.all_reduce(y32)
+            y16.copy_(y32)
         else:
             lay.matvec(x, out=y16)
 
@@ -293,7 +293,7 @@ def run_gpu(args):
             y_ref = ref_layer.matvec(x_full.to(dev), out_dtype=torch.float32).cpu()
             tp_check = {"max_rel_err_vs_unsharded": float((y_tp - y_ref).abs().max() / y_ref.abs().max()),
                         "tolerance": "one bf16 rounding of the output (2^-8 relative to the largest element)",
-                        "exchange": "peer all-reduce kernel (ixb_allreduce)" if ar is not None else "NCCL all-reduce"}
+                        "exchange": "peer stores from the GEMV epilogue + finishing kernel" if ar is not None else "NCCL all-reduce"}
             del ref_layer
         barrier()
 
@@ -401,8 +401,7 @@ def run_gpu(args):
             return
         xd = x_host.to(dev, non_blocking=True)
         if world > 1 and ar is not None:
-            layers[i % copies].matvec(xd, out=y32)
-            y_host.copy_(ar(y32, out=y16), non_blocking=True)
+            y_host.copy_(ar.finish(layers[i % copies]._res.gemv_push(xd, ar), y16), non_blocking=True)
         elif world > 1:
             layers[i % copies].matvec(xd, out=y32)
             dist.all_reduce(y32)
@@ -450,7 +449,8 @@ def run_gpu(args):
             "l2": f"timed steps rotate over {copies} device copies of the weights ({copies * resident_bytes / 1e6:.0f} MB per GPU)",
             "parallelism": ("single GPU" if world == 1 else
                             f"tp{world}: column shards of in_f, fp32 partial outputs summed per step by " +
-                            ("one kernel over peer memory (ixb_allreduce)" if ar is not None else "one NCCL all-reduce")),
+                            ("peer stores from the GEMV's epilogue + one finishing kernel (ixb_p6_gemv_push, ixb_allreduce_finish)" if ar is not None
+                             else "one NCCL all-reduce")),
             "timed_with": (f"CUDA events around {replays} replays of one graph of K launches" if graph_used
                            else f"CUDA events around {replays} x K eager steps"),
             "timed_region_ms": ms, "graph_replays": replays,

@@ -213,6 +213,31 @@ int ixb_set_pdl(int on);
 size_t ixb_allreduce_bytes(int world, int64_t n_max);
 int ixb_allreduce(const void *x_device_f32, int64_t n, void *const *peer_buffers, int rank, int world, int64_t n_max,
                   const void *bias_device, void *y_device, int y_is_f32, ixb_stream_t stream);
+/*
+ * The same exchange with the senders' half inside the GEMV (no counterpart in
+ * the reference; it stands where a tensor-parallel ixrun would run a
+ * row-parallel o_proj / down_proj shard followed by its collective,
+ * ixrun/engine.py:135-168 per shard):
+ * ixb_p6_gemv_push: ixb_p6_gemv of a row-parallel shard whose epilogue stores
+ *   every finished output (m_rows * out_f fp32 partial sums, no bias) as a
+ *   marked word into this rank's slot of EVERY rank's all-reduce buffer -- plain
+ *   peer stores, no local y, no second kernel for the sending side.
+ * ixb_allreduce_finish: waits (bounded) for every rank's words of this call in
+ *   this rank's own buffer, adds them in rank order, adds the bias, writes y;
+ *   n = m_rows * out_f of the push before it.  Every rank calls push, then
+ *   finish, in the same order; calls of ixb_allreduce may be mixed in on the
+ *   same buffers.
+ * ixb_allreduce_spin_limit: polls after which a wait of these kernels gives up
+ *   (0 restores the default of 2^22); returns the previous value.  For tests and
+ *   diagnosis: after a wait gave up the error word behind the counters stays set
+ *   and later waits give up after 64 polls, until the buffers are zeroed again
+ *   (with a barrier between the ranks, as before the first call).
+ */
+int ixb_p6_gemv_push(const ixb_p6 *t, const void *x_device, int64_t m_rows, void *const *peer_buffers, int rank,
+                     int world, int64_t n_max, void *scratch_device, size_t scratch_bytes, ixb_stream_t stream);
+int ixb_allreduce_finish(void *const *peer_buffers, int rank, int world, int64_t n, int64_t n_max,
+                         const void *bias_device, void *y_device, int y_is_f32, ixb_stream_t stream);
+uint32_t ixb_allreduce_spin_limit(uint32_t polls);
 
 /*
  * Fused decode + small-M GEMM on the tensor cores (tcgen05, accumulators in

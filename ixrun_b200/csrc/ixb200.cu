@@ -875,7 +875,7 @@ extern "C" int ixb_set_pdl(int on) { return g_p6_pdl.exchange(on ? 1 : 0); }
 
 template <int XS>
 static cudaError_t launch_p6(const P6 &p, const void *x, uint32_t m_rows, const void *bias, void *y, int y_f32,
-                             float4 *slots, uint32_t *tickets, const P6Plan &pl, cudaStream_t st)
+                             float4 *slots, uint32_t *tickets, const P6Plan &pl, const P6Push &push, cudaStream_t st)
 {
     static bool attr_set[64] = {false};
     cudaError_t oe = opt_in_smem(k_p6_mma<XS>, attr_set, 227 * 1024);
@@ -891,40 +891,53 @@ static cudaError_t launch_p6(const P6 &p, const void *x, uint32_t m_rows, const 
     cfg.attrs = attr;
     cfg.numAttrs = g_p6_pdl.load() ? 1 : 0;
     return cudaLaunchKernelEx(&cfg, k_p6_mma<XS>, p, (const __nv_bfloat16 *)x, m_rows, (const __nv_bfloat16 *)bias, y, y_f32,
-                              slots, tickets, pl.nb, pl.xstride, pl.cq, pl.cr, pl.unit);
+                              slots, tickets, pl.nb, pl.xstride, pl.cq, pl.cr, pl.unit, push);
 }
 
-extern "C" int ixb_p6_gemv(const ixb_p6 *t, const void *x, int64_t m_rows, const void *bias, void *y, int y_is_f32,
-                           void *scratch, size_t scratch_bytes, ixb_stream_t stream)
+static int p6_gemv_impl(const ixb_p6 *t, const void *x, int64_t m_rows, const void *bias, void *y, int y_is_f32,
+                        void *scratch, size_t scratch_bytes, const P6Push &push, ixb_stream_t stream)
 {
     P6 p;
     int rc = to_p6(t, &p);
     if (rc) return rc;
-    if (!x || !y || !scratch) return fail(IXB_E_ARG, "NULL pointer argument");
+    if (!x || (!y && !push.world) || !scratch) return fail(IXB_E_ARG, "NULL pointer argument");
     if (m_rows < 1 || m_rows > 8) return fail(IXB_E_UNSUPPORTED, "m_rows=%lld outside 1..8", (long long)m_rows);
     if ((uintptr_t)x & 15u) return fail(IXB_E_ARG, "x is not 16-byte aligned");
     if ((uintptr_t)scratch & 15u) return fail(IXB_E_ARG, "scratch is not 16-byte aligned");
     if (scratch_bytes < ixb_p6_gemv_scratch_bytes(p.out_f, p.in_f, m_rows)) return fail(IXB_E_SCRATCH, "gemv scratch too small");
+    if (push.world && (size_t)m_rows * p.out_f > push.n_max)
+        return fail(IXB_E_ARG, "m_rows * out_f = %lld exceeds the all-reduce buffer's n_max", (long long)(m_rows * p.out_f));
     P6Plan pl = make_p6_plan(p.out_f, p.in_f, (uint32_t)m_rows);
     if (!pl.xs && (p.in_f % kTileCols))
         return fail(IXB_E_UNSUPPORTED, "in_f=%u: activations too large for shared memory need in_f %% 64 == 0", p.in_f);
     uint32_t *tickets = (uint32_t *)scratch;                  // the first 1024 bytes hold the tile tickets (grid + 1 words)
     float4 *slots = (float4 *)((char *)scratch + 1024);
     cudaStream_t st = (cudaStream_t)stream;
-    cudaError_t e = pl.xs ? launch_p6<1>(p, x, (uint32_t)m_rows, bias, y, y_is_f32, slots, tickets, pl, st)
-                          : launch_p6<0>(p, x, (uint32_t)m_rows, bias, y, y_is_f32, slots, tickets, pl, st);
+    cudaError_t e = pl.xs ? launch_p6<1>(p, x, (uint32_t)m_rows, bias, y, y_is_f32, slots, tickets, pl, push, st)
+                          : launch_p6<0>(p, x, (uint32_t)m_rows, bias, y, y_is_f32, slots, tickets, pl, push, st);
     if (e != cudaSuccess) return fail(IXB_E_CUDA, "k_p6_mma launch: %s", cudaGetErrorString(e));
     return launch_check("k_p6_mma");
+}
+
+extern "C" int ixb_p6_gemv(const ixb_p6 *t, const void *x, int64_t m_rows, const void *bias, void *y, int y_is_f32,
+                           void *scratch, size_t scratch_bytes, ixb_stream_t stream)
+{
+    P6Push push = {};
+    return p6_gemv_impl(t, x, m_rows, bias, y, y_is_f32, scratch, scratch_bytes, push, stream);
 }
 
 // ------------------------------------------------------- one-shot all-reduce over peer memory
 extern "C" size_t ixb_allreduce_bytes(int world, int64_t n_max)
 {
     if (world < 1 || world > kArMaxWorld || n_max <= 0 || (n_max & 3)) return 0;
-    // slots, epoch [ctas], one error word; rounded up to 256 bytes
-    size_t b = ar_slots_bytes(world, n_max) + ((size_t)ar_ctas(n_max) + 1) * 4;
+    // slots, call counters, one error word; rounded up to 256 bytes
+    size_t b = ar_slots_bytes(world, n_max) + ((size_t)ar_counters(n_max) + 1) * 4;
     return (b + 255) & ~(size_t)255;
 }
+
+static std::atomic<uint32_t> g_ar_spin_limit{kArSpinLimit};
+
+extern "C" uint32_t ixb_allreduce_spin_limit(uint32_t polls) { return g_ar_spin_limit.exchange(polls ? polls : kArSpinLimit); }
 
 template <int W>
 static cudaError_t launch_ar(const ArPeers &peers, const void *x, int rank, uint32_t n, uint32_t n_max, const void *bias,
@@ -940,7 +953,7 @@ static cudaError_t launch_ar(const ArPeers &peers, const void *x, int rank, uint
     cfg.attrs = attr;
     cfg.numAttrs = g_p6_pdl.load() ? 1 : 0;
     return cudaLaunchKernelEx(&cfg, k_allreduce_oneshot<W>, peers, (const float *)x, rank, n, n_max,
-                              (const __nv_bfloat16 *)bias, y, y_f32, epoch, err);
+                              (const __nv_bfloat16 *)bias, y, y_f32, epoch, err, g_ar_spin_limit.load());
 }
 
 extern "C" int ixb_allreduce(const void *x, int64_t n, void *const *peer_buffers, int rank, int world, int64_t n_max,
@@ -952,7 +965,7 @@ extern "C" int ixb_allreduce(const void *x, int64_t n, void *const *peer_buffers
     if (((uintptr_t)x & 15u) || ((uintptr_t)y & 7u)) return fail(IXB_E_ARG, "x / y are misaligned");
     ArPeers peers;
     const size_t sb = ar_slots_bytes(world, n_max);
-    const uint32_t ctas = ar_ctas(n_max);
+    const uint32_t ctas = ar_counters(n_max);
     for (int r = 0; r < world; ++r) {
         if (!peer_buffers[r] || ((uintptr_t)peer_buffers[r] & 15u)) return fail(IXB_E_ARG, "peer buffer %d is NULL or misaligned", r);
         peers.slots[r] = (uint2 *)peer_buffers[r];
@@ -970,6 +983,78 @@ extern "C" int ixb_allreduce(const void *x, int64_t n, void *const *peer_buffers
     }
     if (e != cudaSuccess) return fail(IXB_E_CUDA, "k_allreduce_oneshot launch: %s", cudaGetErrorString(e));
     return launch_check("k_allreduce_oneshot");
+}
+
+// ---- the same exchange with the senders' half inside the GEMV: ixb_p6_gemv_push + ixb_allreduce_finish
+static int ar_geometry(void *const *peer_buffers, int rank, int world, int64_t n_max, P6Push *push, uint32_t **epoch,
+                       uint32_t **err)
+{
+    if (!peer_buffers) return fail(IXB_E_ARG, "NULL pointer argument");
+    if (world < 1 || world > kArMaxWorld || rank < 0 || rank >= world) return fail(IXB_E_ARG, "bad rank/world");
+    if (world != 1 && world != 2 && world != 4 && world != 8) return fail(IXB_E_UNSUPPORTED, "world=%d: supported sizes are 1, 2, 4, 8", world);
+    if (n_max <= 0 || (n_max & 3)) return fail(IXB_E_ARG, "n_max must be a positive multiple of 4");
+    for (int r = 0; r < world; ++r) {
+        if (!peer_buffers[r] || ((uintptr_t)peer_buffers[r] & 15u)) return fail(IXB_E_ARG, "peer buffer %d is NULL or misaligned", r);
+        push->slots[r] = (uint2 *)peer_buffers[r];
+    }
+    for (int r = world; r < 8; ++r) push->slots[r] = nullptr;
+    *epoch = (uint32_t *)((char *)peer_buffers[rank] + ar_slots_bytes(world, n_max));
+    *err = *epoch + ar_counters(n_max);
+    push->epoch = *epoch;
+    push->world = (uint32_t)world;
+    push->rank = (uint32_t)rank;
+    push->n_max = (uint32_t)n_max;
+    return IXB_OK;
+}
+
+extern "C" int ixb_p6_gemv_push(const ixb_p6 *t, const void *x, int64_t m_rows, void *const *peer_buffers, int rank,
+                                int world, int64_t n_max, void *scratch, size_t scratch_bytes, ixb_stream_t stream)
+{
+    P6Push push;
+    uint32_t *epoch, *err;
+    int rc = ar_geometry(peer_buffers, rank, world, n_max, &push, &epoch, &err);
+    if (rc) return rc;
+    return p6_gemv_impl(t, x, m_rows, nullptr, nullptr, 1, scratch, scratch_bytes, push, stream);
+}
+
+template <int W>
+static cudaError_t launch_ar_finish(const uint2 *mine, uint32_t n, uint32_t n_max, const void *bias, void *y, int y_f32,
+                                    uint32_t *epoch, uint32_t *err, cudaStream_t st)
+{
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(ar_fin_ctas(n_max));
+    cfg.blockDim = dim3(kArFinThreads);
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = g_p6_pdl.load() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, k_allreduce_finish<W>, mine, n, n_max, (const __nv_bfloat16 *)bias, y, y_f32, epoch, err,
+                              g_ar_spin_limit.load());
+}
+
+extern "C" int ixb_allreduce_finish(void *const *peer_buffers, int rank, int world, int64_t n, int64_t n_max,
+                                    const void *bias, void *y, int y_is_f32, ixb_stream_t stream)
+{
+    P6Push push;
+    uint32_t *epoch, *err;
+    int rc = ar_geometry(peer_buffers, rank, world, n_max, &push, &epoch, &err);
+    if (rc) return rc;
+    if (!y) return fail(IXB_E_ARG, "NULL pointer argument");
+    if (n <= 0 || n > n_max || (n & 3)) return fail(IXB_E_ARG, "n must be a multiple of 4 and at most n_max");
+    if ((uintptr_t)y & 7u) return fail(IXB_E_ARG, "y is misaligned");
+    cudaStream_t st = (cudaStream_t)stream;
+    const uint2 *mine = push.slots[rank];
+    cudaError_t e;
+    switch (world) {
+    case 1: e = launch_ar_finish<1>(mine, (uint32_t)n, (uint32_t)n_max, bias, y, y_is_f32, epoch, err, st); break;
+    case 2: e = launch_ar_finish<2>(mine, (uint32_t)n, (uint32_t)n_max, bias, y, y_is_f32, epoch, err, st); break;
+    case 4: e = launch_ar_finish<4>(mine, (uint32_t)n, (uint32_t)n_max, bias, y, y_is_f32, epoch, err, st); break;
+    default: e = launch_ar_finish<8>(mine, (uint32_t)n, (uint32_t)n_max, bias, y, y_is_f32, epoch, err, st); break;
+    }
+    if (e != cudaSuccess) return fail(IXB_E_CUDA, "k_allreduce_finish launch: %s", cudaGetErrorString(e));
+    return launch_check("k_allreduce_finish");
 }
 
 // ------------------------------------------------------- tensor-core small-M GEMM

@@ -2,13 +2,13 @@
 // packed linears (o_proj / down_proj shards): out_f values per token, 20 KB for the 27B hybrid.
 //
 // The reference is single-GPU; its tensor-parallel form needs one sum of out_f values per row-parallel layer.
-// A library all-reduce costs a launch of its own plus its protocol (15 .. 20 us eagerly, and it could not be
-// captured in a CUDA graph on this pool); at this size the transfer itself is a few hundred nanoseconds of
+// A library all-reduce costs a launch of its own plus its protocol (15 .. 20 us when launched eagerly); at this size
+// the transfer itself is a few hundred nanoseconds of
 // NVLink time, so the whole exchange is done by one small kernel with plain peer stores and local loads, and the
 // data carries its own "arrived" mark, so one crossing of NVLink is all the latency there is:
 //
 //   every rank owns one buffer that all ranks can address (peer pointers):
-//     slots  [2 parities][W ranks][n_max] x {fp32 value, uint32 epoch}      epoch [ctas] uint32      error word
+//     slots  [2 parities][W ranks][n_max] x {fp32 value, uint32 epoch}      epoch [counters] uint32      error word
 //   CTA c of rank r, call number e (epoch[c] + 1), parity e & 1:
 //     1. every thread stores its four values as four 8-byte words {value, e} into slot (parity, r) of EVERY
 //        rank's buffer (an aligned 8-byte store arrives whole, so value and mark cannot be seen apart),
@@ -32,6 +32,8 @@ constexpr int kArMaxWorld = 8;
 constexpr int kArThreads = 256;
 constexpr int kArPerCta = kArThreads * 4;                 // fp32 values per CTA
 constexpr uint32_t kArSpinLimit = 1u << 22;               // polls (>= 32 ns each) before a wait gives up
+constexpr int kArFinThreads = 128;
+constexpr int kArFinPerCta = kArFinThreads * 2;           // fp32 values per CTA of the finishing kernel
 
 struct ArPeers {
     uint2 *slots[kArMaxWorld];                            // every rank's slots, as seen from this rank
@@ -39,11 +41,14 @@ struct ArPeers {
 
 __host__ __device__ __forceinline__ size_t ar_slots_bytes(int world, int64_t n_max) { return (size_t)2 * world * n_max * 8; }
 __host__ __device__ __forceinline__ uint32_t ar_ctas(int64_t n_max) { return (uint32_t)((n_max + kArPerCta - 1) / kArPerCta); }
+__host__ __device__ __forceinline__ uint32_t ar_fin_ctas(int64_t n_max) { return (uint32_t)((n_max + kArFinPerCta - 1) / kArFinPerCta); }
+// call counters behind the slots: one per CTA of the kernel with the larger grid; every kernel advances all of them
+__host__ __device__ __forceinline__ uint32_t ar_counters(int64_t n_max) { return ar_fin_ctas(n_max); }
 
 template <int W>
 __global__ void __launch_bounds__(kArThreads)
 k_allreduce_oneshot(ArPeers peers, const float *__restrict__ x, int rank, uint32_t n, uint32_t n_max,
-                    const __nv_bfloat16 *__restrict__ bias, void *y, int y_f32, uint32_t *epoch, uint32_t *err)
+                    const __nv_bfloat16 *__restrict__ bias, void *y, int y_f32, uint32_t *epoch, uint32_t *err, uint32_t spin_limit)
 {
     __shared__ uint32_t e_s;
     const uint32_t c = blockIdx.x, tid = threadIdx.x;
@@ -71,7 +76,7 @@ k_allreduce_oneshot(ArPeers peers, const float *__restrict__ x, int rank, uint32
         }
         // 2. every sender's words in this rank's own buffer, once they carry this call's mark; 3. sum in rank order
         // (once a wait has given up, later calls give up quickly too instead of stalling for the full limit each time)
-        const uint32_t limit = *(volatile uint32_t *)err ? 64u : kArSpinLimit;
+        const uint32_t limit = *(volatile uint32_t *)err ? 64u : spin_limit;
         float o[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
         for (int s = 0; s < W; ++s) {
@@ -101,6 +106,63 @@ k_allreduce_oneshot(ArPeers peers, const float *__restrict__ x, int rank, uint32
                 if (bias) h = __hadd(h, bias[i + k]);
                 ((__nv_bfloat16 *)y)[i + k] = h;
             }
+        }
+    }
+    if (tid == 0)
+        for (uint32_t k = c; k < ar_counters(n_max); k += gridDim.x) epoch[k] = e;     // all counters advance together
+}
+
+// Second half of the exchange when the senders' words come straight from the epilogue of the GEMV before it
+// (k_p6_mma with a P6Push): wait for every rank's words of this call in this rank's own buffer, add them in rank
+// order, add the bias, write y.  Two values per thread, read as one 16-byte load of two marked words; 128 threads per
+// CTA, so a 5120-value vector is finished by 20 CTAs.  Every CTA keeps its own call counter (epoch[c]); the grid is
+// sized by n_max whatever n is, so all counters advance together, and the pushing GEMV of the next call reads
+// epoch[0] + 1 as its mark.  The waits are bounded like k_allreduce_oneshot's.
+template <int W>
+__global__ void __launch_bounds__(kArFinThreads)
+k_allreduce_finish(const uint2 *__restrict__ mine, uint32_t n, uint32_t n_max, const __nv_bfloat16 *__restrict__ bias,
+                   void *y, int y_f32, uint32_t *epoch, uint32_t *err, uint32_t spin_limit)
+{
+    __shared__ uint32_t e_s;
+    const uint32_t c = blockIdx.x, tid = threadIdx.x;
+    asm volatile("griddepcontrol.launch_dependents;");
+    const uint32_t i = (c * kArFinThreads + tid) * 2u;
+    const bool valid = i < n;                              // n is a multiple of 4
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (tid == 0) e_s = epoch[c] + 1u;
+    __syncthreads();
+    const uint32_t e = e_s, par = e & 1u;
+    if (valid) {
+        const uint32_t limit = *(volatile uint32_t *)err ? 64u : spin_limit;
+        float o0 = 0.f, o1 = 0.f;
+#pragma unroll
+        for (int s = 0; s < W; ++s) {
+            const uint2 *src = mine + ((size_t)(par * W + s)) * n_max + i;
+            uint32_t v0, m0, v1, m1, polls = 0;
+            for (;;) {
+                asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v0), "=r"(m0), "=r"(v1), "=r"(m1) : "l"(src) : "memory");
+                if (m0 == e && m1 == e) break;
+                __nanosleep(20);
+                if (++polls > limit) {
+                    *err = 1u + (uint32_t)s;               // sender s never arrived: the result is wrong, not a hang
+                    break;
+                }
+            }
+            o0 += __uint_as_float(v0);
+            o1 += __uint_as_float(v1);
+        }
+        if (y_f32) {
+            float2 r;
+            r.x = bias ? o0 + __bfloat162float(bias[i]) : o0;
+            r.y = bias ? o1 + __bfloat162float(bias[i + 1]) : o1;
+            *(float2 *)((float *)y + i) = r;
+        } else {
+            __nv_bfloat16 h0 = __float2bfloat16_rn(o0), h1 = __float2bfloat16_rn(o1);
+            if (bias) {
+                h0 = __hadd(h0, bias[i]);
+                h1 = __hadd(h1, bias[i + 1]);
+            }
+            *(__nv_bfloat162 *)((__nv_bfloat16 *)y + i) = __halves2bfloat162(h0, h1);
         }
     }
     if (tid == 0) epoch[c] = e;

@@ -283,29 +283,53 @@ __device__ __forceinline__ uint32_t p6_pair(uint32_t t, uint32_t e2, uint32_t b2
     return w;
 }
 
-__device__ __forceinline__ void p6_store_tile(uint32_t out_f, uint32_t R, int lane, const float (&c)[4], uint32_t m_rows,
-                                              const __nv_bfloat16 *__restrict__ bias, void *y, int y_f32)
+// Where the outputs of a row-parallel shard go instead of y: into this rank's slot of EVERY rank's all-reduce buffer
+// (see ixb_allreduce.cuh: slots [2 parities][world][n_max] of {fp32 value, call number} words), as plain peer stores
+// straight from the GEMV's epilogue.  world == 0: no push, the outputs are written to y.
+struct P6Push {
+    uint2 *slots[8];              // every rank's slots, as seen from this rank
+    const uint32_t *epoch;        // this rank's call counter (the all-reduce's finishing kernel advances it)
+    uint32_t world, rank, n_max;
+};
+
+// one output (activation row m, weight row `row`): to y (+ bias), or as a marked word to every rank
+__device__ __forceinline__ void p6_put_out(const P6Push &push, uint32_t e, uint32_t out_f, uint32_t m, uint32_t row, float v,
+                                           const __nv_bfloat16 *__restrict__ bias, void *y, int y_f32)
+{
+    const size_t o = (size_t)m * out_f + row;
+    if (push.world) {
+        const size_t at = ((size_t)((e & 1u) * push.world + push.rank)) * push.n_max + o;
+#pragma unroll
+        for (int r = 0; r < 8; ++r) {
+            if ((uint32_t)r >= push.world) break;
+            asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(push.slots[r] + at), "r"(__float_as_uint(v)), "r"(e) : "memory");
+        }
+    } else if (y_f32) {
+        ((float *)y)[o] = bias ? v + __bfloat162float(bias[row]) : v;
+    } else {
+        __nv_bfloat16 hv = __float2bfloat16_rn(v);
+        if (bias) hv = __hadd(hv, bias[row]);
+        ((__nv_bfloat16 *)y)[o] = hv;
+    }
+}
+
+__device__ __forceinline__ void p6_store_tile(const P6Push &push, uint32_t e, uint32_t out_f, uint32_t R, int lane,
+                                              const float (&c)[4], uint32_t m_rows, const __nv_bfloat16 *__restrict__ bias,
+                                              void *y, int y_f32)
 {
     const int g = lane >> 2, t = lane & 3;
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
         uint32_t m = 2u * t + (i & 1), row = R * kTileRows + g + 8 * (i >> 1);
         if (m >= m_rows || row >= out_f) continue;
-        size_t o = (size_t)m * out_f + row;
-        float v = c[i];
-        if (y_f32) {
-            ((float *)y)[o] = bias ? v + __bfloat162float(bias[row]) : v;
-        } else {
-            __nv_bfloat16 hv = __float2bfloat16_rn(v);
-            if (bias) hv = __hadd(hv, bias[row]);
-            ((__nv_bfloat16 *)y)[o] = hv;
-        }
+        p6_put_out(push, e, out_f, m, row, c[i], bias, y, y_f32);
     }
 }
 
 // one half of a lane's C fragment: row g + 8 h of the tile, activation rows 2 t and 2 t + 1
-__device__ __forceinline__ void p6_store_pair(uint32_t out_f, uint32_t R, int lane, int h, const float (&v)[2], uint32_t m_rows,
-                                              const __nv_bfloat16 *__restrict__ bias, void *y, int y_f32)
+__device__ __forceinline__ void p6_store_pair(const P6Push &push, uint32_t e, uint32_t out_f, uint32_t R, int lane, int h,
+                                              const float (&v)[2], uint32_t m_rows, const __nv_bfloat16 *__restrict__ bias,
+                                              void *y, int y_f32)
 {
     const int g = lane >> 2, t = lane & 3;
     const uint32_t row = R * kTileRows + g + 8 * h;
@@ -314,14 +338,7 @@ __device__ __forceinline__ void p6_store_pair(uint32_t out_f, uint32_t R, int la
     for (int i = 0; i < 2; ++i) {
         const uint32_t m = 2u * t + i;
         if (m >= m_rows) continue;
-        const size_t o = (size_t)m * out_f + row;
-        if (y_f32) {
-            ((float *)y)[o] = bias ? v[i] + __bfloat162float(bias[row]) : v[i];
-        } else {
-            __nv_bfloat16 hv = __float2bfloat16_rn(v[i]);
-            if (bias) hv = __hadd(hv, bias[row]);
-            ((__nv_bfloat16 *)y)[o] = hv;
-        }
+        p6_put_out(push, e, out_f, m, row, v[i], bias, y, y_f32);
     }
 }
 
@@ -421,7 +438,8 @@ __global__ void __launch_bounds__(256) k_p6_decode_bf16(P6 p, __nv_bfloat16 *out
 template <int XS>
 __global__ void __launch_bounds__(kP6Threads, 1)
 k_p6_mma(P6 p, const __nv_bfloat16 *__restrict__ x, uint32_t m_rows, const __nv_bfloat16 *__restrict__ bias, void *y,
-         int y_f32, float4 *cta_slots, uint32_t *tickets, uint32_t nb, uint32_t xstride, uint32_t cq, uint32_t cr, uint32_t unit)
+         int y_f32, float4 *cta_slots, uint32_t *tickets, uint32_t nb, uint32_t xstride, uint32_t cq, uint32_t cr, uint32_t unit,
+         P6Push push)
 {
     extern __shared__ __align__(128) unsigned char p6_smem[];
     __nv_bfloat16 *xs = (__nv_bfloat16 *)(p6_smem + kP6SmemFixed);                       // [m_rows][xstride]
@@ -496,6 +514,9 @@ k_p6_mma(P6 p, const __nv_bfloat16 *__restrict__ x, uint32_t m_rows, const __nv_
         asm volatile("mov.b32 %0, 0x3F003F00;" : "=r"(e2));            // opaque, so that it stays a register operand
     }
     asm volatile("griddepcontrol.wait;" ::: "memory");
+    // a pushing launch marks its words with the number of this all-reduce call: one more than the counter that the
+    // finishing kernel of the call before left (that kernel is complete: it is ahead of this one in the stream)
+    const uint32_t push_e = push.world ? __ldcg(push.epoch) + 1u : 0u;
     if (XS) {
         // whole 16-byte chunks by cp.async; ragged ends are written with plain stores
         const uint32_t chunks = KB * (kTileCols / 8);
@@ -548,7 +569,7 @@ k_p6_mma(P6 p, const __nv_bfloat16 *__restrict__ x, uint32_t m_rows, const __nv_
         }
         if (inside) {
             const float cc[4] = {s.x, s.y, s.z, s.w};
-            p6_store_tile(p.out_f, R, lane, cc, m_rows, bias, y, y_f32);
+            p6_store_tile(push, push_e, p.out_f, R, lane, cc, m_rows, bias, y, y_f32);
             return;
         }
         const uint32_t chi = clo + span;
@@ -575,7 +596,7 @@ k_p6_mma(P6 p, const __nv_bfloat16 *__restrict__ x, uint32_t m_rows, const __nv_
                 const unsigned long long o = got[h] ^ K;
                 const float v[2] = {mine[2 * h] + __uint_as_float((uint32_t)o),
                                     mine[2 * h + 1] + __uint_as_float((uint32_t)(o >> 32))};
-                p6_store_pair(p.out_f, R, lane, h, v, m_rows, bias, y, y_f32);
+                p6_store_pair(push, push_e, p.out_f, R, lane, h, v, m_rows, bias, y, y_f32);
                 w2[h] = 0ull;
             }
             return;
@@ -599,7 +620,7 @@ k_p6_mma(P6 p, const __nv_bfloat16 *__restrict__ x, uint32_t m_rows, const __nv_
             __stcg(sl, make_float4(0.f, 0.f, 0.f, 0.f));
         }
         const float cc4[4] = {z.x, z.y, z.z, z.w};
-        p6_store_tile(p.out_f, R, lane, cc4, m_rows, bias, y, y_f32);
+        p6_store_tile(push, push_e, p.out_f, R, lane, cc4, m_rows, bias, y, y_f32);
         if (lane == 0) tickets[clo + 1] = 0;
     };
     // Fast tail: a warp that leaves a partial row tile behind counts itself in; the warp that completes the count
@@ -746,7 +767,7 @@ k_p6_mma(P6 p, const __nv_bfloat16 *__restrict__ x, uint32_t m_rows, const __nv_
                 c[i] += c1[i];
                 c1[i] = 0.f;
             }
-            if (whole) p6_store_tile(p.out_f, R, lane, c, m_rows, bias, y, y_f32);
+            if (whole) p6_store_tile(push, push_e, p.out_f, R, lane, c, m_rows, bias, y, y_f32);
             else {
                 wparts[(R == R_first ? 0 : 32) + lane] = make_float4(c[0], c[1], c[2], c[3]);
                 if (fast_tail) tile_arrive(R);

@@ -131,3 +131,20 @@ class P6Packed:
                                      1 if out.dtype == torch.float32 else 0, s.data_ptr(), s.numel(),
                                      _lib.stream_ptr(self.device)))
         return out
+
+    def gemv_push(self, x: torch.Tensor, ar) -> int:
+        """Row-parallel shard: y = x @ W.T as fp32 partial sums stored straight into every rank's all-reduce buffer
+        (``ar``: a parallel.PeerAllReduce) from the GEMV's epilogue.  Returns the number of values pushed; follow it
+        with ``ar.finish(n, out, bias)`` on the same stream."""
+        if x.dtype != torch.bfloat16:
+            raise ValueError("activations must be bf16")
+        x2 = x.reshape(-1, self.in_f)
+        if not x2.is_contiguous():
+            x2 = x2.contiguous()
+        m = x2.shape[0]
+        L = _lib.lib()
+        with torch.cuda.device(self.device):
+            s = self.scratch.reserve(L.ixb_p6_gemv_scratch_bytes(self.out_f, self.in_f, m))
+            _lib.check(L.ixb_p6_gemv_push(C.byref(self.struct), x2.data_ptr(), m, ar._ptrs, ar.rank, ar.world, ar.n_max,
+                                          s.data_ptr(), s.numel(), _lib.stream_ptr(self.device)))
+        return m * self.out_f

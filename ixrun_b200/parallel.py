@@ -72,21 +72,34 @@ class ColumnParallelLinear(torch.nn.Module):
 
 
 class RowParallelLinear(torch.nn.Module):
-    """Columns of the layer owned by this rank: fp32 partial sums, one
-    all-reduce, then the bf16 rounding and the (replicated) bias."""
+    """Columns of the layer owned by this rank, on the resident P6 layout.  With a ``PeerAllReduce`` the fp32
+    partial sums leave the GEMV's epilogue as peer stores into every rank's buffer and one small kernel adds them up
+    (+ the replicated bias, after the bf16 rounding as in ixrun/engine.py:166-168); without one (or for more than 8
+    rows) the partial sums go through an NCCL all-reduce."""
 
-    def __init__(self, packed_shard: dict, bias=None, group=None):
+    def __init__(self, packed_shard: dict, bias=None, group=None, allreduce: "PeerAllReduce | None" = None):
         super().__init__()
-        from .packed import DevicePacked
+        from .p6 import P6Packed
 
-        self.dp = DevicePacked(packed_shard)
-        self.out_features, self.in_features = self.dp.out_f, self.dp.in_f
+        self.res = P6Packed.from_packed(packed_shard)
+        self.out_features, self.in_features = self.res.out_f, self.res.in_f
         self.group = group
-        self.bias = None if bias is None else bias.detach().to(self.dp.device, torch.bfloat16)
+        self.ar = allreduce
+        self.bias = None if bias is None else bias.detach().to(self.res.device, torch.bfloat16)
 
     def forward(self, x_shard):
         rows = x_shard.numel() // self.in_features
-        y32 = self.dp.gemv(x_shard.reshape(rows, self.in_features), out_dtype=torch.float32)
+        x2 = x_shard.reshape(rows, self.in_features)
+        if self.ar is not None and rows <= 8:
+            n = self.res.gemv_push(x2, self.ar)
+            y = torch.empty(rows, self.out_features, dtype=torch.bfloat16, device=x2.device)
+            bias = None if self.bias is None else self.bias.expand(rows, -1).contiguous()
+            self.ar.finish(n, y, bias=bias)
+            return y.view(x_shard.shape[:-1] + (self.out_features,))
+        if rows <= 8:
+            y32 = self.res.gemv(x2, out_dtype=torch.float32)
+        else:
+            y32 = torch.nn.functional.linear(x2, self.res.decode(kind="bf16")).float()
         if dist.is_initialized() and dist.get_world_size(self.group) > 1:
             dist.all_reduce(y32, group=self.group)
         y = y32.to(torch.bfloat16)
@@ -100,8 +113,9 @@ class PeerAllReduce:
 
     Every rank allocates one symmetric-memory buffer, exchanges the peer pointers once, and from then on a call is a
     single launch of this library on the current stream: peer stores of the data, every word marked with the call
-    number, a bounded wait for the marks, a local sum in rank order.  It can be captured in a CUDA graph together with the GEMVs around it, which the NCCL
-    all-reduce of this size could not on this pool.  world_size 1 works on one GPU (the buffer is the rank's own).
+    number, a bounded wait for the marks, a local sum in rank order.  It can be captured in a CUDA graph together
+    with the GEMVs around it.  The sending half can also run inside the GEMV (``P6Packed.gemv_push``), followed by
+    ``finish``.  world_size 1 works on one GPU (the buffer is the rank's own).
     """
 
     def __init__(self, n_max: int, device, group=None):
@@ -135,6 +149,33 @@ class PeerAllReduce:
         self._ptrs = (C.c_void_p * self.world)(*ptrs)
         self._nbytes = nbytes
 
+    @classmethod
+    def loopback(cls, n_max: int, device, world: int, rank: int = 0) -> "PeerAllReduce":
+        """One GPU playing rank `rank` of `world`: every peer pointer is this rank's own buffer.  With world > 1 the
+        other ranks never send, so a wait runs out -- the way to exercise the bounded wait and the error word on one
+        GPU (set a short limit with ``set_spin_limit`` first)."""
+        import ctypes as C
+
+        from . import _lib
+
+        self = cls.__new__(cls)
+        self.n_max, self.device, self.world, self.rank = int(n_max), torch.device(device), int(world), int(rank)
+        nbytes = int(_lib.lib().ixb_allreduce_bytes(self.world, self.n_max))
+        if nbytes == 0:
+            raise ValueError(f"unsupported all-reduce geometry: world={world}, n_max={n_max}")
+        self.buf = torch.zeros(nbytes, dtype=torch.uint8, device=self.device)
+        self._ptrs = (C.c_void_p * self.world)(*([self.buf.data_ptr()] * self.world))
+        self._nbytes = nbytes
+        self._loopback = True
+        return self
+
+    @staticmethod
+    def set_spin_limit(polls: int) -> int:
+        """Polls after which a wait gives up (process-wide; 0 restores the default); returns the previous value."""
+        from . import _lib
+
+        return int(_lib.lib().ixb_allreduce_spin_limit(int(polls)))
+
     def __call__(self, x: torch.Tensor, out: torch.Tensor | None = None, bias: torch.Tensor | None = None,
                  out_dtype=torch.bfloat16) -> torch.Tensor:
         from . import _lib
@@ -153,12 +194,37 @@ class PeerAllReduce:
                                                 1 if out.dtype == torch.float32 else 0, _lib.stream_ptr(self.device)))
         return out
 
+    def finish(self, n: int, out: torch.Tensor, bias: torch.Tensor | None = None) -> torch.Tensor:
+        """Second half of the exchange after ``P6Packed.gemv_push``: wait for every rank's `n` marked words of this
+        call, add them in rank order (+ bias), write `out` (bf16 or fp32, n elements)."""
+        from . import _lib
+
+        if n % 4 or n > self.n_max or out.numel() != n or not out.is_contiguous() or out.dtype not in (torch.bfloat16, torch.float32):
+            raise ValueError("finish needs n (a multiple of 4, at most n_max) and a contiguous bf16/fp32 output of n elements")
+        if bias is not None and (bias.dtype != torch.bfloat16 or bias.numel() != n):
+            raise ValueError("bias must be bf16 with one value per element")
+        with torch.cuda.device(self.device):
+            _lib.check(_lib.lib().ixb_allreduce_finish(self._ptrs, self.rank, self.world, n, self.n_max,
+                                                       None if bias is None else bias.data_ptr(), out.data_ptr(),
+                                                       1 if out.dtype == torch.float32 else 0, _lib.stream_ptr(self.device)))
+        return out
+
+    def reset(self, group=None):
+        """After a wait gave up (``timed_out()``): zero this rank's buffer (slots, call counters, error word) and meet
+        the other ranks at a barrier, as before the first call.  Every rank must call it at the same point, with
+        nothing of the exchange in flight."""
+        torch.cuda.synchronize(self.device)
+        self.buf.zero_()
+        torch.cuda.synchronize(self.device)
+        if self.world > 1 and not getattr(self, "_loopback", False):
+            dist.barrier(group)
+
     def timed_out(self) -> bool:
         """True if a wait inside any call so far gave up (the results since then are not to be trusted)."""
         return bool(self._err_word().item() != 0)
 
     def _err_word(self):
-        # layout of the buffer: slots [2][world][n_max] x 8 bytes, epoch [ctas], error word
-        ctas = (self.n_max + 1023) // 1024
-        off = 2 * self.world * self.n_max * 8 + ctas * 4
+        # layout of the buffer: slots [2][world][n_max] x 8 bytes, call counters (one per 256 values), error word
+        counters = (self.n_max + 255) // 256
+        off = 2 * self.world * self.n_max * 8 + counters * 4
         return self.buf[off:off + 4].view(torch.int32)
