@@ -265,8 +265,12 @@ def run_gpu(args):
 
     def step(i):
         lay = layers[i % copies]
-        if world > 1 and ar is not None:
-            # the shard GEMV's epilogue stores its partial sums into every rank's buffer; one small kernel adds them
+        if world > 1 and ar is not None and args.one_kernel:
+            # ONE kernel: the shard GEMV stores its partial sums into every rank's buffer as its tiles finish, then
+            # its warps add up all ranks' words
+            lay._res.gemv_allreduce(x, ar, out=y16)
+        elif world > 1 and ar is not None:
+            # the GEMV's epilogue stores the partial sums into every rank's buffer; a small second kernel adds them
             ar.finish(lay._res.gemv_push(x, ar), y16)
         elif world > 1:
             lay.matvec(x, out=y32)
@@ -361,7 +365,7 @@ def run_gpu(args):
     ms = timed(graph, replays, sampler)
     clocks = sampler.stop()
     total_steps = replays * args.steps
-    launches = total_steps * (2 if ar is not None else 1) if graph is not None else _lib.lib().ixb_launch_count() - launches0
+    launches = total_steps * (2 if ar is not None and (not args.one_kernel) else 1) if graph is not None else _lib.lib().ixb_launch_count() - launches0
     ms_per_step = ms / total_steps
     value = alg_bytes / (ms_per_step * 1e-3) / 1e9
     if clocks.get("sm_mhz"):
@@ -449,7 +453,8 @@ def run_gpu(args):
             "l2": f"timed steps rotate over {copies} device copies of the weights ({copies * resident_bytes / 1e6:.0f} MB per GPU)",
             "parallelism": ("single GPU" if world == 1 else
                             f"tp{world}: column shards of in_f, fp32 partial outputs summed per step by " +
-                            ("peer stores from the GEMV's epilogue + one finishing kernel (ixb_p6_gemv_push, ixb_allreduce_finish)" if ar is not None
+                            (("peer stores from the GEMV's epilogue + one finishing kernel (ixb_p6_gemv_push, ixb_allreduce_finish)" if (not args.one_kernel)
+                              else "the GEMV kernel itself: peer stores from its epilogue, then its warps add all ranks' words (ixb_p6_gemv_allreduce)") if ar is not None
                              else "one NCCL all-reduce")),
             "timed_with": (f"CUDA events around {replays} replays of one graph of K launches" if graph_used
                            else f"CUDA events around {replays} x K eager steps"),
@@ -509,6 +514,9 @@ def main():
                     help="layout p6: launch the GEMVs without programmatic dependent launch")
     ap.add_argument("--layout", default=DEFAULT_LAYOUT, choices=["p6", "streams"],
                     help="resident weight layout: the P6 re-layout, or the reference's streams read directly")
+    ap.add_argument("--one-kernel", action="store_true",
+                    help="several GPUs: finish the exchange inside the GEMV kernel (ixb_p6_gemv_allreduce) instead of in a "
+                         "second small kernel, which measured faster because the next GEMV's prefetch overlaps it")
     ap.add_argument("--no-model", action="store_true", help="skip the model_27b sub-record (27B-class hybrid stack, ms per token)")
     ap.add_argument("--model-tokens", type=int, default=16, help="tokens timed for the model_27b sub-record")
     args = ap.parse_args()

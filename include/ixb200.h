@@ -227,6 +227,13 @@ int ixb_allreduce(const void *x_device_f32, int64_t n, void *const *peer_buffers
  *   n = m_rows * out_f of the push before it.  Every rank calls push, then
  *   finish, in the same order; calls of ixb_allreduce may be mixed in on the
  *   same buffers.
+ * ixb_p6_gemv_allreduce: both halves in ONE kernel.  The GEMV pushes as
+ *   ixb_p6_gemv_push does; every warp that is done with its blocks then takes a
+ *   share of the outputs, waits (bounded) for all ranks' words of this call,
+ *   adds them in rank order (+ bias after the bf16 rounding, as ixb_gemv) and
+ *   writes y: the sum over the ranks of x @ W.T.  The transfer over NVLink
+ *   overlaps the remaining tiles' arithmetic; no second launch.  Needs an even
+ *   out_f.  Calls of all three kinds may be mixed on the same buffers.
  * ixb_allreduce_spin_limit: polls after which a wait of these kernels gives up
  *   (0 restores the default of 2^22); returns the previous value.  For tests and
  *   diagnosis: after a wait gave up the error word behind the counters stays set
@@ -237,6 +244,9 @@ int ixb_p6_gemv_push(const ixb_p6 *t, const void *x_device, int64_t m_rows, void
                      int world, int64_t n_max, void *scratch_device, size_t scratch_bytes, ixb_stream_t stream);
 int ixb_allreduce_finish(void *const *peer_buffers, int rank, int world, int64_t n, int64_t n_max,
                          const void *bias_device, void *y_device, int y_is_f32, ixb_stream_t stream);
+int ixb_p6_gemv_allreduce(const ixb_p6 *t, const void *x_device, int64_t m_rows, void *const *peer_buffers, int rank,
+                          int world, int64_t n_max, const void *bias_device, void *y_device, int y_is_f32,
+                          void *scratch_device, size_t scratch_bytes, ixb_stream_t stream);
 uint32_t ixb_allreduce_spin_limit(uint32_t polls);
 
 /*

@@ -23,7 +23,7 @@ SYMBOLS = (
     "ixb_gemm_scratch_bytes", "ixb_gemm",
     "ixb_pack_workspace_bytes", "ixb_quantize_codes", "ixb_count_codes", "ixb_pack_codes",
     "ixb_p6_blocks", "ixb_p6_build", "ixb_p6_decode", "ixb_p6_gemv_scratch_bytes", "ixb_p6_gemv", "ixb_set_pdl",
-    "ixb_allreduce_bytes", "ixb_allreduce", "ixb_p6_gemv_push", "ixb_allreduce_finish", "ixb_allreduce_spin_limit",
+    "ixb_allreduce_bytes", "ixb_allreduce", "ixb_p6_gemv_push", "ixb_allreduce_finish", "ixb_p6_gemv_allreduce", "ixb_allreduce_spin_limit",
 )
 
 
@@ -110,6 +110,9 @@ def lib():
     L.ixb_allreduce.argtypes = [vp, i64, C.POINTER(C.c_void_p), C.c_int, C.c_int, i64, vp, vp, C.c_int, vp]
     L.ixb_p6_gemv_push.restype = C.c_int
     L.ixb_p6_gemv_push.argtypes = [C.POINTER(P6Struct), vp, i64, C.POINTER(C.c_void_p), C.c_int, C.c_int, i64, vp, sz, vp]
+    L.ixb_p6_gemv_allreduce.restype = C.c_int
+    L.ixb_p6_gemv_allreduce.argtypes = [C.POINTER(P6Struct), vp, i64, C.POINTER(C.c_void_p), C.c_int, C.c_int, i64, vp, vp,
+                                        C.c_int, vp, sz, vp]
     L.ixb_allreduce_finish.restype = C.c_int
     L.ixb_allreduce_finish.argtypes = [C.POINTER(C.c_void_p), C.c_int, C.c_int, i64, i64, vp, vp, C.c_int, vp]
     L.ixb_allreduce_spin_limit.restype = C.c_uint32

@@ -900,7 +900,7 @@ static int p6_gemv_impl(const ixb_p6 *t, const void *x, int64_t m_rows, const vo
     P6 p;
     int rc = to_p6(t, &p);
     if (rc) return rc;
-    if (!x || (!y && !push.world) || !scratch) return fail(IXB_E_ARG, "NULL pointer argument");
+    if (!x || (!y && (!push.world || push.fin)) || !scratch) return fail(IXB_E_ARG, "NULL pointer argument");
     if (m_rows < 1 || m_rows > 8) return fail(IXB_E_UNSUPPORTED, "m_rows=%lld outside 1..8", (long long)m_rows);
     if ((uintptr_t)x & 15u) return fail(IXB_E_ARG, "x is not 16-byte aligned");
     if ((uintptr_t)scratch & 15u) return fail(IXB_E_ARG, "scratch is not 16-byte aligned");
@@ -910,11 +910,15 @@ static int p6_gemv_impl(const ixb_p6 *t, const void *x, int64_t m_rows, const vo
     P6Plan pl = make_p6_plan(p.out_f, p.in_f, (uint32_t)m_rows);
     if (!pl.xs && (p.in_f % kTileCols))
         return fail(IXB_E_UNSUPPORTED, "in_f=%u: activations too large for shared memory need in_f %% 64 == 0", p.in_f);
-    uint32_t *tickets = (uint32_t *)scratch;                  // the first 1024 bytes hold the tile tickets (grid + 1 words)
+    uint32_t *tickets = (uint32_t *)scratch;                  // the first 1024 bytes hold the tile tickets (grid + 1 words) ...
     float4 *slots = (float4 *)((char *)scratch + 1024);
+    P6Push pu = push;
+    pu.done = tickets + 255;                                   // ... and, in the last word, the count of finished warps
+    if (pu.fin && ((p.out_f & 1u) || pl.grid * (uint32_t)kP6Threads * 2u < (uint32_t)m_rows * p.out_f))
+        return fail(IXB_E_UNSUPPORTED, "a finishing GEMV needs an even out_f and at most %u outputs", pl.grid * (uint32_t)kP6Threads * 2u);
     cudaStream_t st = (cudaStream_t)stream;
-    cudaError_t e = pl.xs ? launch_p6<1>(p, x, (uint32_t)m_rows, bias, y, y_is_f32, slots, tickets, pl, push, st)
-                          : launch_p6<0>(p, x, (uint32_t)m_rows, bias, y, y_is_f32, slots, tickets, pl, push, st);
+    cudaError_t e = pl.xs ? launch_p6<1>(p, x, (uint32_t)m_rows, bias, y, y_is_f32, slots, tickets, pl, pu, st)
+                          : launch_p6<0>(p, x, (uint32_t)m_rows, bias, y, y_is_f32, slots, tickets, pl, pu, st);
     if (e != cudaSuccess) return fail(IXB_E_CUDA, "k_p6_mma launch: %s", cudaGetErrorString(e));
     return launch_check("k_p6_mma");
 }
@@ -1001,9 +1005,15 @@ static int ar_geometry(void *const *peer_buffers, int rank, int world, int64_t n
     *epoch = (uint32_t *)((char *)peer_buffers[rank] + ar_slots_bytes(world, n_max));
     *err = *epoch + ar_counters(n_max);
     push->epoch = *epoch;
+    push->mine = push->slots[rank];
     push->world = (uint32_t)world;
     push->rank = (uint32_t)rank;
     push->n_max = (uint32_t)n_max;
+    push->fin = 0;
+    push->counters = ar_counters(n_max);
+    push->spin_limit = g_ar_spin_limit.load();
+    push->err = *err;
+    push->done = nullptr;
     return IXB_OK;
 }
 
@@ -1015,6 +1025,19 @@ extern "C" int ixb_p6_gemv_push(const ixb_p6 *t, const void *x, int64_t m_rows, 
     int rc = ar_geometry(peer_buffers, rank, world, n_max, &push, &epoch, &err);
     if (rc) return rc;
     return p6_gemv_impl(t, x, m_rows, nullptr, nullptr, 1, scratch, scratch_bytes, push, stream);
+}
+
+extern "C" int ixb_p6_gemv_allreduce(const ixb_p6 *t, const void *x, int64_t m_rows, void *const *peer_buffers, int rank,
+                                     int world, int64_t n_max, const void *bias, void *y, int y_is_f32, void *scratch,
+                                     size_t scratch_bytes, ixb_stream_t stream)
+{
+    P6Push push;
+    uint32_t *epoch, *err;
+    int rc = ar_geometry(peer_buffers, rank, world, n_max, &push, &epoch, &err);
+    if (rc) return rc;
+    if (((uintptr_t)y & 7u)) return fail(IXB_E_ARG, "y is misaligned");
+    push.fin = 1;
+    return p6_gemv_impl(t, x, m_rows, bias, y, y_is_f32, scratch, scratch_bytes, push, stream);
 }
 
 template <int W>
@@ -1045,7 +1068,7 @@ extern "C" int ixb_allreduce_finish(void *const *peer_buffers, int rank, int wor
     if (n <= 0 || n > n_max || (n & 3)) return fail(IXB_E_ARG, "n must be a multiple of 4 and at most n_max");
     if ((uintptr_t)y & 7u) return fail(IXB_E_ARG, "y is misaligned");
     cudaStream_t st = (cudaStream_t)stream;
-    const uint2 *mine = push.slots[rank];
+    const uint2 *mine = push.mine;
     cudaError_t e;
     switch (world) {
     case 1: e = launch_ar_finish<1>(mine, (uint32_t)n, (uint32_t)n_max, bias, y, y_is_f32, epoch, err, st); break;

@@ -134,22 +134,32 @@ k_allreduce_finish(const uint2 *__restrict__ mine, uint32_t n, uint32_t n_max, c
     const uint32_t e = e_s, par = e & 1u;
     if (valid) {
         const uint32_t limit = *(volatile uint32_t *)err ? 64u : spin_limit;
+        // all senders' words are requested together and looked at once they are all back: one round trip to L2
+        // per poll, not one per sender
+        uint32_t v0[W], v1[W], m0[W], m1[W];
+        for (uint32_t polls = 0;; ++polls) {
+            bool all = true;
+#pragma unroll
+            for (int s = 0; s < W; ++s) {
+                const uint2 *src = mine + ((size_t)(par * W + s)) * n_max + i;
+                asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v0[s]), "=r"(m0[s]), "=r"(v1[s]), "=r"(m1[s]) : "l"(src) : "memory");
+            }
+#pragma unroll
+            for (int s = 0; s < W; ++s) all = all && m0[s] == e && m1[s] == e;
+            if (all) break;
+            if (polls > limit) {
+#pragma unroll
+                for (int s = 0; s < W; ++s)
+                    if (m0[s] != e || m1[s] != e) *err = 1u + (uint32_t)s;      // sender s never arrived: the result is wrong, not a hang
+                break;
+            }
+            __nanosleep(20);
+        }
         float o0 = 0.f, o1 = 0.f;
 #pragma unroll
-        for (int s = 0; s < W; ++s) {
-            const uint2 *src = mine + ((size_t)(par * W + s)) * n_max + i;
-            uint32_t v0, m0, v1, m1, polls = 0;
-            for (;;) {
-                asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v0), "=r"(m0), "=r"(v1), "=r"(m1) : "l"(src) : "memory");
-                if (m0 == e && m1 == e) break;
-                __nanosleep(20);
-                if (++polls > limit) {
-                    *err = 1u + (uint32_t)s;               // sender s never arrived: the result is wrong, not a hang
-                    break;
-                }
-            }
-            o0 += __uint_as_float(v0);
-            o1 += __uint_as_float(v1);
+        for (int s = 0; s < W; ++s) {                      // in rank order: the same bits on every rank
+            o0 += __uint_as_float(v0[s]);
+            o1 += __uint_as_float(v1[s]);
         }
         if (y_f32) {
             float2 r;

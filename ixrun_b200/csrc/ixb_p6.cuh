@@ -288,8 +288,15 @@ __device__ __forceinline__ uint32_t p6_pair(uint32_t t, uint32_t e2, uint32_t b2
 // straight from the GEMV's epilogue.  world == 0: no push, the outputs are written to y.
 struct P6Push {
     uint2 *slots[8];              // every rank's slots, as seen from this rank
-    const uint32_t *epoch;        // this rank's call counter (the all-reduce's finishing kernel advances it)
+    const uint2 *mine;            // this rank's own slots (slots[rank])
+    uint32_t *epoch;              // this rank's call counters (whoever finishes the exchange advances them)
     uint32_t world, rank, n_max;
+    // fin != 0: the GEMV also finishes the exchange itself.  When a warp is done with its blocks it takes its share
+    // of the outputs, waits (bounded) for every rank's words of this call in this rank's own buffer, adds them in
+    // rank order (+ bias) and writes y; the last warp of the grid to get there advances the call counters.
+    uint32_t fin, counters, spin_limit;
+    uint32_t *err;                // the buffer's error word
+    uint32_t *done;               // scratch word counting finished warps, zero between launches
 };
 
 // one output (activation row m, weight row `row`): to y (+ bias), or as a marked word to every rank
@@ -779,12 +786,11 @@ k_p6_mma(P6 p, const __nv_bfloat16 *__restrict__ x, uint32_t m_rows, const __nv_
         }
     }
     cp_async_wait<0>();
-    if (fast_tail) return;
-    __syncthreads();
+    if (!fast_tail) __syncthreads();
 
     // ---- more row tiles per CTA than the fast tail tracks: after a CTA-wide barrier, sum the parts of every tile
     // that more than one run of this CTA (or another CTA) touched
-    if (L) {
+    if (!fast_tail && L) {
         for (uint32_t R = Rc0 + wid; R <= Rc1; R += kP6Warps) {
             const uint32_t t0 = R * KB, t1 = t0 + KB;                   // the tile's blocks
             const bool inside = t0 >= cb0 && t1 <= cb1;
@@ -796,6 +802,57 @@ k_p6_mma(P6 p, const __nv_bfloat16 *__restrict__ x, uint32_t m_rows, const __nv_
                 span = p6_part_of(t1 - 1u, cq, cr) - clo;
             }
             finish_tile(R, wlo, whi, inside, clo, span);
+        }
+    }
+    if (!push.fin) return;
+
+    // ---- the exchange's second half, by the same kernel: every thread of the grid looks after one pair of outputs
+    // (the first n / 2 threads have one).  The words of this rank come from this very launch -- from CTAs that are
+    // all resident, one per SM -- and the other ranks' from their launches of the same call.
+    {
+        const uint32_t n = m_rows * p.out_f, i = (blockIdx.x * kP6Threads + threadIdx.x) * 2u, W = push.world;
+        if (i < n) {
+            const uint32_t limit = *(volatile uint32_t *)push.err ? 64u : push.spin_limit;
+            const uint2 *mine = push.mine;
+            float o0 = 0.f, o1 = 0.f;
+            for (uint32_t s = 0; s < W; ++s) {
+                const uint2 *src = mine + ((size_t)((push_e & 1u) * W + s)) * push.n_max + i;
+                uint32_t v0, m0, v1, m1, polls = 0;
+                for (;;) {
+                    asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v0), "=r"(m0), "=r"(v1), "=r"(m1) : "l"(src) : "memory");
+                    if (m0 == push_e && m1 == push_e) break;
+                    __nanosleep(20);
+                    if (++polls > limit) {
+                        *push.err = 1u + s;                // sender s never arrived: the result is wrong, not a hang
+                        break;
+                    }
+                }
+                o0 += __uint_as_float(v0);
+                o1 += __uint_as_float(v1);
+            }
+            const uint32_t r0 = i % p.out_f;               // n is even and so is out_f: both values belong to one activation row
+            if (y_f32) {
+                float2 r;
+                r.x = bias ? o0 + __bfloat162float(bias[r0]) : o0;
+                r.y = bias ? o1 + __bfloat162float(bias[r0 + 1]) : o1;
+                *(float2 *)((float *)y + i) = r;
+            } else {
+                __nv_bfloat16 h0 = __float2bfloat16_rn(o0), h1 = __float2bfloat16_rn(o1);
+                if (bias) {
+                    h0 = __hadd(h0, bias[r0]);
+                    h1 = __hadd(h1, bias[r0 + 1]);
+                }
+                *(__nv_bfloat162 *)((__nv_bfloat16 *)y + i) = __halves2bfloat162(h0, h1);
+            }
+        }
+        // the last warp of the grid to get here advances the call counters: by now every CTA has read them
+        __syncwarp();
+        if (lane == 0) {
+            __threadfence();
+            if (atomicAdd(push.done, 1u) == gridDim.x * kP6Warps - 1u) {
+                for (uint32_t k = 0; k < push.counters; ++k) push.epoch[k] = push_e;
+                *push.done = 0;
+            }
         }
     }
 }

@@ -148,3 +148,28 @@ class P6Packed:
             _lib.check(L.ixb_p6_gemv_push(C.byref(self.struct), x2.data_ptr(), m, ar._ptrs, ar.rank, ar.world, ar.n_max,
                                           s.data_ptr(), s.numel(), _lib.stream_ptr(self.device)))
         return m * self.out_f
+
+    def gemv_allreduce(self, x: torch.Tensor, ar, out: torch.Tensor | None = None, bias: torch.Tensor | None = None,
+                       out_dtype=torch.bfloat16) -> torch.Tensor:
+        """Row-parallel shard, ONE kernel: y = sum over the ranks of x @ W.T (+ bias).  The GEMV stores its partial
+        sums into every rank's all-reduce buffer as its tiles finish, and its warps then add up all ranks' words."""
+        if x.dtype != torch.bfloat16:
+            raise ValueError("activations must be bf16")
+        x2 = x.reshape(-1, self.in_f)
+        if not x2.is_contiguous():
+            x2 = x2.contiguous()
+        m = x2.shape[0]
+        if out is None:
+            out = torch.empty(m, self.out_f, dtype=out_dtype, device=self.device)
+        elif out.dtype not in (torch.bfloat16, torch.float32) or out.numel() != m * self.out_f or not out.is_contiguous():
+            raise ValueError("output must be a contiguous bf16/fp32 tensor of M*out_f elements")
+        if bias is not None and (bias.dtype != torch.bfloat16 or bias.numel() != self.out_f):
+            raise ValueError("bias must be bf16 [out_f]")
+        L = _lib.lib()
+        with torch.cuda.device(self.device):
+            s = self.scratch.reserve(L.ixb_p6_gemv_scratch_bytes(self.out_f, self.in_f, m))
+            _lib.check(L.ixb_p6_gemv_allreduce(C.byref(self.struct), x2.data_ptr(), m, ar._ptrs, ar.rank, ar.world, ar.n_max,
+                                               None if bias is None else bias.data_ptr(), out.data_ptr(),
+                                               1 if out.dtype == torch.float32 else 0, s.data_ptr(), s.numel(),
+                                               _lib.stream_ptr(self.device)))
+        return out

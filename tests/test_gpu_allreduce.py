@@ -81,6 +81,9 @@ def test_gemv_push_then_finish_equals_the_plain_gemv(out_f, in_f, m):
         assert torch.equal(ar.finish(n, y32), ref)
         p6.gemv_push(x, ar)
         assert torch.equal(ar.finish(n, y16, bias=bias), ref.bfloat16() + bias)
+        # both halves in one kernel
+        assert torch.equal(p6.gemv_allreduce(x, ar, out_dtype=torch.float32), ref)
+        assert torch.equal(p6.gemv_allreduce(x, ar, bias=bias[0].contiguous()), ref.bfloat16() + bias[0])
         v = torch.randn(1, 1024, device="cuda")
         assert torch.equal(ar(v, out_dtype=torch.float32), v)          # a plain call in between keeps the counters in step
     x = torch.randn(m, in_f, device="cuda").bfloat16()
@@ -93,6 +96,7 @@ def test_gemv_push_then_finish_equals_the_plain_gemv(out_f, in_f, m):
             for _ in range(3):
                 p6.gemv_push(x, ar)
                 ar.finish(n, y32)
+                p6.gemv_allreduce(x, ar, out=y32)
     for i in range(3):
         x.copy_(torch.randn(m, in_f, device="cuda").bfloat16())
         y32.zero_()
@@ -127,6 +131,9 @@ def test_a_wait_that_runs_out_sets_the_error_word_and_returns():
         assert ar2.timed_out()
         ar2.reset()
         assert not ar2.timed_out()
+        p6.gemv_allreduce(torch.randn(1, 2176, device="cuda").bfloat16(), ar2, out_dtype=torch.float32)
+        torch.cuda.synchronize()
+        assert ar2.timed_out()                          # ... and so does the one-kernel form's
     finally:
         PeerAllReduce.set_spin_limit(prev)
     # a single rank is unaffected
