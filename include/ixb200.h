@@ -250,6 +250,56 @@ int ixb_p6_gemv_allreduce(const ixb_p6 *t, const void *x_device, int64_t m_rows,
 uint32_t ixb_allreduce_spin_limit(uint32_t polls);
 
 /*
+ * Per-token glue of a decode step around the packed linears (batch 1, up to a
+ * few rows).  The reference leaves this work to HuggingFace eager code and to
+ * fla's Triton kernels (ixrun/fla_patch.py:23-72); here each is one launch that
+ * can sit in a captured CUDA graph (positions are read from device memory) and
+ * takes part in programmatic dependent launch (ixb_set_pdl).  bf16 in and out,
+ * fp32 arithmetic, rounded to bf16 where the eager path holds a bf16 tensor.
+ * ixb_add_rmsnorm: h[rows, hidden] += delta (may be NULL); xn = bf16(h * rsqrt(
+ *   mean(h^2) + eps)) * w -- the residual add and the norm in front of the next
+ *   linears (HF LlamaRMSNorm arithmetic).
+ * ixb_swiglu: y = silu(g) * u, n elements.
+ * ixb_rope_kv: optional per-head RMSNorm of q and k (weights [head_dim] or
+ *   NULL), rotate-half rotary embedding of the first rot_dim dimensions with
+ *   the caller's fp32 tables cos / sin [max_seq][rot_dim / 2]; q [rows] (row
+ *   stride q_stride elements, heads contiguous) rotated in place, k and v
+ *   [rows][hkv][head_dim] written into the caches [max_seq][hkv][head_dim] at
+ *   positions pos[0] + row.  head_dim 128 or 256.
+ * ixb_attn_decode: one query per head (q [hq][head_dim]) over positions
+ *   0 .. pos[0] of the static caches, grouped-query (hq a multiple of hkv),
+ *   softmax(scale * q.k) v, the context cut into `splits` ranges that run on
+ *   separate CTAs; optional output gate: out *= sigmoid(gate[head * gate_stride
+ *   + d]).  scratch: ixb_attn_scratch_bytes.
+ * ixb_conv_update: causal depth-wise conv1d step: y_c = silu(sum_j w[c][j] *
+ *   input_{t-k+1+j} + bias_c) over the last k inputs of every channel; state
+ *   [channels][k - 1] (oldest first) takes x in.
+ * ixb_gdn_step: gated delta rule, one recurrent step (the published Gated
+ *   DeltaNet recurrence that fla's fused_recurrent_gated_delta_rule computes):
+ *   qkv = [q (hk * 128) | k (hk * 128) | v (hv * 128)], q and k L2-normalised
+ *   per head, q scaled by 128^-0.5; per value head g = exp(-exp(A_log) *
+ *   softplus(a + dt_bias)), beta = sigmoid(b); S <- g S; delta = (v - S^T k)
+ *   beta; S <- S + k delta^T; o = S^T q; out = rmsnorm(o) * norm_w * silu(z).
+ *   state: fp32 [hv][128][128], updated in place (read once, written once).
+ */
+int ixb_add_rmsnorm(void *h_device, const void *delta_device, const void *w_device, float eps, void *xn_device,
+                    int64_t rows, int64_t hidden, ixb_stream_t stream);
+int ixb_swiglu(const void *g_device, const void *u_device, void *y_device, int64_t n, ixb_stream_t stream);
+int ixb_rope_kv(void *q_device, const void *k_device, const void *v_device, const int32_t *pos_device, void *k_cache_device,
+                void *v_cache_device, const void *q_norm_device, const void *k_norm_device, const float *cos_device,
+                const float *sin_device, int64_t rows, int64_t hq, int64_t hkv, int64_t head_dim, int64_t rot_dim, float eps,
+                int64_t q_stride, int64_t max_seq, ixb_stream_t stream);
+size_t ixb_attn_scratch_bytes(int64_t hq, int64_t head_dim, int64_t splits);
+int ixb_attn_decode(const void *q_device, const void *k_cache_device, const void *v_cache_device, const int32_t *pos_device,
+                    const void *gate_device, int64_t gate_stride, void *out_device, void *scratch_device, size_t scratch_bytes,
+                    int64_t hq, int64_t hkv, int64_t head_dim, int64_t splits, float scale, ixb_stream_t stream);
+int ixb_conv_update(const void *x_device, void *state_device, const void *w_device, const void *bias_device, void *y_device,
+                    int64_t channels, int64_t k, ixb_stream_t stream);
+int ixb_gdn_step(const void *qkv_device, const void *z_device, const void *a_device, const void *b_device,
+                 const float *A_log_device, const float *dt_bias_device, const void *norm_w_device, float *state_device,
+                 void *out_device, int64_t hk, int64_t hv, float eps, ixb_stream_t stream);
+
+/*
  * Fused decode + small-M GEMM on the tensor cores (tcgen05, accumulators in
  * TMEM) for 1 <= m_rows <= 64; intended for 9..64 rows (batched decode, MTP
  * verify), below that ixb_gemv is the better call.  Same result definition and

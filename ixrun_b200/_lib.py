@@ -117,6 +117,21 @@ def lib():
     L.ixb_allreduce_finish.argtypes = [C.POINTER(C.c_void_p), C.c_int, C.c_int, i64, i64, vp, vp, C.c_int, vp]
     L.ixb_allreduce_spin_limit.restype = C.c_uint32
     L.ixb_allreduce_spin_limit.argtypes = [C.c_uint32]
+    f32 = C.c_float
+    L.ixb_add_rmsnorm.restype = C.c_int
+    L.ixb_add_rmsnorm.argtypes = [vp, vp, vp, f32, vp, i64, i64, vp]
+    L.ixb_swiglu.restype = C.c_int
+    L.ixb_swiglu.argtypes = [vp, vp, vp, i64, vp]
+    L.ixb_rope_kv.restype = C.c_int
+    L.ixb_rope_kv.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i64, i64, i64, i64, i64, f32, i64, i64, vp]
+    L.ixb_attn_scratch_bytes.restype = sz
+    L.ixb_attn_scratch_bytes.argtypes = [i64, i64, i64]
+    L.ixb_attn_decode.restype = C.c_int
+    L.ixb_attn_decode.argtypes = [vp, vp, vp, vp, vp, i64, vp, vp, sz, i64, i64, i64, i64, f32, vp]
+    L.ixb_conv_update.restype = C.c_int
+    L.ixb_conv_update.argtypes = [vp, vp, vp, vp, vp, i64, i64, vp]
+    L.ixb_gdn_step.restype = C.c_int
+    L.ixb_gdn_step.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, vp, i64, i64, f32, vp]
     L.ixb_gemv_static.restype = C.c_int
     L.ixb_gemv_static.argtypes = [C.POINTER(Packed), vp, vp, vp, i64, vp, vp, C.c_int, vp]
     _lib = L

@@ -7,6 +7,7 @@
 #include "ixb_pack.cuh"
 #include "ixb_p6.cuh"
 #include "ixb_allreduce.cuh"
+#include "ixb_glue.cuh"
 
 #include <atomic>
 #include <cstdarg>
@@ -1078,6 +1079,121 @@ extern "C" int ixb_allreduce_finish(void *const *peer_buffers, int rank, int wor
     }
     if (e != cudaSuccess) return fail(IXB_E_CUDA, "k_allreduce_finish launch: %s", cudaGetErrorString(e));
     return launch_check("k_allreduce_finish");
+}
+
+// ------------------------------------------------------- per-token glue kernels
+// one launch with the programmatic-stream-serialization attribute when ixb_set_pdl is on
+template <class... KArgs, class... Args>
+static cudaError_t launch_glue(void (*kernel)(KArgs...), dim3 grid, dim3 block, cudaStream_t st, Args... args)
+{
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = g_p6_pdl.load() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+#define IXB_GLUE(what, call)                                                                    \
+    do {                                                                                      \
+        cudaError_t e_ = (call);                                                              \
+        if (e_ != cudaSuccess) return fail(IXB_E_CUDA, "%s launch: %s", what, cudaGetErrorString(e_)); \
+        return launch_check(what);                                                            \
+    } while (0)
+
+extern "C" int ixb_add_rmsnorm(void *h, const void *delta, const void *w, float eps, void *xn, int64_t rows,
+                               int64_t hidden, ixb_stream_t stream)
+{
+    if (!h || !w || !xn) return fail(IXB_E_ARG, "NULL pointer argument");
+    if (rows <= 0 || hidden <= 0 || rows > 65535) return fail(IXB_E_ARG, "bad shape");
+    IXB_GLUE("k_add_rmsnorm", launch_glue(k_add_rmsnorm, dim3((unsigned)rows), dim3(hidden >= 4096 ? 1024 : 256), (cudaStream_t)stream,
+                                          (__nv_bfloat16 *)h, (const __nv_bfloat16 *)delta, (const __nv_bfloat16 *)w, eps,
+                                          (__nv_bfloat16 *)xn, (uint32_t)hidden));
+}
+
+extern "C" int ixb_swiglu(const void *g, const void *u, void *y, int64_t n, ixb_stream_t stream)
+{
+    if (!g || !u || !y) return fail(IXB_E_ARG, "NULL pointer argument");
+    if (n <= 0 || n > 0x7fffffffLL) return fail(IXB_E_ARG, "bad size");
+    IXB_GLUE("k_swiglu", launch_glue(k_swiglu, dim3((unsigned)((n + 255) / 256)), dim3(256), (cudaStream_t)stream,
+                                     (const __nv_bfloat16 *)g, (const __nv_bfloat16 *)u, (__nv_bfloat16 *)y, (uint32_t)n));
+}
+
+extern "C" int ixb_rope_kv(void *q, const void *k, const void *v, const int32_t *pos, void *k_cache, void *v_cache,
+                           const void *q_norm, const void *k_norm, const float *cos_tab, const float *sin_tab, int64_t rows,
+                           int64_t hq, int64_t hkv, int64_t head_dim, int64_t rot_dim, float eps, int64_t q_stride,
+                           int64_t max_seq, ixb_stream_t stream)
+{
+    if (!q || !k || !v || !pos || !k_cache || !v_cache || !cos_tab || !sin_tab) return fail(IXB_E_ARG, "NULL pointer argument");
+    if (rows <= 0 || hq <= 0 || hkv <= 0 || max_seq <= 0) return fail(IXB_E_ARG, "bad shape");
+    if (head_dim != 64 && head_dim != 128 && head_dim != 256) return fail(IXB_E_UNSUPPORTED, "head_dim=%lld: 64, 128 or 256", (long long)head_dim);
+    if (rot_dim <= 0 || rot_dim > head_dim || (rot_dim & 1)) return fail(IXB_E_ARG, "rot_dim must be even and at most head_dim");
+    IXB_GLUE("k_rope_kv", launch_glue(k_rope_kv, dim3((unsigned)rows, (unsigned)(hq + hkv)), dim3((unsigned)(head_dim / 2)), (cudaStream_t)stream,
+                                      (__nv_bfloat16 *)q, (const __nv_bfloat16 *)k, (const __nv_bfloat16 *)v, pos,
+                                      (__nv_bfloat16 *)k_cache, (__nv_bfloat16 *)v_cache, (const __nv_bfloat16 *)q_norm,
+                                      (const __nv_bfloat16 *)k_norm, cos_tab, sin_tab, (uint32_t)hq, (uint32_t)hkv,
+                                      (uint32_t)head_dim, (uint32_t)rot_dim, eps, (uint32_t)q_stride, (uint32_t)max_seq));
+}
+
+extern "C" size_t ixb_attn_scratch_bytes(int64_t hq, int64_t head_dim, int64_t splits)
+{
+    if (hq <= 0 || head_dim <= 0 || splits <= 0) return 0;
+    return (size_t)hq * (size_t)splits * (size_t)(head_dim + 2) * sizeof(float);
+}
+
+extern "C" int ixb_attn_decode(const void *q, const void *k_cache, const void *v_cache, const int32_t *pos, const void *gate,
+                               int64_t gate_stride, void *out, void *scratch, size_t scratch_bytes, int64_t hq, int64_t hkv,
+                               int64_t head_dim, int64_t splits, float scale, ixb_stream_t stream)
+{
+    if (!q || !k_cache || !v_cache || !pos || !out || !scratch) return fail(IXB_E_ARG, "NULL pointer argument");
+    if (hq <= 0 || hkv <= 0 || hq % hkv || splits <= 0 || splits > 1024) return fail(IXB_E_ARG, "bad shape");
+    if (head_dim != 64 && head_dim != 128 && head_dim != 256) return fail(IXB_E_UNSUPPORTED, "head_dim=%lld: 64, 128 or 256", (long long)head_dim);
+    if (scratch_bytes < ixb_attn_scratch_bytes(hq, head_dim, splits)) return fail(IXB_E_SCRATCH, "attention scratch too small");
+    if (((uintptr_t)q | (uintptr_t)k_cache | (uintptr_t)v_cache) & 15u) return fail(IXB_E_ARG, "q / caches are not 16-byte aligned");
+    cudaStream_t st = (cudaStream_t)stream;
+    cudaError_t e;
+    if (head_dim == 64)
+        e = launch_glue(k_attn_decode<64>, dim3((unsigned)hq, (unsigned)splits), dim3(256), st, (const __nv_bfloat16 *)q,
+                        (const __nv_bfloat16 *)k_cache, (const __nv_bfloat16 *)v_cache, pos, (float *)scratch, (uint32_t)hq,
+                        (uint32_t)hkv, scale);
+    else if (head_dim == 128)
+        e = launch_glue(k_attn_decode<128>, dim3((unsigned)hq, (unsigned)splits), dim3(256), st, (const __nv_bfloat16 *)q,
+                        (const __nv_bfloat16 *)k_cache, (const __nv_bfloat16 *)v_cache, pos, (float *)scratch, (uint32_t)hq,
+                        (uint32_t)hkv, scale);
+    else
+        e = launch_glue(k_attn_decode<256>, dim3((unsigned)hq, (unsigned)splits), dim3(256), st, (const __nv_bfloat16 *)q,
+                        (const __nv_bfloat16 *)k_cache, (const __nv_bfloat16 *)v_cache, pos, (float *)scratch, (uint32_t)hq,
+                        (uint32_t)hkv, scale);
+    if (e != cudaSuccess) return fail(IXB_E_CUDA, "k_attn_decode launch: %s", cudaGetErrorString(e));
+    int rc = launch_check("k_attn_decode");
+    if (rc) return rc;
+    IXB_GLUE("k_attn_combine", launch_glue(k_attn_combine, dim3((unsigned)hq), dim3((unsigned)head_dim), st, (const float *)scratch,
+                                           (__nv_bfloat16 *)out, (const __nv_bfloat16 *)gate, (uint32_t)splits, (uint32_t)head_dim,
+                                           (uint32_t)gate_stride));
+}
+
+extern "C" int ixb_conv_update(const void *x, void *state, const void *w, const void *bias, void *y, int64_t channels,
+                               int64_t k, ixb_stream_t stream)
+{
+    if (!x || !state || !w || !y) return fail(IXB_E_ARG, "NULL pointer argument");
+    if (channels <= 0 || k < 2 || k > 8) return fail(IXB_E_ARG, "bad shape (kernel size 2..8)");
+    IXB_GLUE("k_conv_update", launch_glue(k_conv_update, dim3((unsigned)((channels + 255) / 256)), dim3(256), (cudaStream_t)stream,
+                                          (const __nv_bfloat16 *)x, (__nv_bfloat16 *)state, (const __nv_bfloat16 *)w,
+                                          (const __nv_bfloat16 *)bias, (__nv_bfloat16 *)y, (uint32_t)channels, (uint32_t)k));
+}
+
+extern "C" int ixb_gdn_step(const void *qkv, const void *z, const void *a, const void *b, const float *A_log,
+                            const float *dt_bias, const void *norm_w, float *state, void *out, int64_t hk, int64_t hv,
+                            float eps, ixb_stream_t stream)
+{
+    if (!qkv || !z || !a || !b || !A_log || !dt_bias || !norm_w || !state || !out) return fail(IXB_E_ARG, "NULL pointer argument");
+    if (hk <= 0 || hv <= 0 || hv % hk) return fail(IXB_E_ARG, "value heads must be a multiple of key heads");
+    IXB_GLUE("k_gdn_step", launch_glue(k_gdn_step, dim3((unsigned)hv), dim3(256), (cudaStream_t)stream, (const __nv_bfloat16 *)qkv,
+                                       (const __nv_bfloat16 *)z, (const __nv_bfloat16 *)a, (const __nv_bfloat16 *)b, A_log, dt_bias,
+                                       (const __nv_bfloat16 *)norm_w, state, (__nv_bfloat16 *)out, (uint32_t)hk, (uint32_t)hv, eps));
 }
 
 // ------------------------------------------------------- tensor-core small-M GEMM

@@ -1,0 +1,123 @@
+"""Per-token glue kernels of a decode step (see ``csrc/ixb_glue.cuh``): thin wrappers over the C ABI.
+
+The reference leaves this work to HuggingFace eager code and to fla's Triton
+kernels (ixrun/fla_patch.py:23-72).  Every function is one launch (attention:
+two) on the current stream, allocates nothing when its outputs are passed in,
+and can be captured in a CUDA graph: positions are device tensors.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _lib
+
+__all__ = ["add_rmsnorm", "swiglu", "rope_kv", "AttnDecode", "conv_update", "gdn_step", "rope_tables"]
+
+
+def _st(t):
+    return _lib.stream_ptr(t.device)
+
+
+def _bf16(*ts):
+    for t in ts:
+        if t is not None and (t.dtype != torch.bfloat16 or not t.is_contiguous() or not t.is_cuda):
+            raise ValueError("glue kernels take contiguous bf16 CUDA tensors")
+
+
+def add_rmsnorm(h: torch.Tensor, delta: torch.Tensor | None, w: torch.Tensor, eps: float, out: torch.Tensor | None = None):
+    """h [rows, hidden] += delta (in place; None: no add); returns rmsnorm(h) * w."""
+    _bf16(h, delta, w)
+    rows, hidden = h.reshape(-1, h.shape[-1]).shape
+    if out is None:
+        out = torch.empty_like(h)
+    with torch.cuda.device(h.device):
+        _lib.check(_lib.lib().ixb_add_rmsnorm(h.data_ptr(), None if delta is None else delta.data_ptr(), w.data_ptr(),
+                                              float(eps), out.data_ptr(), rows, hidden, _st(h)))
+    return out
+
+
+def swiglu(g: torch.Tensor, u: torch.Tensor, out: torch.Tensor | None = None):
+    _bf16(g, u)
+    if out is None:
+        out = torch.empty_like(g)
+    with torch.cuda.device(g.device):
+        _lib.check(_lib.lib().ixb_swiglu(g.data_ptr(), u.data_ptr(), out.data_ptr(), g.numel(), _st(g)))
+    return out
+
+
+def rope_tables(max_seq: int, rot_dim: int, theta: float, device):
+    """fp32 cos / sin [max_seq][rot_dim / 2] of the rotate-half convention (the tables the eager path builds)."""
+    half = rot_dim // 2
+    inv = 1.0 / (theta ** (torch.arange(0, half, dtype=torch.float32) / half))
+    ang = torch.arange(max_seq, dtype=torch.float32)[:, None] * inv[None, :]
+    return ang.cos().to(device).contiguous(), ang.sin().to(device).contiguous()
+
+
+def rope_kv(q, k, v, pos, k_cache, v_cache, cos, sin, hq: int, hkv: int, head_dim: int, rot_dim: int | None = None,
+            q_norm=None, k_norm=None, eps: float = 1e-6, q_stride: int | None = None):
+    """q [rows, >= hq*head_dim] rotated in place; k, v [rows, hkv*head_dim] into the caches [max_seq, hkv, head_dim] at
+    positions pos[0] + row (pos: int32 device tensor of one element)."""
+    _bf16(q, k, v, k_cache, v_cache, q_norm, k_norm)
+    if pos.dtype != torch.int32 or not pos.is_cuda:
+        raise ValueError("pos must be an int32 CUDA tensor")
+    rows = k.reshape(-1, hkv * head_dim).shape[0]
+    with torch.cuda.device(q.device):
+        _lib.check(_lib.lib().ixb_rope_kv(q.data_ptr(), k.data_ptr(), v.data_ptr(), pos.data_ptr(), k_cache.data_ptr(),
+                                          v_cache.data_ptr(), None if q_norm is None else q_norm.data_ptr(),
+                                          None if k_norm is None else k_norm.data_ptr(), cos.data_ptr(), sin.data_ptr(),
+                                          rows, hq, hkv, head_dim, rot_dim or head_dim, float(eps),
+                                          q_stride if q_stride is not None else q.reshape(rows, -1).shape[1],
+                                          k_cache.shape[0], _st(q)))
+    return q
+
+
+class AttnDecode:
+    """Single-query grouped-query attention over a static KV cache; owns the scratch of the context splits."""
+
+    def __init__(self, hq: int, hkv: int, head_dim: int, device, splits: int | None = None):
+        self.hq, self.hkv, self.d = hq, hkv, head_dim
+        if splits is None:
+            sms = torch.cuda.get_device_properties(device).multi_processor_count
+            splits = max(1, (2 * sms) // hq)
+        self.splits = int(splits)
+        self.scratch = torch.empty(_lib.lib().ixb_attn_scratch_bytes(hq, head_dim, self.splits), dtype=torch.uint8, device=device)
+
+    def __call__(self, q, k_cache, v_cache, pos, out=None, gate=None, gate_stride: int | None = None, scale: float | None = None):
+        """q [hq*head_dim] (contiguous heads), caches [max_seq, hkv, head_dim], pos int32 [1] = index of the newest
+        key; returns out [hq*head_dim] (optionally gated by sigmoid(gate[head*gate_stride + d]))."""
+        _bf16(k_cache, v_cache, gate)
+        if out is None:
+            out = torch.empty(self.hq * self.d, dtype=torch.bfloat16, device=q.device)
+        with torch.cuda.device(q.device):
+            _lib.check(_lib.lib().ixb_attn_decode(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), pos.data_ptr(),
+                                                  None if gate is None else gate.data_ptr(),
+                                                  gate_stride if gate_stride is not None else self.d, out.data_ptr(),
+                                                  self.scratch.data_ptr(), self.scratch.numel(), self.hq, self.hkv, self.d,
+                                                  self.splits, float(scale if scale is not None else self.d ** -0.5), _st(q)))
+        return out
+
+
+def conv_update(x, state, w, bias=None, out=None):
+    """x [C]; state [C, K-1] (updated in place); w [C, K]; returns silu(conv) [C]."""
+    _bf16(x, state, w, bias)
+    if out is None:
+        out = torch.empty_like(x)
+    with torch.cuda.device(x.device):
+        _lib.check(_lib.lib().ixb_conv_update(x.data_ptr(), state.data_ptr(), w.data_ptr(),
+                                              None if bias is None else bias.data_ptr(), out.data_ptr(), x.numel(),
+                                              w.shape[-1], _st(x)))
+    return out
+
+
+def gdn_step(qkv, z, a, b, A_log, dt_bias, norm_w, state, hk: int, hv: int, eps: float = 1e-6, out=None):
+    """One gated-delta-rule step for all value heads; state fp32 [hv, 128, 128] updated in place; returns [hv*128]."""
+    _bf16(qkv, z, a, b, norm_w)
+    if state.dtype != torch.float32 or A_log.dtype != torch.float32 or dt_bias.dtype != torch.float32:
+        raise ValueError("state, A_log and dt_bias are fp32")
+    if out is None:
+        out = torch.empty(hv * 128, dtype=torch.bfloat16, device=qkv.device)
+    with torch.cuda.device(qkv.device):
+        _lib.check(_lib.lib().ixb_gdn_step(qkv.data_ptr(), z.data_ptr(), a.data_ptr(), b.data_ptr(), A_log.data_ptr(),
+                                           dt_bias.data_ptr(), norm_w.data_ptr(), state.data_ptr(), out.data_ptr(), hk, hv,
+                                           float(eps), _st(qkv)))
+    return out
