@@ -24,6 +24,7 @@ SYMBOLS = (
     "ixb_pack_workspace_bytes", "ixb_quantize_codes", "ixb_count_codes", "ixb_pack_codes",
     "ixb_p6_blocks", "ixb_p6_build", "ixb_p6_decode", "ixb_p6_gemv_scratch_bytes", "ixb_p6_gemv", "ixb_set_pdl",
     "ixb_allreduce_bytes", "ixb_allreduce", "ixb_p6_gemv_push", "ixb_allreduce_finish", "ixb_p6_gemv_allreduce", "ixb_allreduce_spin_limit",
+    "ixb_add_rmsnorm", "ixb_swiglu", "ixb_rope_kv", "ixb_attn_scratch_bytes", "ixb_attn_decode", "ixb_conv_update", "ixb_gdn_step",
 )
 
 
