@@ -166,12 +166,15 @@ typedef struct ixb_p6 {
     const void *blk_off;
     const void *esc;
     int64_t n_esc;
-    const void *scale;    /* one bf16 */
+    const void *scale;    /* scale_stride 0: one bf16; 1: one bf16 per 16-row tile */
     int64_t out_f;
     int64_t in_f;
+    int64_t scale_stride; /* 1: a tensor fused row-wise from several (q|k|v, gate|up), every part a
+                             whole number of row tiles with its own per-tensor scale */
 } ixb_p6;
 int64_t ixb_p6_blocks(int64_t out_f, int64_t in_f);
-int ixb_p6_build(const int8_t *codes_device, const void *scale_device, int64_t out_f, int64_t in_f, void *plane_device,
+int ixb_p6_build(const int8_t *codes_device, const void *scale_device, int64_t scale_stride, int64_t out_f, int64_t in_f,
+                 void *plane_device,
                  int32_t *blk_off_device, void *esc_device, int64_t n_esc, void *ws_device, size_t ws_bytes,
                  ixb_stream_t stream);
 int ixb_p6_decode(const ixb_p6 *t, void *out_device, int out_kind, ixb_stream_t stream);

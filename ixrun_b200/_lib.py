@@ -52,6 +52,7 @@ class P6Struct(C.Structure):
     _fields_ = [
         ("plane", C.c_void_p), ("blk_off", C.c_void_p), ("esc", C.c_void_p),
         ("n_esc", C.c_int64), ("scale", C.c_void_p), ("out_f", C.c_int64), ("in_f", C.c_int64),
+        ("scale_stride", C.c_int64),
     ]
 
 
@@ -96,7 +97,7 @@ def lib():
     L.ixb_p6_blocks.restype = i64
     L.ixb_p6_blocks.argtypes = [i64, i64]
     L.ixb_p6_build.restype = C.c_int
-    L.ixb_p6_build.argtypes = [vp, vp, i64, i64, vp, vp, vp, i64, vp, sz, vp]
+    L.ixb_p6_build.argtypes = [vp, vp, i64, i64, i64, vp, vp, vp, i64, vp, sz, vp]
     L.ixb_p6_decode.restype = C.c_int
     L.ixb_p6_decode.argtypes = [C.POINTER(P6Struct), vp, C.c_int, vp]
     L.ixb_p6_gemv_scratch_bytes.restype = sz

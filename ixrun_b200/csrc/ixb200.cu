@@ -761,6 +761,8 @@ static int to_p6(const ixb_p6 *t, P6 *p)
     p->blk_off = (const int32_t *)t->blk_off;
     p->esc = (const uint32_t *)t->esc;
     p->scale = (const __nv_bfloat16 *)t->scale;
+    if (t->scale_stride != 0 && t->scale_stride != 1) return fail(IXB_E_ARG, "scale_stride must be 0 or 1");
+    p->scale_stride = (uint32_t)t->scale_stride;
     p->out_f = (uint32_t)t->out_f;
     p->in_f = (uint32_t)t->in_f;
     p->rt = (p->out_f + kTileRows - 1) / kTileRows;
@@ -768,10 +770,12 @@ static int to_p6(const ixb_p6 *t, P6 *p)
     return IXB_OK;
 }
 
-extern "C" int ixb_p6_build(const int8_t *codes, const void *scale, int64_t out_f, int64_t in_f, void *plane,
-                            int32_t *blk_off, void *esc, int64_t n_esc, void *ws, size_t ws_bytes, ixb_stream_t stream)
+extern "C" int ixb_p6_build(const int8_t *codes, const void *scale, int64_t scale_stride, int64_t out_f, int64_t in_f,
+                            void *plane, int32_t *blk_off, void *esc, int64_t n_esc, void *ws, size_t ws_bytes,
+                            ixb_stream_t stream)
 {
     if (!codes || !scale || !plane || !blk_off || !esc || !ws) return fail(IXB_E_ARG, "NULL pointer argument");
+    if (scale_stride != 0 && scale_stride != 1) return fail(IXB_E_ARG, "scale_stride must be 0 or 1");
     if (out_f <= 0 || in_f <= 0 || out_f * in_f > 800000000LL) return fail(IXB_E_ARG, "bad shape");
     if (n_esc < 0) return fail(IXB_E_ARG, "bad outlier count");
     if (((uintptr_t)plane & 15u) || ((uintptr_t)esc & 15u)) return fail(IXB_E_ARG, "P6 plane or entries are misaligned");
@@ -791,7 +795,8 @@ extern "C" int ixb_p6_build(const int8_t *codes, const void *scale, int64_t out_
     if ((rc = launch_check("k_excl_scan"))) return rc;
     if (n_esc) {
         k_p6_esc<<<(nb + 7) / 8, 256, 0, st>>>(codes, (uint32_t)out_f, (uint32_t)in_f, rt, kb, blk_off,
-                                               (const __nv_bfloat16 *)scale, (uint32_t *)esc, (uint32_t)n_esc);
+                                               (const __nv_bfloat16 *)scale, (uint32_t)scale_stride, (uint32_t *)esc,
+                                               (uint32_t)n_esc);
         if ((rc = launch_check("k_p6_esc"))) return rc;
     }
     return IXB_OK;

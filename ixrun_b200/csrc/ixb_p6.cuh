@@ -83,9 +83,10 @@ struct P6 {
     const unsigned char *plane;  // [(nb + slack) * 768]
     const int32_t *blk_off;      // [nb + 1] first outlier entry of every block
     const uint32_t *esc;         // [n_esc + slack] outlier entries
-    const __nv_bfloat16 *scale;
+    const __nv_bfloat16 *scale;  // scale_stride 0: one scale; 1: one per row tile (a tensor fused from several)
     uint32_t out_f, in_f;
     uint32_t rt, kb;             // row tiles, column blocks per row tile; nb = rt * kb
+    uint32_t scale_stride;
 };
 
 __host__ __device__ __forceinline__ uint32_t p6_field(int code) { return (uint32_t)(code >= 0 ? 32 + code : 32 + 2 * code); }
@@ -144,13 +145,14 @@ k_p6_plane(const int8_t *__restrict__ codes, uint32_t out_f, uint32_t in_f, uint
 // outlier entries of every block, in (lane, pair, half) order (one warp per block)
 __global__ void __launch_bounds__(256)
 k_p6_esc(const int8_t *__restrict__ codes, uint32_t out_f, uint32_t in_f, uint32_t rt, uint32_t kb,
-         const int32_t *__restrict__ blk_off, const __nv_bfloat16 *__restrict__ scale, uint32_t *esc, uint32_t n_esc)
+         const int32_t *__restrict__ blk_off, const __nv_bfloat16 *__restrict__ scale, uint32_t scale_stride, uint32_t *esc,
+         uint32_t n_esc)
 {
     uint32_t b = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     int lane = threadIdx.x & 31;
     if (b >= rt * kb) return;
     uint32_t R = b / kb, kbi = b - R * kb;
-    float sc = __bfloat162float(*scale);
+    float sc = __bfloat162float(scale[R * scale_stride]);
     int code[32];
     uint32_t n_out = 0;
 #pragma unroll
@@ -184,7 +186,7 @@ __global__ void __launch_bounds__(256) k_p6_decode_plane(P6 p, void *out)
     int lane = threadIdx.x & 31;
     if (b >= p.rt * p.kb) return;
     uint32_t R = b / p.kb, kbi = b - R * p.kb;
-    float sc = __bfloat162float(*p.scale);
+    float sc = __bfloat162float(p.scale[R * p.scale_stride]);
     const unsigned char *blk = p.plane + (size_t)b * kP6BlockBytes;
     const uint4 a = ((const uint4 *)blk)[lane];
     const uint2 a2 = ((const uint2 *)(blk + 512))[lane];
@@ -228,7 +230,7 @@ __global__ void __launch_bounds__(256) k_p6_decode_esc(P6 p, void *out)
     int lane = threadIdx.x & 31;
     if (b >= p.rt * p.kb) return;
     uint32_t R = b / p.kb, kbi = b - R * p.kb;
-    float sc = __bfloat162float(*p.scale);
+    float sc = __bfloat162float(p.scale[R * p.scale_stride]);
     for (int32_t j = p.blk_off[b] + lane; j < p.blk_off[b + 1]; j += 32) {
         uint32_t ent = p.esc[j];
         uint32_t row = R * kTileRows + ((ent >> 12) & 15u), col = kbi * kTileCols + (ent & 63u);
@@ -387,7 +389,7 @@ __global__ void __launch_bounds__(256) k_p6_decode_bf16(P6 p, __nv_bfloat16 *out
     }
     __syncwarp();
     uint32_t R = b / p.kb, kbi = b - R * p.kb;
-    const float s32 = 32.f * __bfloat162float(*p.scale);
+    const float s32 = 32.f * __bfloat162float(p.scale[R * p.scale_stride]);
     const uint32_t bb = (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(s32));
     const uint32_t b2 = bb | (bb << 16), c2 = b2 ^ 0x80008000u, e2 = 0x3F003F00u;
     const unsigned char *blk = p.plane + (size_t)b * kP6BlockBytes;
@@ -512,14 +514,23 @@ k_p6_mma(P6 p, const __nv_bfloat16 *__restrict__ x, uint32_t m_rows, const __nv_
 #pragma unroll
         for (int r = 0; r < 16; ++r) oacc[r * 32 + lane] = 0.f;
     }
-    uint32_t e2, b2, c2;
+    // the scale of the run's first row tile and of the one after it (a fused tensor has one per row tile); the
+    // walk below always holds the next tile's scale one segment ahead, so the load is never waited for
+    uint32_t e2, b2 = 0, c2 = 0;
+    uint32_t sc_cur = 0, sc_next = 0;
     {
-        const float s32 = 32.f * __bfloat162float(*p.scale);
+        const uint32_t R0 = min(b_begin / KB, p.rt - 1u);
+        sc_cur = (uint32_t)__bfloat16_as_ushort(p.scale[R0 * p.scale_stride]);
+        sc_next = (uint32_t)__bfloat16_as_ushort(p.scale[min(R0 + 1u, p.rt - 1u) * p.scale_stride]);
+        asm volatile("mov.b32 %0, 0x3F003F00;" : "=r"(e2));            // opaque, so that it stays a register operand
+    }
+    auto set_scale = [&](uint32_t bits) {
+        const float s32 = 32.f * __uint_as_float(bits << 16);
         const uint32_t bb = (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(s32));    // exact: a power-of-two multiple
         b2 = bb | (bb << 16);
         c2 = b2 ^ 0x80008000u;
-        asm volatile("mov.b32 %0, 0x3F003F00;" : "=r"(e2));            // opaque, so that it stays a register operand
-    }
+    };
+    set_scale(sc_cur);
     asm volatile("griddepcontrol.wait;" ::: "memory");
     // a pushing launch marks its words with the number of this all-reduce call: one more than the counter that the
     // finishing kernel of the call before left (that kernel is complete: it is ahead of this one in the stream)
@@ -783,6 +794,12 @@ k_p6_mma(P6 p, const __nv_bfloat16 *__restrict__ x, uint32_t m_rows, const __nv_
             b = seg_e;
             seg_j = seg_je;
             ++R;
+#ifndef IXB_P6_UNIFORM_SCALE
+            if (p.scale_stride) {                                         // warp uniform
+                set_scale(sc_next);
+                sc_next = (uint32_t)__bfloat16_as_ushort(p.scale[min(R + 1u, p.rt - 1u) * p.scale_stride]);
+            }
+#endif
         }
     }
     cp_async_wait<0>();

@@ -7,12 +7,16 @@ graph capture was not possible with HF's dynamic KV cache.  This runner keeps a
 static KV cache and position tensors so that one token step is a fixed launch
 sequence: per layer RMSNorm -> q/k/v packed GEMVs -> RoPE -> cache write ->
 attention over the static cache -> o_proj GEMV -> RMSNorm -> gate/up GEMVs ->
-SwiGLU -> down GEMV.  The packed linears run the fused decode+GEMV kernel; the
-glue (norms, RoPE, attention, SwiGLU, lm_head) is plain torch for now.
+SwiGLU -> down GEMV.  The packed linears run the fused decode+GEMV kernel; with
+`glue="kernels"` the work between them is this library's glue kernels (residual
+add + RMSNorm, RoPE + cache write, split-context attention, SwiGLU) and q|k|v
+and gate|up are one fused packed tensor each: 10 launches per layer, all taking
+part in programmatic dependent launch; with
+`glue="eager"` it is plain torch.  Prefill (many rows) always takes the torch path.
 
 `weights="packed"` uses StreamingLinear (fused kernels); `weights="decoded"`
 builds the same model with the packed weights decoded to bf16 and dense
-matmuls -- the ground truth for greedy-token agreement.
+matmuls -- with eager glue the ground truth for greedy-token agreement.
 """
 from __future__ import annotations
 
@@ -67,29 +71,66 @@ def _rms(x, w, eps):
     return (v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + eps)).to(x.dtype) * w
 
 
+class FusedPackedLinear(torch.nn.Module):
+    """Several packed linears that share their input (q|k|v, gate|up) as ONE resident tensor and one launch; every
+    part keeps its own per-tensor scale (p6.P6Packed.fuse).  forward returns the parts' outputs."""
+
+    def __init__(self, packed_parts: list):
+        super().__init__()
+        from .p6 import P6Packed
+
+        self.res = P6Packed.fuse(packed_parts)
+        self.in_features = self.res.in_f
+        self._w_buf = None
+
+    def _set_shared_buf(self, buf):
+        self._w_buf = buf
+
+    def forward(self, x):
+        rows = x.numel() // self.in_features
+        x2 = x.reshape(rows, self.in_features)
+        if rows <= 8:
+            y = self.res.gemv(x2)
+        else:                                   # prefill: decode into the shared buffer, dense matmul
+            y = F.linear(x2, self.res.decode(out=self._w_buf[: self.res.N], kind="bf16"))
+        return [y[:, a:a + n] for a, n in self.res.sections]
+
+
 class PackedLlama(torch.nn.Module):
     def __init__(self, cfg: LlamaConfig, packed_layers: list, embed: torch.Tensor, lm_head: torch.Tensor,
-                 norms: list | None = None, weights: str = "packed", device="cuda"):
+                 norms: list | None = None, weights: str = "packed", device="cuda", glue: str | None = None):
         """packed_layers[i][name] = packed dict of layer i's linear `name`;
-        embed [vocab, hidden] and lm_head [vocab, hidden] stay bf16."""
+        embed [vocab, hidden] and lm_head [vocab, hidden] stay bf16.
+        glue: "kernels" (default for packed weights) or "eager" (default for decoded weights)."""
         super().__init__()
         if weights not in ("packed", "decoded"):
             raise ValueError("weights must be 'packed' or 'decoded'")
-        self.cfg = cfg
+        glue = glue or ("kernels" if weights == "packed" else "eager")
+        if glue not in ("kernels", "eager"):
+            raise ValueError("glue must be 'kernels' or 'eager'")
+        self.cfg, self.glue, self.weights = cfg, glue, weights
         dev = torch.device(device)
         mk = StreamingLinear if weights == "packed" else _DenseLinear
         self.layers = torch.nn.ModuleList()
         max_n = 0
         for li in range(cfg.n_layers):
-            mods = torch.nn.ModuleDict({n: mk(packed_layers[li][n]) for n in LINEARS})
+            pl = packed_layers[li]
+            if weights == "packed":
+                # linears that share their input are one resident tensor and one launch
+                mods = torch.nn.ModuleDict({"qkv": FusedPackedLinear([pl["q_proj"], pl["k_proj"], pl["v_proj"]]),
+                                            "o_proj": mk(pl["o_proj"]),
+                                            "gate_up": FusedPackedLinear([pl["gate_proj"], pl["up_proj"]]),
+                                            "down_proj": mk(pl["down_proj"])})
+                max_n = max([max_n, pl["o_proj"]["N"], pl["down_proj"]["N"], mods["qkv"].res.N, mods["gate_up"].res.N])
+            else:
+                mods = torch.nn.ModuleDict({n: mk(pl[n]) for n in LINEARS})
             self.layers.append(mods)
-            max_n = max(max_n, max(packed_layers[li][n]["N"] for n in LINEARS))
         if weights == "packed":
             # one shared decode buffer for inputs of more than 8 rows (prefill), like the streaming engine
             self._shared = torch.empty(max_n, dtype=torch.bfloat16, device=dev)
             for mods in self.layers:
-                for n in LINEARS:
-                    mods[n]._set_shared_buf(self._shared)
+                for m in mods.values():
+                    m._set_shared_buf(self._shared)
         ones = torch.ones(cfg.hidden, dtype=torch.bfloat16, device=dev)
         self.ln1 = [ones.clone() if norms is None else norms[i][0].to(dev) for i in range(cfg.n_layers)]
         self.ln2 = [ones.clone() if norms is None else norms[i][1].to(dev) for i in range(cfg.n_layers)]
@@ -107,8 +148,29 @@ class PackedLlama(torch.nn.Module):
         # static inputs / outputs of the captured step
         self.tok = torch.zeros(1, dtype=torch.long, device=dev)
         self.pos = torch.zeros(1, dtype=torch.long, device=dev)
+        self.pos32 = torch.zeros(1, dtype=torch.int32, device=dev)
         self.logits = None
         self.graph = None
+        if glue == "kernels":
+            from .glue import AttnDecode
+
+            bf = dict(dtype=torch.bfloat16, device=dev)
+            qd, kd = cfg.n_heads * cfg.head_dim, cfg.n_kv_heads * cfg.head_dim
+            # static activations of the one-row step
+            self._h = torch.zeros(1, cfg.hidden, **bf)
+            self._xn = torch.zeros(1, cfg.hidden, **bf)
+            if weights == "packed":                                # outputs of the fused linears and the parts' views
+                self._qkv = torch.zeros(1, self.layers[0]["qkv"].res.out_f, **bf)
+                self._q, self._k, self._v = self.layers[0]["qkv"].res.split(self._qkv)
+                self._gu = torch.zeros(1, self.layers[0]["gate_up"].res.out_f, **bf)
+                self._g, self._u = self.layers[0]["gate_up"].res.split(self._gu)
+            else:
+                self._q, self._k, self._v = torch.zeros(qd, **bf), torch.zeros(kd, **bf), torch.zeros(kd, **bf)
+                self._g, self._u = torch.zeros(cfg.intermediate, **bf), torch.zeros(cfg.intermediate, **bf)
+            self._a = torch.zeros(1, qd, **bf)
+            self._d = torch.zeros(1, cfg.hidden, **bf)             # output of o_proj / down_proj: the next residual
+            self._act = torch.zeros(1, cfg.intermediate, **bf)
+            self._attn = AttnDecode(cfg.n_heads, cfg.n_kv_heads, cfg.head_dim, dev)
 
     # ------------------------------------------------------------------ core
     def _rope(self, x, pos):
@@ -123,9 +185,10 @@ class PackedLlama(torch.nn.Module):
         cfg, m = self.cfg, self.layers[li]
         t = h.shape[0]
         x = _rms(h, self.ln1[li], cfg.rms_eps)
-        q = m["q_proj"](x).view(t, cfg.n_heads, cfg.head_dim)
-        k = m["k_proj"](x).view(t, cfg.n_kv_heads, cfg.head_dim)
-        v = m["v_proj"](x).view(t, cfg.n_kv_heads, cfg.head_dim)
+        q, k, v = m["qkv"](x) if self.weights == "packed" else (m["q_proj"](x), m["k_proj"](x), m["v_proj"](x))
+        q = q.reshape(t, cfg.n_heads, cfg.head_dim)
+        k = k.reshape(t, cfg.n_kv_heads, cfg.head_dim)
+        v = v.reshape(t, cfg.n_kv_heads, cfg.head_dim)
         q, k = self._rope(q, pos), self._rope(k, pos)
         self.k_cache[li].index_copy_(0, pos, k)
         self.v_cache[li].index_copy_(0, pos, v)
@@ -138,9 +201,52 @@ class PackedLlama(torch.nn.Module):
         a = a.transpose(0, 1).reshape(t, cfg.n_heads * cfg.head_dim)
         h = h + m["o_proj"](a)
         x = _rms(h, self.ln2[li], cfg.rms_eps)
-        return h + m["down_proj"](F.silu(m["gate_proj"](x)) * m["up_proj"](x))
+        g, u = m["gate_up"](x) if self.weights == "packed" else (m["gate_proj"](x), m["up_proj"](x))
+        return h + m["down_proj"](F.silu(g) * u)
+
+    def _lin(self, li, name, x, out):
+        m = self.layers[li][name]
+        if self.weights == "packed":
+            return m._res.gemv(x, out=out) if m._res is not None else out.copy_(m(x))
+        return torch.matmul(x, m.weight.t(), out=out.view(1, -1))
+
+    def _qkv_step(self, li):
+        if self.weights == "packed":
+            return self.layers[li]["qkv"].res.gemv(self._xn, out=self._qkv)
+        for n, o in (("q_proj", self._q), ("k_proj", self._k), ("v_proj", self._v)):
+            self._lin(li, n, self._xn, o)
+
+    def _gate_up_step(self, li):
+        if self.weights == "packed":
+            return self.layers[li]["gate_up"].res.gemv(self._xn, out=self._gu)
+        self._lin(li, "gate_proj", self._xn, self._g)
+        self._lin(li, "up_proj", self._xn, self._u)
+
+    def _step_kernels(self):
+        """One row at position self.pos32 (device) through all layers on the glue kernels; static buffers only."""
+        from . import glue as G
+
+        cfg = self.cfg
+        torch.index_select(self.embed, 0, self.tok, out=self._h)
+        delta = None
+        for li in range(cfg.n_layers):
+            G.add_rmsnorm(self._h, delta, self.ln1[li], cfg.rms_eps, out=self._xn)
+            self._qkv_step(li)
+            G.rope_kv(self._q, self._k, self._v, self.pos32, self.k_cache[li], self.v_cache[li], self.cos, self.sin,
+                      cfg.n_heads, cfg.n_kv_heads, cfg.head_dim)
+            self._attn(self._q, self.k_cache[li], self.v_cache[li], self.pos32, out=self._a)
+            self._lin(li, "o_proj", self._a, self._d)
+            G.add_rmsnorm(self._h, self._d, self.ln2[li], cfg.rms_eps, out=self._xn)
+            self._gate_up_step(li)
+            G.swiglu(self._g, self._u, out=self._act[0])
+            self._lin(li, "down_proj", self._act, self._d)
+            delta = self._d
+        G.add_rmsnorm(self._h, delta, self.ln_f, cfg.rms_eps, out=self._xn)
+        return F.linear(self._xn, self.lm_head).float()
 
     def _forward(self, tok, pos):
+        if self.glue == "kernels" and tok.numel() == 1 and tok.data_ptr() == self.tok.data_ptr():
+            return self._step_kernels()
         h = self.embed.index_select(0, tok)
         for li in range(self.cfg.n_layers):
             h = self._block(li, h, pos)
@@ -180,6 +286,7 @@ class PackedLlama(torch.nn.Module):
         (a static tensor when the step is graph-captured)."""
         self.tok.copy_(tok.reshape(1))
         self.pos.fill_(pos)
+        self.pos32.fill_(pos)
         if self.graph is not None:
             self.graph.replay()
             return self.logits

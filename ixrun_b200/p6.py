@@ -63,7 +63,8 @@ class GemvScratch:
 class P6Packed:
     def __init__(self, codes: torch.Tensor, scale: torch.Tensor, out_f: int, in_f: int, total_bytes: int = 0,
                  scratch: GemvScratch | None = None):
-        """codes: int8 [out_f*in_f] on a CUDA device; scale: bf16 scalar."""
+        """codes: int8 [out_f*in_f] on a CUDA device; scale: one bf16 value, or one per 16-row tile (a tensor fused
+        row-wise from several, see ``fuse``)."""
         if not codes.is_cuda or codes.dtype != torch.int8 or codes.numel() != out_f * in_f:
             raise ValueError("P6Packed needs out_f*in_f int8 codes on a CUDA device")
         dev = codes.device
@@ -78,14 +79,18 @@ class P6Packed:
         self.blk_off = torch.empty(nb + 1, dtype=torch.int32, device=dev)
         self.esc = torch.empty(n_esc + SLACK_ENTRIES, dtype=torch.int32, device=dev)
         self.n_esc = n_esc
-        self.scale = scale.detach().to(dev, torch.bfloat16).reshape(()).contiguous()
+        self.scale = scale.detach().to(dev, torch.bfloat16).reshape(-1).contiguous()
+        if self.scale.numel() not in (1, (self.out_f + 15) // 16):
+            raise ValueError("scale must hold one value, or one per 16-row tile")
+        stride = 0 if self.scale.numel() == 1 else 1
+        self.sections = [(0, self.out_f)]            # (first row, rows) of every fused part
         ws = torch.empty((nb + 1) * 4, dtype=torch.uint8, device=dev)
         with torch.cuda.device(dev):
-            _lib.check(L.ixb_p6_build(c.data_ptr(), self.scale.data_ptr(), self.out_f, self.in_f, self.plane.data_ptr(),
+            _lib.check(L.ixb_p6_build(c.data_ptr(), self.scale.data_ptr(), stride, self.out_f, self.in_f, self.plane.data_ptr(),
                                       self.blk_off.data_ptr(), self.esc.data_ptr(), n_esc,
                                       ws.data_ptr(), ws.numel(), _lib.stream_ptr(dev)))
         self.struct = _lib.P6Struct(self.plane.data_ptr(), self.blk_off.data_ptr(), self.esc.data_ptr(), n_esc,
-                                    self.scale.data_ptr(), self.out_f, self.in_f)
+                                    self.scale.data_ptr(), self.out_f, self.in_f, stride)
         self.resident_bytes = nb * BLOCK_BYTES + 4 * (nb + 1 + n_esc) + 2
         self.scratch = scratch if scratch is not None else GemvScratch.shared(dev)
 
@@ -95,6 +100,40 @@ class P6Packed:
         dp = packed if isinstance(packed, DevicePacked) else DevicePacked(packed)
         codes = dp.decode(kind="codes").reshape(-1)
         return cls(codes, dp.scale, dp.out_f, dp.in_f, total_bytes=dp.total_bytes, **kw)
+
+    @classmethod
+    def fuse(cls, parts, **kw):
+        """One resident tensor from several packed tensors that share their input (q|k|v, gate|up, the four
+        in-projections of a gated-delta-rule layer): the parts' codes stacked row-wise, every part padded with zero
+        codes to a whole number of 16-row tiles and keeping its own per-tensor scale, so the fused GEMV gives every
+        part's outputs bit for bit as the part alone would.  ``sections`` lists (first row, rows) of every part in
+        the fused output; ``split(y)`` cuts a one-row output into the parts' views."""
+        dps = [p if isinstance(p, DevicePacked) else DevicePacked(p) for p in parts]
+        in_f = dps[0].in_f
+        if any(d.in_f != in_f for d in dps):
+            raise ValueError("fused tensors must share in_f")
+        dev = dps[0].device
+        codes, scales, sections, row = [], [], [], 0
+        for d in dps:
+            c = d.decode(kind="codes").reshape(d.out_f, in_f)
+            pad = (-d.out_f) % 16
+            if pad:
+                c = torch.cat([c, torch.zeros(pad, in_f, dtype=torch.int8, device=dev)])
+            codes.append(c)
+            scales.append(d.scale.detach().to(dev, torch.bfloat16).reshape(1).expand((d.out_f + pad) // 16))
+            sections.append((row, d.out_f))
+            row += d.out_f + pad
+        self = cls(torch.cat(codes).reshape(-1), torch.cat(scales), row, in_f,
+                   total_bytes=sum(d.total_bytes for d in dps), **kw)
+        self.sections = sections
+        return self
+
+    def split(self, y: torch.Tensor):
+        """Views of a one-row output [1, out_f] (or [out_f]) per fused part."""
+        flat = y.reshape(-1)
+        if flat.numel() != self.out_f:
+            raise ValueError("split takes a one-row output")
+        return [flat[a:a + n] for a, n in self.sections]
 
     def decode(self, out: torch.Tensor | None = None, kind: str = "bf16") -> torch.Tensor:
         dtype = {"bf16": torch.bfloat16, "codes": torch.int8}[kind]

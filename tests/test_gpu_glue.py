@@ -6,6 +6,8 @@ import pytest
 import torch
 import torch.nn.functional as F
 
+from glue_refs import gdn_ref, rope_ref
+
 pytestmark = pytest.mark.gpu
 
 BF16_ULP = 2.0 ** -8
@@ -40,15 +42,6 @@ def test_swiglu():
     g = torch.randn(17408, device="cuda").bfloat16() * 3
     u = torch.randn(17408, device="cuda").bfloat16()
     close(swiglu(g, u), F.silu(g) * u, BF16_ULP)
-
-
-def rope_ref(x, cos, sin, pos, rot):
-    """x [T, H, D] fp32, rotate-half over the first `rot` dimensions"""
-    c = cos[pos][:, None, :]
-    s = sin[pos][:, None, :]
-    xr, rest = x[..., :rot], x[..., rot:]
-    x1, x2 = xr.chunk(2, dim=-1)
-    return torch.cat([x1 * c - x2 * s, x2 * c + x1 * s, rest], dim=-1)
 
 
 @pytest.mark.parametrize("hq,hkv,d,rot,norm", [(16, 8, 128, 128, False), (24, 4, 256, 64, True), (3, 1, 256, 256, False)])
@@ -123,28 +116,6 @@ def test_conv_update():
         close(y, ref, BF16_ULP)
         hist = full[:, 1:].to(torch.bfloat16)
         assert torch.equal(state, hist)
-
-
-def gdn_ref(qkv, z, a, b, A_log, dt_bias, norm_w, S, hk, hv, eps):
-    """fp32 restatement of one gated-delta-rule step + gated RMSNorm (the published recurrence)."""
-    dk = dv = 128
-    q = qkv[: hk * dk].float().view(hk, dk)
-    k = qkv[hk * dk: 2 * hk * dk].float().view(hk, dk)
-    v = qkv[2 * hk * dk:].float().view(hv, dv)
-    q = q * torch.rsqrt(q.pow(2).sum(-1, keepdim=True) + 1e-6) * dk ** -0.5
-    k = k * torch.rsqrt(k.pow(2).sum(-1, keepdim=True) + 1e-6)
-    rep = hv // hk
-    q, k = q.repeat_interleave(rep, 0), k.repeat_interleave(rep, 0)
-    g = torch.exp(-A_log.exp() * F.softplus(a.float() + dt_bias))
-    beta = torch.sigmoid(b.float())
-    S = S * g[:, None, None]
-    kv = torch.einsum("hij,hi->hj", S, k)
-    delta = (v - kv) * beta[:, None]
-    S = S + k[:, :, None] * delta[:, None, :]
-    o = torch.einsum("hij,hi->hj", S, q).to(torch.bfloat16).float()
-    o = (o * torch.rsqrt(o.pow(2).mean(-1, keepdim=True) + eps)).to(torch.bfloat16) * norm_w
-    out = o * F.silu(z.float().view(hv, dv)).to(torch.bfloat16)
-    return out.reshape(-1), S
 
 
 @pytest.mark.parametrize("hk,hv", [(16, 48), (2, 6), (1, 1)])

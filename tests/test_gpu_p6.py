@@ -172,3 +172,35 @@ def test_p6_programmatic_dependent_launch_gives_the_same_result():
         assert torch.equal(h, h_ref) and torch.equal(y, y_ref)
     finally:
         set_pdl(prev)
+
+
+@pytest.mark.parametrize("in_f,rows", [(512, (48, 100, 256)), (5120, (1536, 256, 6, 6)), (2048, (2048, 1024, 1024))])
+def test_p6_fused_tensor_gives_every_part_its_own_result(in_f, rows):
+    """Tensors fused row-wise keep their own per-tensor scales: decoding gives every part's weights bit for bit, the
+    GEMV every part's outputs (the fp32 sums may be added in another order than in the part alone: 1e-6 of the
+    largest output; the tile layout and the products are the same)."""
+    from ixrun_b200.p6 import P6Packed
+    from ixrun_b200.synth import synthetic_packed
+
+    parts = [synthetic_packed(r, in_f, seed=11 + i) for i, r in enumerate(rows)]
+    for i, p in enumerate(parts):                       # clearly different scales
+        p["scale"] = (p["scale"].float() * (1.0 + 0.37 * i)).to(torch.bfloat16)
+    alone = [P6Packed.from_packed(p) for p in parts]
+    fused = P6Packed.fuse(parts)
+    assert [n for _, n in fused.sections] == list(rows) and all(a % 16 == 0 for a, _ in fused.sections)
+    w = fused.decode(kind="bf16")
+    c = fused.decode(kind="codes").view(fused.out_f, in_f)
+    for (a, n), one in zip(fused.sections, alone):
+        assert torch.equal(w[a:a + n], one.decode(kind="bf16"))
+        assert torch.equal(c[a:a + n], one.decode(kind="codes").view(n, in_f))
+    for m in (1, 3):
+        x = torch.randn(m, in_f, device="cuda").bfloat16()
+        y = fused.gemv(x, out_dtype=torch.float32)
+        yb = fused.gemv(x)
+        for (a, n), one in zip(fused.sections, alone):
+            ref = one.gemv(x, out_dtype=torch.float32)
+            assert float((y[:, a:a + n] - ref).abs().max()) <= 1e-6 * float(ref.abs().max())
+            assert float((yb[:, a:a + n].float() - ref).abs().max()) <= 2.0 ** -8 * float(ref.abs().max())
+    if len(rows) == 3:
+        q, k, v = fused.split(fused.gemv(torch.randn(1, in_f, device="cuda").bfloat16()))
+        assert q.numel() == rows[0] and k.numel() == rows[1] and v.numel() == rows[2]

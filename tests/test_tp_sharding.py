@@ -82,3 +82,19 @@ def test_shard_bounds_and_errors():
         P.shard_codes(codes, 4, 64, 2, 0, "diagonal")
     with pytest.raises(ValueError):
         P.shard_codes(codes, 4, 64, 2, 0, "column", sections=[1, 2])
+
+
+def test_shard_geometry_of_the_full_model():
+    from ixrun_b200.hybrid27b import HybridConfig, linear_shapes, shard_geometry
+
+    cfg = HybridConfig()
+    for world in (1, 2, 4, 8):
+        g = shard_geometry(cfg, world)
+        s = linear_shapes(cfg, world)
+        assert g["hq"] % g["hkv"] == 0 and g["hv"] % g["hk"] == 0
+        assert s["gdn"]["out_proj"][1] * world == cfg.gdn_v_heads * cfg.gdn_dim
+        assert s["attn"]["o_proj"][1] * world == cfg.attn_heads * cfg.attn_dim
+        assert s["mlp"]["down_proj"][1] * world == cfg.ffn
+        for kind in s.values():
+            for r, c in kind.values():
+                assert c % 64 == 0
