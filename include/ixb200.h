@@ -287,6 +287,13 @@ uint32_t ixb_allreduce_spin_limit(uint32_t polls);
  */
 int ixb_add_rmsnorm(void *h_device, const void *delta_device, const void *w_device, float eps, void *xn_device,
                     int64_t rows, int64_t hidden, ixb_stream_t stream);
+/* ixb_allreduce_finish with the residual add and the RMSNorm that follow a row-parallel linear in the same kernel:
+ * h [rows][hidden] (bf16, in/out) += bf16(sum over the ranks' words of this call), xn = rmsnorm(h) * w.  rows <= 8,
+ * hidden a multiple of 8 and at most 5120, rows * hidden <= n_max.  No reference counterpart (the reference is
+ * single-GPU); the result equals ixb_allreduce_finish into a bf16 vector followed by ixb_add_rmsnorm. */
+int ixb_allreduce_finish_add_rmsnorm(void *const *peer_buffers, int rank, int world, int64_t n_max, void *h_device,
+                                     const void *w_device, float eps, void *xn_device, int64_t rows, int64_t hidden,
+                                     ixb_stream_t stream);
 int ixb_swiglu(const void *g_device, const void *u_device, void *y_device, int64_t n, ixb_stream_t stream);
 int ixb_rope_kv(void *q_device, const void *k_device, const void *v_device, const int32_t *pos_device, void *k_cache_device,
                 void *v_cache_device, const void *q_norm_device, const void *k_norm_device, const float *cos_device,

@@ -1109,22 +1109,75 @@ static cudaError_t launch_glue(void (*kernel)(KArgs...), dim3 grid, dim3 block, 
         return launch_check(what);                                                            \
     } while (0)
 
+static bool norm_vector_ok(const void *h, const void *delta, const void *w, const void *xn, int64_t hidden, int64_t limit)
+{
+    return (hidden & 7) == 0 && hidden <= limit &&
+           ((((uintptr_t)h | (uintptr_t)delta | (uintptr_t)w | (uintptr_t)xn) & 15u) == 0);
+}
+
 extern "C" int ixb_add_rmsnorm(void *h, const void *delta, const void *w, float eps, void *xn, int64_t rows,
                                int64_t hidden, ixb_stream_t stream)
 {
     if (!h || !w || !xn) return fail(IXB_E_ARG, "NULL pointer argument");
     if (rows <= 0 || hidden <= 0 || rows > 65535) return fail(IXB_E_ARG, "bad shape");
-    IXB_GLUE("k_add_rmsnorm", launch_glue(k_add_rmsnorm, dim3((unsigned)rows), dim3(hidden >= 4096 ? 1024 : 256), (cudaStream_t)stream,
-                                          (__nv_bfloat16 *)h, (const __nv_bfloat16 *)delta, (const __nv_bfloat16 *)w, eps,
-                                          (__nv_bfloat16 *)xn, (uint32_t)hidden));
+    if (norm_vector_ok(h, delta, w, xn, hidden, 8192)) {
+        const unsigned threads = (unsigned)(((hidden / 8) + 31) / 32 * 32);
+        NormExchange none = {};
+        IXB_GLUE("k_add_rmsnorm", launch_glue(k_add_rmsnorm<0>, dim3((unsigned)rows), dim3(threads), (cudaStream_t)stream,
+                                              (__nv_bfloat16 *)h, (const __nv_bfloat16 *)delta, none, (const __nv_bfloat16 *)w,
+                                              eps, (__nv_bfloat16 *)xn, (uint32_t)hidden));
+    }
+    IXB_GLUE("k_add_rmsnorm_any", launch_glue(k_add_rmsnorm_any, dim3((unsigned)rows), dim3(hidden >= 4096 ? 1024 : 256), (cudaStream_t)stream,
+                                              (__nv_bfloat16 *)h, (const __nv_bfloat16 *)delta, (const __nv_bfloat16 *)w, eps,
+                                              (__nv_bfloat16 *)xn, (uint32_t)hidden));
+}
+
+extern "C" int ixb_allreduce_finish_add_rmsnorm(void *const *peer_buffers, int rank, int world, int64_t n_max, void *h,
+                                                const void *w, float eps, void *xn, int64_t rows, int64_t hidden,
+                                                ixb_stream_t stream)
+{
+    P6Push push;
+    uint32_t *epoch, *err;
+    int rc = ar_geometry(peer_buffers, rank, world, n_max, &push, &epoch, &err);
+    if (rc) return rc;
+    if (!h || !w || !xn) return fail(IXB_E_ARG, "NULL pointer argument");
+    if (rows <= 0 || rows > 8 || hidden <= 0 || rows * hidden > n_max) return fail(IXB_E_ARG, "bad shape");
+    if (!norm_vector_ok(h, nullptr, w, xn, hidden, 8 * kNormExchangeThreads))
+        return fail(IXB_E_UNSUPPORTED, "hidden=%lld: a multiple of 8, at most %d, 16-byte aligned rows", (long long)hidden,
+                    8 * kNormExchangeThreads);
+    NormExchange ex;
+    ex.mine = push.mine;
+    ex.epoch = epoch;
+    ex.err = err;
+    ex.world = (uint32_t)world;
+    ex.n_max = (uint32_t)n_max;
+    ex.counters = ar_counters(n_max);
+    ex.spin_limit = g_ar_spin_limit.load();
+    const unsigned threads = (unsigned)(((hidden / 8) + 31) / 32 * 32);
+    cudaStream_t st = (cudaStream_t)stream;
+    cudaError_t e;
+#define IXB_NORM_EX(W)                                                                                                  \
+    e = launch_glue(k_add_rmsnorm<W>, dim3((unsigned)rows), dim3(threads), st, (__nv_bfloat16 *)h, (const __nv_bfloat16 *)nullptr, \
+                    ex, (const __nv_bfloat16 *)w, eps, (__nv_bfloat16 *)xn, (uint32_t)hidden)
+    switch (world) {
+    case 1: IXB_NORM_EX(1); break;
+    case 2: IXB_NORM_EX(2); break;
+    case 4: IXB_NORM_EX(4); break;
+    default: IXB_NORM_EX(8); break;
+    }
+#undef IXB_NORM_EX
+    if (e != cudaSuccess) return fail(IXB_E_CUDA, "k_add_rmsnorm (exchange) launch: %s", cudaGetErrorString(e));
+    return launch_check("k_add_rmsnorm (exchange)");
 }
 
 extern "C" int ixb_swiglu(const void *g, const void *u, void *y, int64_t n, ixb_stream_t stream)
 {
     if (!g || !u || !y) return fail(IXB_E_ARG, "NULL pointer argument");
     if (n <= 0 || n > 0x7fffffffLL) return fail(IXB_E_ARG, "bad size");
-    IXB_GLUE("k_swiglu", launch_glue(k_swiglu, dim3((unsigned)((n + 255) / 256)), dim3(256), (cudaStream_t)stream,
-                                     (const __nv_bfloat16 *)g, (const __nv_bfloat16 *)u, (__nv_bfloat16 *)y, (uint32_t)n));
+    const int vec = (n & 7) == 0 && ((((uintptr_t)g | (uintptr_t)u | (uintptr_t)y) & 15u) == 0);
+    const int64_t threads = vec ? n / 8 : n;
+    IXB_GLUE("k_swiglu", launch_glue(k_swiglu, dim3((unsigned)((threads + 127) / 128)), dim3(128), (cudaStream_t)stream,
+                                     (const __nv_bfloat16 *)g, (const __nv_bfloat16 *)u, (__nv_bfloat16 *)y, (uint32_t)n, vec));
 }
 
 extern "C" int ixb_rope_kv(void *q, const void *k, const void *v, const int32_t *pos, void *k_cache, void *v_cache,
@@ -1149,33 +1202,46 @@ extern "C" size_t ixb_attn_scratch_bytes(int64_t hq, int64_t head_dim, int64_t s
     return (size_t)hq * (size_t)splits * (size_t)(head_dim + 2) * sizeof(float);
 }
 
+template <int D>
+static cudaError_t launch_attn(int64_t hq, int64_t hkv, int64_t splits, cudaStream_t st, const void *q, const void *k_cache,
+                               const void *v_cache, const int32_t *pos, void *scratch, float scale)
+{
+    const int64_t rep = hq / hkv;
+#define IXB_ATTN(G)                                                                                                        \
+    return launch_glue(k_attn_decode<D, G>, dim3((unsigned)(hq / G), (unsigned)splits), dim3(256), st, (const __nv_bfloat16 *)q, \
+                       (const __nv_bfloat16 *)k_cache, (const __nv_bfloat16 *)v_cache, pos, (float *)scratch, (uint32_t)hq,  \
+                       (uint32_t)hkv, scale)
+    switch (rep) {                      // all query heads of a KV head in one CTA where that is a supported group size
+    case 2: IXB_ATTN(2);
+    case 3: IXB_ATTN(3);
+    case 4: IXB_ATTN(4);
+    case 6: IXB_ATTN(6);
+    case 8: IXB_ATTN(8);
+    default: IXB_ATTN(1);
+    }
+#undef IXB_ATTN
+}
+
 extern "C" int ixb_attn_decode(const void *q, const void *k_cache, const void *v_cache, const int32_t *pos, const void *gate,
                                int64_t gate_stride, void *out, void *scratch, size_t scratch_bytes, int64_t hq, int64_t hkv,
                                int64_t head_dim, int64_t splits, float scale, ixb_stream_t stream)
 {
     if (!q || !k_cache || !v_cache || !pos || !out || !scratch) return fail(IXB_E_ARG, "NULL pointer argument");
-    if (hq <= 0 || hkv <= 0 || hq % hkv || splits <= 0 || splits > 1024) return fail(IXB_E_ARG, "bad shape");
+    if (hq <= 0 || hkv <= 0 || hq % hkv || splits <= 0 || splits > kAttnMaxSplits) return fail(IXB_E_ARG, "bad shape");
     if (head_dim != 64 && head_dim != 128 && head_dim != 256) return fail(IXB_E_UNSUPPORTED, "head_dim=%lld: 64, 128 or 256", (long long)head_dim);
     if (scratch_bytes < ixb_attn_scratch_bytes(hq, head_dim, splits)) return fail(IXB_E_SCRATCH, "attention scratch too small");
     if (((uintptr_t)q | (uintptr_t)k_cache | (uintptr_t)v_cache) & 15u) return fail(IXB_E_ARG, "q / caches are not 16-byte aligned");
+    if ((uintptr_t)scratch & 7u) return fail(IXB_E_ARG, "attention scratch is misaligned");
     cudaStream_t st = (cudaStream_t)stream;
     cudaError_t e;
-    if (head_dim == 64)
-        e = launch_glue(k_attn_decode<64>, dim3((unsigned)hq, (unsigned)splits), dim3(256), st, (const __nv_bfloat16 *)q,
-                        (const __nv_bfloat16 *)k_cache, (const __nv_bfloat16 *)v_cache, pos, (float *)scratch, (uint32_t)hq,
-                        (uint32_t)hkv, scale);
-    else if (head_dim == 128)
-        e = launch_glue(k_attn_decode<128>, dim3((unsigned)hq, (unsigned)splits), dim3(256), st, (const __nv_bfloat16 *)q,
-                        (const __nv_bfloat16 *)k_cache, (const __nv_bfloat16 *)v_cache, pos, (float *)scratch, (uint32_t)hq,
-                        (uint32_t)hkv, scale);
-    else
-        e = launch_glue(k_attn_decode<256>, dim3((unsigned)hq, (unsigned)splits), dim3(256), st, (const __nv_bfloat16 *)q,
-                        (const __nv_bfloat16 *)k_cache, (const __nv_bfloat16 *)v_cache, pos, (float *)scratch, (uint32_t)hq,
-                        (uint32_t)hkv, scale);
+    if (head_dim == 64) e = launch_attn<64>(hq, hkv, splits, st, q, k_cache, v_cache, pos, scratch, scale);
+    else if (head_dim == 128) e = launch_attn<128>(hq, hkv, splits, st, q, k_cache, v_cache, pos, scratch, scale);
+    else e = launch_attn<256>(hq, hkv, splits, st, q, k_cache, v_cache, pos, scratch, scale);
     if (e != cudaSuccess) return fail(IXB_E_CUDA, "k_attn_decode launch: %s", cudaGetErrorString(e));
     int rc = launch_check("k_attn_decode");
     if (rc) return rc;
-    IXB_GLUE("k_attn_combine", launch_glue(k_attn_combine, dim3((unsigned)hq), dim3((unsigned)head_dim), st, (const float *)scratch,
+    const unsigned threads = (unsigned)std::max<int64_t>(head_dim, (splits + 31) / 32 * 32);
+    IXB_GLUE("k_attn_combine", launch_glue(k_attn_combine, dim3((unsigned)hq), dim3(threads), st, (const float *)scratch,
                                            (__nv_bfloat16 *)out, (const __nv_bfloat16 *)gate, (uint32_t)splits, (uint32_t)head_dim,
                                            (uint32_t)gate_stride));
 }
@@ -1185,6 +1251,12 @@ extern "C" int ixb_conv_update(const void *x, void *state, const void *w, const 
 {
     if (!x || !state || !w || !y) return fail(IXB_E_ARG, "NULL pointer argument");
     if (channels <= 0 || k < 2 || k > 8) return fail(IXB_E_ARG, "bad shape (kernel size 2..8)");
+    if (k == 4 && (channels & 3) == 0 && ((((uintptr_t)x | (uintptr_t)state | (uintptr_t)y | (uintptr_t)bias) & 7u) == 0) &&
+        ((uintptr_t)w & 15u) == 0) {
+        IXB_GLUE("k_conv_update4", launch_glue(k_conv_update4, dim3((unsigned)((channels / 4 + 63) / 64)), dim3(64), (cudaStream_t)stream,
+                                               (const __nv_bfloat16 *)x, (__nv_bfloat16 *)state, (const __nv_bfloat16 *)w,
+                                               (const __nv_bfloat16 *)bias, (__nv_bfloat16 *)y, (uint32_t)channels));
+    }
     IXB_GLUE("k_conv_update", launch_glue(k_conv_update, dim3((unsigned)((channels + 255) / 256)), dim3(256), (cudaStream_t)stream,
                                           (const __nv_bfloat16 *)x, (__nv_bfloat16 *)state, (const __nv_bfloat16 *)w,
                                           (const __nv_bfloat16 *)bias, (__nv_bfloat16 *)y, (uint32_t)channels, (uint32_t)k));

@@ -38,9 +38,10 @@ __device__ __forceinline__ float cta_sum(float v, float *red)
 
 // ---------------------------------------------------------------- residual add + RMSNorm
 // One CTA per row.  h (bf16, in/out) += delta (bf16, may be null); xn = bf16(h * rsqrt(mean(h^2) + eps)) * w.
+// Generic form (any hidden size): two passes of scalar accesses.
 __global__ void __launch_bounds__(1024)
-k_add_rmsnorm(__nv_bfloat16 *h, const __nv_bfloat16 *__restrict__ delta, const __nv_bfloat16 *__restrict__ w, float eps,
-              __nv_bfloat16 *xn, uint32_t hidden)
+k_add_rmsnorm_any(__nv_bfloat16 *h, const __nv_bfloat16 *__restrict__ delta, const __nv_bfloat16 *__restrict__ w, float eps,
+                  __nv_bfloat16 *xn, uint32_t hidden)
 {
     __shared__ float red[32];
     asm volatile("griddepcontrol.launch_dependents;");
@@ -63,14 +64,155 @@ k_add_rmsnorm(__nv_bfloat16 *h, const __nv_bfloat16 *__restrict__ delta, const _
     }
 }
 
+__device__ __forceinline__ void unpack8(const uint4 &r, float (&f)[8])
+{
+    const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        f[2 * j] = __uint_as_float(w[j] << 16);
+        f[2 * j + 1] = __uint_as_float(w[j] & 0xffff0000u);
+    }
+}
+__device__ __forceinline__ uint4 pack8(const float (&f)[8])
+{
+    uint32_t w[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+        w[j] = (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(f[2 * j])) |
+               ((uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(f[2 * j + 1])) << 16);
+    return make_uint4(w[0], w[1], w[2], w[3]);
+}
+
+// Where the residual's increment comes from when the row-parallel linear before this norm was sharded: the ranks'
+// fp32 partial sums lie as marked words in this rank's exchange buffer (see ixb_allreduce.cuh; stored there by the
+// epilogue of every rank's GEMV).  world == 0: the increment is the bf16 vector `delta` (or nothing).
+struct NormExchange {
+    const uint2 *mine;            // this rank's slots [2 parities][world][n_max]
+    uint32_t *epoch;              // this rank's call counters
+    uint32_t *err;
+    uint32_t world, n_max, counters, spin_limit;
+};
+
+// Vector form: hidden a multiple of 8 and at most 8192 (5120 with an exchange); thread t keeps elements 8 t .. 8 t + 7 in registers, so the
+// row is read once, with all loads in flight together; the norm weights are requested before the dependency wait.
+// With an exchange (W > 0) the kernel is also the second half of the all-reduce: it waits (bounded) for every
+// rank's words of this call, adds them in rank order and rounds the sum to bf16 (the value a separate finishing
+// kernel would have written), then goes on as above; the last step advances the call counters.
+constexpr int kNormExchangeThreads = 640;           // the exchange variant holds more registers: hidden <= 5120
+template <int W>
+__global__ void __launch_bounds__(W > 0 ? kNormExchangeThreads : 1024)
+k_add_rmsnorm(__nv_bfloat16 *h, const __nv_bfloat16 *__restrict__ delta, NormExchange ex, const __nv_bfloat16 *__restrict__ w,
+              float eps, __nv_bfloat16 *xn, uint32_t hidden)
+{
+    __shared__ float red[32];
+    __shared__ uint32_t e_s;
+    asm volatile("griddepcontrol.launch_dependents;");
+    const uint32_t t = threadIdx.x, i = 8u * t;
+    const bool on = i < hidden;
+    const size_t base = (size_t)blockIdx.x * hidden;
+    uint4 wr = make_uint4(0, 0, 0, 0);
+    if (on) wr = *(const uint4 *)(w + i);
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    float v[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) v[k] = 0.f;
+    uint32_t e = 0;
+    if (W > 0) {
+        if (t == 0) e_s = ex.epoch[blockIdx.x] + 1u;
+        __syncthreads();
+        e = e_s;
+    }
+    if (on) {
+        const uint4 hr = *(const uint4 *)(h + base + i);
+        unpack8(hr, v);
+        if (W > 0) {
+            const uint32_t limit = *(volatile uint32_t *)ex.err ? 64u : ex.spin_limit;
+            const uint2 *src0 = ex.mine + (size_t)((e & 1u) * W) * ex.n_max + base + i;
+            constexpr int GRP = W < 4 ? (W > 0 ? W : 1) : 4;       // senders polled together (their loads are in flight at once)
+            float o[8];
+#pragma unroll
+            for (int k = 0; k < 8; ++k) o[k] = 0.f;
+#pragma unroll
+            for (int s0 = 0; s0 < W; s0 += GRP) {
+                uint32_t val[GRP][8], mark[GRP][8];
+                for (uint32_t polls = 0;; ++polls) {
+                    bool all = true;
+#pragma unroll
+                    for (int s = 0; s < GRP; ++s) {
+                        const uint2 *src = src0 + (size_t)(s0 + s) * ex.n_max;
+#pragma unroll
+                        for (int q = 0; q < 4; ++q)
+                            asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+                                         : "=r"(val[s][2 * q]), "=r"(mark[s][2 * q]), "=r"(val[s][2 * q + 1]), "=r"(mark[s][2 * q + 1])
+                                         : "l"(src + 2 * q) : "memory");
+                    }
+#pragma unroll
+                    for (int s = 0; s < GRP; ++s)
+#pragma unroll
+                        for (int k = 0; k < 8; ++k) all = all && mark[s][k] == e;
+                    if (all) break;
+                    if (polls > limit) {
+#pragma unroll
+                        for (int s = 0; s < GRP; ++s)
+#pragma unroll
+                            for (int k = 0; k < 8; ++k)
+                                if (mark[s][k] != e) *ex.err = 1u + (uint32_t)(s0 + s);   // that sender never arrived: wrong result, no hang
+                        break;
+                    }
+                    __nanosleep(20);
+                }
+#pragma unroll
+                for (int s = 0; s < GRP; ++s)                      // in rank order: the same bits on every rank
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) o[k] += __uint_as_float(val[s][k]);
+            }
+#pragma unroll
+            for (int k = 0; k < 8; ++k) v[k] = bfround(v[k] + bfround(o[k]));
+            *(uint4 *)(h + base + i) = pack8(v);
+        } else if (delta) {
+            float d[8];
+            unpack8(*(const uint4 *)(delta + base + i), d);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) v[k] = bfround(v[k] + d[k]);
+            *(uint4 *)(h + base + i) = pack8(v);
+        }
+    }
+    float ss = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) ss += v[k] * v[k];
+    ss = cta_sum(ss, red);
+    const float r = rsqrtf(ss / (float)hidden + eps);
+    if (on) {
+        float wf[8], o[8];
+        unpack8(wr, wf);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) o[k] = bfround(v[k] * r) * wf[k];
+        *(uint4 *)(xn + base + i) = pack8(o);
+    }
+    if (W > 0 && t == 0)
+        for (uint32_t k = blockIdx.x; k < ex.counters; k += gridDim.x) ex.epoch[k] = e;   // all counters advance together
+}
+
 // ---------------------------------------------------------------- SwiGLU
-__global__ void __launch_bounds__(256)
-k_swiglu(const __nv_bfloat16 *__restrict__ g, const __nv_bfloat16 *__restrict__ u, __nv_bfloat16 *y, uint32_t n)
+// n a multiple of 8 and 16-byte aligned pointers: eight values per thread; otherwise one value per thread
+__global__ void __launch_bounds__(128)
+k_swiglu(const __nv_bfloat16 *__restrict__ g, const __nv_bfloat16 *__restrict__ u, __nv_bfloat16 *y, uint32_t n, int vec)
 {
     asm volatile("griddepcontrol.launch_dependents;");
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < n) y[i] = __hmul(__float2bfloat16_rn(silu_f(bf2f(g[i]))), u[i]);
+    const uint32_t t = blockIdx.x * blockDim.x + threadIdx.x;
+    if (vec) {
+        const uint32_t i = 8u * t;
+        if (i >= n) return;
+        float a[8], b[8], o[8];
+        unpack8(*(const uint4 *)(g + i), a);
+        unpack8(*(const uint4 *)(u + i), b);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) o[k] = bfround(silu_f(a[k])) * b[k];
+        *(uint4 *)(y + i) = pack8(o);
+    } else if (t < n) {
+        y[t] = __hmul(__float2bfloat16_rn(silu_f(bf2f(g[t]))), u[t]);
+    }
 }
 
 // ---------------------------------------------------------------- q/k norm + RoPE + cache write
@@ -134,12 +276,14 @@ k_rope_kv(__nv_bfloat16 *q, const __nv_bfloat16 *__restrict__ k, const __nv_bflo
 }
 
 // ---------------------------------------------------------------- single-query attention over the static cache
-// grid (q heads, splits), 256 threads (8 warps).  The context [0, n_ctx) (n_ctx = pos[0] + 1) is cut into `splits`
-// contiguous ranges; a warp walks its share of a range one position at a time: D / 8 lanes hold 8 elements each of
-// the position's K row (one 16-byte load), a shuffle tree gives the score, the warp keeps a running maximum,
-// denominator and weighted V sum (online softmax).  The eight warps are joined in shared memory, the split's
-// (maximum, denominator, sum[D]) goes to `part`; k_attn_combine joins the splits.
-template <int D>
+// grid (groups, splits), 256 threads (8 warps).  A group is G consecutive query heads that share one KV head
+// (G = query heads per KV head, or 1): the K and V rows of a position are loaded once and used for all G heads.
+// The context [0, n_ctx) (n_ctx = pos[0] + 1) is cut into `splits` contiguous ranges; a warp walks its share of a range
+// PPW positions at a time: D / 8 lanes hold 8 elements each of a position's K and V rows (one 16-byte load each, the
+// next iteration's rows requested before this one's arithmetic), a shuffle tree gives the G scores, and every
+// lane keeps a running maximum, denominator and weighted V sum per head (online softmax).  The CTA's warps are joined
+// in shared memory; the split's (maximum, denominator, sum[D]) per head goes to `part`; k_attn_combine joins the splits.
+template <int D, int G>
 __global__ void __launch_bounds__(256)
 k_attn_decode(const __nv_bfloat16 *__restrict__ q, const __nv_bfloat16 *__restrict__ k_cache,
               const __nv_bfloat16 *__restrict__ v_cache, const int32_t *pos, float *part, uint32_t hq, uint32_t hkv,
@@ -147,111 +291,193 @@ k_attn_decode(const __nv_bfloat16 *__restrict__ q, const __nv_bfloat16 *__restri
 {
     constexpr int LPP = D / 8;                         // lanes per position
     constexpr int PPW = 32 / LPP;                      // positions per warp iteration
-    __shared__ float sm_m[8 * PPW], sm_l[8 * PPW], sm_acc[8 * PPW][D];
+    constexpr int NS = 8 * PPW;                        // partial states per head in the CTA
+    __shared__ float sm_m[G][NS], sm_l[G][NS];
+    __shared__ float sm_acc[NS][D];                    // one head at a time
     asm volatile("griddepcontrol.launch_dependents;");
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    const uint32_t head = blockIdx.x, split = blockIdx.y, splits = gridDim.y;
-    const uint32_t kvh = head / (hq / hkv);
+    const uint32_t head0 = blockIdx.x * G, split = blockIdx.y, splits = gridDim.y;
+    const uint32_t kvh = head0 / (hq / hkv);
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
     const int sub = lane / LPP, li = lane % LPP;       // which of the warp's positions, which 8 elements
     const uint32_t n_ctx = (uint32_t)pos[0] + 1u;
     const uint32_t per = (n_ctx + splits - 1) / splits, p0 = split * per, p1 = min(p0 + per, n_ctx);
-    float qv[8];
-    {
-        const uint4 raw = *(const uint4 *)(q + (size_t)head * D + li * 8);
-        const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+    float qv[G][8];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            qv[2 * j] = __uint_as_float(w[j] << 16) * scale;
-            qv[2 * j + 1] = __uint_as_float(w[j] & 0xffff0000u) * scale;
-        }
+    for (int h = 0; h < G; ++h) {
+        unpack8(*(const uint4 *)(q + (size_t)(head0 + h) * D + li * 8), qv[h]);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) qv[h][j] *= scale;
     }
-    float m = -INFINITY, l = 0.f, acc[8];
+    float m[G], l[G], acc[G][8];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+    for (int h = 0; h < G; ++h) {
+        m[h] = -INFINITY;
+        l[h] = 0.f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[h][j] = 0.f;
+    }
     // the trip count is the same for all lanes of a warp (the shuffles below need every lane); a lane whose position
     // lies beyond the range reads position p1 - 1 and drops the result
-    for (uint32_t pb = p0 + (uint32_t)(wid * PPW); pb < p1; pb += 8 * PPW) {
+    const size_t row_stride = (size_t)hkv * D;
+    const __nv_bfloat16 *kb = k_cache + (size_t)kvh * D + li * 8, *vb = v_cache + (size_t)kvh * D + li * 8;
+    uint32_t pb = p0 + (uint32_t)(wid * PPW);
+    uint4 kn = make_uint4(0, 0, 0, 0), vn = kn;
+    if (pb < p1) {
+        const uint32_t p = min(pb + (uint32_t)sub, p1 - 1u);
+        kn = *(const uint4 *)(kb + p * row_stride);
+        vn = *(const uint4 *)(vb + p * row_stride);
+    }
+    for (; pb < p1; pb += 8 * PPW) {
         const bool live = pb + (uint32_t)sub < p1;
-        const uint32_t p = live ? pb + (uint32_t)sub : p1 - 1u;
-        const size_t off = ((size_t)p * hkv + kvh) * D + li * 8;
-        const uint4 kr = *(const uint4 *)(k_cache + off);
-        const uint4 vr = *(const uint4 *)(v_cache + off);
-        const uint32_t kw[4] = {kr.x, kr.y, kr.z, kr.w}, vw[4] = {vr.x, vr.y, vr.z, vr.w};
-        float s = 0.f;
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            s = fmaf(qv[2 * j], __uint_as_float(kw[j] << 16), s);
-            s = fmaf(qv[2 * j + 1], __uint_as_float(kw[j] & 0xffff0000u), s);
+        const uint4 kr = kn, vr = vn;
+        const uint32_t nb = pb + 8 * PPW;
+        if (nb < p1) {                                 // warp uniform
+            const uint32_t p = min(nb + (uint32_t)sub, p1 - 1u);
+            kn = *(const uint4 *)(kb + p * row_stride);
+            vn = *(const uint4 *)(vb + p * row_stride);
         }
+        float kf[8], vf[8];
+        unpack8(kr, kf);
+        unpack8(vr, vf);
 #pragma unroll
-        for (int d = LPP / 2; d > 0; d >>= 1) s += __shfl_xor_sync(0xffffffffu, s, d);
-        if (live) {
-            const float mn = fmaxf(m, s), c = __expf(m - mn), e = __expf(s - mn);
-            l = l * c + e;
+        for (int h = 0; h < G; ++h) {
+            float s = 0.f;
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                acc[2 * j] = fmaf(acc[2 * j], c, e * __uint_as_float(vw[j] << 16));
-                acc[2 * j + 1] = fmaf(acc[2 * j + 1], c, e * __uint_as_float(vw[j] & 0xffff0000u));
+            for (int j = 0; j < 8; ++j) s = fmaf(qv[h][j], kf[j], s);
+#pragma unroll
+            for (int d = LPP / 2; d > 0; d >>= 1) s += __shfl_xor_sync(0xffffffffu, s, d);
+            if (live) {
+                const float mn = fmaxf(m[h], s), c = __expf(m[h] - mn), e = __expf(s - mn);
+                l[h] = l[h] * c + e;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) acc[h][j] = fmaf(acc[h][j], c, e * vf[j]);
+                m[h] = mn;
             }
-            m = mn;
         }
     }
-    // join the 8 * PPW partial states of the CTA
+    // join the NS partial states of the CTA, head by head
     const int slot = wid * PPW + sub;
     if (li == 0) {
-        sm_m[slot] = m;
-        sm_l[slot] = l;
+#pragma unroll
+        for (int h = 0; h < G; ++h) {
+            sm_m[h][slot] = m[h];
+            sm_l[h][slot] = l[h];
+        }
     }
 #pragma unroll
-    for (int j = 0; j < 8; ++j) sm_acc[slot][li * 8 + j] = acc[j];
-    __syncthreads();
-    float M = -INFINITY;
-    for (int s2 = 0; s2 < 8 * PPW; ++s2) M = fmaxf(M, sm_m[s2]);
-    float *out = part + ((size_t)head * splits + split) * (D + 2);
-    if (threadIdx.x < D) {
-        float a = 0.f;
-        for (int s2 = 0; s2 < 8 * PPW; ++s2)
-            if (sm_m[s2] != -INFINITY) a += sm_acc[s2][threadIdx.x] * __expf(sm_m[s2] - M);
-        out[2 + threadIdx.x] = a;
-    }
-    if (threadIdx.x == 0) {
-        float L = 0.f;
-        for (int s2 = 0; s2 < 8 * PPW; ++s2)
-            if (sm_m[s2] != -INFINITY) L += sm_l[s2] * __expf(sm_m[s2] - M);
-        out[0] = M;
-        out[1] = L;
+    for (int h = 0; h < G; ++h) {
+        __syncthreads();                               // sm_acc is free (and, first time, sm_m / sm_l are written)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) sm_acc[slot][li * 8 + j] = acc[h][j];
+        __syncthreads();
+        float M = -INFINITY;
+#pragma unroll
+        for (int s2 = 0; s2 < NS; ++s2) M = fmaxf(M, sm_m[h][s2]);
+        float *out = part + ((size_t)(head0 + h) * splits + split) * (D + 2);
+        if (threadIdx.x < D) {
+            float a = 0.f;
+#pragma unroll
+            for (int s2 = 0; s2 < NS; ++s2)
+                if (sm_m[h][s2] != -INFINITY) a += sm_acc[s2][threadIdx.x] * __expf(sm_m[h][s2] - M);
+            out[2 + threadIdx.x] = a;
+        }
+        if (threadIdx.x == 0) {
+            float L = 0.f;
+            for (int s2 = 0; s2 < NS; ++s2)
+                if (sm_m[h][s2] != -INFINITY) L += sm_l[h][s2] * __expf(sm_m[h][s2] - M);
+            out[0] = M;
+            out[1] = L;
+        }
     }
 }
 
-// grid q heads, D threads: out[head][d] = sum over the splits, optional sigmoid gate (gate[head][d], bf16)
+// grid q heads, D threads: out[head][d] = sum over the splits, optional sigmoid gate (gate[head][d], bf16).
+// The splits' maxima and denominators are fetched by one thread each, the weighted sums with independent loads.
+constexpr int kAttnMaxSplits = 256;
 __global__ void __launch_bounds__(256)
 k_attn_combine(const float *__restrict__ part, __nv_bfloat16 *out, const __nv_bfloat16 *__restrict__ gate, uint32_t splits,
                uint32_t D, uint32_t gate_stride)
 {
+    __shared__ float wgt[kAttnMaxSplits], red[32];
     asm volatile("griddepcontrol.launch_dependents;");
+    const uint32_t head = blockIdx.x, t = threadIdx.x;
+    float gv = 0.f;
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    const uint32_t head = blockIdx.x, d = threadIdx.x;
-    if (d >= D) return;
+    if (gate && t < D) gv = bf2f(gate[(size_t)head * gate_stride + t]);
     const float *p = part + (size_t)head * splits * (D + 2);
-    float M = -INFINITY;
-    for (uint32_t s = 0; s < splits; ++s) M = fmaxf(M, p[s * (D + 2)]);
-    float L = 0.f, a = 0.f;
-    for (uint32_t s = 0; s < splits; ++s) {
-        const float ms = p[s * (D + 2)];
-        if (ms == -INFINITY) continue;
-        const float c = __expf(ms - M);
-        L += p[s * (D + 2) + 1] * c;
-        a += p[s * (D + 2) + 2 + d] * c;
+    float ms = -INFINITY, ls = 0.f;
+    if (t < splits) {
+        const float2 ml = *(const float2 *)(p + (size_t)t * (D + 2));
+        ms = ml.x;
+        ls = ml.y;
     }
+    // CTA-wide maximum
+    float M = ms;
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, d));
+    if ((t & 31u) == 0) red[t >> 5] = M;
+    __syncthreads();
+    M = red[0];
+    for (uint32_t i = 1; i < (blockDim.x >> 5); ++i) M = fmaxf(M, red[i]);
+    const float c = ms == -INFINITY ? 0.f : __expf(ms - M);
+    if (t < splits) wgt[t] = c;
+    const float L = cta_sum(ls * c, red);              // (its barriers also publish wgt)
+    if (t >= D) return;
+    float a = 0.f;
+#pragma unroll 4
+    for (uint32_t s = 0; s < splits; ++s) a = fmaf(p[(size_t)s * (D + 2) + 2 + t], wgt[s], a);
     float o = bfround(a / L);
-    if (gate) o = bf2f(__hmul(__float2bfloat16_rn(o), __float2bfloat16_rn(sigmoid_f(bf2f(gate[(size_t)head * gate_stride + d])))));
-    out[(size_t)head * D + d] = __float2bfloat16_rn(o);
+    if (gate) o = bfround(o) * bfround(sigmoid_f(gv));
+    out[(size_t)head * D + t] = __float2bfloat16_rn(o);
 }
 
-// ---------------------------------------------------------------- causal conv1d update (depth-wise, kernel K <= 8)
+// ---------------------------------------------------------------- causal conv1d update (depth-wise)
 // state [C][K - 1] (bf16, oldest first) holds the last K - 1 inputs of every channel;
 // y_c = silu(sum_j w[c][j] * input_{t - K + 1 + j} + bias_c), then the state takes x in.
+// K == 4 and C a multiple of 4: a thread looks after four channels with 8- and 16-byte accesses, everything
+// requested at once (the weights before the dependency wait); other shapes take the scalar kernel.
+__global__ void __launch_bounds__(64)
+k_conv_update4(const __nv_bfloat16 *__restrict__ x, __nv_bfloat16 *state, const __nv_bfloat16 *__restrict__ w,
+               const __nv_bfloat16 *__restrict__ bias, __nv_bfloat16 *y, uint32_t C)
+{
+    asm volatile("griddepcontrol.launch_dependents;");
+    const uint32_t c = 4u * (blockIdx.x * blockDim.x + threadIdx.x);
+    const bool on = c < C;
+    uint4 w0 = make_uint4(0, 0, 0, 0), w1 = w0;
+    uint2 bb = make_uint2(0, 0);
+    if (on) {
+        w0 = *(const uint4 *)(w + (size_t)c * 4);
+        w1 = *(const uint4 *)(w + (size_t)c * 4 + 8);
+        if (bias) bb = *(const uint2 *)(bias + c);
+    }
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (!on) return;
+    uint2 *sp = (uint2 *)(state + (size_t)c * 3);      // 12 state values of the four channels: 24 bytes
+    const uint2 s0 = sp[0], s1 = sp[1], s2 = sp[2];
+    const uint2 xr = *(const uint2 *)(x + c);
+    const uint32_t sw[6] = {s0.x, s0.y, s1.x, s1.y, s2.x, s2.y}, ww[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+    const uint32_t xw[2] = {xr.x, xr.y}, bw[2] = {bb.x, bb.y};
+    auto half = [](const uint32_t *a, int i) { return __uint_as_float((i & 1) ? (a[i >> 1] & 0xffff0000u) : (a[i >> 1] << 16)); };
+    auto bits = [](const uint32_t *a, int i) { return (i & 1) ? (a[i >> 1] >> 16) : (a[i >> 1] & 0xffffu); };
+    uint32_t ns[12], yo[4];
+#pragma unroll
+    for (int ch = 0; ch < 4; ++ch) {
+        float acc = half(bw, ch);
+#pragma unroll
+        for (int j = 0; j < 3; ++j) acc = fmaf(half(ww, 4 * ch + j), half(sw, 3 * ch + j), acc);
+        acc = fmaf(half(ww, 4 * ch + 3), half(xw, ch), acc);
+        yo[ch] = (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(silu_f(acc)));
+        ns[3 * ch] = bits(sw, 3 * ch + 1);
+        ns[3 * ch + 1] = bits(sw, 3 * ch + 2);
+        ns[3 * ch + 2] = bits(xw, ch);
+    }
+    sp[0] = make_uint2(ns[0] | ns[1] << 16, ns[2] | ns[3] << 16);
+    sp[1] = make_uint2(ns[4] | ns[5] << 16, ns[6] | ns[7] << 16);
+    sp[2] = make_uint2(ns[8] | ns[9] << 16, ns[10] | ns[11] << 16);
+    *(uint2 *)(y + c) = make_uint2(yo[0] | yo[1] << 16, yo[2] | yo[3] << 16);
+}
+
 __global__ void __launch_bounds__(256)
 k_conv_update(const __nv_bfloat16 *__restrict__ x, __nv_bfloat16 *state, const __nv_bfloat16 *__restrict__ w,
               const __nv_bfloat16 *__restrict__ bias, __nv_bfloat16 *y, uint32_t C, uint32_t K)
@@ -290,9 +516,16 @@ k_gdn_step(const __nv_bfloat16 *__restrict__ qkv, const __nv_bfloat16 *__restric
     constexpr int DK = 128, DV = 128;
     __shared__ float red[32], qs[DK], ks[DK], part_k[2][DV], part_q[2][DV];
     asm volatile("griddepcontrol.launch_dependents;");
-    asm volatile("griddepcontrol.wait;" ::: "memory");
     const uint32_t vh = blockIdx.x, kh = vh / (hv / hk);
     const uint32_t tid = threadIdx.x, j = tid & 127u, ih = tid >> 7;
+    // the head's state was last written by this kernel one token ago and its parameters are constants: both are
+    // requested before the dependency wait, so the longest loads overlap the tail of the kernel ahead
+    float *S = state + (size_t)vh * DK * DV;
+    float s[64];
+#pragma unroll
+    for (int i = 0; i < 64; ++i) s[i] = S[(size_t)(64 * ih + i) * DV + j];
+    const float a_log = A_log[vh], dtb = dt_bias[vh], nw = bf2f(norm_w[j]);
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     // qkv = [q (hk * DK) | k (hk * DK) | v (hv * DV)]
     const __nv_bfloat16 *qp = qkv + (size_t)kh * DK, *kp = qkv + (size_t)(hk + kh) * DK;
     const __nv_bfloat16 *vp = qkv + (size_t)2 * hk * DK + (size_t)vh * DV;
@@ -307,15 +540,13 @@ k_gdn_step(const __nv_bfloat16 *__restrict__ qkv, const __nv_bfloat16 *__restric
         ks[tid] = ke * rsqrtf(kn + 1e-6f);
     }
     __syncthreads();
-    const float av = bf2f(a_in[vh]) + dt_bias[vh];
+    const float av = bf2f(a_in[vh]) + dtb;
     const float sp = av > 20.f ? av : log1pf(__expf(av));
-    const float g = __expf(-__expf(A_log[vh]) * sp), beta = sigmoid_f(bf2f(b_in[vh]));
-    float *S = state + (size_t)vh * DK * DV;
-    float s[64];
+    const float g = __expf(-__expf(a_log) * sp), beta = sigmoid_f(bf2f(b_in[vh]));
     float sk = 0.f, sq = 0.f;
 #pragma unroll
     for (int i = 0; i < 64; ++i) {
-        s[i] = S[(size_t)(64 * ih + i) * DV + j] * g;
+        s[i] *= g;
         sk = fmaf(s[i], ks[64 * ih + i], sk);
         sq = fmaf(s[i], qs[64 * ih + i], sq);
     }
@@ -334,7 +565,7 @@ k_gdn_step(const __nv_bfloat16 *__restrict__ qkv, const __nv_bfloat16 *__restric
     const float ss = cta_sum(ih == 0 ? ob * ob : 0.f, red);
     if (ih == 0) {
         const float r = rsqrtf(ss / (float)DV + eps);
-        const __nv_bfloat16 nv = __hmul(__float2bfloat16_rn(ob * r), norm_w[j]);
+        const __nv_bfloat16 nv = __float2bfloat16_rn(bfround(ob * r) * nw);
         const float zg = silu_f(bf2f(z[(size_t)vh * DV + j]));
         out[(size_t)vh * DV + j] = __hmul(nv, __float2bfloat16_rn(zg));
     }

@@ -11,7 +11,7 @@ import torch
 
 from . import _lib
 
-__all__ = ["add_rmsnorm", "swiglu", "rope_kv", "AttnDecode", "conv_update", "gdn_step", "rope_tables"]
+__all__ = ["add_rmsnorm", "finish_add_rmsnorm", "swiglu", "rope_kv", "AttnDecode", "conv_update", "gdn_step", "rope_tables"]
 
 
 def _st(t):
@@ -33,6 +33,20 @@ def add_rmsnorm(h: torch.Tensor, delta: torch.Tensor | None, w: torch.Tensor, ep
     with torch.cuda.device(h.device):
         _lib.check(_lib.lib().ixb_add_rmsnorm(h.data_ptr(), None if delta is None else delta.data_ptr(), w.data_ptr(),
                                               float(eps), out.data_ptr(), rows, hidden, _st(h)))
+    return out
+
+
+def finish_add_rmsnorm(ar, h: torch.Tensor, w: torch.Tensor, eps: float, out: torch.Tensor | None = None):
+    """Second half of a row-parallel exchange (after ``P6Packed.gemv_push(x, ar)``) fused with the residual add and the
+    RMSNorm that follow it: h [rows, hidden] += bf16(sum over the ranks' partial sums); returns rmsnorm(h) * w.
+    The same bits as ``ar.finish`` into a bf16 vector followed by ``add_rmsnorm``."""
+    _bf16(h, w)
+    rows, hidden = h.reshape(-1, h.shape[-1]).shape
+    if out is None:
+        out = torch.empty_like(h)
+    with torch.cuda.device(h.device):
+        _lib.check(_lib.lib().ixb_allreduce_finish_add_rmsnorm(ar._ptrs, ar.rank, ar.world, ar.n_max, h.data_ptr(), w.data_ptr(),
+                                                               float(eps), out.data_ptr(), rows, hidden, _st(h)))
     return out
 
 
@@ -77,8 +91,12 @@ class AttnDecode:
     def __init__(self, hq: int, hkv: int, head_dim: int, device, splits: int | None = None):
         self.hq, self.hkv, self.d = hq, hkv, head_dim
         if splits is None:
+            # one CTA looks after all query heads of a KV head (group sizes 2, 3, 4, 6, 8; else one head per CTA):
+            # as many context splits as give about one CTA per SM
             sms = torch.cuda.get_device_properties(device).multi_processor_count
-            splits = max(1, (2 * sms) // hq)
+            rep = hq // hkv
+            groups = hq // rep if rep in (2, 3, 4, 6, 8) else hq
+            splits = max(1, min(256, sms // groups))
         self.splits = int(splits)
         self.scratch = torch.empty(_lib.lib().ixb_attn_scratch_bytes(hq, head_dim, self.splits), dtype=torch.uint8, device=device)
 

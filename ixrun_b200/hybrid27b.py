@@ -7,7 +7,7 @@ SwiGLU 17408, vocabulary 151936) on packed INT8-X linears, tensor-parallel with 
 The whole token step -- embedding row, 64 blocks, final norm, lm_head, greedy arg-max, the token fed back and the
 position advanced -- is ONE CUDA graph with no host round trip, so a decode of T tokens is T graph replays.
 
-Per block (9 or 10 launches on one GPU, two more on several); the packed linears that share an input are fused
+Per block (9 or 10 launches, on one GPU as on several); the packed linears that share an input are fused
 row-wise into one resident tensor, every part keeping its own per-tensor scale (p6.P6Packed.fuse):
   gated-delta-rule layer  residual add + RMSNorm -> ONE packed GEMV for in_proj_qkv | z | a | b -> causal conv1d
                           update + SiLU -> one recurrent step per value head (state fp32 [heads][128][128], read and
@@ -21,8 +21,8 @@ it is this library's glue kernels, all of them part of the programmatic-dependen
 
 Tensor parallelism: in-projections, gate and up are column-parallel (heads / rows split; with more ranks than KV heads
 a rank still holds one whole KV head), out_proj / o_proj / down_proj are row-parallel: their fp32 partial sums leave the
-GEMV's epilogue as peer stores into every rank's exchange buffer and one small kernel adds them up -- one exchange per
-token-mixer block and one per MLP block.  lm_head is split by vocabulary; the ranks exchange (max, index) pairs.
+GEMV's epilogue as peer stores into every rank's exchange buffer, and the residual add + RMSNorm kernel that follows
+waits for them and adds them up -- one exchange per token-mixer block and one per MLP block, no launch of its own.  lm_head is split by vocabulary; the ranks exchange (max, index) pairs.
 With --nccl the partial sums go through eager NCCL all-reduces instead (no graph; a cross-check, not a fast path).
 
 The fused q|gate projection is stored as [all q heads | all gate heads] (a row permutation of the per-head
@@ -214,16 +214,24 @@ class Hybrid27B:
 
     # ------------------------------------------------------------------ one block
     def _row_parallel(self, lin, x):
-        """Row-parallel linear + the exchange; the summed bf16 result lands in self.d_out."""
+        """Row-parallel linear.  One GPU: the bf16 result lands in self.d_out, the caller's next add + norm takes it
+        from there.  Several: the fp32 partial sums leave the GEMV as peer stores; returns None, and the caller's next
+        norm kernel is also the second half of the exchange (glue.finish_add_rmsnorm)."""
         if self.ar is not None:
-            self.ar.finish(lin.gemv_push(x, self.ar), self.d_out)
-        elif self.nccl:
+            lin.gemv_push(x, self.ar)
+            return None
+        if self.nccl:
             lin.gemv(x, out=self.y32)
             dist.all_reduce(self.y32)
             self.d_out.copy_(self.y32)
         else:
             lin.gemv(x, out=self.d_out)
         return self.d_out
+
+    def _add_norm(self, delta, w, first=False):
+        if self.ar is not None and not first:
+            return G.finish_add_rmsnorm(self.ar, self.h, w, self.cfg.eps, out=self.xn)
+        return G.add_rmsnorm(self.h, delta, w, self.cfg.eps, out=self.xn)
 
     def _mixer(self, L):
         cfg, g = self.cfg, self.geo
@@ -245,15 +253,16 @@ class Hybrid27B:
     def _step(self):
         cfg = self.cfg
         torch.index_select(self.embed, 0, self.tok, out=self.h)
-        delta = None
+        delta, first = None, True
         for L in self.layers:
-            G.add_rmsnorm(self.h, delta, L["ln1"], cfg.eps, out=self.xn)
+            self._add_norm(delta, L["ln1"], first)
+            first = False
             delta = self._mixer(L)
-            G.add_rmsnorm(self.h, delta, L["ln2"], cfg.eps, out=self.xn)
+            self._add_norm(delta, L["ln2"])
             L["gate_up"].gemv(self.xn, out=self.gu)
             G.swiglu(self.g_, self.u_, out=self.act[0])
             delta = self._row_parallel(L["down"], self.act)
-        G.add_rmsnorm(self.h, delta, self.ln_f, cfg.eps, out=self.xn)
+        self._add_norm(delta, self.ln_f, first)
         if self.lm_head is not None:
             logits = F.linear(self.xn, self.lm_head).float()
             val, idx = logits.max(dim=-1)
@@ -312,7 +321,7 @@ def launches_per_token(cfg: HybridConfig, world: int) -> int:
     """Kernels of this library in one token step (packed GEMVs, glue, exchange)."""
     n = 0
     for li in range(cfg.n_layers):
-        n += (6 if cfg.is_attn(li) else 5) + 4 + (2 if world > 1 else 0)
+        n += (6 if cfg.is_attn(li) else 5) + 4          # on several GPUs the norm kernels also finish the exchanges
     return n + 1 + (1 if world > 1 else 0)
 
 

@@ -150,10 +150,12 @@ class PeerAllReduce:
         self._nbytes = nbytes
 
     @classmethod
-    def loopback(cls, n_max: int, device, world: int, rank: int = 0) -> "PeerAllReduce":
+    def loopback(cls, n_max: int, device, world: int, rank: int = 0, share: "PeerAllReduce | None" = None) -> "PeerAllReduce":
         """One GPU playing rank `rank` of `world`: every peer pointer is this rank's own buffer.  With world > 1 the
         other ranks never send, so a wait runs out -- the way to exercise the bounded wait and the error word on one
-        GPU (set a short limit with ``set_spin_limit`` first)."""
+        GPU (set a short limit with ``set_spin_limit`` first).  With `share` (another loopback object of the same
+        geometry) the two use one buffer: the ranks' sending halves (``P6Packed.gemv_push``) can then be run one after
+        the other on one GPU, each as its own rank, before a single finishing call adds them up."""
         import ctypes as C
 
         from . import _lib
@@ -163,7 +165,9 @@ class PeerAllReduce:
         nbytes = int(_lib.lib().ixb_allreduce_bytes(self.world, self.n_max))
         if nbytes == 0:
             raise ValueError(f"unsupported all-reduce geometry: world={world}, n_max={n_max}")
-        self.buf = torch.zeros(nbytes, dtype=torch.uint8, device=self.device)
+        if share is not None and (share.world, share.n_max) != (self.world, self.n_max):
+            raise ValueError("shared loopback objects must have the same geometry")
+        self.buf = share.buf if share is not None else torch.zeros(nbytes, dtype=torch.uint8, device=self.device)
         self._ptrs = (C.c_void_p * self.world)(*([self.buf.data_ptr()] * self.world))
         self._nbytes = nbytes
         self._loopback = True

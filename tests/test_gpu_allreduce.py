@@ -139,3 +139,38 @@ def test_a_wait_that_runs_out_sets_the_error_word_and_returns():
     # a single rank is unaffected
     ar1 = PeerAllReduce(n, "cuda")
     assert torch.equal(ar1(x, out_dtype=torch.float32), x) and not ar1.timed_out()
+
+
+@pytest.mark.parametrize("world", [1, 2, 4, 8])
+@pytest.mark.parametrize("rows,hidden", [(1, 5120), (3, 512), (1, 2048)])
+def test_finishing_norm_equals_finish_then_add_rmsnorm(world, rows, hidden):
+    """Every rank's sending half runs in turn on this one GPU (loopback objects sharing one buffer, each launch as its
+    own rank with its own shard), then ONE finishing call adds the words up: the fused finish + residual add + RMSNorm
+    kernel gives the same bits as the finishing kernel followed by the add + norm kernel, call after call."""
+    from ixrun_b200.glue import add_rmsnorm, finish_add_rmsnorm
+    from ixrun_b200.parallel import PeerAllReduce
+
+    in_f = 2176
+    n = rows * hidden
+    ars = [PeerAllReduce.loopback(max(n, 5120), "cuda", world=world, rank=0)]
+    ars += [PeerAllReduce.loopback(max(n, 5120), "cuda", world=world, rank=r, share=ars[0]) for r in range(1, world)]
+    shards = [_shard(hidden, in_f, 20 + r) for r in range(world)]
+    w = (1 + 0.1 * torch.randn(hidden, device="cuda")).bfloat16()
+    for call in range(3):
+        xs = [torch.randn(rows, in_f, device="cuda").bfloat16() for _ in range(world)]
+        h0 = torch.randn(rows, hidden, device="cuda").bfloat16()
+        # two kernels
+        for r in range(world):
+            shards[r].gemv_push(xs[r], ars[r])
+        d = ars[0].finish(n, torch.empty(rows, hidden, dtype=torch.bfloat16, device="cuda"))
+        ref32 = sum(shards[r].gemv(xs[r], out_dtype=torch.float32) for r in range(world))
+        assert float((d.float() - ref32).abs().max()) <= 2.0 ** -7 * float(ref32.abs().max())
+        h_ref = h0.clone()
+        xn_ref = add_rmsnorm(h_ref, d, w, 1e-6)
+        # one kernel
+        for r in range(world):
+            shards[r].gemv_push(xs[r], ars[r])
+        h = h0.clone()
+        xn = finish_add_rmsnorm(ars[0], h, w, 1e-6)
+        assert torch.equal(h, h_ref) and torch.equal(xn, xn_ref)
+    assert not ars[0].timed_out()
