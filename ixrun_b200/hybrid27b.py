@@ -277,8 +277,8 @@ class Hybrid27B:
                     allv = self.mx.clone()
                     dist.all_reduce(allv)
                 pairs = allv[: 2 * self.world].view(self.world, 2)
-                best = pairs[:, 0].argmax()
-                idx = pairs[best, 1].long().view(1)
+                best = pairs[:, 0].argmax().view(1)
+                idx = pairs[:, 1].index_select(0, best).long()          # (no host round trip: this runs inside the graph)
             self.toks.index_copy_(0, self.n_done, idx)
             self.tok.copy_(idx)
         self.n_done += 1
