@@ -321,38 +321,52 @@ k_attn_decode(const __nv_bfloat16 *__restrict__ q, const __nv_bfloat16 *__restri
     // lies beyond the range reads position p1 - 1 and drops the result
     const size_t row_stride = (size_t)hkv * D;
     const __nv_bfloat16 *kb = k_cache + (size_t)kvh * D + li * 8, *vb = v_cache + (size_t)kvh * D + li * 8;
+    // a ring of PF iterations' rows in registers: the loads of iteration i + PF are requested before the arithmetic
+    // of iteration i, so a warp has PF round trips to memory in flight
+    constexpr int PF = 4;
+    constexpr uint32_t STR = 8 * PPW;                  // positions the CTA covers per iteration
     uint32_t pb = p0 + (uint32_t)(wid * PPW);
-    uint4 kn = make_uint4(0, 0, 0, 0), vn = kn;
-    if (pb < p1) {
-        const uint32_t p = min(pb + (uint32_t)sub, p1 - 1u);
-        kn = *(const uint4 *)(kb + p * row_stride);
-        vn = *(const uint4 *)(vb + p * row_stride);
-    }
-    for (; pb < p1; pb += 8 * PPW) {
-        const bool live = pb + (uint32_t)sub < p1;
-        const uint4 kr = kn, vr = vn;
-        const uint32_t nb = pb + 8 * PPW;
-        if (nb < p1) {                                 // warp uniform
-            const uint32_t p = min(nb + (uint32_t)sub, p1 - 1u);
-            kn = *(const uint4 *)(kb + p * row_stride);
-            vn = *(const uint4 *)(vb + p * row_stride);
+    uint4 kq[PF], vq[PF];
+#pragma unroll
+    for (int st = 0; st < PF; ++st) {
+        kq[st] = make_uint4(0, 0, 0, 0);
+        vq[st] = kq[st];
+        const uint32_t cur = pb + st * STR;
+        if (cur < p1) {                                // warp uniform
+            const uint32_t p = min(cur + (uint32_t)sub, p1 - 1u);
+            kq[st] = *(const uint4 *)(kb + p * row_stride);
+            vq[st] = *(const uint4 *)(vb + p * row_stride);
         }
-        float kf[8], vf[8];
-        unpack8(kr, kf);
-        unpack8(vr, vf);
+    }
+    for (; pb < p1; pb += PF * STR) {
 #pragma unroll
-        for (int h = 0; h < G; ++h) {
-            float s = 0.f;
+        for (int st = 0; st < PF; ++st) {
+            const uint32_t cur = pb + st * STR;
+            if (cur >= p1) break;                      // warp uniform
+            const bool live = cur + (uint32_t)sub < p1;
+            float kf[8], vf[8];
+            unpack8(kq[st], kf);
+            unpack8(vq[st], vf);
+            const uint32_t nxt = cur + PF * STR;
+            if (nxt < p1) {                            // warp uniform
+                const uint32_t p = min(nxt + (uint32_t)sub, p1 - 1u);
+                kq[st] = *(const uint4 *)(kb + p * row_stride);
+                vq[st] = *(const uint4 *)(vb + p * row_stride);
+            }
 #pragma unroll
-            for (int j = 0; j < 8; ++j) s = fmaf(qv[h][j], kf[j], s);
+            for (int h = 0; h < G; ++h) {
+                float s = 0.f;
 #pragma unroll
-            for (int d = LPP / 2; d > 0; d >>= 1) s += __shfl_xor_sync(0xffffffffu, s, d);
-            if (live) {
-                const float mn = fmaxf(m[h], s), c = __expf(m[h] - mn), e = __expf(s - mn);
-                l[h] = l[h] * c + e;
+                for (int j = 0; j < 8; ++j) s = fmaf(qv[h][j], kf[j], s);
 #pragma unroll
-                for (int j = 0; j < 8; ++j) acc[h][j] = fmaf(acc[h][j], c, e * vf[j]);
-                m[h] = mn;
+                for (int d = LPP / 2; d > 0; d >>= 1) s += __shfl_xor_sync(0xffffffffu, s, d);
+                if (live) {
+                    const float mn = fmaxf(m[h], s), c = __expf(m[h] - mn), e = __expf(s - mn);
+                    l[h] = l[h] * c + e;
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) acc[h][j] = fmaf(acc[h][j], c, e * vf[j]);
+                    m[h] = mn;
+                }
             }
         }
     }
@@ -424,9 +438,27 @@ k_attn_combine(const float *__restrict__ part, __nv_bfloat16 *out, const __nv_bf
     if (t < splits) wgt[t] = c;
     const float L = cta_sum(ls * c, red);              // (its barriers also publish wgt)
     if (t >= D) return;
-    float a = 0.f;
-#pragma unroll 4
-    for (uint32_t s = 0; s < splits; ++s) a = fmaf(p[(size_t)s * (D + 2) + 2 + t], wgt[s], a);
+    float a0 = 0.f, a1 = 0.f;
+    const float *pt = p + 2 + t;
+    uint32_t s2 = 0;
+    for (; s2 + 16 <= splits; s2 += 16) {              // sixteen independent loads in flight
+        float v[16];
+#pragma unroll
+        for (int k = 0; k < 16; ++k) v[k] = pt[(size_t)(s2 + k) * (D + 2)];
+#pragma unroll
+        for (int k = 0; k < 16; k += 2) {
+            a0 = fmaf(v[k], wgt[s2 + k], a0);
+            a1 = fmaf(v[k + 1], wgt[s2 + k + 1], a1);
+        }
+    }
+    {
+        float v[16];
+#pragma unroll
+        for (int k = 0; k < 16; ++k) v[k] = s2 + k < splits ? pt[(size_t)(s2 + k) * (D + 2)] : 0.f;
+#pragma unroll
+        for (int k = 0; k < 16; ++k) a0 = fmaf(v[k], s2 + k < splits ? wgt[s2 + k] : 0.f, a0);
+    }
+    const float a = a0 + a1;
     float o = bfround(a / L);
     if (gate) o = bfround(o) * bfround(sigmoid_f(gv));
     out[(size_t)head * D + t] = __float2bfloat16_rn(o);
