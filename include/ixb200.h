@@ -181,6 +181,14 @@ int ixb_p6_decode(const ixb_p6 *t, void *out_device, int out_kind, ixb_stream_t 
 size_t ixb_p6_gemv_scratch_bytes(int64_t out_f, int64_t in_f, int64_t m_rows);
 int ixb_p6_gemv(const ixb_p6 *t, const void *x_device, int64_t m_rows, const void *bias_device,
                 void *y_device, int y_is_f32, void *scratch_device, size_t scratch_bytes, ixb_stream_t stream);
+/* Small-M GEMM on the resident layout: 1..64 activation rows, y[m][n] as ixb_p6_gemv defines it, in one pass over
+ * the tensor's bytes on the tcgen05 tensor cores (accumulator in TMEM); the bf16 weights exist only in shared memory.
+ * Takes the place of the reference's decode + dense matmul for 9..64 rows (ixrun/engine.py:171-173; precedent for a
+ * fused kernel: ixrun/tpab_gemm.py:34-94).  in_f must be a multiple of 64.  scratch: ixb_p6_gemm_scratch_bytes bytes,
+ * 256-byte aligned, any contents (split-K partial sums, added in a fixed order: reproducible). */
+size_t ixb_p6_gemm_scratch_bytes(int64_t out_f, int64_t in_f, int64_t m_rows);
+int ixb_p6_gemm(const ixb_p6 *t, const void *x_device, int64_t m_rows, const void *bias_device, void *y_device,
+                int y_is_f32, void *scratch_device, size_t scratch_bytes, ixb_stream_t stream);
 /*
  * Programmatic dependent launch for ixb_p6_gemv (process-wide switch, off by
  * default; returns the previous setting).  No counterpart in the reference,

@@ -23,6 +23,7 @@ SYMBOLS = (
     "ixb_gemm_scratch_bytes", "ixb_gemm",
     "ixb_pack_workspace_bytes", "ixb_quantize_codes", "ixb_count_codes", "ixb_pack_codes",
     "ixb_p6_blocks", "ixb_p6_build", "ixb_p6_decode", "ixb_p6_gemv_scratch_bytes", "ixb_p6_gemv", "ixb_set_pdl",
+    "ixb_p6_gemm_scratch_bytes", "ixb_p6_gemm",
     "ixb_allreduce_bytes", "ixb_allreduce", "ixb_p6_gemv_push", "ixb_allreduce_finish", "ixb_p6_gemv_allreduce", "ixb_allreduce_spin_limit",
     "ixb_add_rmsnorm", "ixb_allreduce_finish_add_rmsnorm", "ixb_swiglu", "ixb_rope_kv", "ixb_attn_scratch_bytes", "ixb_attn_decode", "ixb_conv_update", "ixb_gdn_step",
 )
@@ -128,6 +129,10 @@ def lib():
     L.ixb_rope_kv.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i64, i64, i64, i64, i64, f32, i64, i64, vp]
     L.ixb_allreduce_finish_add_rmsnorm.restype = C.c_int
     L.ixb_allreduce_finish_add_rmsnorm.argtypes = [C.POINTER(C.c_void_p), C.c_int, C.c_int, i64, vp, vp, f32, vp, i64, i64, vp]
+    L.ixb_p6_gemm_scratch_bytes.restype = sz
+    L.ixb_p6_gemm_scratch_bytes.argtypes = [i64, i64, i64]
+    L.ixb_p6_gemm.restype = C.c_int
+    L.ixb_p6_gemm.argtypes = [C.POINTER(P6Struct), vp, i64, vp, vp, C.c_int, vp, sz, vp]
     L.ixb_attn_scratch_bytes.restype = sz
     L.ixb_attn_scratch_bytes.argtypes = [i64, i64, i64]
     L.ixb_attn_decode.restype = C.c_int

@@ -4,6 +4,7 @@
 #include <cstdlib>
 #include "ixb_common.cuh"
 #include "ixb_gemm_tc.cuh"
+#include "ixb_p6_gemm.cuh"
 #include "ixb_pack.cuh"
 #include "ixb_p6.cuh"
 #include "ixb_allreduce.cuh"
@@ -1317,6 +1318,56 @@ extern "C" int ixb_gemm(const ixb_packed *w, const int32_t *blk_q1, const int32_
     if ((rc = launch_check("k_gemm_tc"))) return rc;
     uint32_t total = (uint32_t)m_rows * s.out_f;
     k_gemm_finalize<<<(total + 255) / 256, 256, 0, st>>>(part, p.n_kslab, (uint32_t)m_rows, s.out_f,
+                                                         (const __nv_bfloat16 *)bias, y, y_is_f32, err);
+    return launch_check("k_gemm_finalize");
+}
+
+// ------------------------------------------------ small-M GEMM on the resident P6 layout
+static PgPlan make_pg_plan(uint32_t out_f, uint32_t in_f)
+{
+    PgPlan p;
+    const uint32_t rt = (out_f + kTileRows - 1) / kTileRows, kb = (in_f + kTileCols - 1) / kTileCols;
+    p.groups = (rt + kPgConv - 1) / kPgConv;
+    int dev = 0, sms = 148;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    // K is split only as far as it takes to give about every SM one CTA; a split keeps at least eight column blocks
+    uint32_t splits = std::max<uint32_t>(1u, (uint32_t)sms / p.groups);
+    splits = std::min<uint32_t>(splits, std::max<uint32_t>(1u, kb / 8u));
+    p.splits = std::min<uint32_t>(splits, 16u);
+    p.grid = p.groups * p.splits;
+    return p;
+}
+
+extern "C" size_t ixb_p6_gemm_scratch_bytes(int64_t out_f, int64_t in_f, int64_t m_rows)
+{
+    if (out_f <= 0 || in_f <= 0 || m_rows < 1 || m_rows > kPgTok || out_f * in_f > 800000000LL) return 0;
+    PgPlan p = make_pg_plan((uint32_t)out_f, (uint32_t)in_f);
+    return 256 + (size_t)p.splits * (size_t)m_rows * (size_t)out_f * sizeof(float);
+}
+
+extern "C" int ixb_p6_gemm(const ixb_p6 *t, const void *x, int64_t m_rows, const void *bias, void *y, int y_is_f32,
+                           void *scratch, size_t scratch_bytes, ixb_stream_t stream)
+{
+    P6 p;
+    int rc = to_p6(t, &p);
+    if (rc) return rc;
+    if (!x || !y || !scratch) return fail(IXB_E_ARG, "NULL pointer argument");
+    if (m_rows < 1 || m_rows > kPgTok) return fail(IXB_E_UNSUPPORTED, "m_rows=%lld outside 1..%d", (long long)m_rows, kPgTok);
+    if (p.in_f % (uint32_t)kTileCols) return fail(IXB_E_UNSUPPORTED, "in_f=%u is not a multiple of %d", p.in_f, kTileCols);
+    if ((uintptr_t)x & 15u) return fail(IXB_E_ARG, "x is not 16-byte aligned");
+    if ((uintptr_t)scratch & 255u) return fail(IXB_E_ARG, "scratch is not 256-byte aligned");
+    if (scratch_bytes < ixb_p6_gemm_scratch_bytes(p.out_f, p.in_f, m_rows)) return fail(IXB_E_SCRATCH, "gemm scratch too small");
+    PgPlan plan = make_pg_plan(p.out_f, p.in_f);
+    cudaStream_t st = (cudaStream_t)stream;
+    static bool attr_set[64] = {false};
+    IXB_CUDA(opt_in_smem(k_p6_gemm, attr_set, (int)kPgSmemBytes));
+    uint32_t *err = (uint32_t *)scratch;
+    float *part = (float *)((char *)scratch + 256);
+    IXB_CUDA(cudaMemsetAsync(scratch, 0, 256, st));
+    k_p6_gemm<<<plan.grid, kPgThreads, kPgSmemBytes, st>>>(p, (const __nv_bfloat16 *)x, (uint32_t)m_rows, part, err, plan);
+    if ((rc = launch_check("k_p6_gemm"))) return rc;
+    uint32_t total = (uint32_t)m_rows * p.out_f;
+    k_gemm_finalize<<<(total + 255) / 256, 256, 0, st>>>(part, plan.splits, (uint32_t)m_rows, p.out_f,
                                                          (const __nv_bfloat16 *)bias, y, y_is_f32, err);
     return launch_check("k_gemm_finalize");
 }

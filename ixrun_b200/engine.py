@@ -81,8 +81,10 @@ class StreamingLinear(nn.Module):
                 self.register_buffer("_q2", q2, persistent=False)
         self.register_buffer("_scale", dp.scale, persistent=False)
         self._y32 = None
-        # 9..64 rows: fused decode+GEMM on the tensor cores straight from the streams (needs them kept and
-        # in_f % 1024 == 0).  Off by default.
+        # 9..64 rows on the resident layout: one pass over the packed bytes on the tcgen05 tensor cores
+        # (ixb_p6_gemm, in_f % 64 == 0); set _use_p6_gemm = False to take decode + dense matmul instead.
+        # _use_tc: the older tensor-core kernel that reads the streams (needs them kept, in_f % 1024 == 0); off.
+        self._use_p6_gemm = True
         self._use_tc = False
         if bias is not None:
             self.register_buffer("_bias", bias.detach().clone().to(dp.device), persistent=False)
@@ -135,6 +137,10 @@ class StreamingLinear(nn.Module):
         if self._res is not None and x.dtype == torch.bfloat16 and 1 <= rows <= FUSED_MAX_ROWS \
                 and x.shape[-1] == self.in_features:
             y = self._res.gemv(x.reshape(rows, self.in_features), bias=self._bias_bf16)
+            return y.view(x.shape[:-1] + (self.out_features,))
+        if self._res is not None and self._use_p6_gemm and x.dtype == torch.bfloat16 and rows <= TC_MAX_ROWS \
+                and self.in_features % 64 == 0 and x.shape[-1] == self.in_features:
+            y = self._res.gemm(x.reshape(rows, self.in_features), bias=self._bias_bf16)
             return y.view(x.shape[:-1] + (self.out_features,))
         if self._use_fused and x.dtype == torch.bfloat16 and 1 <= rows <= FUSED_MAX_ROWS \
                 and x.shape[-1] == self.in_features:

@@ -171,6 +171,37 @@ class P6Packed:
                                      _lib.stream_ptr(self.device)))
         return out
 
+    GEMM_MAX_ROWS = 64
+
+    def gemm(self, x: torch.Tensor, bias: torch.Tensor | None = None, out: torch.Tensor | None = None,
+             out_dtype=torch.bfloat16) -> torch.Tensor:
+        """y[M, out_f] = x[M, in_f] @ W.T for 1 <= M <= 64 on the tensor cores, reading the resident layout once
+        (in_f a multiple of 64).  The scratch (split-K partial sums) is kept per tensor shape on this object."""
+        if x.dtype != torch.bfloat16:
+            raise ValueError("activations must be bf16")
+        x2 = x.reshape(-1, self.in_f)
+        if not x2.is_contiguous():
+            x2 = x2.contiguous()
+        m = x2.shape[0]
+        if out is None:
+            out = torch.empty(m, self.out_f, dtype=out_dtype, device=self.device)
+        elif out.dtype not in (torch.bfloat16, torch.float32) or out.numel() != m * self.out_f or not out.is_contiguous():
+            raise ValueError("gemm output must be a contiguous bf16/fp32 tensor of M*out_f elements")
+        if bias is not None and (bias.dtype != torch.bfloat16 or bias.numel() != self.out_f):
+            raise ValueError("bias must be bf16 [out_f]")
+        L = _lib.lib()
+        need = int(L.ixb_p6_gemm_scratch_bytes(self.out_f, self.in_f, m))
+        if need == 0:
+            raise ValueError(f"unsupported GEMM shape: {m} rows")
+        ws = getattr(self, "_gemm_ws", None)
+        if ws is None or ws.numel() < need:
+            ws = self._gemm_ws = torch.empty(need, dtype=torch.uint8, device=self.device)
+        with torch.cuda.device(self.device):
+            _lib.check(L.ixb_p6_gemm(C.byref(self.struct), x2.data_ptr(), m, None if bias is None else bias.data_ptr(),
+                                     out.data_ptr(), 1 if out.dtype == torch.float32 else 0, ws.data_ptr(), ws.numel(),
+                                     _lib.stream_ptr(self.device)))
+        return out
+
     def gemv_push(self, x: torch.Tensor, ar) -> int:
         """Row-parallel shard: y = x @ W.T as fp32 partial sums stored straight into every rank's all-reduce buffer
         (``ar``: a parallel.PeerAllReduce) from the GEMV's epilogue.  Returns the number of values pushed; follow it

@@ -10,8 +10,9 @@ and an L2-sized buffer is overwritten between repetitions; with --graph the
 launches sit back to back in a CUDA graph that rotates over enough copies of the
 layer to keep the weights out of L2, and the graph is replayed until the timed
 region is long (the number a model step sees).
-Kernels: p6 / p6decode (resident layout: fused GEMV for 1..8 rows, decode to
-bf16), gemv / gemm / decode (the reference's streams read directly), dense (bf16
+Kernels: p6 / p6gemm / p6decode (resident layout: fused GEMV for 1..8 rows,
+tcgen05 GEMM for up to 64 rows, decode to bf16; p6decode+dense = decode then a
+dense matmul, what the GEMM replaces), gemv / gemm / decode (the reference's streams read directly), dense (bf16
 matmul on decoded weights, the "cached mode" of the reference).
 """
 from __future__ import annotations
@@ -77,6 +78,11 @@ def run_case(dp: DevicePacked, total_bytes: int, kernel: str, rows: int, reps: i
         fn = lambda: dp.gemv(x, out=y)
     elif kernel == "p6":
         fn = lambda: p6.gemv(x, out=y)
+    elif kernel == "p6gemm":
+        fn = lambda: p6.gemm(x, out=y)
+    elif kernel == "p6decode+dense":
+        w = torch.empty(out_f * in_f, dtype=torch.bfloat16, device=dp.device)
+        fn = lambda: torch.nn.functional.linear(x, p6.decode(out=w))
     elif kernel == "p6decode":
         w = torch.empty(out_f * in_f, dtype=torch.bfloat16, device=dp.device)
         fn = lambda: p6.decode(out=w)
@@ -136,7 +142,7 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--shape", default="5120x17408")
     ap.add_argument("--rows", type=int, default=1)
-    ap.add_argument("--kernel", default="p6", choices=["gemv", "p6", "p6decode", "gemm", "decode", "dense"])
+    ap.add_argument("--kernel", default="p6", choices=["gemv", "p6", "p6gemm", "p6decode+dense", "p6decode", "gemm", "decode", "dense"])
     ap.add_argument("--reps", type=int, default=30)
     ap.add_argument("--no-flush", action="store_true")
     ap.add_argument("--sweep", action="store_true")

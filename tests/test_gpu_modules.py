@@ -72,16 +72,27 @@ def test_streaming_linear_many_tokens_uses_decode_buffer():
     w, p, b, codes = make_layer(out_f, in_f, 1, bias=True)
     sl = StreamingLinear(p, bias=b, keep_streams=True)
     x = torch.randn(2, 16, in_f).bfloat16().cuda()
+    ref = oracle_y(codes, p["scale"], x, out_f, in_f).reshape(2, 16, out_f) + b.float().numpy()
+    # 9..64 rows: the tensor-core GEMM on the resident layout, no decode buffer involved (the fused paths round the
+    # sum to bf16 and then add the bias in bf16, ixrun/engine.py:166-168: up to one more bf16 ulp than the dense path)
+    y_gemm = sl(x)
+    assert np.abs(y_gemm.float().cpu().numpy() - ref).max() / np.abs(ref).max() < 1e-2
+    assert torch.equal(y_gemm.reshape(32, out_f), sl._res.gemm(x.reshape(32, in_f)) + b.cuda())
+    # more than 64 rows (or the GEMM switched off): decode into the shared buffer + dense matmul
+    sl._use_p6_gemm = False
     with pytest.raises(RuntimeError):
         sl(x)                                  # no shared buffer yet
     buf = torch.empty(out_f * in_f + 100, dtype=torch.bfloat16, device="cuda")
     sl._set_shared_buf(buf)
     y = sl(x)
+    x_many = torch.randn(100, in_f).bfloat16().cuda()
+    sl._use_p6_gemm = True
+    assert sl(x_many).shape == (100, out_f)    # beyond the GEMM's row count: the decode path
+    sl._use_p6_gemm = False
     w_dec = bf16(O.decode_bf16({**p, "scale": int(bits(p["scale"].reshape(1))[0]),
                                 "bitmaps": [t.numpy() for t in p["bitmaps"]],
                                 "streams": [t.numpy() for t in p["streams"]]}))
     assert torch.equal(sl._decode().cpu(), w_dec)
-    ref = oracle_y(codes, p["scale"], x, out_f, in_f).reshape(2, 16, out_f) + b.float().numpy()
     err = np.abs(y.float().cpu().numpy() - ref).max() / np.abs(ref).max()
     assert err < 5e-3
     # the same input through the tensor-core fused kernel (opt-in)

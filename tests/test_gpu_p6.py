@@ -204,3 +204,41 @@ def test_p6_fused_tensor_gives_every_part_its_own_result(in_f, rows):
     if len(rows) == 3:
         q, k, v = fused.split(fused.gemv(torch.randn(1, in_f, device="cuda").bfloat16()))
         assert q.numel() == rows[0] and k.numel() == rows[1] and v.numel() == rows[2]
+
+
+@pytest.mark.parametrize("out_f,in_f,m", [(128, 512, 16), (16, 1024, 64), (40, 5120, 33), (100, 1024, 9), (300, 512, 64),
+                                          (512, 5120, 64), (1000, 2176, 17), (3, 3072, 1), (2048, 2048, 32)])
+def test_p6_gemm_small_m_against_the_oracle(out_f, in_f, m):
+    """tcgen05 GEMM on the resident layout (1..64 rows) against the oracle's fp32 result; bias, bf16 output and
+    repeatability; within fp32 summation-order rounding of the GEMV for the rows both take."""
+    codes, scale, p6 = make(out_f, in_f, out_f * 3 + m)
+    sc_bits = int(scale.view(torch.int16).item()) & 0xFFFF
+    xb = O.f32_to_bf16_bits(np.random.default_rng(m).standard_normal((m, in_f)).astype(np.float32))
+    ref = O.gemm_f32(codes, sc_bits, xb, out_f, in_f).astype(np.float64)
+    x = bits_to_bf16(xb).cuda()
+    bias = torch.randn(out_f).bfloat16().cuda()
+    y32 = p6.gemm(x, out_dtype=torch.float32)
+    assert rel_err(y32.cpu().numpy(), ref) < 2e-5
+    assert torch.equal(p6.gemm(x), y32.bfloat16())
+    assert torch.equal(p6.gemm(x, bias=bias), p6.gemm(x) + bias)
+    assert torch.equal(p6.gemm(x, out_dtype=torch.float32), y32)          # deterministic
+    if m <= 8:
+        assert rel_err(p6.gemv(x, out_dtype=torch.float32).cpu().numpy(), y32.cpu().numpy().astype(np.float64)) < 2e-5
+
+
+@pytest.mark.parametrize("out_f,in_f", [(17408, 5120), (5120, 17408)])
+@pytest.mark.parametrize("m", [16, 32, 64])
+def test_p6_gemm_full_size(out_f, in_f, m):
+    """The batched-serving shapes at full size: against an fp32 matmul on the decoded weights (the reference's
+    decode + dense matmul in fp32; 1e-3 is the path's stated tolerance, the observed error is fp32 rounding)."""
+    from ixrun_b200.p6 import P6Packed
+    from ixrun_b200.synth import synthetic_packed
+
+    p6 = P6Packed.from_packed(synthetic_packed(out_f, in_f, seed=3))
+    x = torch.randn(m, in_f, device="cuda").bfloat16()
+    w = p6.decode(kind="bf16")
+    ref = x.double() @ w.double().t()
+    y = p6.gemm(x, out_dtype=torch.float32)
+    err = float((y.double() - ref).abs().max() / ref.abs().max())
+    assert err < 2e-5, err
+    assert torch.equal(p6.gemm(x), y.bfloat16())
