@@ -14,7 +14,8 @@ N > 1 the tensor is split by columns (row-parallel linear: each rank owns
 in_f/N columns of every row) and the partial outputs are summed by one kernel
 over peer memory per step (NCCL with --nccl); the summed output is checked
 against the unsharded layer.  Unless --no-model is given the line also carries
-`model_27b`: ms per token of the tensor-parallel 27B-class hybrid stack at the
+`model_27b`: ms per token of the tensor-parallel 27B-class hybrid decoder (real
+token mixers, 4096 positions of context, greedy feedback on the device) at the
 same N.
 
 `--impl reference` times the CPU port of the reference's own layer path (decode
@@ -518,7 +519,7 @@ def main():
                     help="several GPUs: finish the exchange inside the GEMV kernel (ixb_p6_gemv_allreduce) instead of in a "
                          "second small kernel, which measured faster because the next GEMV's prefetch overlaps it")
     ap.add_argument("--no-model", action="store_true", help="skip the model_27b sub-record (27B-class hybrid stack, ms per token)")
-    ap.add_argument("--model-tokens", type=int, default=16, help="tokens timed for the model_27b sub-record")
+    ap.add_argument("--model-tokens", type=int, default=64, help="tokens decoded for the model_27b sub-record (256 is the configuration's count)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

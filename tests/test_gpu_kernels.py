@@ -205,6 +205,25 @@ def test_tensor_core_gemm_small_m(out_f, in_f, m):
         assert rel_err(dp.gemv(x, out_dtype=torch.float32).cpu().numpy(), y32.cpu().numpy().astype(np.float64)) < 2e-5
 
 
+@pytest.mark.parametrize("out_f,in_f", [(17408, 5120), (5120, 17408)])
+@pytest.mark.parametrize("m", [16, 32, 64])
+def test_tensor_core_gemm_on_the_streams_full_size(out_f, in_f, m):
+    """ixb_gemm (the reference's streams read directly) at the batched-serving shapes: against a float64 matmul on
+    the decoded weights, and equal to the GEMM on the resident layout up to fp32 summation order."""
+    from ixrun_b200.p6 import P6Packed
+    from ixrun_b200.packed import DevicePacked
+    from ixrun_b200.synth import synthetic_packed
+
+    dp = DevicePacked(synthetic_packed(out_f, in_f, seed=4))
+    x = torch.randn(m, in_f, device="cuda").bfloat16()
+    w = dp.decode(kind="bf16").view(out_f, in_f)
+    ref = x.double() @ w.double().t()
+    y = dp.gemm(x, out_dtype=torch.float32)
+    assert float((y.double() - ref).abs().max() / ref.abs().max()) < 2e-5
+    y6 = P6Packed.from_packed(dp).gemm(x, out_dtype=torch.float32)
+    assert float((y6 - y).abs().max() / ref.abs().max()) < 2e-5
+
+
 def test_tensor_core_gemm_extreme_levels_and_errors():
     from ixrun_b200 import _lib
     from ixrun_b200.packed import DevicePacked

@@ -56,3 +56,26 @@ def test_static_scratch_rejects_oversize_shapes():
     assert L.ixb_gemv_scratch_bytes(p.out_f, p.in_f, 8) > 4 * 1024 * 1024
     rc = L.ixb_gemv_static(C.byref(p), None, None, None, 8, None, None, 0, None)
     assert rc == 4 and b"built-in array" in L.ixb_last_error()
+
+
+def test_static_scratch_call_allocates_no_device_memory():
+    """Free device memory (cudaMemGetInfo) and the caching allocator's counters are the same before and after calls
+    of ixb_gemv_static: the entry point neither allocates nor frees."""
+    dp = _layer(640, 5120, seed=5)
+    x = torch.randn(2, 5120).bfloat16().cuda()
+    _static(dp, x, torch.bfloat16)                       # first call on this device: symbol address looked up
+    torch.cuda.synchronize()
+    y = torch.empty(2, 640, dtype=torch.bfloat16, device="cuda")
+    from ixrun_b200 import _lib
+
+    L = _lib.lib()
+    free0, _ = torch.cuda.mem_get_info()
+    stats0 = (torch.cuda.memory_allocated(), torch.cuda.memory_reserved(), torch.cuda.memory_stats().get("num_alloc_retries", 0))
+    for _ in range(3):
+        _lib.check(L.ixb_gemv_static(C.byref(dp.struct), dp.blk_q1.data_ptr(), dp.blk_q2.data_ptr(), x.data_ptr(), 2, None,
+                                     y.data_ptr(), 0, _lib.stream_ptr(x.device)))
+    torch.cuda.synchronize()
+    free1, _ = torch.cuda.mem_get_info()
+    stats1 = (torch.cuda.memory_allocated(), torch.cuda.memory_reserved(), torch.cuda.memory_stats().get("num_alloc_retries", 0))
+    assert free1 == free0 and stats1 == stats0
+    assert torch.equal(y, dp.gemv(x))
