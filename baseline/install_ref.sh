@@ -4,7 +4,7 @@
 # pyproject/setup.py, so `pip install --target` has nothing to build; its pure-Python package directory is taken as is.
 set -e
 here=$(cd "$(dirname "$0")" && pwd)
-src=${1:-/root/reference}
+src=${1:?usage: install_ref.sh <path of the reference checkout>}
 rm -rf "$here/_ref"
 mkdir -p "$here/_ref"
 if ! python -m pip install --no-index --no-build-isolation --no-deps --find-links /opt/wheelhouse --target "$here/_ref" "$src" >"$here/_ref/pip.log" 2>&1; then

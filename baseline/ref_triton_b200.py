@@ -1,6 +1,6 @@
 """Same-box baseline: the UNMODIFIED reference Triton kernels on this GPU, beside this library's kernels.
 
-    sh baseline/install_ref.sh            # once, where the reference tree is mounted
+    sh baseline/install_ref.sh <reference checkout>   # once, where the reference tree is mounted
     python baseline/ref_triton_b200.py    # on the GPU box; one JSON line per shape, then a summary line
 
 For every config-1 shape the reference's own quantiser packs the same synthetic weights, its
@@ -42,7 +42,7 @@ def median_us(fn, reps, flush):
 
 def main():
     if not os.path.isdir(os.path.join(REF, "ixrun")):
-        print(json.dumps({"unavailable": "baseline/_ref/ixrun is missing: run baseline/install_ref.sh where the reference is mounted"}))
+        print(json.dumps({"unavailable": "baseline/_ref/ixrun is missing: run baseline/install_ref.sh <reference checkout> where the reference is mounted"}))
         return
     sys.path.insert(0, REF)
     sys.path.insert(0, ROOT)
