@@ -316,6 +316,13 @@ int ixb_conv_update(const void *x_device, void *state_device, const void *w_devi
 int ixb_gdn_step(const void *qkv_device, const void *z_device, const void *a_device, const void *b_device,
                  const float *A_log_device, const float *dt_bias_device, const void *norm_w_device, float *state_device,
                  void *out_device, int64_t hk, int64_t hv, float eps, ixb_stream_t stream);
+/* ixb_conv_update (kernel size 4, no bias) and ixb_gdn_step in one kernel: qkv_raw is the projection before the conv;
+ * conv_state [2][channels][3] (bf16, channels = (2 hk + hv) * 128) keeps the conv's history twice: the step at position
+ * pos[0] reads copy pos[0] & 1 and writes the other one, so the caller advances pos[0] by one per step. */
+int ixb_gdn_conv_step(const void *qkv_raw_device, void *conv_state_device, const void *conv_w_device,
+                      const int32_t *pos_device, const void *z_device, const void *a_device, const void *b_device,
+                      const float *A_log_device, const float *dt_bias_device, const void *norm_w_device, float *state_device,
+                      void *out_device, int64_t hk, int64_t hv, float eps, ixb_stream_t stream);
 
 /*
  * Fused decode + small-M GEMM on the tensor cores (tcgen05, accumulators in

@@ -25,7 +25,7 @@ SYMBOLS = (
     "ixb_p6_blocks", "ixb_p6_build", "ixb_p6_decode", "ixb_p6_gemv_scratch_bytes", "ixb_p6_gemv", "ixb_set_pdl",
     "ixb_p6_gemm_scratch_bytes", "ixb_p6_gemm",
     "ixb_allreduce_bytes", "ixb_allreduce", "ixb_p6_gemv_push", "ixb_allreduce_finish", "ixb_p6_gemv_allreduce", "ixb_allreduce_spin_limit",
-    "ixb_add_rmsnorm", "ixb_allreduce_finish_add_rmsnorm", "ixb_swiglu", "ixb_rope_kv", "ixb_attn_scratch_bytes", "ixb_attn_decode", "ixb_conv_update", "ixb_gdn_step",
+    "ixb_add_rmsnorm", "ixb_allreduce_finish_add_rmsnorm", "ixb_swiglu", "ixb_rope_kv", "ixb_attn_scratch_bytes", "ixb_attn_decode", "ixb_conv_update", "ixb_gdn_step", "ixb_gdn_conv_step",
 )
 
 
@@ -139,6 +139,8 @@ def lib():
     L.ixb_attn_decode.argtypes = [vp, vp, vp, vp, vp, i64, vp, vp, sz, i64, i64, i64, i64, f32, vp]
     L.ixb_conv_update.restype = C.c_int
     L.ixb_conv_update.argtypes = [vp, vp, vp, vp, vp, i64, i64, vp]
+    L.ixb_gdn_conv_step.restype = C.c_int
+    L.ixb_gdn_conv_step.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i64, i64, f32, vp]
     L.ixb_gdn_step.restype = C.c_int
     L.ixb_gdn_step.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, vp, i64, i64, f32, vp]
     L.ixb_gemv_static.restype = C.c_int

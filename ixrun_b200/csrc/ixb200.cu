@@ -1269,9 +1269,25 @@ extern "C" int ixb_gdn_step(const void *qkv, const void *z, const void *a, const
 {
     if (!qkv || !z || !a || !b || !A_log || !dt_bias || !norm_w || !state || !out) return fail(IXB_E_ARG, "NULL pointer argument");
     if (hk <= 0 || hv <= 0 || hv % hk) return fail(IXB_E_ARG, "value heads must be a multiple of key heads");
-    IXB_GLUE("k_gdn_step", launch_glue(k_gdn_step, dim3((unsigned)hv), dim3(256), (cudaStream_t)stream, (const __nv_bfloat16 *)qkv,
+    IXB_GLUE("k_gdn_step", launch_glue(k_gdn_step<false>, dim3((unsigned)hv), dim3(256), (cudaStream_t)stream, (const __nv_bfloat16 *)qkv,
                                        (const __nv_bfloat16 *)z, (const __nv_bfloat16 *)a, (const __nv_bfloat16 *)b, A_log, dt_bias,
-                                       (const __nv_bfloat16 *)norm_w, state, (__nv_bfloat16 *)out, (uint32_t)hk, (uint32_t)hv, eps));
+                                       (const __nv_bfloat16 *)norm_w, state, (__nv_bfloat16 *)out, (uint32_t)hk, (uint32_t)hv, eps,
+                                       (__nv_bfloat16 *)nullptr, (const __nv_bfloat16 *)nullptr, (const int32_t *)nullptr, 0u));
+}
+
+extern "C" int ixb_gdn_conv_step(const void *qkv_raw, void *conv_state, const void *conv_w, const int32_t *pos, const void *z,
+                                 const void *a, const void *b, const float *A_log, const float *dt_bias, const void *norm_w,
+                                 float *state, void *out, int64_t hk, int64_t hv, float eps, ixb_stream_t stream)
+{
+    if (!qkv_raw || !conv_state || !conv_w || !pos || !z || !a || !b || !A_log || !dt_bias || !norm_w || !state || !out)
+        return fail(IXB_E_ARG, "NULL pointer argument");
+    if (hk <= 0 || hv <= 0 || hv % hk) return fail(IXB_E_ARG, "value heads must be a multiple of key heads");
+    const uint32_t C = (uint32_t)((2 * hk + hv) * 128);
+    IXB_GLUE("k_gdn_step (conv)", launch_glue(k_gdn_step<true>, dim3((unsigned)hv), dim3(256), (cudaStream_t)stream,
+                                              (const __nv_bfloat16 *)qkv_raw, (const __nv_bfloat16 *)z, (const __nv_bfloat16 *)a,
+                                              (const __nv_bfloat16 *)b, A_log, dt_bias, (const __nv_bfloat16 *)norm_w, state,
+                                              (__nv_bfloat16 *)out, (uint32_t)hk, (uint32_t)hv, eps, (__nv_bfloat16 *)conv_state,
+                                              (const __nv_bfloat16 *)conv_w, pos, C));
 }
 
 // ------------------------------------------------------- tensor-core small-M GEMM

@@ -540,15 +540,21 @@ k_conv_update(const __nv_bfloat16 *__restrict__ x, __nv_bfloat16 *state, const _
 //   S <- g S;  delta = (v - S^T k) beta;  S <- S + k delta^T;  o = S^T q
 //   o <- rmsnorm(o) * norm_w * silu(z)                                  (the head's gated output norm)
 // The state is read once and written once.
+// CONV: the causal depth-wise conv (K = 4) + SiLU of the layer runs in the same kernel on the channels this head needs
+// (its key head's q and k, its own v): qkv is then the raw projection, conv_state [2][C][3] holds the last three inputs
+// of every channel twice -- the step at position p reads copy p & 1 and writes copy (p + 1) & 1, because the value heads
+// that share a key head all read its q / k channels while one of them (the first) writes them.
+template <bool CONV>
 __global__ void __launch_bounds__(256)
 k_gdn_step(const __nv_bfloat16 *__restrict__ qkv, const __nv_bfloat16 *__restrict__ z, const __nv_bfloat16 *__restrict__ a_in,
            const __nv_bfloat16 *__restrict__ b_in, const float *__restrict__ A_log, const float *__restrict__ dt_bias,
-           const __nv_bfloat16 *__restrict__ norm_w, float *state, __nv_bfloat16 *out, uint32_t hk, uint32_t hv, float eps)
+           const __nv_bfloat16 *__restrict__ norm_w, float *state, __nv_bfloat16 *out, uint32_t hk, uint32_t hv, float eps,
+           __nv_bfloat16 *conv_state, const __nv_bfloat16 *__restrict__ conv_w, const int32_t *pos, uint32_t C)
 {
     constexpr int DK = 128, DV = 128;
-    __shared__ float red[32], qs[DK], ks[DK], part_k[2][DV], part_q[2][DV];
+    __shared__ float red[32], qs[DK], ks[DK], vs[DV], part_k[2][DV], part_q[2][DV];
     asm volatile("griddepcontrol.launch_dependents;");
-    const uint32_t vh = blockIdx.x, kh = vh / (hv / hk);
+    const uint32_t vh = blockIdx.x, rep = hv / hk, kh = vh / rep;
     const uint32_t tid = threadIdx.x, j = tid & 127u, ih = tid >> 7;
     // the head's state was last written by this kernel one token ago and its parameters are constants: both are
     // requested before the dependency wait, so the longest loads overlap the tail of the kernel ahead
@@ -557,20 +563,61 @@ k_gdn_step(const __nv_bfloat16 *__restrict__ qkv, const __nv_bfloat16 *__restric
 #pragma unroll
     for (int i = 0; i < 64; ++i) s[i] = S[(size_t)(64 * ih + i) * DV + j];
     const float a_log = A_log[vh], dtb = dt_bias[vh], nw = bf2f(norm_w[j]);
+    // qkv = [q (hk * DK) | k (hk * DK) | v (hv * DV)]; channels of this head
+    const uint32_t cq = kh * DK + j, ck = (hk + kh) * DK + j, cv = 2u * hk * DK + vh * DV + j;
+    // conv: thread j < 128 looks after q channel j and v channel j, thread 128 + j after k channel j
+    const uint32_t c0 = ih == 0 ? cq : ck, c1 = cv;
+    float cw0[4] = {0.f, 0.f, 0.f, 0.f}, cw1[4] = {0.f, 0.f, 0.f, 0.f}, st0[3] = {0.f, 0.f, 0.f}, st1[3] = {0.f, 0.f, 0.f};
+    uint32_t par = 0;
+    if (CONV) {
+        par = (uint32_t)pos[0] & 1u;                     // (written at the end of the token step before this one)
+        const __nv_bfloat16 *rd = conv_state + (size_t)par * C * 3;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) cw0[k] = bf2f(conv_w[(size_t)c0 * 4 + k]);
+#pragma unroll
+        for (int k = 0; k < 3; ++k) st0[k] = bf2f(rd[(size_t)c0 * 3 + k]);
+        if (ih == 0) {
+#pragma unroll
+            for (int k = 0; k < 4; ++k) cw1[k] = bf2f(conv_w[(size_t)c1 * 4 + k]);
+#pragma unroll
+            for (int k = 0; k < 3; ++k) st1[k] = bf2f(rd[(size_t)c1 * 3 + k]);
+        }
+    }
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    // qkv = [q (hk * DK) | k (hk * DK) | v (hv * DV)]
-    const __nv_bfloat16 *qp = qkv + (size_t)kh * DK, *kp = qkv + (size_t)(hk + kh) * DK;
-    const __nv_bfloat16 *vp = qkv + (size_t)2 * hk * DK + (size_t)vh * DV;
     float qe = 0.f, ke = 0.f;
-    if (tid < DK) {
-        qe = bf2f(qp[tid]);
-        ke = bf2f(kp[tid]);
+    if (CONV) {
+        auto conv = [&](uint32_t c, const float (&w)[4], const float (&st)[3], bool write) -> float {
+            const __nv_bfloat16 xin = qkv[c];
+            float acc = 0.f;
+#pragma unroll
+            for (int k = 0; k < 3; ++k) acc = fmaf(w[k], st[k], acc);
+            acc = fmaf(w[3], bf2f(xin), acc);
+            if (write) {
+                __nv_bfloat16 *wr = conv_state + ((size_t)(par ^ 1u) * C + c) * 3;
+                wr[0] = __float2bfloat16_rn(st[1]);
+                wr[1] = __float2bfloat16_rn(st[2]);
+                wr[2] = xin;
+            }
+            return bfround(silu_f(acc));                 // the conv's output is a bf16 tensor in the eager path
+        };
+        const float y0 = conv(c0, cw0, st0, vh % rep == 0);      // q or k: written by the key head's first value head
+        if (ih == 0) {
+            qe = y0;
+            vs[j] = conv(c1, cw1, st1, true);
+        } else {
+            ke = y0;
+        }
+    } else {
+        if (ih == 0) {
+            qe = bf2f(qkv[cq]);
+            vs[j] = bf2f(qkv[cv]);
+        } else {
+            ke = bf2f(qkv[ck]);
+        }
     }
-    const float qn = cta_sum(qe * qe, red), kn = cta_sum(ke * ke, red);
-    if (tid < DK) {
-        qs[tid] = qe * rsqrtf(qn + 1e-6f) * rsqrtf((float)DK);
-        ks[tid] = ke * rsqrtf(kn + 1e-6f);
-    }
+    const float qn = cta_sum(qe * qe, red), kn = cta_sum(ke * ke, red);     // (q lives in threads 0..127, k in 128..255)
+    if (ih == 0) qs[j] = qe * rsqrtf(qn + 1e-6f) * rsqrtf((float)DK);
+    else ks[j] = ke * rsqrtf(kn + 1e-6f);
     __syncthreads();
     const float av = bf2f(a_in[vh]) + dtb;
     const float sp = av > 20.f ? av : log1pf(__expf(av));
@@ -588,7 +635,7 @@ k_gdn_step(const __nv_bfloat16 *__restrict__ qkv, const __nv_bfloat16 *__restric
     if (tid < DK) kq = ks[tid] * qs[tid];
     kq = cta_sum(kq, red);                             // k . q (also the barrier for part_k / part_q)
     const float kv_mem = part_k[0][j] + part_k[1][j];
-    const float delta = (bf2f(vp[j]) - kv_mem) * beta;
+    const float delta = (vs[j] - kv_mem) * beta;
 #pragma unroll
     for (int i = 0; i < 64; ++i) S[(size_t)(64 * ih + i) * DV + j] = fmaf(ks[64 * ih + i], delta, s[i]);
     // o_j = sum_i (S_ij + k_i delta_j) q_i = (S^T q)_j + delta_j (k . q)

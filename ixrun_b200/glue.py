@@ -11,7 +11,7 @@ import torch
 
 from . import _lib
 
-__all__ = ["add_rmsnorm", "finish_add_rmsnorm", "swiglu", "rope_kv", "AttnDecode", "conv_update", "gdn_step", "rope_tables"]
+__all__ = ["gdn_conv_step", "add_rmsnorm", "finish_add_rmsnorm", "swiglu", "rope_kv", "AttnDecode", "conv_update", "gdn_step", "rope_tables"]
 
 
 def _st(t):
@@ -138,4 +138,24 @@ def gdn_step(qkv, z, a, b, A_log, dt_bias, norm_w, state, hk: int, hv: int, eps:
         _lib.check(_lib.lib().ixb_gdn_step(qkv.data_ptr(), z.data_ptr(), a.data_ptr(), b.data_ptr(), A_log.data_ptr(),
                                            dt_bias.data_ptr(), norm_w.data_ptr(), state.data_ptr(), out.data_ptr(), hk, hv,
                                            float(eps), _st(qkv)))
+    return out
+
+
+def gdn_conv_step(qkv_raw, conv_state, conv_w, pos, z, a, b, A_log, dt_bias, norm_w, state, hk: int, hv: int,
+                  eps: float = 1e-6, out=None):
+    """``conv_update`` (kernel size 4, no bias) + ``gdn_step`` in one launch.  conv_state: bf16 [2, C, 3] with
+    C = (2 hk + hv) * 128 -- the step at position pos[0] reads copy pos[0] & 1 and writes the other one, so pos (int32
+    device tensor) must advance by one per step."""
+    _bf16(qkv_raw, conv_state, conv_w, z, a, b, norm_w)
+    if conv_state.shape != (2, (2 * hk + hv) * 128, 3) or conv_w.shape[-1] != 4:
+        raise ValueError("conv_state must be [2, (2 hk + hv) * 128, 3] and the kernel size 4")
+    if state.dtype != torch.float32 or A_log.dtype != torch.float32 or dt_bias.dtype != torch.float32 or pos.dtype != torch.int32:
+        raise ValueError("state, A_log and dt_bias are fp32, pos int32")
+    if out is None:
+        out = torch.empty(hv * 128, dtype=torch.bfloat16, device=qkv_raw.device)
+    with torch.cuda.device(qkv_raw.device):
+        _lib.check(_lib.lib().ixb_gdn_conv_step(qkv_raw.data_ptr(), conv_state.data_ptr(), conv_w.data_ptr(), pos.data_ptr(),
+                                                z.data_ptr(), a.data_ptr(), b.data_ptr(), A_log.data_ptr(), dt_bias.data_ptr(),
+                                                norm_w.data_ptr(), state.data_ptr(), out.data_ptr(), hk, hv, float(eps),
+                                                _st(qkv_raw)))
     return out

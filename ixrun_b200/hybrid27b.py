@@ -7,11 +7,11 @@ SwiGLU 17408, vocabulary 151936) on packed INT8-X linears, tensor-parallel with 
 The whole token step -- embedding row, 64 blocks, final norm, lm_head, greedy arg-max, the token fed back and the
 position advanced -- is ONE CUDA graph with no host round trip, so a decode of T tokens is T graph replays.
 
-Per block (9 or 10 launches, on one GPU as on several); the packed linears that share an input are fused
+Per block (8 or 10 launches, on one GPU as on several); the packed linears that share an input are fused
 row-wise into one resident tensor, every part keeping its own per-tensor scale (p6.P6Packed.fuse):
-  gated-delta-rule layer  residual add + RMSNorm -> ONE packed GEMV for in_proj_qkv | z | a | b -> causal conv1d
-                          update + SiLU -> one recurrent step per value head (state fp32 [heads][128][128], read and
-                          written once) with the gated output norm -> out_proj
+  gated-delta-rule layer  residual add + RMSNorm -> ONE packed GEMV for in_proj_qkv | z | a | b -> ONE kernel for the
+                          causal conv1d update + SiLU and the recurrent step per value head (state fp32
+                          [heads][128][128], read and written once) with the gated output norm -> out_proj
   attention layer         residual add + RMSNorm -> ONE packed GEMV for q (+ gate) | k | v -> per-head q/k RMSNorm +
                           partial RoPE + KV-cache write -> split-context grouped-query attention over the static
                           cache with the sigmoid output gate -> o_proj
@@ -186,7 +186,8 @@ class Hybrid27B:
             self.k_cache[:, :context] = torch.randn(n_attn, context, g["hkv"], da, device=self.dev, generator=kv_gen).bfloat16()
             self.v_cache[:, :context] = torch.randn(n_attn, context, g["hkv"], da, device=self.dev, generator=kv_gen).bfloat16()
         self.gdn_state = torch.zeros(max(n_gdn, 1), g["hv"], d, d, dtype=torch.float32, device=self.dev)
-        self.conv_state = torch.zeros(max(n_gdn, 1), self.conv_ch, cfg.conv_k - 1, **bf)
+        # the conv's history is kept twice: the step at position p reads copy p & 1 and writes the other (glue.gdn_conv_step)
+        self.conv_state = torch.zeros(max(n_gdn, 1), 2, self.conv_ch, cfg.conv_k - 1, **bf)
         self.cos, self.sin = G.rope_tables(self.max_seq, cfg.rot_dim, cfg.rope_theta, self.dev)
         self.attn = G.AttnDecode(g["hq"], g["hkv"], da, self.dev) if n_attn else None
         # static activations of the one-row step
@@ -245,9 +246,8 @@ class Hybrid27B:
             self.attn(self.qg, self.k_cache[s], self.v_cache[s], self.pos32, out=self.att, gate=self.qg[nq:])
             return self._row_parallel(L["out"], self.att)
         L["in"].gemv(self.xn, out=self.in_gdn)
-        G.conv_update(self.qkv, self.conv_state[s], L["conv_w"], out=self.qkv_c[0])
-        G.gdn_step(self.qkv_c[0], self.z_, self.a_, self.b_, L["A_log"], L["dt_bias"], L["gn_w"],
-                   self.gdn_state[s], g["hk"], g["hv"], cfg.eps, out=self.mix[0])
+        G.gdn_conv_step(self.qkv, self.conv_state[s], L["conv_w"], self.pos32, self.z_, self.a_, self.b_, L["A_log"],
+                        L["dt_bias"], L["gn_w"], self.gdn_state[s], g["hk"], g["hv"], cfg.eps, out=self.mix[0])
         return self._row_parallel(L["out"], self.mix)
 
     def _step(self):
@@ -321,7 +321,7 @@ def launches_per_token(cfg: HybridConfig, world: int) -> int:
     """Kernels of this library in one token step (packed GEMVs, glue, exchange)."""
     n = 0
     for li in range(cfg.n_layers):
-        n += (6 if cfg.is_attn(li) else 5) + 4          # on several GPUs the norm kernels also finish the exchanges
+        n += (6 if cfg.is_attn(li) else 4) + 4          # on several GPUs the norm kernels also finish the exchanges
     return n + 1 + (1 if world > 1 else 0)
 
 

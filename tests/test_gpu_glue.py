@@ -137,3 +137,34 @@ def test_gdn_step(hk, hv):
         out = gdn_step(qkv, z, a, b, A_log, dt_bias, norm_w, S_gpu, hk, hv, 1e-6)
         close(S_gpu, S, 1e-4)
         close(out, ref, 2 * BF16_ULP)
+
+
+@pytest.mark.parametrize("hk,hv", [(16, 48), (2, 6), (1, 1)])
+def test_gdn_conv_step_equals_conv_then_gdn(hk, hv):
+    """The fused kernel (conv history kept twice, read copy pos & 1, write the other) gives the bits of the conv
+    kernel followed by the recurrent kernel, step after step."""
+    from ixrun_b200.glue import conv_update, gdn_conv_step, gdn_step
+
+    dev = "cuda"
+    C = (2 * hk + hv) * 128
+    conv_w = (torch.randn(C, 4, device=dev) * 0.3).bfloat16()
+    A_log = torch.randn(hv, device=dev) * 0.5
+    dt_bias = torch.randn(hv, device=dev) * 0.5
+    norm_w = (1 + 0.1 * torch.randn(128, device=dev)).bfloat16()
+    S_a = torch.randn(hv, 128, 128, device=dev) * 0.1
+    S_b = S_a.clone()
+    hist = torch.randn(C, 3, device=dev).bfloat16()
+    start = 5                                              # an odd first position: the first step reads copy 1
+    state2 = torch.zeros(2, C, 3, dtype=torch.bfloat16, device=dev)
+    state2[start & 1] = hist
+    pos = torch.tensor([start], dtype=torch.int32, device=dev)
+    for step in range(4):
+        qkv = torch.randn(C, device=dev).bfloat16()
+        z = torch.randn(hv * 128, device=dev).bfloat16()
+        a = torch.randn(hv, device=dev).bfloat16()
+        b = torch.randn(hv, device=dev).bfloat16()
+        ref = gdn_step(conv_update(qkv, hist, conv_w), z, a, b, A_log, dt_bias, norm_w, S_a, hk, hv, 1e-6)
+        out = gdn_conv_step(qkv, state2, conv_w, pos, z, a, b, A_log, dt_bias, norm_w, S_b, hk, hv, 1e-6)
+        assert torch.equal(out, ref) and torch.equal(S_a, S_b)
+        pos += 1
+        assert torch.equal(state2[int(pos.item()) & 1], hist)

@@ -25,7 +25,7 @@ def lin(p6, x):
 class RefState:
     def __init__(self, m):
         self.k, self.v = m.k_cache.clone(), m.v_cache.clone()
-        self.S, self.conv = m.gdn_state.clone(), m.conv_state.clone()
+        self.S, self.conv = m.gdn_state.clone(), m.conv_state[:, 0].clone()     # (the model keeps the history twice)
 
 
 def ref_step(m, st, tok, pos):
