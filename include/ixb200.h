@@ -270,18 +270,22 @@ uint32_t ixb_allreduce_spin_limit(uint32_t polls);
  * ixb_add_rmsnorm: h[rows, hidden] += delta (may be NULL); xn = bf16(h * rsqrt(
  *   mean(h^2) + eps)) * w -- the residual add and the norm in front of the next
  *   linears (HF LlamaRMSNorm arithmetic).
- * ixb_swiglu: y = silu(g) * u, n elements.
+ * ixb_swiglu: y [rows][cols] = silu(g) * u; g and u may be column slices of a
+ *   wider matrix (row pitch in_stride elements).
  * ixb_rope_kv: optional per-head RMSNorm of q and k (weights [head_dim] or
  *   NULL), rotate-half rotary embedding of the first rot_dim dimensions with
  *   the caller's fp32 tables cos / sin [max_seq][rot_dim / 2]; q [rows] (row
  *   stride q_stride elements, heads contiguous) rotated in place, k and v
- *   [rows][hkv][head_dim] written into the caches [max_seq][hkv][head_dim] at
+ *   [rows][hkv][head_dim] (row pitch kv_stride) written into the caches [max_seq][hkv][head_dim] at
  *   positions pos[0] + row.  head_dim 128 or 256.
  * ixb_attn_decode: one query per head (q [hq][head_dim]) over positions
  *   0 .. pos[0] of the static caches, grouped-query (hq a multiple of hkv),
  *   softmax(scale * q.k) v, the context cut into `splits` ranges that run on
  *   separate CTAs; optional output gate: out *= sigmoid(gate[head * gate_stride
- *   + d]).  scratch: ixb_attn_scratch_bytes.
+ *   + d]).  scratch: batch * ixb_attn_scratch_bytes.
+ *   Batched decode (ixrun/batching.py:88-234 drives B sequences per step): batch_stride > 0 in ixb_rope_kv makes
+ *   row r the newest token of sequence r (position pos[r], cache r starts batch_stride elements after cache r - 1);
+ *   ixb_attn_decode takes `batch` queries (row pitch q_stride, gate row pitch gate_row_stride), one per sequence.
  * ixb_conv_update: causal depth-wise conv1d step: y_c = silu(sum_j w[c][j] *
  *   input_{t-k+1+j} + bias_c) over the last k inputs of every channel; state
  *   [channels][k - 1] (oldest first) takes x in.
@@ -302,15 +306,17 @@ int ixb_add_rmsnorm(void *h_device, const void *delta_device, const void *w_devi
 int ixb_allreduce_finish_add_rmsnorm(void *const *peer_buffers, int rank, int world, int64_t n_max, void *h_device,
                                      const void *w_device, float eps, void *xn_device, int64_t rows, int64_t hidden,
                                      ixb_stream_t stream);
-int ixb_swiglu(const void *g_device, const void *u_device, void *y_device, int64_t n, ixb_stream_t stream);
+int ixb_swiglu(const void *g_device, const void *u_device, void *y_device, int64_t rows, int64_t cols, int64_t in_stride,
+               ixb_stream_t stream);
 int ixb_rope_kv(void *q_device, const void *k_device, const void *v_device, const int32_t *pos_device, void *k_cache_device,
                 void *v_cache_device, const void *q_norm_device, const void *k_norm_device, const float *cos_device,
                 const float *sin_device, int64_t rows, int64_t hq, int64_t hkv, int64_t head_dim, int64_t rot_dim, float eps,
-                int64_t q_stride, int64_t max_seq, ixb_stream_t stream);
+                int64_t q_stride, int64_t max_seq, int64_t kv_stride, int64_t batch_stride, ixb_stream_t stream);
 size_t ixb_attn_scratch_bytes(int64_t hq, int64_t head_dim, int64_t splits);
 int ixb_attn_decode(const void *q_device, const void *k_cache_device, const void *v_cache_device, const int32_t *pos_device,
                     const void *gate_device, int64_t gate_stride, void *out_device, void *scratch_device, size_t scratch_bytes,
-                    int64_t hq, int64_t hkv, int64_t head_dim, int64_t splits, float scale, ixb_stream_t stream);
+                    int64_t hq, int64_t hkv, int64_t head_dim, int64_t splits, float scale, int64_t batch, int64_t q_stride,
+                    int64_t batch_stride, int64_t gate_row_stride, ixb_stream_t stream);
 int ixb_conv_update(const void *x_device, void *state_device, const void *w_device, const void *bias_device, void *y_device,
                     int64_t channels, int64_t k, ixb_stream_t stream);
 int ixb_gdn_step(const void *qkv_device, const void *z_device, const void *a_device, const void *b_device,

@@ -124,9 +124,9 @@ def lib():
     L.ixb_add_rmsnorm.restype = C.c_int
     L.ixb_add_rmsnorm.argtypes = [vp, vp, vp, f32, vp, i64, i64, vp]
     L.ixb_swiglu.restype = C.c_int
-    L.ixb_swiglu.argtypes = [vp, vp, vp, i64, vp]
+    L.ixb_swiglu.argtypes = [vp, vp, vp, i64, i64, i64, vp]
     L.ixb_rope_kv.restype = C.c_int
-    L.ixb_rope_kv.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i64, i64, i64, i64, i64, f32, i64, i64, vp]
+    L.ixb_rope_kv.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i64, i64, i64, i64, i64, f32, i64, i64, i64, i64, vp]
     L.ixb_allreduce_finish_add_rmsnorm.restype = C.c_int
     L.ixb_allreduce_finish_add_rmsnorm.argtypes = [C.POINTER(C.c_void_p), C.c_int, C.c_int, i64, vp, vp, f32, vp, i64, i64, vp]
     L.ixb_p6_gemm_scratch_bytes.restype = sz
@@ -136,7 +136,7 @@ def lib():
     L.ixb_attn_scratch_bytes.restype = sz
     L.ixb_attn_scratch_bytes.argtypes = [i64, i64, i64]
     L.ixb_attn_decode.restype = C.c_int
-    L.ixb_attn_decode.argtypes = [vp, vp, vp, vp, vp, i64, vp, vp, sz, i64, i64, i64, i64, f32, vp]
+    L.ixb_attn_decode.argtypes = [vp, vp, vp, vp, vp, i64, vp, vp, sz, i64, i64, i64, i64, f32, i64, i64, i64, i64, vp]
     L.ixb_conv_update.restype = C.c_int
     L.ixb_conv_update.argtypes = [vp, vp, vp, vp, vp, i64, i64, vp]
     L.ixb_gdn_conv_step.restype = C.c_int

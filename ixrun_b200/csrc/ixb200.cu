@@ -1171,21 +1171,24 @@ extern "C" int ixb_allreduce_finish_add_rmsnorm(void *const *peer_buffers, int r
     return launch_check("k_add_rmsnorm (exchange)");
 }
 
-extern "C" int ixb_swiglu(const void *g, const void *u, void *y, int64_t n, ixb_stream_t stream)
+extern "C" int ixb_swiglu(const void *g, const void *u, void *y, int64_t rows, int64_t cols, int64_t in_stride,
+                          ixb_stream_t stream)
 {
     if (!g || !u || !y) return fail(IXB_E_ARG, "NULL pointer argument");
-    if (n <= 0 || n > 0x7fffffffLL) return fail(IXB_E_ARG, "bad size");
-    const int vec = (n & 7) == 0 && ((((uintptr_t)g | (uintptr_t)u | (uintptr_t)y) & 15u) == 0);
-    const int64_t threads = vec ? n / 8 : n;
+    if (rows <= 0 || cols <= 0 || in_stride < cols || rows * cols > 0x7fffffffLL) return fail(IXB_E_ARG, "bad shape");
+    const int vec = (cols & 7) == 0 && (in_stride & 7) == 0 && ((((uintptr_t)g | (uintptr_t)u | (uintptr_t)y) & 15u) == 0);
+    const int64_t threads = vec ? rows * cols / 8 : rows * cols;
     IXB_GLUE("k_swiglu", launch_glue(k_swiglu, dim3((unsigned)((threads + 127) / 128)), dim3(128), (cudaStream_t)stream,
-                                     (const __nv_bfloat16 *)g, (const __nv_bfloat16 *)u, (__nv_bfloat16 *)y, (uint32_t)n, vec));
+                                     (const __nv_bfloat16 *)g, (const __nv_bfloat16 *)u, (__nv_bfloat16 *)y, (uint32_t)rows,
+                                     (uint32_t)cols, (uint32_t)in_stride, vec));
 }
 
 extern "C" int ixb_rope_kv(void *q, const void *k, const void *v, const int32_t *pos, void *k_cache, void *v_cache,
                            const void *q_norm, const void *k_norm, const float *cos_tab, const float *sin_tab, int64_t rows,
                            int64_t hq, int64_t hkv, int64_t head_dim, int64_t rot_dim, float eps, int64_t q_stride,
-                           int64_t max_seq, ixb_stream_t stream)
+                           int64_t max_seq, int64_t kv_stride, int64_t batch_stride, ixb_stream_t stream)
 {
+    if (kv_stride < hkv * head_dim || batch_stride < 0 || q_stride < hq * head_dim) return fail(IXB_E_ARG, "bad strides");
     if (!q || !k || !v || !pos || !k_cache || !v_cache || !cos_tab || !sin_tab) return fail(IXB_E_ARG, "NULL pointer argument");
     if (rows <= 0 || hq <= 0 || hkv <= 0 || max_seq <= 0) return fail(IXB_E_ARG, "bad shape");
     if (head_dim != 64 && head_dim != 128 && head_dim != 256) return fail(IXB_E_UNSUPPORTED, "head_dim=%lld: 64, 128 or 256", (long long)head_dim);
@@ -1194,7 +1197,8 @@ extern "C" int ixb_rope_kv(void *q, const void *k, const void *v, const int32_t 
                                       (__nv_bfloat16 *)q, (const __nv_bfloat16 *)k, (const __nv_bfloat16 *)v, pos,
                                       (__nv_bfloat16 *)k_cache, (__nv_bfloat16 *)v_cache, (const __nv_bfloat16 *)q_norm,
                                       (const __nv_bfloat16 *)k_norm, cos_tab, sin_tab, (uint32_t)hq, (uint32_t)hkv,
-                                      (uint32_t)head_dim, (uint32_t)rot_dim, eps, (uint32_t)q_stride, (uint32_t)max_seq));
+                                      (uint32_t)head_dim, (uint32_t)rot_dim, eps, (uint32_t)q_stride, (uint32_t)max_seq,
+                                      (uint32_t)kv_stride, (size_t)batch_stride));
 }
 
 extern "C" size_t ixb_attn_scratch_bytes(int64_t hq, int64_t head_dim, int64_t splits)
@@ -1205,13 +1209,14 @@ extern "C" size_t ixb_attn_scratch_bytes(int64_t hq, int64_t head_dim, int64_t s
 
 template <int D>
 static cudaError_t launch_attn(int64_t hq, int64_t hkv, int64_t splits, cudaStream_t st, const void *q, const void *k_cache,
-                               const void *v_cache, const int32_t *pos, void *scratch, float scale)
+                               const void *v_cache, const int32_t *pos, void *scratch, float scale, int64_t batch,
+                               int64_t q_stride, int64_t batch_stride)
 {
     const int64_t rep = hq / hkv;
 #define IXB_ATTN(G)                                                                                                        \
-    return launch_glue(k_attn_decode<D, G>, dim3((unsigned)(hq / G), (unsigned)splits), dim3(256), st, (const __nv_bfloat16 *)q, \
-                       (const __nv_bfloat16 *)k_cache, (const __nv_bfloat16 *)v_cache, pos, (float *)scratch, (uint32_t)hq,  \
-                       (uint32_t)hkv, scale)
+    return launch_glue(k_attn_decode<D, G>, dim3((unsigned)(hq / G), (unsigned)splits, (unsigned)batch), dim3(256), st,   \
+                       (const __nv_bfloat16 *)q, (const __nv_bfloat16 *)k_cache, (const __nv_bfloat16 *)v_cache, pos,      \
+                       (float *)scratch, (uint32_t)hq, (uint32_t)hkv, scale, (uint32_t)q_stride, (size_t)batch_stride)
     switch (rep) {                      // all query heads of a KV head in one CTA where that is a supported group size
     case 2: IXB_ATTN(2);
     case 3: IXB_ATTN(3);
@@ -1225,26 +1230,28 @@ static cudaError_t launch_attn(int64_t hq, int64_t hkv, int64_t splits, cudaStre
 
 extern "C" int ixb_attn_decode(const void *q, const void *k_cache, const void *v_cache, const int32_t *pos, const void *gate,
                                int64_t gate_stride, void *out, void *scratch, size_t scratch_bytes, int64_t hq, int64_t hkv,
-                               int64_t head_dim, int64_t splits, float scale, ixb_stream_t stream)
+                               int64_t head_dim, int64_t splits, float scale, int64_t batch, int64_t q_stride,
+                               int64_t batch_stride, int64_t gate_row_stride, ixb_stream_t stream)
 {
     if (!q || !k_cache || !v_cache || !pos || !out || !scratch) return fail(IXB_E_ARG, "NULL pointer argument");
     if (hq <= 0 || hkv <= 0 || hq % hkv || splits <= 0 || splits > kAttnMaxSplits) return fail(IXB_E_ARG, "bad shape");
+    if (batch < 1 || batch > 65535 || q_stride < 0 || batch_stride < 0 || (batch > 1 && (q_stride & 7))) return fail(IXB_E_ARG, "bad batch");
     if (head_dim != 64 && head_dim != 128 && head_dim != 256) return fail(IXB_E_UNSUPPORTED, "head_dim=%lld: 64, 128 or 256", (long long)head_dim);
-    if (scratch_bytes < ixb_attn_scratch_bytes(hq, head_dim, splits)) return fail(IXB_E_SCRATCH, "attention scratch too small");
+    if (scratch_bytes < (size_t)batch * ixb_attn_scratch_bytes(hq, head_dim, splits)) return fail(IXB_E_SCRATCH, "attention scratch too small");
     if (((uintptr_t)q | (uintptr_t)k_cache | (uintptr_t)v_cache) & 15u) return fail(IXB_E_ARG, "q / caches are not 16-byte aligned");
     if ((uintptr_t)scratch & 7u) return fail(IXB_E_ARG, "attention scratch is misaligned");
     cudaStream_t st = (cudaStream_t)stream;
     cudaError_t e;
-    if (head_dim == 64) e = launch_attn<64>(hq, hkv, splits, st, q, k_cache, v_cache, pos, scratch, scale);
-    else if (head_dim == 128) e = launch_attn<128>(hq, hkv, splits, st, q, k_cache, v_cache, pos, scratch, scale);
-    else e = launch_attn<256>(hq, hkv, splits, st, q, k_cache, v_cache, pos, scratch, scale);
+    if (head_dim == 64) e = launch_attn<64>(hq, hkv, splits, st, q, k_cache, v_cache, pos, scratch, scale, batch, q_stride, batch_stride);
+    else if (head_dim == 128) e = launch_attn<128>(hq, hkv, splits, st, q, k_cache, v_cache, pos, scratch, scale, batch, q_stride, batch_stride);
+    else e = launch_attn<256>(hq, hkv, splits, st, q, k_cache, v_cache, pos, scratch, scale, batch, q_stride, batch_stride);
     if (e != cudaSuccess) return fail(IXB_E_CUDA, "k_attn_decode launch: %s", cudaGetErrorString(e));
     int rc = launch_check("k_attn_decode");
     if (rc) return rc;
     const unsigned threads = (unsigned)std::max<int64_t>(head_dim, (splits + 31) / 32 * 32);
-    IXB_GLUE("k_attn_combine", launch_glue(k_attn_combine, dim3((unsigned)hq), dim3(threads), st, (const float *)scratch,
+    IXB_GLUE("k_attn_combine", launch_glue(k_attn_combine, dim3((unsigned)hq, (unsigned)batch), dim3(threads), st, (const float *)scratch,
                                            (__nv_bfloat16 *)out, (const __nv_bfloat16 *)gate, (uint32_t)splits, (uint32_t)head_dim,
-                                           (uint32_t)gate_stride));
+                                           (uint32_t)gate_stride, (uint32_t)gate_row_stride));
 }
 
 extern "C" int ixb_conv_update(const void *x, void *state, const void *w, const void *bias, void *y, int64_t channels,

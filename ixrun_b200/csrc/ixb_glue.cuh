@@ -194,24 +194,29 @@ k_add_rmsnorm(__nv_bfloat16 *h, const __nv_bfloat16 *__restrict__ delta, NormExc
 }
 
 // ---------------------------------------------------------------- SwiGLU
-// n a multiple of 8 and 16-byte aligned pointers: eight values per thread; otherwise one value per thread
+// y [rows][cols] = silu(g) * u; g and u may be column slices of a wider matrix (row pitch in_stride elements, e.g. the
+// two halves of a fused gate|up output).  vec: cols and in_stride multiples of 8 and 16-byte aligned pointers: eight
+// values per thread; otherwise one value per thread.
 __global__ void __launch_bounds__(128)
-k_swiglu(const __nv_bfloat16 *__restrict__ g, const __nv_bfloat16 *__restrict__ u, __nv_bfloat16 *y, uint32_t n, int vec)
+k_swiglu(const __nv_bfloat16 *__restrict__ g, const __nv_bfloat16 *__restrict__ u, __nv_bfloat16 *y, uint32_t rows,
+         uint32_t cols, uint32_t in_stride, int vec)
 {
     asm volatile("griddepcontrol.launch_dependents;");
     asm volatile("griddepcontrol.wait;" ::: "memory");
     const uint32_t t = blockIdx.x * blockDim.x + threadIdx.x;
     if (vec) {
-        const uint32_t i = 8u * t;
-        if (i >= n) return;
+        const uint32_t per_row = cols / 8u, r = t / per_row, c = (t - r * per_row) * 8u;
+        if (r >= rows) return;
         float a[8], b[8], o[8];
-        unpack8(*(const uint4 *)(g + i), a);
-        unpack8(*(const uint4 *)(u + i), b);
+        unpack8(*(const uint4 *)(g + (size_t)r * in_stride + c), a);
+        unpack8(*(const uint4 *)(u + (size_t)r * in_stride + c), b);
 #pragma unroll
         for (int k = 0; k < 8; ++k) o[k] = bfround(silu_f(a[k])) * b[k];
-        *(uint4 *)(y + i) = pack8(o);
-    } else if (t < n) {
-        y[t] = __hmul(__float2bfloat16_rn(silu_f(bf2f(g[t]))), u[t]);
+        *(uint4 *)(y + (size_t)r * cols + c) = pack8(o);
+    } else {
+        const uint32_t r = t / cols, c = t - r * cols;
+        if (r >= rows) return;
+        y[(size_t)r * cols + c] = __hmul(__float2bfloat16_rn(silu_f(bf2f(g[(size_t)r * in_stride + c]))), u[(size_t)r * in_stride + c]);
     }
 }
 
@@ -220,21 +225,24 @@ k_swiglu(const __nv_bfloat16 *__restrict__ g, const __nv_bfloat16 *__restrict__ 
 // rotate-half convention; the first rot_dim elements are rotated with the caller's tables cos / sin [max_seq][rot_dim / 2]
 // (the same fp32 tables as the eager path, so the results agree bit for bit), the rest pass through.
 // q_norm / k_norm (per-head RMSNorm weights [D], may be null) are applied first.  q is rotated in place; k and v go
-// into the caches [max_seq][kv heads][D] at position pos[0] + row.
+// into the caches [max_seq][kv heads][D].  batch_stride == 0: the rows are consecutive positions pos[0] + row of one
+// sequence; batch_stride > 0: row r is the newest token of sequence r, at position pos[r] of the cache that starts
+// batch_stride elements after the one before it.  Row pitches of q, k / v: q_stride, kv_stride elements.
 __global__ void __launch_bounds__(128)
 k_rope_kv(__nv_bfloat16 *q, const __nv_bfloat16 *__restrict__ k, const __nv_bfloat16 *__restrict__ v, const int32_t *pos,
           __nv_bfloat16 *k_cache, __nv_bfloat16 *v_cache, const __nv_bfloat16 *__restrict__ q_norm,
           const __nv_bfloat16 *__restrict__ k_norm, const float *__restrict__ cos_tab, const float *__restrict__ sin_tab,
-          uint32_t hq, uint32_t hkv, uint32_t D, uint32_t rot_dim, float eps, uint32_t q_stride, uint32_t max_seq)
+          uint32_t hq, uint32_t hkv, uint32_t D, uint32_t rot_dim, float eps, uint32_t q_stride, uint32_t max_seq,
+          uint32_t kv_stride, size_t batch_stride)
 {
     __shared__ float red[32];
     asm volatile("griddepcontrol.launch_dependents;");
     asm volatile("griddepcontrol.wait;" ::: "memory");
     const uint32_t row = blockIdx.x, head = blockIdx.y, i = threadIdx.x, half = D / 2;
-    const uint32_t p = (uint32_t)pos[0] + row;
+    const uint32_t p = batch_stride ? (uint32_t)pos[row] : (uint32_t)pos[0] + row;
     const bool is_q = head < hq;
     __nv_bfloat16 *src = is_q ? q + (size_t)row * q_stride + (size_t)head * D
-                              : const_cast<__nv_bfloat16 *>(k) + ((size_t)row * hkv + (head - hq)) * D;
+                              : const_cast<__nv_bfloat16 *>(k) + (size_t)row * kv_stride + (size_t)(head - hq) * D;
     float a = bf2f(src[i]), b = bf2f(src[i + half]);
     const __nv_bfloat16 *nw = is_q ? q_norm : k_norm;
     if (nw) {
@@ -248,10 +256,10 @@ k_rope_kv(__nv_bfloat16 *q, const __nv_bfloat16 *__restrict__ k, const __nv_bflo
         dst_a = src + i;
         dst_b = src + i + half;
     } else {
-        const size_t at = ((size_t)min(p, max_seq - 1u) * hkv + (head - hq)) * D;
+        const size_t at = (size_t)row * batch_stride + ((size_t)min(p, max_seq - 1u) * hkv + (head - hq)) * D;
         dst_a = k_cache + at + i;
         dst_b = k_cache + at + i + half;
-        const __nv_bfloat16 *vs = v + ((size_t)row * hkv + (head - hq)) * D;
+        const __nv_bfloat16 *vs = v + (size_t)row * kv_stride + (size_t)(head - hq) * D;
         v_cache[at + i] = vs[i];
         v_cache[at + i + half] = vs[i + half];
     }
@@ -287,8 +295,14 @@ template <int D, int G>
 __global__ void __launch_bounds__(256)
 k_attn_decode(const __nv_bfloat16 *__restrict__ q, const __nv_bfloat16 *__restrict__ k_cache,
               const __nv_bfloat16 *__restrict__ v_cache, const int32_t *pos, float *part, uint32_t hq, uint32_t hkv,
-              float scale)
+              float scale, uint32_t q_stride, size_t batch_stride)
 {
+    // blockIdx.z: the sequence (its query row, its caches batch_stride elements after the previous one's, its position)
+    q += (size_t)blockIdx.z * q_stride;
+    k_cache += (size_t)blockIdx.z * batch_stride;
+    v_cache += (size_t)blockIdx.z * batch_stride;
+    pos += blockIdx.z;
+    part += (size_t)blockIdx.z * hq * gridDim.y * (D + 2);
     constexpr int LPP = D / 8;                         // lanes per position
     constexpr int PPW = 32 / LPP;                      // positions per warp iteration
     constexpr int NS = 8 * PPW;                        // partial states per head in the CTA
@@ -411,11 +425,15 @@ k_attn_decode(const __nv_bfloat16 *__restrict__ q, const __nv_bfloat16 *__restri
 constexpr int kAttnMaxSplits = 256;
 __global__ void __launch_bounds__(256)
 k_attn_combine(const float *__restrict__ part, __nv_bfloat16 *out, const __nv_bfloat16 *__restrict__ gate, uint32_t splits,
-               uint32_t D, uint32_t gate_stride)
+               uint32_t D, uint32_t gate_stride, uint32_t gate_row_stride)
 {
     __shared__ float wgt[kAttnMaxSplits], red[32];
     asm volatile("griddepcontrol.launch_dependents;");
     const uint32_t head = blockIdx.x, t = threadIdx.x;
+    // blockIdx.y: the sequence
+    part += (size_t)blockIdx.y * gridDim.x * splits * (D + 2);
+    out += (size_t)blockIdx.y * gridDim.x * D;
+    if (gate) gate += (size_t)blockIdx.y * gate_row_stride;
     float gv = 0.f;
     asm volatile("griddepcontrol.wait;" ::: "memory");
     if (gate && t < D) gv = bf2f(gate[(size_t)head * gate_stride + t]);

@@ -26,6 +26,9 @@ def main():
     ap.add_argument("--new", type=int, default=256)
     ap.add_argument("--shared-layer-weights", action="store_true",
                     help="generate one tensor per linear type and reuse it in every layer (faster set-up)")
+    ap.add_argument("--batched", default="",
+                    help="comma-separated batch sizes: also time lock-step decoding of B sequences (BatchedGreedyDecoder; "
+                         "B <= 8 on the fused GEMV, up to 64 on the tensor-core GEMM) and report tokens per second")
     ap.add_argument("--no-pdl", action="store_true",
                     help="launch the packed GEMVs without programmatic dependent launch")
     args = ap.parse_args()
@@ -78,6 +81,31 @@ def main():
         if not same:
             min_margin = min(min_margin, float(top2[0] - top2[1]))
         tok = b.argmax(-1)
+    batched = None
+    if args.batched:
+        from .llama_runner import BatchedGreedyDecoder
+
+        batched = []
+        g = torch.Generator().manual_seed(2)
+        for b in (int(v) for v in args.batched.split(",")):
+            dec = BatchedGreedyDecoder(packed, b)
+            tok = dec.prefill([torch.randint(0, cfg.vocab, (128,), generator=g) for _ in range(b)])
+            dec.capture()
+            for _ in range(3):
+                tok = dec.step(tok).argmax(-1)
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            steps = 32
+            e0.record()
+            for _ in range(steps):
+                tok = dec.step(tok).argmax(-1)
+            e1.record()
+            torch.cuda.synchronize()
+            ms = e0.elapsed_time(e1) / steps
+            batched.append({"sequences": b, "ms_per_step": round(ms, 4), "tokens_per_s": round(b / ms * 1e3, 1),
+                            "linears": "fused GEMV" if b <= 8 else "tcgen05 GEMM"})
+            del dec
+            torch.cuda.empty_cache()
     print(json.dumps({
         "model": f"llama-style {args.layers}L h{cfg.hidden} ffn{cfg.intermediate} {cfg.n_heads}q/{cfg.n_kv_heads}kv vocab{cfg.vocab}",
         "packed_linears": len(layers) * 7, "packed_weights": n_weights, "packed_MB": packed_bytes / 1e6,
@@ -87,7 +115,7 @@ def main():
         "greedy_agreement_teacher_forced": agree / args.new, "steps_with_exact_top1_tie": ties,
         "free_running_prefix_match": int((toks_packed == toks_dense).long().cumprod(0).sum().item()),
         "min_top1_top2_margin_at_mismatch": None if agree == args.new else min_margin,
-        "setup_s": setup_s,
+        "setup_s": setup_s, "batched_decode_128_token_prompts": batched,
     }), flush=True)
 
 

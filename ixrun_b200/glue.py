@@ -50,12 +50,29 @@ def finish_add_rmsnorm(ar, h: torch.Tensor, w: torch.Tensor, eps: float, out: to
     return out
 
 
+def _rows_view(t: torch.Tensor, what: str):
+    """(rows, cols, row pitch) of a bf16 CUDA tensor that is a matrix with unit column stride (a column slice of a wider
+    contiguous matrix is fine), or a vector."""
+    if t.dtype != torch.bfloat16 or not t.is_cuda:
+        raise ValueError(f"{what}: bf16 CUDA tensor expected")
+    if t.dim() == 1:
+        t = t.unsqueeze(0)
+    if t.dim() != 2 or t.stride(1) != 1:
+        raise ValueError(f"{what}: a [rows, cols] tensor with contiguous columns expected")
+    return t.shape[0], t.shape[1], t.stride(0) if t.shape[0] > 1 else t.shape[1]
+
+
 def swiglu(g: torch.Tensor, u: torch.Tensor, out: torch.Tensor | None = None):
-    _bf16(g, u)
+    """silu(g) * u; g and u: vectors, or [rows, cols] matrices that may be column slices of one wider matrix (the two
+    halves of a fused gate|up output); out: contiguous [rows, cols]."""
+    rows, cols, pitch = _rows_view(g, "g")
+    if _rows_view(u, "u") != (rows, cols, pitch):
+        raise ValueError("g and u must have the same shape and row pitch")
     if out is None:
-        out = torch.empty_like(g)
+        out = torch.empty(g.shape, dtype=torch.bfloat16, device=g.device)
+    _bf16(out)
     with torch.cuda.device(g.device):
-        _lib.check(_lib.lib().ixb_swiglu(g.data_ptr(), u.data_ptr(), out.data_ptr(), g.numel(), _st(g)))
+        _lib.check(_lib.lib().ixb_swiglu(g.data_ptr(), u.data_ptr(), out.data_ptr(), rows, cols, pitch, _st(g)))
     return out
 
 
@@ -68,50 +85,72 @@ def rope_tables(max_seq: int, rot_dim: int, theta: float, device):
 
 
 def rope_kv(q, k, v, pos, k_cache, v_cache, cos, sin, hq: int, hkv: int, head_dim: int, rot_dim: int | None = None,
-            q_norm=None, k_norm=None, eps: float = 1e-6, q_stride: int | None = None):
-    """q [rows, >= hq*head_dim] rotated in place; k, v [rows, hkv*head_dim] into the caches [max_seq, hkv, head_dim] at
-    positions pos[0] + row (pos: int32 device tensor of one element)."""
-    _bf16(q, k, v, k_cache, v_cache, q_norm, k_norm)
+            q_norm=None, k_norm=None, eps: float = 1e-6, q_stride: int | None = None, batched: bool = False):
+    """q [rows, >= hq*head_dim] rotated in place; k, v [rows, hkv*head_dim] (column slices allowed) into the caches.
+    batched=False: one sequence, caches [max_seq, hkv, head_dim], the rows are positions pos[0] + row (pos: int32 device
+    tensor of one element).  batched=True: row r is the newest token of sequence r: caches [rows, max_seq, hkv, head_dim],
+    pos int32 [rows]."""
+    _bf16(k_cache, v_cache, q_norm, k_norm)
     if pos.dtype != torch.int32 or not pos.is_cuda:
         raise ValueError("pos must be an int32 CUDA tensor")
-    rows = k.reshape(-1, hkv * head_dim).shape[0]
+    rows, kcols, kv_pitch = _rows_view(k, "k")
+    if _rows_view(v, "v") != (rows, kcols, kv_pitch) or kcols != hkv * head_dim:
+        raise ValueError("k and v must be [rows, hkv*head_dim] with the same row pitch")
+    if q_stride is None:
+        q_stride = _rows_view(q, "q")[2]
+    max_seq = k_cache.shape[-3]
+    batch_stride = max_seq * hkv * head_dim if batched else 0
+    if batched and (k_cache.dim() != 4 or k_cache.shape[0] < rows or pos.numel() < rows):
+        raise ValueError("batched caches are [rows, max_seq, hkv, head_dim] with one position per row")
     with torch.cuda.device(q.device):
         _lib.check(_lib.lib().ixb_rope_kv(q.data_ptr(), k.data_ptr(), v.data_ptr(), pos.data_ptr(), k_cache.data_ptr(),
                                           v_cache.data_ptr(), None if q_norm is None else q_norm.data_ptr(),
                                           None if k_norm is None else k_norm.data_ptr(), cos.data_ptr(), sin.data_ptr(),
-                                          rows, hq, hkv, head_dim, rot_dim or head_dim, float(eps),
-                                          q_stride if q_stride is not None else q.reshape(rows, -1).shape[1],
-                                          k_cache.shape[0], _st(q)))
+                                          rows, hq, hkv, head_dim, rot_dim or head_dim, float(eps), q_stride, max_seq,
+                                          kv_pitch, batch_stride, _st(q)))
     return q
 
 
 class AttnDecode:
-    """Single-query grouped-query attention over a static KV cache; owns the scratch of the context splits."""
+    """Single-query grouped-query attention over static KV caches, for one sequence or a batch of them; owns the scratch
+    of the context splits."""
 
-    def __init__(self, hq: int, hkv: int, head_dim: int, device, splits: int | None = None):
-        self.hq, self.hkv, self.d = hq, hkv, head_dim
+    def __init__(self, hq: int, hkv: int, head_dim: int, device, splits: int | None = None, batch: int = 1):
+        self.hq, self.hkv, self.d, self.batch = hq, hkv, head_dim, int(batch)
         if splits is None:
             # one CTA looks after all query heads of a KV head (group sizes 2, 3, 4, 6, 8; else one head per CTA):
             # as many context splits as give about one CTA per SM
             sms = torch.cuda.get_device_properties(device).multi_processor_count
             rep = hq // hkv
             groups = hq // rep if rep in (2, 3, 4, 6, 8) else hq
-            splits = max(1, min(256, sms // groups))
+            splits = max(1, min(256, sms // (groups * self.batch)))
         self.splits = int(splits)
-        self.scratch = torch.empty(_lib.lib().ixb_attn_scratch_bytes(hq, head_dim, self.splits), dtype=torch.uint8, device=device)
+        self.scratch = torch.empty(self.batch * _lib.lib().ixb_attn_scratch_bytes(hq, head_dim, self.splits), dtype=torch.uint8,
+                                   device=device)
 
-    def __call__(self, q, k_cache, v_cache, pos, out=None, gate=None, gate_stride: int | None = None, scale: float | None = None):
-        """q [hq*head_dim] (contiguous heads), caches [max_seq, hkv, head_dim], pos int32 [1] = index of the newest
-        key; returns out [hq*head_dim] (optionally gated by sigmoid(gate[head*gate_stride + d]))."""
-        _bf16(k_cache, v_cache, gate)
+    def __call__(self, q, k_cache, v_cache, pos, out=None, gate=None, gate_stride: int | None = None, scale: float | None = None,
+                 q_stride: int | None = None, gate_row_stride: int = 0):
+        """One sequence: q [hq*head_dim] (contiguous heads), caches [max_seq, hkv, head_dim], pos int32 [1] = index of
+        the newest key; returns out [hq*head_dim] (optionally gated by sigmoid(gate[head*gate_stride + d])).
+        A batch (constructed with batch = B): q [B, >= hq*head_dim] (row pitch q_stride, default its own), caches
+        [B, max_seq, hkv, head_dim], pos int32 [B]; returns out [B, hq*head_dim]."""
+        _bf16(k_cache, v_cache)
+        b = self.batch
+        if b > 1:
+            if q_stride is None:
+                q_stride = _rows_view(q, "q")[2]
+            if k_cache.dim() != 4 or k_cache.shape[0] < b or pos.numel() < b:
+                raise ValueError("batched caches are [B, max_seq, hkv, head_dim] with one position per sequence")
+        batch_stride = k_cache.shape[-3] * self.hkv * self.d if b > 1 else 0
         if out is None:
-            out = torch.empty(self.hq * self.d, dtype=torch.bfloat16, device=q.device)
+            out = torch.empty((b, self.hq * self.d) if b > 1 else (self.hq * self.d,), dtype=torch.bfloat16, device=q.device)
         with torch.cuda.device(q.device):
             _lib.check(_lib.lib().ixb_attn_decode(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), pos.data_ptr(),
                                                   None if gate is None else gate.data_ptr(),
                                                   gate_stride if gate_stride is not None else self.d, out.data_ptr(),
                                                   self.scratch.data_ptr(), self.scratch.numel(), self.hq, self.hkv, self.d,
-                                                  self.splits, float(scale if scale is not None else self.d ** -0.5), _st(q)))
+                                                  self.splits, float(scale if scale is not None else self.d ** -0.5), b,
+                                                  q_stride or 0, batch_stride, gate_row_stride, _st(q)))
         return out
 
 

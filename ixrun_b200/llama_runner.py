@@ -307,6 +307,122 @@ class PackedLlama(torch.nn.Module):
         return torch.cat(out)
 
 
+class BatchedGreedyDecoder:
+    """B sequences decoded in lock-step on a packed model: the decode loop of the reference's batched generator
+    (ixrun/batching.py:88-234: per-row greedy arg-max, sequences of different lengths, one KV cache per row) without its
+    request queue and tokenizer.  Every packed linear sees B rows per step -- the fused GEMV for B <= 8, the tensor-core
+    GEMM on the resident layout up to 64 -- and the glue kernels take one row per sequence (its own position, its own
+    cache).  One step is one CUDA graph."""
+
+    def __init__(self, model: PackedLlama, batch: int):
+        from .glue import AttnDecode
+
+        if model.weights != "packed" or model.glue != "kernels":
+            raise ValueError("the batched decoder runs on packed weights and the glue kernels")
+        if not 1 <= batch <= 64:
+            raise ValueError("1..64 sequences")
+        self.m, self.b = model, int(batch)
+        cfg, dev = model.cfg, model.embed.device
+        bf = dict(dtype=torch.bfloat16, device=dev)
+        b = self.b
+        self.k_cache = torch.zeros(cfg.n_layers, b, cfg.max_seq, cfg.n_kv_heads, cfg.head_dim, **bf)
+        self.v_cache = torch.zeros_like(self.k_cache)
+        qd = cfg.n_heads * cfg.head_dim
+        first = model.layers[0]
+        self._h, self._xn, self._d = (torch.zeros(b, cfg.hidden, **bf) for _ in range(3))
+        self._qkv = torch.zeros(b, first["qkv"].res.out_f, **bf)
+        self._q, self._k, self._v = (self._qkv[:, a:a + n] for a, n in first["qkv"].res.sections)
+        self._gu = torch.zeros(b, first["gate_up"].res.out_f, **bf)
+        self._g, self._u = (self._gu[:, a:a + n] for a, n in first["gate_up"].res.sections)
+        self._a = torch.zeros(b, qd, **bf)
+        self._act = torch.zeros(b, cfg.intermediate, **bf)
+        # the same context splits as the one-sequence step: a sequence then gets the same bits alone or in a batch
+        self._attn = AttnDecode(cfg.n_heads, cfg.n_kv_heads, cfg.head_dim, dev, splits=model._attn.splits, batch=b)
+        self.tok = torch.zeros(b, dtype=torch.long, device=dev)
+        self.pos32 = torch.zeros(b, dtype=torch.int32, device=dev)
+        self.logits = None
+        self.graph = None
+
+    def _lin(self, res, x, out):
+        return res.gemv(x, out=out) if self.b <= 8 else res.gemm(x, out=out)
+
+    def _step_kernels(self):
+        from . import glue as G
+
+        m, cfg = self.m, self.m.cfg
+        torch.index_select(m.embed, 0, self.tok, out=self._h)
+        delta = None
+        for li in range(cfg.n_layers):
+            L = m.layers[li]
+            G.add_rmsnorm(self._h, delta, m.ln1[li], cfg.rms_eps, out=self._xn)
+            self._lin(L["qkv"].res, self._xn, self._qkv)
+            G.rope_kv(self._q, self._k, self._v, self.pos32, self.k_cache[li], self.v_cache[li], m.cos, m.sin,
+                      cfg.n_heads, cfg.n_kv_heads, cfg.head_dim, batched=True)
+            self._attn(self._q, self.k_cache[li], self.v_cache[li], self.pos32, out=self._a, q_stride=self._qkv.shape[1])
+            self._lin(L["o_proj"]._res, self._a, self._d)
+            G.add_rmsnorm(self._h, self._d, m.ln2[li], cfg.rms_eps, out=self._xn)
+            self._lin(L["gate_up"].res, self._xn, self._gu)
+            G.swiglu(self._g, self._u, out=self._act)
+            self._lin(L["down_proj"]._res, self._act, self._d)
+            delta = self._d
+        G.add_rmsnorm(self._h, delta, m.ln_f, cfg.rms_eps, out=self._xn)
+        return F.linear(self._xn, m.lm_head).float()
+
+    @torch.no_grad()
+    def prefill(self, prompts: list) -> torch.Tensor:
+        """Run every prompt through the model (the many-row path), keep its keys and values in the row's own cache;
+        returns the first generated token of every sequence [B]."""
+        if len(prompts) != self.b:
+            raise ValueError(f"{self.b} prompts expected")
+        first = []
+        for r, ids in enumerate(prompts):
+            logits = self.m.prefill(ids)
+            n = ids.numel()
+            self.k_cache[:, r, :n] = self.m.k_cache[:, :n]
+            self.v_cache[:, r, :n] = self.m.v_cache[:, :n]
+            self.pos32[r] = n
+            first.append(logits.argmax(-1))
+        return torch.cat(first)
+
+    @torch.no_grad()
+    def capture(self):
+        saved = self.pos32.clone()
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(2):
+                self._step_kernels()
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            self.logits = self._step_kernels()
+        self.pos32.copy_(saved)
+        return self
+
+    @torch.no_grad()
+    def step(self, tokens: torch.Tensor) -> torch.Tensor:
+        """Feed one token per sequence (at the sequences' current positions); returns logits [B, vocab]."""
+        self.tok.copy_(tokens.reshape(self.b))
+        if self.graph is not None:
+            self.graph.replay()
+            out = self.logits
+        else:
+            out = self._step_kernels()
+        self.pos32 += 1
+        return out
+
+    @torch.no_grad()
+    def generate(self, prompts: list, n_new: int) -> torch.Tensor:
+        """Greedy decode of n_new tokens for every prompt; returns [B, n_new]."""
+        tok = self.prefill(prompts)
+        out = []
+        for _ in range(n_new):
+            out.append(tok.clone())
+            tok = self.step(tok).argmax(-1)
+        return torch.stack(out, dim=1)
+
+
 def synthetic_llama(cfg: LlamaConfig, seed: int = 0, distinct_layers: bool = True):
     """Random-init weights of the config: Laplace codes for every linear (one
     tensor per linear type and layer when distinct_layers, else one per type
