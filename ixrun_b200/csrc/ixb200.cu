@@ -1386,13 +1386,23 @@ extern "C" int ixb_p6_gemm(const ixb_p6 *t, const void *x, int64_t m_rows, const
     IXB_CUDA(opt_in_smem(k_p6_gemm, attr_set, (int)kPgSmemBytes));
     uint32_t *err = (uint32_t *)scratch;
     float *part = (float *)((char *)scratch + 256);
-    IXB_CUDA(cudaMemsetAsync(scratch, 0, 256, st));
-    k_p6_gemm<<<plan.grid, kPgThreads, kPgSmemBytes, st>>>(p, (const __nv_bfloat16 *)x, (uint32_t)m_rows, part, err, plan);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(plan.grid);
+    cfg.blockDim = dim3(kPgThreads);
+    cfg.dynamicSmemBytes = kPgSmemBytes;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = g_p6_pdl.load() ? 1 : 0;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, k_p6_gemm, p, (const __nv_bfloat16 *)x, (uint32_t)m_rows, part, err, plan);
+    if (e != cudaSuccess) return fail(IXB_E_CUDA, "k_p6_gemm launch: %s", cudaGetErrorString(e));
     if ((rc = launch_check("k_p6_gemm"))) return rc;
     uint32_t total = (uint32_t)m_rows * p.out_f;
-    k_gemm_finalize<<<(total + 255) / 256, 256, 0, st>>>(part, plan.splits, (uint32_t)m_rows, p.out_f,
-                                                         (const __nv_bfloat16 *)bias, y, y_is_f32, err);
-    return launch_check("k_gemm_finalize");
+    IXB_GLUE("k_gemm_finalize", launch_glue(k_gemm_finalize, dim3((total + 255) / 256), dim3(256), st, (const float *)part,
+                                            plan.splits, (uint32_t)m_rows, p.out_f, (const __nv_bfloat16 *)bias, y, y_is_f32,
+                                            (const uint32_t *)err));
 }
 
 // ------------------------------------------------ gemv without caller scratch

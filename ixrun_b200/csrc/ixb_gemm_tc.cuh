@@ -248,9 +248,12 @@ k_gemm_tc(Streams s, const int32_t *__restrict__ q1, const int32_t *__restrict__
 }
 
 // y[t][n] = sum over k-slabs of the partial results, in slab order
+// (takes part in programmatic dependent launch: nothing of it runs ahead of the dependency wait)
 __global__ void k_gemm_finalize(const float *__restrict__ part, uint32_t n_kslab, uint32_t m_tok, uint32_t out_f,
                                 const __nv_bfloat16 *__restrict__ bias, void *y, int y_f32, const uint32_t *err)
 {
+    asm volatile("griddepcontrol.launch_dependents;");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= m_tok * out_f) return;
     float v = 0.f;

@@ -16,8 +16,7 @@
 //              the 16-byte stores of the converter warps and of the activation copies conflict free.  Six stages.
 //   warps    0,2,3  activation loaders, every third stage each: cp.async of the rows as soon as the slot is free
 //            1      one thread issues four tcgen05.mma (M = 128 rows, N = tokens, K = 16) per stage into a
-//                   128 x N fp32 accumulator and commits the slot back to its producers (one wait, one commit per
-//                   stage: the single issuing thread is the pipeline's pacemaker)
+//                   128 x N fp32 accumulator and commits the slot back to its producers
 //            4..27  converters, three per row tile, every third block each: P6 blocks through a private cp.async
 //                   ring (as in the GEMV), the GEMV's shift / mask / fma conversion, four 16-byte stores into the
 //                   B operand, then the block's outliers (requested two blocks ahead) written over their
@@ -40,16 +39,18 @@ constexpr int kPgLoaders = 3;                            // warps 0, 2, 3
 constexpr int kPgRows = kPgConv * kTileRows;             // 128 weight rows per CTA (MMA N)
 constexpr int kPgTok = 64;                               // MMA M
 constexpr int kPgStages = 6;                             // deep enough that a slot's round trip through the tensor core is hidden
-constexpr int kPgStagesA = kPgStages, kPgStagesB = kPgStages;
 constexpr uint32_t kPgALbo = kPgTok * 16 + 16;           // 1040: next core matrix along K of the A operand (16 bytes of padding)
 constexpr uint32_t kPgBLbo = kPgRows * 16 + 16;          // 2064: ... of the B operand (16 bytes of padding)
 constexpr uint32_t kPgABytes = (kTileCols / 8) * kPgALbo;      // 8320
 constexpr uint32_t kPgBBytes = (kTileCols / 8) * kPgBLbo;      // 16512
-constexpr uint32_t kPgAOff = 0, kPgBOff = kPgStagesA * kPgABytes;
-constexpr uint32_t kPgRingOff = kPgBOff + kPgStagesB * kPgBBytes;
+constexpr uint32_t kPgAOff = 0, kPgBOff = kPgStages * kPgABytes;
+constexpr uint32_t kPgRingOff = kPgBOff + kPgStages * kPgBBytes;
 constexpr uint32_t kPgRingBytes = kPgConv * kPgPhases * kP6RingBytes;
 constexpr uint32_t kPgBarOff = kPgRingOff + kPgRingBytes;
-constexpr int kPgBars = 2 * kPgStages + 1;
+constexpr int kPgGroup = 1;                              // stages per hand-shake (2 was measured slower: the ring gets coarser)
+constexpr int kPgGroups = kPgStages / kPgGroup;
+constexpr int kPgBars = 2 * kPgGroups + 1;
+static_assert(kPgStages % kPgGroup == 0, "whole groups of stages");
 constexpr uint32_t kPgSmemBytes = kPgBarOff + kPgBars * 8 + 16;
 constexpr uint32_t kPgTmemCols = 64;
 static_assert(kPgABytes % 16 == 0 && kPgBBytes % 16 == 0 && kPgBarOff % 8 == 0, "operand stages and barriers keep their alignment");
@@ -79,13 +80,13 @@ k_p6_gemm(P6 p, const __nv_bfloat16 *__restrict__ x, uint32_t m_tok, float *__re
     const uint32_t smem0 = (uint32_t)__cvta_generic_to_shared(pg_smem);
     const uint32_t bar0 = smem0 + kPgBarOff;             // full[S], empty[S], done
     uint32_t *tmem_slot = (uint32_t *)(pg_smem + kPgBarOff + kPgBars * 8);
-    // one pair of barriers per stage: `full` collects the stage's activation loader and its eight converters,
-    // `empty` is the tensor core's commit (the single issuing thread does as little per stage as possible)
-    auto full_a = [&](uint32_t s) { return bar0 + s * 8u; };
-    auto empty_a = [&](uint32_t s) { return bar0 + (kPgStages + s) * 8u; };
-    auto full_b = full_a;
-    auto empty_b = empty_a;
-    const uint32_t done_bar = bar0 + 2 * kPgStages * 8u;
+    // one pair of barriers per group of kPgGroup consecutive stages (one stage today): `full` collects the activation
+    // loaders and the converters of the group's stages, `empty` is the tensor core's commit
+    auto grp = [&](uint32_t i) { return (i / kPgGroup) % kPgGroups; };               // barrier index of stage i
+    auto grp_par = [&](uint32_t i) { return ((i / kPgGroup) / kPgGroups) & 1u; };    // its phase parity
+    auto full_bar = [&](uint32_t gi) { return bar0 + gi * 8u; };
+    auto empty_bar = [&](uint32_t gi) { return bar0 + (kPgGroups + gi) * 8u; };
+    const uint32_t done_bar = bar0 + 2 * kPgGroups * 8u;
     auto a_stage = [&](uint32_t s) { return smem0 + kPgAOff + s * kPgABytes; };
     auto b_stage = [&](uint32_t s) { return smem0 + kPgBOff + s * kPgBBytes; };
 
@@ -93,11 +94,13 @@ k_p6_gemm(P6 p, const __nv_bfloat16 *__restrict__ x, uint32_t m_tok, float *__re
     const uint32_t KB = p.kb;
     const uint32_t kq = KB / plan.splits, kr = KB - kq * plan.splits;
     const uint32_t kb0 = p6_begin(split, kq, kr), kb1 = p6_begin(split + 1, kq, kr), nk = kb1 - kb0;
+    // stages are handed over in groups: the stages nk .. nkp - 1 do not exist, their producers only arrive
+    const uint32_t nkp = (nk + kPgGroup - 1) / kPgGroup * kPgGroup;
 
     if (tid == 0) {
-        for (uint32_t s = 0; s < (uint32_t)kPgStages; ++s) {
-            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(full_a(s)), "r"(kPgConv + 1) : "memory");
-            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(empty_a(s)) : "memory");
+        for (uint32_t gi = 0; gi < (uint32_t)kPgGroups; ++gi) {
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(full_bar(gi)), "r"(kPgGroup * (kPgConv + 1)) : "memory");
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(empty_bar(gi)) : "memory");
         }
         asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(done_bar) : "memory");
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -107,22 +110,45 @@ k_p6_gemm(P6 p, const __nv_bfloat16 *__restrict__ x, uint32_t m_tok, float *__re
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot_addr), "r"(kPgTmemCols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
-    // token rows beyond m_tok and weight rows beyond out_f stay zero for the whole kernel
-    for (uint32_t c = tid; c < kPgRingOff / 16; c += kPgThreads) ((uint4 *)pg_smem)[c] = make_uint4(0, 0, 0, 0);
+    // Only what no producer ever writes is zeroed, and stays zero for the whole kernel: the token rows between m_tok
+    // and the MMA's N (the token count rounded up to 16) in every activation stage, and, in the last row group of a
+    // tensor whose row count is not a multiple of 128, the weight rows of the row tiles that do not exist.
+    {
+        const uint32_t n_pad = (m_tok + 15u) & ~15u, zr = n_pad - m_tok;          // zr token rows x 8 core-matrix columns
+        for (uint32_t c = tid; c < kPgStages * 8u * zr; c += kPgThreads) {
+            const uint32_t st = c / (8u * zr), r = c - st * 8u * zr, kc = r / zr, tok = m_tok + (r - kc * zr);
+            *(uint4 *)(pg_smem + kPgAOff + st * kPgABytes + kc * kPgALbo + tok * 16u) = make_uint4(0, 0, 0, 0);
+        }
+        const uint32_t tiles = min((uint32_t)kPgConv, p.rt - group * kPgConv);      // row tiles of this group that exist
+        if (tiles < (uint32_t)kPgConv) {
+            const uint32_t row0 = tiles * kTileRows, zrows = kPgRows - row0;
+            for (uint32_t c = tid; c < kPgStages * 8u * zrows; c += kPgThreads) {
+                const uint32_t st = c / (8u * zrows), r = c - st * 8u * zrows, kc = r / zrows, row = row0 + (r - kc * zrows);
+                *(uint4 *)(pg_smem + kPgBOff + st * kPgBBytes + kc * kPgBLbo + row * 16u) = make_uint4(0, 0, 0, 0);
+            }
+        }
+    }
+    asm volatile("griddepcontrol.launch_dependents;");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    // everything above touches only this CTA's shared memory and TMEM; from here on the kernel reads the activations
+    // and (at its end) writes the partial results, which the kernels ahead of it in the stream may still be using
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    // the error word of this call: cleared by the first CTA (all CTAs of the grid are resident at once, one per SM, and
+    // a wait gives up only after tens of milliseconds, so no CTA can have reported before this store)
+    if (blockIdx.x == 0 && tid == 0) *err = 0u;
     const uint32_t tmem_base = *tmem_slot;
     bool ok = true;
 
     if (warp == 0 || warp == 2 || warp == 3) {
         // ---- activation loaders: loader j takes the stages i = j, j + 3, ...; a stage's rows are requested as soon as
-        // its slot is free (up to kPgStagesA stages ahead of the tensor core) and handed over two of the loader's own
+        // its slot is free (up to kPgStages stages ahead of the tensor core) and handed over two of the loader's own
         // iterations later
         const uint32_t j0 = warp == 0 ? 0u : (uint32_t)warp - 1u;
         const uint32_t chunks = m_tok * (kTileCols / 8);            // 16-byte chunks per stage
-        const uint32_t mine = nk > j0 ? (nk - j0 + kPgLoaders - 1) / kPgLoaders : 0u;
+        const uint32_t mine = nkp > j0 ? (nkp - j0 + kPgLoaders - 1) / kPgLoaders : 0u;
         for (uint32_t n = 0; n < mine + 2; ++n) {
             if (n >= 2) {
                 // the rows requested two iterations ago have landed: hand that stage over (before waiting for a free
@@ -130,11 +156,12 @@ k_p6_gemm(P6 p, const __nv_bfloat16 *__restrict__ x, uint32_t m_tok, float *__re
                 cp_async_wait<1>();
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 __syncwarp();
-                if (lane == 0) pg_arrive(full_a((j0 + (n - 2) * kPgLoaders) % kPgStagesA));
+                if (lane == 0) pg_arrive(full_bar(grp(j0 + (n - 2) * kPgLoaders)));
             }
-            if (n < mine) {
-                const uint32_t i = j0 + n * kPgLoaders, s = i % kPgStagesA, ph = (i / kPgStagesA) & 1u;
-                ok = mbar_wait(empty_a(s), ph ^ 1u) && ok;
+            const uint32_t i = j0 + n * kPgLoaders;
+            if (n < mine && i < nk) {
+                const uint32_t s = i % kPgStages;
+                ok = mbar_wait(empty_bar(grp(i)), grp_par(i) ^ 1u) && ok;
                 const __nv_bfloat16 *src = x + (size_t)(kb0 + i) * kTileCols;
                 for (uint32_t c = lane; c < chunks; c += 32) {      // eight lanes fetch the 128 contiguous bytes of one row
                     const uint32_t kc = c & 7u, tok = c >> 3;
@@ -147,22 +174,26 @@ k_p6_gemm(P6 p, const __nv_bfloat16 *__restrict__ x, uint32_t m_tok, float *__re
         // ---- one thread feeds the tensor core
         if (lane == 0) {
             const uint32_t idesc = pg_idesc((m_tok + 15u) & ~15u);
-            for (uint32_t i = 0; i < nk; ++i) {
-                const uint32_t st = i % kPgStages, par = (i / kPgStages) & 1u;
-                ok = mbar_wait(full_a(st), par) && ok;
+            for (uint32_t i0 = 0; i0 < nk; i0 += kPgGroup) {
+                ok = mbar_wait(full_bar(grp(i0)), grp_par(i0)) && ok;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                uint64_t dw = umma_desc(b_stage(st), kPgBLbo, 128u);   // weights: the M side
-                uint64_t dx = umma_desc(a_stage(st), kPgALbo, 128u);   // activations: the N side
 #pragma unroll
-                for (uint32_t k = 0; k < kTileCols / 16; ++k) {
-                    const uint32_t acc = (i | k) ? 1u : 0u;
-                    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-                                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
-                                 :: "r"(tmem_base), "l"(dw), "l"(dx), "r"(idesc), "r"(acc), "r"(0u) : "memory");
-                    dw += (2u * kPgBLbo) >> 4;                        // two core matrices further along K
-                    dx += (2u * kPgALbo) >> 4;
+                for (uint32_t gs = 0; gs < (uint32_t)kPgGroup; ++gs) {
+                    const uint32_t i = i0 + gs, st = i % kPgStages;
+                    if (i >= nk) break;
+                    uint64_t dw = umma_desc(b_stage(st), kPgBLbo, 128u);   // weights: the M side
+                    uint64_t dx = umma_desc(a_stage(st), kPgALbo, 128u);   // activations: the N side
+#pragma unroll
+                    for (uint32_t k = 0; k < kTileCols / 16; ++k) {
+                        const uint32_t acc = (i | k) ? 1u : 0u;
+                        asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                                     "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
+                                     :: "r"(tmem_base), "l"(dw), "l"(dx), "r"(idesc), "r"(acc), "r"(0u) : "memory");
+                        dw += (2u * kPgBLbo) >> 4;                        // two core matrices further along K
+                        dx += (2u * kPgALbo) >> 4;
+                    }
                 }
-                asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(empty_a(st)) : "memory");
+                asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(empty_bar(grp(i0))) : "memory");
             }
             asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(done_bar) : "memory");
         }
@@ -222,8 +253,12 @@ k_p6_gemm(P6 p, const __nv_bfloat16 *__restrict__ x, uint32_t m_tok, float *__re
         }
         Ent en0 = fetch_entries(ph3), en1 = fetch_entries(ph3 + kStep);     // this warp's current and next block
         uint32_t cs = 0, is = 3 * kP6BlockBytes;
-        for (uint32_t i = ph3; i < nk; i += kStep) {
-            const uint32_t s = i % kPgStagesB, ph = (i / kPgStagesB) & 1u;
+        for (uint32_t i = ph3; i < nkp; i += kStep) {
+            if (i >= nk) {                                            // a stage that only completes its group
+                if (lane == 0) pg_arrive(full_bar(grp(i)));
+                continue;
+            }
+            const uint32_t s = i % kPgStages;
             uint32_t f[16];
             const Ent en2 = fetch_entries(i + 2 * kStep);
             if (have) {
@@ -251,7 +286,7 @@ k_p6_gemm(P6 p, const __nv_bfloat16 *__restrict__ x, uint32_t m_tok, float *__re
                 is = cs;
                 cs = cs == (uint32_t)(3 * kP6BlockBytes) ? 0u : cs + (uint32_t)kP6BlockBytes;
             }
-            ok = mbar_wait(empty_b(s), ph ^ 1u) && ok;               // the stage's last reader (the tensor core) is done
+            ok = mbar_wait(empty_bar(grp(i)), grp_par(i) ^ 1u) && ok;   // the slot's last reader (the tensor core) is done
             if (have) {
                 // rows g and g + 8 of the tile, columns 16 t .. 16 t + 15: four 16-byte pieces
                 const uint32_t bs = b_stage(s) + (2u * cw) * 128u + (uint32_t)g * 16u;
@@ -275,7 +310,7 @@ k_p6_gemm(P6 p, const __nv_bfloat16 *__restrict__ x, uint32_t m_tok, float *__re
             }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             __syncwarp();
-            if (lane == 0) pg_arrive(full_b(s));
+            if (lane == 0) pg_arrive(full_bar(grp(i)));
             en0 = en1;
             en1 = en2;
         }

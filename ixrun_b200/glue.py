@@ -129,19 +129,21 @@ class AttnDecode:
                                    device=device)
 
     def __call__(self, q, k_cache, v_cache, pos, out=None, gate=None, gate_stride: int | None = None, scale: float | None = None,
-                 q_stride: int | None = None, gate_row_stride: int = 0):
+                 q_stride: int | None = None, gate_row_stride: int = 0, shared_cache: bool = False):
         """One sequence: q [hq*head_dim] (contiguous heads), caches [max_seq, hkv, head_dim], pos int32 [1] = index of
         the newest key; returns out [hq*head_dim] (optionally gated by sigmoid(gate[head*gate_stride + d])).
         A batch (constructed with batch = B): q [B, >= hq*head_dim] (row pitch q_stride, default its own), caches
-        [B, max_seq, hkv, head_dim], pos int32 [B]; returns out [B, hq*head_dim]."""
+        [B, max_seq, hkv, head_dim], pos int32 [B]; returns out [B, hq*head_dim].  shared_cache=True: the B queries
+        are B positions of ONE sequence (caches [max_seq, hkv, head_dim], pos[r] = index of the newest key query r may
+        see): causal attention of a short run of new tokens, as in the verification step of speculative decoding."""
         _bf16(k_cache, v_cache)
         b = self.batch
         if b > 1:
             if q_stride is None:
                 q_stride = _rows_view(q, "q")[2]
-            if k_cache.dim() != 4 or k_cache.shape[0] < b or pos.numel() < b:
+            if pos.numel() < b or (not shared_cache and (k_cache.dim() != 4 or k_cache.shape[0] < b)):
                 raise ValueError("batched caches are [B, max_seq, hkv, head_dim] with one position per sequence")
-        batch_stride = k_cache.shape[-3] * self.hkv * self.d if b > 1 else 0
+        batch_stride = k_cache.shape[-3] * self.hkv * self.d if b > 1 and not shared_cache else 0
         if out is None:
             out = torch.empty((b, self.hq * self.d) if b > 1 else (self.hq * self.d,), dtype=torch.bfloat16, device=q.device)
         with torch.cuda.device(q.device):

@@ -307,6 +307,102 @@ class PackedLlama(torch.nn.Module):
         return torch.cat(out)
 
 
+class Verifier:
+    """T new tokens of ONE sequence in one pass (the verification forward of speculative decoding,
+    ixrun/mtp.py:198-280: the draft's tokens go through the model together and the longest prefix that the model's own
+    arg-max confirms is kept).  Every packed linear sees T rows (fused GEMV for T <= 8, tensor-core GEMM up to 64), the
+    keys and values of the T positions are written into the sequence's cache, and query r attends up to position
+    pos0 + r.  Runs on the model's own cache: a rejected tail is simply overwritten by the next call."""
+
+    def __init__(self, model: PackedLlama, rows: int):
+        from .glue import AttnDecode
+
+        if model.weights != "packed" or model.glue != "kernels":
+            raise ValueError("the verifier runs on packed weights and the glue kernels")
+        if not 1 <= rows <= 64:
+            raise ValueError("1..64 rows")
+        self.m, self.t = model, int(rows)
+        cfg, dev = model.cfg, model.embed.device
+        bf = dict(dtype=torch.bfloat16, device=dev)
+        t = self.t
+        first = model.layers[0]
+        self._h, self._xn, self._d = (torch.zeros(t, cfg.hidden, **bf) for _ in range(3))
+        self._qkv = torch.zeros(t, first["qkv"].res.out_f, **bf)
+        self._q, self._k, self._v = (self._qkv[:, a:a + n] for a, n in first["qkv"].res.sections)
+        self._gu = torch.zeros(t, first["gate_up"].res.out_f, **bf)
+        self._g, self._u = (self._gu[:, a:a + n] for a, n in first["gate_up"].res.sections)
+        self._a = torch.zeros(t, cfg.n_heads * cfg.head_dim, **bf)
+        self._act = torch.zeros(t, cfg.intermediate, **bf)
+        self._attn = AttnDecode(cfg.n_heads, cfg.n_kv_heads, cfg.head_dim, dev, splits=model._attn.splits, batch=t)
+        self.tok = torch.zeros(t, dtype=torch.long, device=dev)
+        self.pos0 = torch.zeros(1, dtype=torch.int32, device=dev)                 # position of the first row
+        self.pos_rows = torch.zeros(t, dtype=torch.int32, device=dev)             # pos0 + r
+        self._ramp = torch.arange(t, dtype=torch.int32, device=dev)
+        self.logits = None
+        self.graph = None
+
+    def _lin(self, res, x, out):
+        return res.gemv(x, out=out) if self.t <= 8 else res.gemm(x, out=out)
+
+    def _forward(self):
+        from . import glue as G
+
+        m, cfg = self.m, self.m.cfg
+        torch.add(self._ramp, self.pos0, out=self.pos_rows)
+        torch.index_select(m.embed, 0, self.tok, out=self._h)
+        delta = None
+        for li in range(cfg.n_layers):
+            L = m.layers[li]
+            G.add_rmsnorm(self._h, delta, m.ln1[li], cfg.rms_eps, out=self._xn)
+            self._lin(L["qkv"].res, self._xn, self._qkv)
+            G.rope_kv(self._q, self._k, self._v, self.pos0, m.k_cache[li], m.v_cache[li], m.cos, m.sin,
+                      cfg.n_heads, cfg.n_kv_heads, cfg.head_dim)              # rows = consecutive positions pos0 + r
+            self._attn(self._q, m.k_cache[li], m.v_cache[li], self.pos_rows, out=self._a, q_stride=self._qkv.shape[1],
+                       shared_cache=True)
+            self._lin(L["o_proj"]._res, self._a, self._d)
+            G.add_rmsnorm(self._h, self._d, m.ln2[li], cfg.rms_eps, out=self._xn)
+            self._lin(L["gate_up"].res, self._xn, self._gu)
+            G.swiglu(self._g, self._u, out=self._act)
+            self._lin(L["down_proj"]._res, self._act, self._d)
+            delta = self._d
+        G.add_rmsnorm(self._h, delta, m.ln_f, cfg.rms_eps, out=self._xn)
+        return F.linear(self._xn, m.lm_head).float()
+
+    @torch.no_grad()
+    def capture(self):
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(2):
+                self._forward()
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            self.logits = self._forward()
+        return self
+
+    @torch.no_grad()
+    def __call__(self, tokens: torch.Tensor, pos0: int) -> torch.Tensor:
+        """tokens [T] at positions pos0 .. pos0 + T - 1; returns logits [T, vocab] (row r = the model's prediction for
+        position pos0 + r + 1)."""
+        self.tok.copy_(tokens.reshape(self.t))
+        self.pos0.fill_(pos0)
+        if self.graph is not None:
+            self.graph.replay()
+            return self.logits
+        return self._forward()
+
+    @torch.no_grad()
+    def accept(self, tokens: torch.Tensor, pos0: int):
+        """tokens[0] is the last confirmed token, tokens[1:] a draft of what follows.  Returns (number of draft tokens the
+        model's greedy arg-max confirms, the model's own next token after the confirmed prefix)."""
+        pred = self(tokens, pos0).argmax(-1)                          # pred[r]: greedy token for position pos0 + r + 1
+        ok = (pred[:-1] == tokens[1:].to(pred.device)).long().cumprod(0)
+        n = int(ok.sum().item())
+        return n, pred[n]
+
+
 class BatchedGreedyDecoder:
     """B sequences decoded in lock-step on a packed model: the decode loop of the reference's batched generator
     (ixrun/batching.py:88-234: per-row greedy arg-max, sequences of different lengths, one KV cache per row) without its

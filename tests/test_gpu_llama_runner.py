@@ -92,3 +92,45 @@ def test_batched_decoder_on_the_tensor_core_gemm():
         ref = packed.step(tok[r], prompts[r].numel())
         assert (logits[r] - ref[0]).abs().max() <= 0.05 * ref.abs().max()
     assert torch.isfinite(logits).all()
+
+
+def test_verifier_gives_the_logits_of_the_steps_one_by_one():
+    """Five tokens of one sequence in one pass (5 rows per linear, causal attention among them): the logits of every row
+    are, bit for bit, those of the batch-1 steps taken one after the other; eager and from the captured graph; and the
+    acceptance rule keeps exactly the prefix of a draft that greedy decoding would have produced."""
+    from ixrun_b200.llama_runner import Verifier
+
+    cfg, packed, _ = tiny()
+    prompt = torch.randint(0, cfg.vocab, (30,), generator=torch.Generator().manual_seed(9))
+    first = packed.prefill(prompt).argmax(-1)
+    greedy = packed.generate(prompt, 8)                               # greedy[0] == first
+    assert int(greedy[0]) == int(first)
+    packed.prefill(prompt)
+    ref = torch.cat([packed.step(greedy[i], 30 + i) for i in range(5)])     # logits after feeding greedy[0..4]
+    ver = Verifier(packed, 5)
+    for mode in ("eager", "graph"):
+        packed.prefill(prompt)
+        if mode == "graph":
+            ver.capture()
+            packed.prefill(prompt)
+        got = ver(greedy[:5], 30)
+        assert torch.equal(got, ref), mode
+    # a draft whose third token is wrong: two draft tokens are confirmed, the model's own token replaces the third
+    packed.prefill(prompt)
+    draft = greedy[:5].clone()
+    draft[3] = (draft[3] + 1) % cfg.vocab
+    n, nxt = ver.accept(draft, 30)
+    assert n == 2 and int(nxt) == int(greedy[3])
+
+
+def test_verifier_on_the_tensor_core_gemm():
+    from ixrun_b200.llama_runner import Verifier
+
+    cfg, packed, _ = tiny()
+    prompt = torch.randint(0, cfg.vocab, (25,), generator=torch.Generator().manual_seed(10))
+    packed.prefill(prompt)
+    toks = torch.randint(0, cfg.vocab, (12,), generator=torch.Generator().manual_seed(11))
+    ref = torch.cat([packed.step(toks[i], 25 + i) for i in range(12)])
+    packed.prefill(prompt)
+    got = Verifier(packed, 12)(toks, 25)
+    assert (got - ref).abs().max() <= 0.05 * ref.abs().max()
