@@ -127,6 +127,13 @@ int ixb_count_codes(const int8_t *codes_device, int64_t n_elements, void *b1_dev
 int ixb_pack_codes(const int8_t *codes_device, const ixb_packed *out, const int32_t *blk_q1_device,
                    const int32_t *blk_q2_device, ixb_stream_t stream);
 
+/* Sibling format with one fp16 scale per `group` consecutive elements (ixgs/quantize.py:35-112; decode
+ * ixgs/kernels.py:31-102): its five streams are read by ixb_decode unchanged (out_kind 0: int8 codes; the per-tensor
+ * scale of the ixb_packed is not used then), and this call turns codes + group scales into the bf16 weights
+ * bf16(f32(code) * f32(scale[e / group])). */
+int ixb_group_scale(const int8_t *codes_device, const void *group_scales_fp16_device, int64_t n, int64_t group,
+                    void *out_bf16_device, ixb_stream_t stream);
+
 /*
  * Resident re-layout "P6".  It has no counterpart in the reference, whose
  * kernels read the (3,5,8) streams directly; it plays the role of the

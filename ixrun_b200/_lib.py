@@ -21,7 +21,7 @@ SYMBOLS = (
     "ixb_prefix_workspace_bytes", "ixb_prefix_tables",
     "ixb_decode", "ixb_gemv_scratch_bytes", "ixb_gemv", "ixb_gemv_static",
     "ixb_gemm_scratch_bytes", "ixb_gemm",
-    "ixb_pack_workspace_bytes", "ixb_quantize_codes", "ixb_count_codes", "ixb_pack_codes",
+    "ixb_pack_workspace_bytes", "ixb_quantize_codes", "ixb_count_codes", "ixb_pack_codes", "ixb_group_scale",
     "ixb_p6_blocks", "ixb_p6_build", "ixb_p6_decode", "ixb_p6_gemv_scratch_bytes", "ixb_p6_gemv", "ixb_set_pdl",
     "ixb_p6_gemm_scratch_bytes", "ixb_p6_gemm",
     "ixb_allreduce_bytes", "ixb_allreduce", "ixb_p6_gemv_push", "ixb_allreduce_finish", "ixb_p6_gemv_allreduce", "ixb_allreduce_spin_limit",
@@ -133,6 +133,8 @@ def lib():
     L.ixb_p6_gemm_scratch_bytes.argtypes = [i64, i64, i64]
     L.ixb_p6_gemm.restype = C.c_int
     L.ixb_p6_gemm.argtypes = [C.POINTER(P6Struct), vp, i64, vp, vp, C.c_int, vp, sz, vp]
+    L.ixb_group_scale.restype = C.c_int
+    L.ixb_group_scale.argtypes = [vp, vp, i64, i64, vp, vp]
     L.ixb_attn_scratch_bytes.restype = sz
     L.ixb_attn_scratch_bytes.argtypes = [i64, i64, i64]
     L.ixb_attn_decode.restype = C.c_int

@@ -2,6 +2,7 @@
 // Built for sm_100a only.  See include/ixb200.h for the contract of each call.
 #include "../../include/ixb200.h"
 #include <cstdlib>
+#include <cuda_fp16.h>
 #include "ixb_common.cuh"
 #include "ixb_gemm_tc.cuh"
 #include "ixb_p6_gemm.cuh"
@@ -741,6 +742,17 @@ extern "C" int ixb_pack_codes(const int8_t *codes, const ixb_packed *out, const 
     k_pack<<<(nb + 7) / 8, 256, 0, st>>>(codes, s.n, blk_q1, blk_q2, (uint32_t *)s.b2, (uint32_t *)s.l1,
                                          (uint32_t *)s.l2, (uint8_t *)s.l3);
     return launch_check("k_pack");
+}
+
+extern "C" int ixb_group_scale(const int8_t *codes, const void *group_scales_fp16, int64_t n, int64_t group, void *out,
+                               ixb_stream_t stream)
+{
+    if (!codes || !group_scales_fp16 || !out) return fail(IXB_E_ARG, "NULL pointer argument");
+    if (n <= 0 || n > 0x7fffffffLL || group <= 0) return fail(IXB_E_ARG, "bad size");
+    const uint32_t threads = (uint32_t)((n + 7) / 8);
+    k_group_scale<<<(threads + 255) / 256, 256, 0, (cudaStream_t)stream>>>(codes, (const __half *)group_scales_fp16, (uint32_t)n,
+                                                                         (uint32_t)group, (__nv_bfloat16 *)out);
+    return launch_check("k_group_scale");
 }
 
 // ------------------------------------------------------------- resident P6 layout

@@ -124,4 +124,34 @@ k_pack(const int8_t *__restrict__ codes, uint32_t n, const int32_t *__restrict__
     }
 }
 
+// ---------------------------------------------------------------- sibling format: per-group scales
+// The group-scale variant of the format (ixgs/quantize.py:35-112, decode ixgs/kernels.py:31-102 and
+// ixgs/quantize.py:116-151) stores the same five (3,5,8) streams (fields offset by -3 / -15 / -127, so the stream
+// decoder above serves it unchanged) and one fp16 scale per `group` consecutive elements of the flat tensor instead of
+// one per tensor: w[e] = bf16(f32(code[e]) * f32(scale[e / group])).  Eight weights per thread where the shape allows.
+__global__ void __launch_bounds__(256)
+k_group_scale(const int8_t *__restrict__ codes, const __half *__restrict__ gscale, uint32_t n, uint32_t group,
+              __nv_bfloat16 *__restrict__ out)
+{
+    const uint32_t e0 = (blockIdx.x * blockDim.x + threadIdx.x) * 8u;
+    if (e0 >= n) return;
+    if (e0 + 8u <= n && (group & 7u) == 0 && (((uintptr_t)codes | (uintptr_t)out) & 15u) == 0) {
+        const float sc = __half2float(gscale[e0 / group]);             // eight consecutive elements share a group
+        const uint2 c = *(const uint2 *)(codes + e0);
+        const uint32_t cw[2] = {c.x, c.y};
+        uint32_t o[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const int a = (int)(int8_t)((cw[k >> 1] >> (16 * (k & 1))) & 0xff);
+            const int b = (int)(int8_t)((cw[k >> 1] >> (16 * (k & 1) + 8)) & 0xff);
+            o[k] = (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn((float)a * sc)) |
+                   ((uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn((float)b * sc)) << 16);
+        }
+        *(uint4 *)(out + e0) = make_uint4(o[0], o[1], o[2], o[3]);
+    } else {
+        for (uint32_t e = e0; e < min(e0 + 8u, n); ++e)
+            out[e] = __float2bfloat16_rn((float)codes[e] * __half2float(gscale[e / group]));
+    }
+}
+
 }  // namespace ixb

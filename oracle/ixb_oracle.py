@@ -178,6 +178,20 @@ def decode_bf16(p: dict) -> np.ndarray:
     return codes_to_bf16(decode_codes(p), p["scale"]).reshape(p["out_f"], p["in_f"])
 
 
+def ixgs_decode_bf16(p: dict) -> np.ndarray:
+    """Group-scale sibling format (ixgs/quantize.py:116-151): the same five streams, fields offset by -3 / -15 / -127,
+    then w[e] = bf16(f32(code[e]) * f32(fp16 scale[e // group])).  `p`: the ixgs dict with numpy arrays
+    (group_scales as fp16 bit patterns).  Returns bf16 bit patterns [out_f, in_f]."""
+    n1, n2, n3 = (int(c) for c in p["counts"])
+    n = int(p["out_f"]) * int(p["in_f"])
+    main = {"N": n, "bitmaps": [np.asarray(p["b1"]), np.asarray(p["b2"])[: (n2 + n3 + 31) // 32]],
+            "streams": [np.asarray(p["l1"]), np.asarray(p["l2"]), np.asarray(p["l3"])[:n3]]}
+    codes = decode_codes(main).astype(np.float32)
+    scales = np.asarray(p["group_scales"], dtype=np.uint16).view(np.float16).astype(np.float32)
+    per_elem = np.repeat(scales, int(p["group_size"]))[:n]
+    return f32_to_bf16_bits(codes * per_elem).reshape(int(p["out_f"]), int(p["in_f"]))
+
+
 # ------------------------------------------------------------ gemv / gemm ---
 def gemm_f32(codes: np.ndarray, scale_bits: int, x_bits: np.ndarray, out_f: int, in_f: int):
     """y[M, out_f] (float32) for x bf16 bits [M, in_f]."""

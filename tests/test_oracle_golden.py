@@ -104,3 +104,12 @@ def test_full_size_tensor_hashes(golden_dir):
     assert sha(O.decode_bf16(p)) == big["sha_w_dec"]
     q1, q2 = O.prefixes(p, 1024)
     assert sha(q1) == big["sha_blk_q1"] and sha(q2) == big["sha_blk_q2"]
+
+
+def test_group_scale_sibling_format_golden(golden_dir):
+    """The oracle's restatement of the group-scale format against the reference's own decode (fixture written by
+    tests/golden/make_ixgs_golden.py from ixgs.quantize.decode_weight_scatter)."""
+    d = np.load(os.path.join(golden_dir, "ixgs_48x320.npz"))
+    p = {k: d[k] for k in d.files}
+    got = O.ixgs_decode_bf16(p)
+    assert np.array_equal(got, d["decoded"])
