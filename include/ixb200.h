@@ -127,6 +127,32 @@ int ixb_count_codes(const int8_t *codes_device, int64_t n_elements, void *b1_dev
 int ixb_pack_codes(const int8_t *codes_device, const ixb_packed *out, const int32_t *blk_q1_device,
                    const int32_t *blk_q2_device, ixb_stream_t stream);
 
+/* TPAB tile format (ixrun/tpab.py:37-203; GEMV ixrun/tpab_gemv.py:28-143): tiles of tile_r x 64, per tile a bit
+ * width 2..6, an fp16 scale and its element offset inside the group of tiles of that width; element L of tile t is
+ * the field at bit gbase_bit[b] + (goff[t] + L) * b of `body` (uint32 words, two readable words behind the last),
+ * weight bf16(f32(field - (2^(b-1) - 1)) * f32(scale)); outliers replace their weights.  The packed dict of
+ * ixrun.tpab.encode_tpab is consumed as it is (bodies concatenated as ixrun.tpab.stage_gpu does).
+ * ixb_tpab_decode: -> bf16 [out_f, in_f] (outliers (tile, element, fp16 value) scattered over their weights).
+ * ixb_tpab_gemv: batch-1 y = W x, fp32 accumulation, one rounding, bias after it; the outliers as per-row lists
+ *   (ol_offs [out_f + 1], columns, fp16 values: what ixrun.tpab_gemv.prepare_gemv_stage builds).  Reproducible (no
+ *   floating-point atomics).  scratch: ixb_tpab_gemv_scratch_bytes, any contents. */
+typedef struct ixb_tpab {
+    const void *body;
+    const void *bits;
+    const void *scales;
+    const void *goff;
+    int32_t gbase_bit[8];
+    int64_t out_f;
+    int64_t in_f;
+    int64_t tile_r;
+} ixb_tpab;
+int ixb_tpab_decode(const ixb_tpab *t, const int32_t *ol_t_device, const int32_t *ol_l_device, const void *ol_val_fp16_device,
+                    int64_t n_outliers, void *out_bf16_device, ixb_stream_t stream);
+size_t ixb_tpab_gemv_scratch_bytes(int64_t out_f, int64_t in_f, int64_t tile_r);
+int ixb_tpab_gemv(const ixb_tpab *t, const void *x_device, const int32_t *ol_offs_device, const int32_t *ol_k_device,
+                  const void *ol_v_fp16_device, const void *bias_device, void *y_device, int y_is_f32, void *scratch_device,
+                  size_t scratch_bytes, ixb_stream_t stream);
+
 /* Sibling format with one fp16 scale per `group` consecutive elements (ixgs/quantize.py:35-112; decode
  * ixgs/kernels.py:31-102): its five streams are read by ixb_decode unchanged (out_kind 0: int8 codes; the per-tensor
  * scale of the ixb_packed is not used then), and this call turns codes + group scales into the bf16 weights

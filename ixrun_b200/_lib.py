@@ -21,7 +21,7 @@ SYMBOLS = (
     "ixb_prefix_workspace_bytes", "ixb_prefix_tables",
     "ixb_decode", "ixb_gemv_scratch_bytes", "ixb_gemv", "ixb_gemv_static",
     "ixb_gemm_scratch_bytes", "ixb_gemm",
-    "ixb_pack_workspace_bytes", "ixb_quantize_codes", "ixb_count_codes", "ixb_pack_codes", "ixb_group_scale",
+    "ixb_pack_workspace_bytes", "ixb_quantize_codes", "ixb_count_codes", "ixb_pack_codes", "ixb_group_scale", "ixb_tpab_decode", "ixb_tpab_gemv_scratch_bytes", "ixb_tpab_gemv",
     "ixb_p6_blocks", "ixb_p6_build", "ixb_p6_decode", "ixb_p6_gemv_scratch_bytes", "ixb_p6_gemv", "ixb_set_pdl",
     "ixb_p6_gemm_scratch_bytes", "ixb_p6_gemm",
     "ixb_allreduce_bytes", "ixb_allreduce", "ixb_p6_gemv_push", "ixb_allreduce_finish", "ixb_p6_gemv_allreduce", "ixb_allreduce_spin_limit",
@@ -55,6 +55,13 @@ class P6Struct(C.Structure):
         ("n_esc", C.c_int64), ("scale", C.c_void_p), ("out_f", C.c_int64), ("in_f", C.c_int64),
         ("scale_stride", C.c_int64),
     ]
+
+
+class TpabStruct(C.Structure):
+    """Mirror of ``struct ixb_tpab``."""
+
+    _fields_ = [("body", C.c_void_p), ("bits", C.c_void_p), ("scales", C.c_void_p), ("goff", C.c_void_p),
+                ("gbase_bit", C.c_int32 * 8), ("out_f", C.c_int64), ("in_f", C.c_int64), ("tile_r", C.c_int64)]
 
 
 def lib():
@@ -133,6 +140,12 @@ def lib():
     L.ixb_p6_gemm_scratch_bytes.argtypes = [i64, i64, i64]
     L.ixb_p6_gemm.restype = C.c_int
     L.ixb_p6_gemm.argtypes = [C.POINTER(P6Struct), vp, i64, vp, vp, C.c_int, vp, sz, vp]
+    L.ixb_tpab_decode.restype = C.c_int
+    L.ixb_tpab_decode.argtypes = [C.POINTER(TpabStruct), vp, vp, vp, i64, vp, vp]
+    L.ixb_tpab_gemv_scratch_bytes.restype = sz
+    L.ixb_tpab_gemv_scratch_bytes.argtypes = [i64, i64, i64]
+    L.ixb_tpab_gemv.restype = C.c_int
+    L.ixb_tpab_gemv.argtypes = [C.POINTER(TpabStruct), vp, vp, vp, vp, vp, vp, C.c_int, vp, sz, vp]
     L.ixb_group_scale.restype = C.c_int
     L.ixb_group_scale.argtypes = [vp, vp, i64, i64, vp, vp]
     L.ixb_attn_scratch_bytes.restype = sz

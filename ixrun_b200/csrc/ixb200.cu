@@ -10,6 +10,7 @@
 #include "ixb_p6.cuh"
 #include "ixb_allreduce.cuh"
 #include "ixb_glue.cuh"
+#include "ixb_tpab.cuh"
 
 #include <atomic>
 #include <cstdarg>
@@ -753,6 +754,83 @@ extern "C" int ixb_group_scale(const int8_t *codes, const void *group_scales_fp1
     k_group_scale<<<(threads + 255) / 256, 256, 0, (cudaStream_t)stream>>>(codes, (const __half *)group_scales_fp16, (uint32_t)n,
                                                                          (uint32_t)group, (__nv_bfloat16 *)out);
     return launch_check("k_group_scale");
+}
+
+// ------------------------------------------------------------- TPAB tile format
+static int to_tpab(const ixb_tpab *t, Tpab *p)
+{
+    if (!t) return fail(IXB_E_ARG, "TPAB tensor is NULL");
+    if (!t->body || !t->bits || !t->scales || !t->goff) return fail(IXB_E_ARG, "NULL TPAB pointer");
+    if (t->out_f <= 0 || t->in_f <= 0 || (t->in_f & 63)) return fail(IXB_E_ARG, "in_f must be a positive multiple of 64");
+    if (t->tile_r < 1 || t->tile_r > 64 || (t->tile_r & (t->tile_r - 1)) || t->out_f % t->tile_r)
+        return fail(IXB_E_ARG, "tile_r must be a power of two <= 64 that divides out_f");
+    if ((long long)t->out_f * t->in_f > 800000000LL) return fail(IXB_E_UNSUPPORTED, "tensor too large");
+    p->body = (const uint32_t *)t->body;
+    p->bits = (const uint8_t *)t->bits;
+    p->scales = (const __half *)t->scales;
+    p->goff = (const int32_t *)t->goff;
+    for (int b = 0; b < 8; ++b) p->gbase[b] = t->gbase_bit[b];
+    p->out_f = (uint32_t)t->out_f;
+    p->in_f = (uint32_t)t->in_f;
+    p->tile_r = (uint32_t)t->tile_r;
+    p->t_c = p->in_f / 64u;
+    p->t_r = p->out_f / p->tile_r;
+    return IXB_OK;
+}
+
+extern "C" int ixb_tpab_decode(const ixb_tpab *t, const int32_t *ol_t, const int32_t *ol_l, const void *ol_val_fp16,
+                               int64_t n_ol, void *out, ixb_stream_t stream)
+{
+    Tpab p;
+    int rc = to_tpab(t, &p);
+    if (rc) return rc;
+    if (!out || ((uintptr_t)out & 15u)) return fail(IXB_E_ARG, "output is NULL or misaligned");
+    if (n_ol < 0 || (n_ol && (!ol_t || !ol_l || !ol_val_fp16))) return fail(IXB_E_ARG, "bad outlier arrays");
+    cudaStream_t st = (cudaStream_t)stream;
+    const uint32_t rows = p.t_r * p.t_c * p.tile_r;
+    k_tpab_decode<<<(rows + 127) / 128, 128, 0, st>>>(p, (__nv_bfloat16 *)out);
+    if ((rc = launch_check("k_tpab_decode"))) return rc;
+    if (n_ol) {
+        k_tpab_scatter<<<(unsigned)((n_ol + 255) / 256), 256, 0, st>>>(p, ol_t, ol_l, (const __half *)ol_val_fp16, (uint32_t)n_ol,
+                                                                     (__nv_bfloat16 *)out);
+        rc = launch_check("k_tpab_scatter");
+    }
+    return rc;
+}
+
+static uint32_t tpab_splits(uint32_t t_r, uint32_t t_c)
+{
+    int dev = 0, sms = 148;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    uint32_t s = std::max<uint32_t>(1u, (2u * (uint32_t)sms) / t_r);
+    s = std::min<uint32_t>(s, std::max<uint32_t>(1u, t_c / (uint32_t)kTpabWarps));
+    return std::min<uint32_t>(s, 32u);
+}
+
+extern "C" size_t ixb_tpab_gemv_scratch_bytes(int64_t out_f, int64_t in_f, int64_t tile_r)
+{
+    if (out_f <= 0 || in_f <= 0 || (in_f & 63) || tile_r < 1 || out_f % tile_r) return 0;
+    return (size_t)tpab_splits((uint32_t)(out_f / tile_r), (uint32_t)(in_f / 64)) * (size_t)out_f * sizeof(float);
+}
+
+extern "C" int ixb_tpab_gemv(const ixb_tpab *t, const void *x, const int32_t *ol_offs, const int32_t *ol_k, const void *ol_v_fp16,
+                             const void *bias, void *y, int y_is_f32, void *scratch, size_t scratch_bytes, ixb_stream_t stream)
+{
+    Tpab p;
+    int rc = to_tpab(t, &p);
+    if (rc) return rc;
+    if (!x || !y || !scratch) return fail(IXB_E_ARG, "NULL pointer argument");
+    if ((uintptr_t)x & 3u) return fail(IXB_E_ARG, "x is misaligned");
+    if (ol_offs && (!ol_k || !ol_v_fp16)) return fail(IXB_E_ARG, "bad outlier arrays");
+    if (scratch_bytes < ixb_tpab_gemv_scratch_bytes(p.out_f, p.in_f, p.tile_r)) return fail(IXB_E_SCRATCH, "TPAB scratch too small");
+    const uint32_t splits = tpab_splits(p.t_r, p.t_c);
+    cudaStream_t st = (cudaStream_t)stream;
+    k_tpab_gemv<<<dim3(p.t_r, splits), kTpabWarps * 32, 0, st>>>(p, (const __nv_bfloat16 *)x, (float *)scratch, splits);
+    if ((rc = launch_check("k_tpab_gemv"))) return rc;
+    k_tpab_finalize<<<(p.out_f + 255) / 256, 256, 0, st>>>((const float *)scratch, splits, p.out_f, ol_offs, ol_k,
+                                                           (const __half *)ol_v_fp16, (const __nv_bfloat16 *)x,
+                                                           (const __nv_bfloat16 *)bias, y, y_is_f32);
+    return launch_check("k_tpab_finalize");
 }
 
 // ------------------------------------------------------------- resident P6 layout

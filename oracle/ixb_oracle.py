@@ -192,6 +192,42 @@ def ixgs_decode_bf16(p: dict) -> np.ndarray:
     return f32_to_bf16_bits(codes * per_elem).reshape(int(p["out_f"]), int(p["in_f"]))
 
 
+# ------------------------------------------------------------ TPAB tiles ----
+def tpab_decode_bf16(p: dict) -> np.ndarray:
+    """TPAB tile format (ixrun/tpab.py:180-203): tiles of tile_r x 64, per tile a bit width b in 2..6, an fp16 scale
+    and its element offset `goff` inside the group of tiles of that width; element L of tile t is the b-bit field at
+    bit gbase_bit[b] + (goff[t] + L) * b of the uint32 body, q = field - (2^(b-1) - 1), w = bf16(f32(q) * f32(scale));
+    outliers (tile, element, fp16 value) replace their weights.  `p`: numpy arrays (fp16 / bf16 as bit patterns).
+    Returns bf16 bit patterns [out_f, in_f]."""
+    out_f, in_f, tr = int(p["out_f"]), int(p["in_f"]), int(p["tile_r"])
+    n_per, t_c = tr * 64, in_f // 64
+    body = np.ascontiguousarray(p["body"]).view(np.uint32).astype(np.uint64)
+    body = np.concatenate([body, np.zeros(2, dtype=np.uint64)])
+    bits_ = np.asarray(p["bits"]).astype(np.int64)
+    scales = np.asarray(p["scales"], dtype=np.uint16).view(np.float16).astype(np.float32)
+    goff = np.asarray(p["goff"]).astype(np.int64)
+    gbase = np.asarray(p["gbase_bit"]).astype(np.int64)
+    n_t = bits_.size
+    L = np.arange(n_per, dtype=np.int64)[None, :]
+    b = bits_[:, None]
+    pos = gbase[bits_][:, None] + (goff[:, None] + L) * b
+    word, sh = pos >> 5, (pos & 31).astype(np.uint64)
+    raw = ((body[word] | (body[word + 1] << np.uint64(32))) >> sh) & ((np.uint64(1) << b.astype(np.uint64)) - np.uint64(1))
+    q = raw.astype(np.int64) - ((1 << (b - 1)) - 1)
+    w = f32_to_bf16_bits((q.astype(np.float32) * scales[:, None]).astype(np.float32)).reshape(n_t, n_per)
+    ol_t, ol_l = np.asarray(p["ol_t"]).astype(np.int64), np.asarray(p["ol_l"]).astype(np.int64)
+    ol = np.asarray(p["ol_val"], dtype=np.uint16).view(np.float16).astype(np.float32)
+    w[ol_t, ol_l] = f32_to_bf16_bits(ol)
+    return w.reshape(out_f // tr, t_c, tr, 64).transpose(0, 2, 1, 3).reshape(out_f, in_f)
+
+
+def tpab_gemv_f32(p: dict, x_bits: np.ndarray) -> np.ndarray:
+    """y = W x in float64-accumulated float32 for the decoded TPAB weights (ixrun/tpab_gemv.py:72-124)."""
+    w = bf16_bits_to_f32(tpab_decode_bf16(p)).astype(np.float64)
+    x = bf16_bits_to_f32(np.asarray(x_bits, dtype=np.uint16)).astype(np.float64)
+    return (w @ x).astype(np.float32)
+
+
 # ------------------------------------------------------------ gemv / gemm ---
 def gemm_f32(codes: np.ndarray, scale_bits: int, x_bits: np.ndarray, out_f: int, in_f: int):
     """y[M, out_f] (float32) for x bf16 bits [M, in_f]."""

@@ -113,3 +113,14 @@ def test_group_scale_sibling_format_golden(golden_dir):
     p = {k: d[k] for k in d.files}
     got = O.ixgs_decode_bf16(p)
     assert np.array_equal(got, d["decoded"])
+
+
+@pytest.mark.parametrize("name", ["tpab_128x256", "tpab_48x192", "tpab_64x512", "tpab_64x128"])
+def test_tpab_tile_format_golden(golden_dir, name):
+    """The oracle's restatement of the TPAB tile format against the reference's own decode and matmul (fixtures written
+    by tests/golden/make_tpab_golden.py from ixrun.tpab.encode_tpab / decode_tpab_ref)."""
+    d = np.load(os.path.join(golden_dir, name + ".npz"))
+    p = {k: d[k] for k in d.files}
+    assert np.array_equal(O.tpab_decode_bf16(p), d["decoded"])
+    y = O.tpab_gemv_f32(p, d["x"])
+    assert np.abs(y - d["y"]).max() <= 1e-5 * np.abs(d["y"]).max()
