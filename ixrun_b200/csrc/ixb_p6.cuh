@@ -519,9 +519,13 @@ k_p6_mma(P6 p, const __nv_bfloat16 *__restrict__ x, uint32_t m_rows, const __nv_
     uint32_t e2, b2 = 0, c2 = 0;
     uint32_t sc_cur = 0, sc_next = 0;
     {
-        const uint32_t R0 = min(b_begin / KB, p.rt - 1u);
-        sc_cur = (uint32_t)__bfloat16_as_ushort(p.scale[R0 * p.scale_stride]);
-        sc_next = (uint32_t)__bfloat16_as_ushort(p.scale[min(R0 + 1u, p.rt - 1u) * p.scale_stride]);
+        if (p.scale_stride) {                                          // (uniform) a fused tensor: one scale per row tile
+            const uint32_t R0 = min(b_begin / KB, p.rt - 1u);
+            sc_cur = (uint32_t)__bfloat16_as_ushort(p.scale[R0]);
+            sc_next = (uint32_t)__bfloat16_as_ushort(p.scale[min(R0 + 1u, p.rt - 1u)]);
+        } else {
+            sc_cur = (uint32_t)__bfloat16_as_ushort(p.scale[0]);
+        }
         asm volatile("mov.b32 %0, 0x3F003F00;" : "=r"(e2));            // opaque, so that it stays a register operand
     }
     auto set_scale = [&](uint32_t bits) {
