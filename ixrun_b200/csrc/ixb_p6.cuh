@@ -771,7 +771,7 @@ k_p6_mma(P6 p, const __nv_bfloat16 *__restrict__ x, uint32_t m_rows, const __nv_
             if (first) {
                 // three block iterations complete the copy group of the entries for this lane, the warp barrier
                 // for all lanes
-                mid = min(b + 3u, seg_e);
+                mid = min(b + 3u + 2u * ((uint32_t)wid & 7u), seg_e);      // (the warps' outlier passes do not all fall on the same moment)
                 run(b, mid);
                 if (mid - b < 3u) cp_async_wait<0>();
                 __syncwarp();
