@@ -70,9 +70,6 @@ class HybridConfig:
         return li % self.attn_every == self.attn_every - 1
 
 
-HIDDEN, FFN = HybridConfig.hidden, HybridConfig.ffn
-
-
 @contextlib.contextmanager
 def _stdout_to_stderr():
     """File descriptor 1 points at stderr inside the block (for output that native libraries write themselves)."""

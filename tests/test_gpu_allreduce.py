@@ -52,8 +52,6 @@ def test_single_rank_allreduce_replays_from_a_cuda_graph():
 
 
 def _shard(out_f, in_f, seed):
-    import numpy as np
-
     from ixrun_b200.p6 import P6Packed
     from oracle import ixb_oracle as O
 

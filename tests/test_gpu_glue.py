@@ -1,6 +1,5 @@
 """Per-token glue kernels against plain torch fp32 references of the same operations (tolerance 1e-3 of the largest
 output unless the output itself is a bf16 tensor, where one bf16 rounding, 2^-8, is allowed)."""
-import math
 
 import pytest
 import torch

@@ -7,7 +7,6 @@ the shared array).  This file is named so that pytest collects it last.
 """
 import ctypes as C
 
-import numpy as np
 import pytest
 import torch
 
