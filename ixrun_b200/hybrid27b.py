@@ -21,8 +21,9 @@ it is this library's glue kernels, all of them part of the programmatic-dependen
 
 Tensor parallelism: in-projections, gate and up are column-parallel (heads / rows split; with more ranks than KV heads
 a rank still holds one whole KV head), out_proj / o_proj / down_proj are row-parallel: their fp32 partial sums leave the
-GEMV's epilogue as peer stores into every rank's exchange buffer, and the residual add + RMSNorm kernel that follows
-waits for them and adds them up -- one exchange per token-mixer block and one per MLP block, no launch of its own.  lm_head is split by vocabulary; the ranks exchange (max, index) pairs.
+GEMV's epilogue as peer stores into every rank's exchange buffer; the sum is taken by the residual add + RMSNorm kernel
+that follows (two ranks: no launch of its own) or by a 20-CTA finishing kernel in front of it (more ranks: one CTA
+cannot pull every rank's words through its SM fast enough) -- one exchange per token-mixer block and one per MLP block.  lm_head is split by vocabulary; the ranks exchange (max, index) pairs.
 With --nccl the partial sums go through eager NCCL all-reduces instead (no graph; a cross-check, not a fast path).
 
 The fused q|gate projection is stored as [all q heads | all gate heads] (a row permutation of the per-head
@@ -112,13 +113,19 @@ class Hybrid27B:
     """One rank's share of the model and the state of one decoding sequence."""
 
     def __init__(self, cfg: HybridConfig, world: int, rank: int, dev, context: int = 4096, max_new: int = 272,
-                 nccl: bool = False, seed: int = 0, lm_head: bool = True):
+                 nccl: bool = False, seed: int = 0, lm_head: bool = True, fused_finish: bool | None = None):
         from .p6 import P6Packed
 
         self.cfg, self.world, self.rank, self.dev = cfg, world, rank, torch.device(dev)
         self.geo = g = shard_geometry(cfg, world)
         self.context, self.max_seq = context, context + max_new
         self.nccl = nccl and world > 1
+        # second half of the exchange: inside the next norm kernel, or as the 20-CTA finishing kernel followed by the
+        # plain norm kernel.  The norm kernel is ONE CTA: at 8 ranks it has to pull 328 KB of marked words through one
+        # SM per exchange (12 us measured, against 3 us for the finishing kernel that spreads them over 20 SMs), so
+        # the fused form is the default only up to two ranks.  IXB200_FUSED_FINISH=0/1 overrides.
+        env = os.environ.get("IXB200_FUSED_FINISH")
+        self.fused_finish = fused_finish if fused_finish is not None else (env != "0" if env is not None else world <= 2)
         self.ar = None
         if world > 1 and not nccl:
             from .parallel import PeerAllReduce
@@ -216,8 +223,10 @@ class Hybrid27B:
         from there.  Several: the fp32 partial sums leave the GEMV as peer stores; returns None, and the caller's next
         norm kernel is also the second half of the exchange (glue.finish_add_rmsnorm)."""
         if self.ar is not None:
-            lin.gemv_push(x, self.ar)
-            return None
+            n = lin.gemv_push(x, self.ar)
+            if self.fused_finish:
+                return None
+            return self.ar.finish(n, self.d_out)
         if self.nccl:
             lin.gemv(x, out=self.y32)
             dist.all_reduce(self.y32)
@@ -227,7 +236,7 @@ class Hybrid27B:
         return self.d_out
 
     def _add_norm(self, delta, w, first=False):
-        if self.ar is not None and not first:
+        if self.ar is not None and not first and self.fused_finish:
             return G.finish_add_rmsnorm(self.ar, self.h, w, self.cfg.eps, out=self.xn)
         return G.add_rmsnorm(self.h, delta, w, self.cfg.eps, out=self.xn)
 
@@ -318,7 +327,7 @@ def launches_per_token(cfg: HybridConfig, world: int) -> int:
     """Kernels of this library in one token step (packed GEMVs, glue, exchange)."""
     n = 0
     for li in range(cfg.n_layers):
-        n += (6 if cfg.is_attn(li) else 4) + 4          # on several GPUs the norm kernels also finish the exchanges
+        n += (6 if cfg.is_attn(li) else 4) + 4 + (2 if world > 2 else 0)      # beyond two ranks: a finishing kernel per exchange
     return n + 1 + (1 if world > 1 else 0)
 
 
