@@ -21,9 +21,10 @@ it is this library's glue kernels, all of them part of the programmatic-dependen
 
 Tensor parallelism: in-projections, gate and up are column-parallel (heads / rows split; with more ranks than KV heads
 a rank still holds one whole KV head), out_proj / o_proj / down_proj are row-parallel: their fp32 partial sums leave the
-GEMV's epilogue as peer stores into every rank's exchange buffer; the sum is taken by the residual add + RMSNorm kernel
-that follows (two ranks: no launch of its own) or by a 20-CTA finishing kernel in front of it (more ranks: one CTA
-cannot pull every rank's words through its SM fast enough) -- one exchange per token-mixer block and one per MLP block.  lm_head is split by vocabulary; the ranks exchange (max, index) pairs.
+GEMV's epilogue as peer stores into every rank's exchange buffer and a 20-CTA finishing kernel adds them up in front of
+the next residual add + RMSNorm kernel (the norm kernel can also take the sum itself, which saves two launches per block
+but was measured slower: one CTA cannot pull every rank's words through its SM fast enough) -- one exchange per
+token-mixer block and one per MLP block.  lm_head is split by vocabulary; the ranks exchange (max, index) pairs.
 With --nccl the partial sums go through eager NCCL all-reduces instead (no graph; a cross-check, not a fast path).
 
 The fused q|gate projection is stored as [all q heads | all gate heads] (a row permutation of the per-head
@@ -120,12 +121,12 @@ class Hybrid27B:
         self.geo = g = shard_geometry(cfg, world)
         self.context, self.max_seq = context, context + max_new
         self.nccl = nccl and world > 1
-        # second half of the exchange: inside the next norm kernel, or as the 20-CTA finishing kernel followed by the
-        # plain norm kernel.  The norm kernel is ONE CTA: at 8 ranks it has to pull 328 KB of marked words through one
-        # SM per exchange (12 us measured, against 3 us for the finishing kernel that spreads them over 20 SMs), so
-        # the fused form is the default only up to two ranks.  IXB200_FUSED_FINISH=0/1 overrides.
+        # second half of the exchange: the 20-CTA finishing kernel followed by the plain norm kernel (default), or inside
+        # the norm kernel itself (fused_finish / IXB200_FUSED_FINISH=1).  The norm kernel is ONE CTA and has to pull every
+        # rank's marked words through one SM: measured slower at every world size (2 ranks: 4.50 vs 4.38 ms/token,
+        # 8 ranks: 4.11 vs 3.02), although it saves two launches per block.
         env = os.environ.get("IXB200_FUSED_FINISH")
-        self.fused_finish = fused_finish if fused_finish is not None else (env != "0" if env is not None else world <= 2)
+        self.fused_finish = fused_finish if fused_finish is not None else (env == "1")
         self.ar = None
         if world > 1 and not nccl:
             from .parallel import PeerAllReduce
@@ -327,7 +328,7 @@ def launches_per_token(cfg: HybridConfig, world: int) -> int:
     """Kernels of this library in one token step (packed GEMVs, glue, exchange)."""
     n = 0
     for li in range(cfg.n_layers):
-        n += (6 if cfg.is_attn(li) else 4) + 4 + (2 if world > 2 else 0)      # beyond two ranks: a finishing kernel per exchange
+        n += (6 if cfg.is_attn(li) else 4) + 4 + (2 if world > 1 else 0)      # a finishing kernel per exchange
     return n + 1 + (1 if world > 1 else 0)
 
 
