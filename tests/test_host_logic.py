@@ -103,3 +103,29 @@ def test_no_cpu_fallback():
     p = Q.int8x_quantize(torch.randn(4, 64).bfloat16())
     with pytest.raises(_lib.IxbError):
         DevicePacked(p)
+
+
+def test_ctypes_prototypes_match_the_header():
+    """Every function declared in include/ixb200.h has a ctypes prototype with the same number of parameters, and the
+    mirrored structs have the header's field count (an ABI drift between header, library and binding fails here, on
+    the CPU)."""
+    from ixrun_b200 import _lib
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    hdr = open(os.path.join(root, "include", "ixb200.h")).read()
+    hdr_nc = re.sub(r"/\*.*?\*/", "", hdr, flags=re.S)                     # without comments
+    L = _lib.lib()
+    decls = re.findall(r"\b(?:int|size_t|int64_t|const char \*|unsigned long long)\s*\**\s*(ixb_[a-z0-9_]+)\s*\(([^;{]*?)\)\s*;", hdr_nc, flags=re.S)
+    assert len(decls) >= 30
+    for name, args in decls:
+        args = args.strip()
+        n = 0 if args in ("", "void") else len([a for a in args.split(",") if a.strip()])
+        fn = getattr(L, name)
+        if n == 0 and fn.argtypes is None:
+            continue
+        assert fn.argtypes is not None, f"{name} has no ctypes prototype"
+        assert len(fn.argtypes) == n, f"{name}: header has {n} parameters, the binding {len(fn.argtypes)}"
+    for struct, mirror in (("ixb_packed", _lib.Packed), ("ixb_p6", _lib.P6Struct), ("ixb_tpab", _lib.TpabStruct)):
+        body = re.search(r"typedef struct " + struct + r"\s*\{(.*?)\}\s*" + struct + r"\s*;", hdr_nc, flags=re.S).group(1)
+        fields = [f for f in body.split(";") if f.strip()]
+        assert len(fields) == len(mirror._fields_), f"{struct}: header has {len(fields)} fields, the mirror {len(mirror._fields_)}"
