@@ -309,8 +309,9 @@ uint32_t ixb_allreduce_spin_limit(uint32_t polls);
  *   NULL), rotate-half rotary embedding of the first rot_dim dimensions with
  *   the caller's fp32 tables cos / sin [max_seq][rot_dim / 2]; q [rows] (row
  *   stride q_stride elements, heads contiguous) rotated in place, k and v
- *   [rows][hkv][head_dim] (row pitch kv_stride) written into the caches [max_seq][hkv][head_dim] at
- *   positions pos[0] + row.  head_dim 128 or 256.
+ *   [rows][hkv][head_dim] (row pitch kv_stride) written into the caches
+ *   [max_seq][hkv][head_dim] at
+ *   positions pos[0] + row.  head_dim 64, 128 or 256.
  * ixb_attn_decode: one query per head (q [hq][head_dim]) over positions
  *   0 .. pos[0] of the static caches, grouped-query (hq a multiple of hkv),
  *   softmax(scale * q.k) v, the context cut into `splits` ranges that run on
@@ -335,7 +336,8 @@ int ixb_add_rmsnorm(void *h_device, const void *delta_device, const void *w_devi
 /* ixb_allreduce_finish with the residual add and the RMSNorm that follow a row-parallel linear in the same kernel:
  * h [rows][hidden] (bf16, in/out) += bf16(sum over the ranks' words of this call), xn = rmsnorm(h) * w.  rows <= 8,
  * hidden a multiple of 8 and at most 5120, rows * hidden <= n_max.  No reference counterpart (the reference is
- * single-GPU); the result equals ixb_allreduce_finish into a bf16 vector followed by ixb_add_rmsnorm. */
+ * single-GPU); the result equals ixb_allreduce_finish into a bf16 vector followed by ixb_add_rmsnorm.  One CTA per row
+ * pulls every rank's words through one SM: fewer launches, but slower than the two calls (measured at 2 and 8 ranks). */
 int ixb_allreduce_finish_add_rmsnorm(void *const *peer_buffers, int rank, int world, int64_t n_max, void *h_device,
                                      const void *w_device, float eps, void *xn_device, int64_t rows, int64_t hidden,
                                      ixb_stream_t stream);
